@@ -1,0 +1,114 @@
+// extern "C" surface of the library: argument validation, dispatch between the tensor-core and the
+// CUDA-core convolution, error strings, launch counter, device status word.
+#include <atomic>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace aether {
+
+static thread_local char g_err[512] = "";
+static std::atomic<unsigned long long> g_launches{0};
+static int* g_status_host = nullptr;   // pinned + mapped; the device pointer is identical under UVA
+
+int set_error(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+
+int* device_status_word() {
+    if (!g_status_host) {
+        int* p = nullptr;
+        if (cudaHostAlloc(reinterpret_cast<void**>(&p), sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) ==
+            cudaSuccess) {
+            *p = 0;
+            g_status_host = p;
+        }
+    }
+    return g_status_host;   // may be null: kernels then skip reporting
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(AE_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return AE_OK;
+}
+
+static int validate_desc(const AetherConvDesc* d, const char* fn) {
+    if (!d) return set_error(AE_BAD_ARG, "%s: null descriptor", fn);
+    if (d->S <= 0 || d->H <= 0 || d->W <= 0 || d->Cin <= 0 || d->Cout <= 0 || d->fH <= 0 || d->fW <= 0 || d->sH <= 0 ||
+        d->sW <= 0 || d->padH < 0 || d->padW < 0)
+        return set_error(AE_BAD_ARG, "%s: non-positive dimension in descriptor", fn);
+    if (d->math_mode < AETHER_MATH_BF16 || d->math_mode > AETHER_MATH_FP32)
+        return set_error(AE_BAD_ARG, "%s: unknown math_mode %d", fn, d->math_mode);
+    int Ho, Wo;
+    conv_out_hw(*d, Ho, Wo);
+    if (d->H + 2 * d->padH < d->fH || d->W + 2 * d->padW < d->fW || Ho < 1 || Wo < 1)
+        return set_error(AE_BAD_ARG, "%s: filter %dx%d larger than padded input %dx%d", fn, d->fH, d->fW,
+                         d->H + 2 * d->padH, d->W + 2 * d->padW);
+    return AE_OK;
+}
+
+static int pending_timeout(const char* fn) {
+    if (g_status_host && *reinterpret_cast<volatile int*>(g_status_host) != 0)
+        return set_error(AE_DEVICE_TIMEOUT, "%s: an earlier kernel abandoned a bounded wait (status %d)", fn,
+                         *reinterpret_cast<volatile int*>(g_status_host));
+    return AE_OK;
+}
+
+}  // namespace aether
+
+using namespace aether;
+
+extern "C" int aether_version(void) { return 100; }
+extern "C" const char* aether_last_error(void) { return g_err; }
+extern "C" uint64_t aether_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+extern "C" int aether_device_status(void) { return g_status_host ? *reinterpret_cast<volatile int*>(g_status_host) : 0; }
+extern "C" void aether_device_status_clear(void) {
+    if (g_status_host) *reinterpret_cast<volatile int*>(g_status_host) = 0;
+}
+
+extern "C" size_t aether_conv2d_workspace_bytes(const AetherConvDesc* d) {
+    if (validate_desc(d, "aether_conv2d_workspace_bytes")) return 0;
+    size_t g = generic_conv_workspace_bytes(*d);
+    if (tc_conv_eligible(*d)) {
+        size_t t = tc_conv_workspace_bytes(*d);
+        return t > g ? t : g;
+    }
+    return g;
+}
+
+extern "C" int aether_conv2d_fwd(const AetherConvDesc* d, const float* x, const float* w, const float* b, float* y,
+                                 void* ws, size_t ws_bytes, void* stream) {
+    int rc = validate_desc(d, "aether_conv2d_fwd");
+    if (rc) return rc;
+    if (!x || !w || !y) return set_error(AE_BAD_ARG, "aether_conv2d_fwd: null pointer");
+    if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (ws && !aligned16(ws)))
+        return set_error(AE_BAD_ARG, "aether_conv2d_fwd: arrays must be 16-byte aligned");
+    if ((rc = pending_timeout("aether_conv2d_fwd"))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, ws, ws_bytes, st);
+    return generic_conv_fwd(*d, x, w, b, y, st);
+}
+
+extern "C" int aether_conv2d_bwd(const AetherConvDesc* d, const float* x, const float* dy, const float* w, float* dx,
+                                 float* dw, float* db, void* ws, size_t ws_bytes, int x_shadow_valid, void* stream) {
+    int rc = validate_desc(d, "aether_conv2d_bwd");
+    if (rc) return rc;
+    if (!dy || !w || ((dw != nullptr) && !x)) return set_error(AE_BAD_ARG, "aether_conv2d_bwd: null pointer");
+    if (!aligned16(x) || !aligned16(dy) || !aligned16(w) || !aligned16(dx) || !aligned16(dw) || (ws && !aligned16(ws)))
+        return set_error(AE_BAD_ARG, "aether_conv2d_bwd: arrays must be 16-byte aligned");
+    if ((rc = pending_timeout("aether_conv2d_bwd"))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (tc_conv_eligible(*d)) return tc_conv_bwd(*d, x, dy, w, dx, dw, db, ws, ws_bytes, x_shadow_valid, st);
+    if (dx && (rc = generic_conv_bwd_data(*d, dy, w, dx, st))) return rc;
+    if (dw || db) return generic_conv_bwd_filter(*d, x, dy, dw, db, ws, ws_bytes, st);
+    return AE_OK;
+}

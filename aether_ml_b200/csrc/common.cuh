@@ -1,0 +1,53 @@
+// Shared host-side plumbing of the library: error reporting, the device status word that
+// bounded waits report into, the launch counter, and the internal entry points of each .cu file.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/aether_b200.h"
+
+namespace aether {
+
+// Return codes of every extern "C" entry point (0 = success).
+enum : int {
+    AE_OK = 0,
+    AE_BAD_ARG = -1,       // null pointer, misaligned pointer, non-positive size, workspace too small
+    AE_UNSUPPORTED = -2,   // shape/mode the library has no kernel for
+    AE_CUDA = -3,          // a CUDA runtime/driver call failed
+    AE_DEVICE_TIMEOUT = -4 // an earlier kernel gave up a bounded wait (see aether_device_status)
+};
+
+int set_error(int code, const char* fmt, ...);
+void count_launch(int n = 1);
+// Pinned, device-visible int that kernels write a DeviceStatus code into; allocated once per process.
+int* device_status_word();
+// Checks cudaGetLastError after a launch; returns AE_OK or AE_CUDA (with message).
+int check_launch(const char* what);
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- conv_generic.cu : fp32 CUDA-core convolution for any filter/stride/padding
+int generic_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, cudaStream_t st);
+int generic_conv_bwd_data(const AetherConvDesc& d, const float* dy, const float* w, float* dx, cudaStream_t st);
+int generic_conv_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy, float* dw, float* db, void* ws,
+                            size_t ws_bytes, cudaStream_t st);
+size_t generic_conv_workspace_bytes(const AetherConvDesc& d);
+
+// ---- conv_tc.cu : tcgen05 implicit-GEMM convolution (stride 1)
+bool tc_conv_eligible(const AetherConvDesc& d);
+size_t tc_conv_workspace_bytes(const AetherConvDesc& d);
+int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, void* ws,
+                size_t ws_bytes, cudaStream_t st);
+int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const float* w, float* dx, float* dw,
+                float* db, void* ws, size_t ws_bytes, int x_shadow_valid, cudaStream_t st);
+
+static inline void conv_out_hw(const AetherConvDesc& d, int& Ho, int& Wo) {
+    Ho = (d.H + 2 * d.padH - d.fH) / d.sH + 1;
+    Wo = (d.W + 2 * d.padW - d.fW) / d.sW + 1;
+}
+
+}  // namespace aether

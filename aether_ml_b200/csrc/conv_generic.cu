@@ -1,0 +1,206 @@
+// fp32 CUDA-core convolution for every filter size / stride / padding Conv_Layer accepts
+// (CNN/models/CNN_classes_cupy.py:70-154).  It serves the shapes the tensor-core kernels do not
+// take: the first layers with 1 or 3 input channels (HBM-bound, a few FLOP per byte), strided
+// convolutions, channel counts that are not a multiple of 4, and AETHER_MATH_FP32.
+#include "common.cuh"
+
+namespace aether {
+
+static constexpr int GEN_MAX_W_SMEM = 12 * 1024;  // floats of filter kept in shared memory (48 KB)
+
+// ---------------------------------------------------------------------------------- forward
+// One thread per output element, consecutive threads on consecutive output channels (coalesced
+// filter reads and output writes); the filter sits in shared memory when it fits.
+template <bool W_IN_SMEM>
+__global__ void __launch_bounds__(256) gen_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                      const float* __restrict__ b, float* __restrict__ y, int S, int H,
+                                                      int W, int Cin, int Cout, int fH, int fW, int sH, int sW, int pH,
+                                                      int pW, int Ho, int Wo) {
+    extern __shared__ float wsm[];
+    const int wcount = fH * fW * Cin * Cout;
+    if (W_IN_SMEM) {
+        for (int i = threadIdx.x; i < wcount; i += blockDim.x) wsm[i] = w[i];
+        __syncthreads();
+    }
+    const float* wp = W_IN_SMEM ? wsm : w;
+    const long long total = 1LL * S * Ho * Wo * Cout;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int d = (int)(idx % Cout);
+        long long pix = idx / Cout;
+        const int wo = (int)(pix % Wo);
+        pix /= Wo;
+        const int ho = (int)(pix % Ho);
+        const int s = (int)(pix / Ho);
+        float acc = b ? b[d] : 0.f;
+        for (int i = 0; i < fH; ++i) {
+            const int hi = ho * sH + i - pH;
+            if (hi < 0 || hi >= H) continue;
+            for (int j = 0; j < fW; ++j) {
+                const int wi = wo * sW + j - pW;
+                if (wi < 0 || wi >= W) continue;
+                const float* xp = x + (((size_t)s * H + hi) * W + wi) * Cin;
+                const float* wq = wp + ((size_t)(i * fW + j) * Cin) * Cout + d;
+                for (int c = 0; c < Cin; ++c) acc = fmaf(xp[c], wq[(size_t)c * Cout], acc);
+            }
+        }
+        y[idx] = acc;
+    }
+}
+
+// ---------------------------------------------------------------------------------- dX (gather form)
+// dx[s,h,w,c] = sum over taps (i,j) and d of dy[s,ho,wo,d] * w[i,j,c,d] with ho*sH + i - pH == h.
+__global__ void __launch_bounds__(256) gen_dx_kernel(const float* __restrict__ dy, const float* __restrict__ w,
+                                                     float* __restrict__ dx, int S, int H, int W, int Cin, int Cout,
+                                                     int fH, int fW, int sH, int sW, int pH, int pW, int Ho, int Wo) {
+    const long long total = 1LL * S * H * W * Cin;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(idx % Cin);
+        long long pix = idx / Cin;
+        const int wi = (int)(pix % W);
+        pix /= W;
+        const int hi = (int)(pix % H);
+        const int s = (int)(pix / H);
+        float acc = 0.f;
+        for (int i = 0; i < fH; ++i) {
+            const int hn = hi + pH - i;
+            if (hn < 0 || hn % sH) continue;
+            const int ho = hn / sH;
+            if (ho >= Ho) continue;
+            for (int j = 0; j < fW; ++j) {
+                const int wn = wi + pW - j;
+                if (wn < 0 || wn % sW) continue;
+                const int wo = wn / sW;
+                if (wo >= Wo) continue;
+                const float* dyp = dy + (((size_t)s * Ho + ho) * Wo + wo) * Cout;
+                const float* wq = w + ((size_t)(i * fW + j) * Cin + c) * Cout;
+                for (int d = 0; d < Cout; ++d) acc = fmaf(dyp[d], wq[d], acc);
+            }
+        }
+        dx[idx] = acc;
+    }
+}
+
+// ---------------------------------------------------------------------------------- dW, dB
+// Block b owns a contiguous chunk of output pixels; thread t accumulates filter entries t, t+256, ...
+// over that chunk and writes them to part[b][entry].  A second kernel adds the chunks in fixed order.
+__global__ void __launch_bounds__(256) gen_dw_partial_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                             float* __restrict__ part, int S, int H, int W, int Cin,
+                                                             int Cout, int fH, int fW, int sH, int sW, int pH, int pW,
+                                                             int Ho, int Wo, long long pix_per_block) {
+    const long long npix = 1LL * S * Ho * Wo;
+    const long long p0 = blockIdx.x * pix_per_block;
+    long long p1 = p0 + pix_per_block;
+    if (p1 > npix) p1 = npix;
+    const int entries = fH * fW * Cin * Cout;
+    for (int e = threadIdx.x; e < entries + Cout; e += blockDim.x) {
+        float acc = 0.f;
+        if (e < entries && x == nullptr) {
+            acc = 0.f;                             // only dB was requested
+        } else if (e < entries) {
+            const int d = e % Cout;
+            const int c = (e / Cout) % Cin;
+            const int tap = e / (Cout * Cin);
+            const int i = tap / fW, j = tap % fW;
+            for (long long p = p0; p < p1; ++p) {
+                const int wo = (int)(p % Wo);
+                const int ho = (int)((p / Wo) % Ho);
+                const int s = (int)(p / ((long long)Wo * Ho));
+                const int hi = ho * sH + i - pH, wi = wo * sW + j - pW;
+                if (hi < 0 || hi >= H || wi < 0 || wi >= W) continue;
+                acc = fmaf(x[(((size_t)s * H + hi) * W + wi) * Cin + c], dy[(size_t)p * Cout + d], acc);
+            }
+        } else {                                   // trailing Cout entries: dB
+            const int d = e - entries;
+            for (long long p = p0; p < p1; ++p) acc += dy[(size_t)p * Cout + d];
+        }
+        part[(size_t)blockIdx.x * (entries + Cout) + e] = acc;
+    }
+}
+
+__global__ void gen_dw_reduce_kernel(const float* __restrict__ part, int nblocks, int entries, int Cout,
+                                     float* __restrict__ dw, float* __restrict__ db) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= entries + Cout) return;
+    float s = 0.f;
+    for (int b = 0; b < nblocks; ++b) s += part[(size_t)b * (entries + Cout) + e];
+    if (e < entries) {
+        if (dw) dw[e] = s;
+    } else if (db) {
+        db[e - entries] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------------- host
+static int gen_blocks(long long total, int threads) {
+    long long b = (total + threads - 1) / threads;
+    const long long cap = 148LL * 16;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+int generic_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, cudaStream_t st) {
+    int Ho, Wo;
+    conv_out_hw(d, Ho, Wo);
+    const long long total = 1LL * d.S * Ho * Wo * d.Cout;
+    const int wcount = d.fH * d.fW * d.Cin * d.Cout;
+    if (wcount <= GEN_MAX_W_SMEM) {
+        gen_fwd_kernel<true><<<gen_blocks(total, 256), 256, wcount * sizeof(float), st>>>(
+            x, w, b, y, d.S, d.H, d.W, d.Cin, d.Cout, d.fH, d.fW, d.sH, d.sW, d.padH, d.padW, Ho, Wo);
+    } else {
+        gen_fwd_kernel<false><<<gen_blocks(total, 256), 256, 0, st>>>(x, w, b, y, d.S, d.H, d.W, d.Cin, d.Cout, d.fH,
+                                                                      d.fW, d.sH, d.sW, d.padH, d.padW, Ho, Wo);
+    }
+    count_launch();
+    return check_launch("gen_fwd_kernel");
+}
+
+int generic_conv_bwd_data(const AetherConvDesc& d, const float* dy, const float* w, float* dx, cudaStream_t st) {
+    int Ho, Wo;
+    conv_out_hw(d, Ho, Wo);
+    const long long total = 1LL * d.S * d.H * d.W * d.Cin;
+    gen_dx_kernel<<<gen_blocks(total, 256), 256, 0, st>>>(dy, w, dx, d.S, d.H, d.W, d.Cin, d.Cout, d.fH, d.fW, d.sH,
+                                                          d.sW, d.padH, d.padW, Ho, Wo);
+    count_launch();
+    return check_launch("gen_dx_kernel");
+}
+
+static int gen_dw_blocks(const AetherConvDesc& d) {
+    int Ho, Wo;
+    conv_out_hw(d, Ho, Wo);
+    const long long npix = 1LL * d.S * Ho * Wo;
+    long long nb = npix / 64;
+    if (nb > 148LL * 4) nb = 148LL * 4;
+    if (nb < 1) nb = 1;
+    return (int)nb;
+}
+
+size_t generic_conv_workspace_bytes(const AetherConvDesc& d) {
+    const size_t entries = (size_t)d.fH * d.fW * d.Cin * d.Cout + d.Cout;
+    return align_up((size_t)gen_dw_blocks(d) * entries * sizeof(float), 1024);
+}
+
+int generic_conv_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy, float* dw, float* db, void* ws,
+                            size_t ws_bytes, cudaStream_t st) {
+    int Ho, Wo;
+    conv_out_hw(d, Ho, Wo);
+    if (!ws || ws_bytes < generic_conv_workspace_bytes(d))
+        return set_error(AE_BAD_ARG, "conv workspace too small: %zu < %zu", ws_bytes, generic_conv_workspace_bytes(d));
+    const int nb = gen_dw_blocks(d);
+    const long long npix = 1LL * d.S * Ho * Wo;
+    const long long ppb = (npix + nb - 1) / nb;
+    const int entries = d.fH * d.fW * d.Cin * d.Cout;
+    float* part = static_cast<float*>(ws);
+    gen_dw_partial_kernel<<<nb, 256, 0, st>>>(x, dy, part, d.S, d.H, d.W, d.Cin, d.Cout, d.fH, d.fW, d.sH, d.sW, d.padH,
+                                              d.padW, Ho, Wo, ppb);
+    count_launch();
+    int rc = check_launch("gen_dw_partial_kernel");
+    if (rc) return rc;
+    gen_dw_reduce_kernel<<<ceil_div(entries + d.Cout, 256), 256, 0, st>>>(part, nb, entries, d.Cout, dw, db);
+    count_launch();
+    return check_launch("gen_dw_reduce_kernel");
+}
+
+}  // namespace aether

@@ -1,0 +1,939 @@
+// Tensor-core convolution for sm_100a: NHWC implicit GEMM with TMA-staged operand tiles,
+// tcgen05.mma accumulating in TMEM, fp32 in/out arrays in the layouts of Aether-ML's Conv_Layer
+// (activations NHWC, filters (fH,fW,Cin,Cout); CNN/models/CNN_classes_cupy.py:37-161).
+//
+//   forward  y[p,d]  = sum_{tap,c} x[p+tap, c] * W[tap,c,d] + b[d]      (einsum at :115, bias :116)
+//   dX       dx[p,c] = sum_{tap,d} dy[p-tap, d] * W[tap,c,d]            (einsum :138 + scatter :141-146)
+//   dW       dW[tap,c,d] = sum_p x[p+tap, c] * dy[p, d]                 (einsum :134),  dB = sum_p dy (:132)
+//
+// Nothing is materialised: 'same' padding is the zero fill of out-of-range TMA coordinates, each
+// filter tap is a coordinate shift of the same tensor map, and dX is a gather (every dx element is
+// written once) instead of the reference's 9x-sized contributions tensor and atomic scatter.
+//
+// Operand precision: bf16 (kind::f16) on bf16 shadow copies made by a cast kernel, or TF32
+// (kind::tf32) straight from the caller's fp32 arrays.  Accumulation is fp32 in TMEM.
+#include <stdio.h>
+#include <string.h>
+
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace aether {
+
+// ====================================================================================== tiling
+// One M tile is a box of BN images x BH rows x BW columns of output pixels, at most 128 of them.
+struct PixelTiling {
+    int BW, BH, BN, rows;
+    int tiles_w, tiles_h, tiles_n;
+    long long total() const { return 1LL * tiles_w * tiles_h * tiles_n; }
+};
+
+static PixelTiling choose_tiling(int S, int H, int W) {
+    // Exhaustive search over box shapes with <=128 pixels: minimise the number of tiles (i.e. wasted
+    // MMA rows), prefer wide boxes on ties (longer contiguous runs per TMA row).
+    PixelTiling best{};
+    long long best_tiles = -1;
+    for (int bw = 1; bw <= W && bw <= 128; ++bw) {
+        for (int bh = 1; bh <= H && bw * bh <= 128; ++bh) {
+            int bn = 128 / (bw * bh);
+            if (bn > S) bn = S;
+            if (bn < 1) continue;
+            if (bh < H && bn > 1) continue;  // stack images only once a box covers a whole image height
+            long long t = 1LL * ceil_div(W, bw) * ceil_div(H, bh) * ceil_div(S, bn);
+            if (best_tiles < 0 || t < best_tiles || (t == best_tiles && bw > best.BW)) {
+                best_tiles = t;
+                best = PixelTiling{bw, bh, bn, bw * bh * bn, ceil_div(W, bw), ceil_div(H, bh), ceil_div(S, bn)};
+            }
+        }
+    }
+    return best;
+}
+
+// ====================================================================================== tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// NHWC tensor seen as 4-D (C, W, H, N), 128-byte swizzle, box (box_c, BW, BH, BN).
+static int make_map_nhwc(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elt, int C, int W, int H, int N,
+                         int box_c, int BW, int BH, int BN, CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(AE_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    cuuint64_t strides[3] = {(cuuint64_t)C * elt, (cuuint64_t)C * elt * W, (cuuint64_t)C * elt * W * H};
+    cuuint32_t box[4] = {(cuuint32_t)box_c, (cuuint32_t)BW, (cuuint32_t)BH, (cuuint32_t)BN};
+    cuuint32_t es[4] = {1, 1, 1, 1};
+    CUresult r = fn(m, dt, 4, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return set_error(AE_CUDA, "cuTensorMapEncodeTiled(4d C=%d W=%d H=%d N=%d box %d,%d,%d,%d) failed: %d", C, W, H,
+                         N, box_c, BW, BH, BN, (int)r);
+    return AE_OK;
+}
+// Row-major matrix (inner = K elements contiguous, `rows` rows), box (box_k, box_rows).
+static int make_map_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elt, int inner, long long rows,
+                       int box_k, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(AE_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)inner * elt};
+    cuuint32_t box[2] = {(cuuint32_t)box_k, (cuuint32_t)box_rows};
+    cuuint32_t es[2] = {1, 1};
+    CUresult r = fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return set_error(AE_CUDA, "cuTensorMapEncodeTiled(2d inner=%d rows=%lld box %d,%d) failed: %d", inner, rows,
+                         box_k, box_rows, (int)r);
+    return AE_OK;
+}
+
+// ====================================================================================== igemm (forward and dX)
+struct IgemmParams {
+    CUtensorMap tm_in;   // activations (C, W, H, N), box (128 B of channels, BW, BH, BN)
+    CUtensorMap tm_w;    // filter matrix, K contiguous: (K, taps * rows_per_tap), box (128 B of K, NT)
+    CUtensorMap tm_out;  // fp32 output (C, W, H, N), box (32, BW, BH, BN)
+    const float* bias;   // nullable, n_out entries
+    int* status;
+    int n_out;
+    int BW, BH, BN, rows;
+    int tiles_w, tiles_h, tiles_n, n_tiles_n;
+    int rows_per_tap;
+    int fH, fW, sgn, off_h, off_w;
+    int kchunks;
+};
+
+static constexpr int TILE_A_BYTES = 128 * 128;  // 128 pixel rows x 128 B
+static constexpr int STAGING_BYTES = 128 * 128; // 128 rows x 32 fp32
+static constexpr int IGEMM_THREADS = 192;       // warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 epilogue
+
+template <int NT>
+struct IgemmCfg {
+    static constexpr int STAGES = (NT == 256) ? 4 : (NT == 128 ? 6 : 8);
+    static constexpr int TILE_B_BYTES = NT * 128;
+    static constexpr int SMEM_BYTES =
+        1024 + STAGES * (TILE_A_BYTES + TILE_B_BYTES) + 2 * STAGING_BYTES + 256;
+};
+
+template <bool TF32, int NT>
+__global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __grid_constant__ IgemmParams p) {
+    using Cfg = IgemmCfg<NT>;
+    constexpr int STAGES = Cfg::STAGES;
+    constexpr int KC = TF32 ? 32 : 64;            // K elements per 128-byte row
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sA = smem_base;
+    const uint32_t sB = sA + STAGES * TILE_A_BYTES;
+    const uint32_t sStage = sB + STAGES * Cfg::TILE_B_BYTES;
+    const uint32_t sBar = sStage + 2 * STAGING_BYTES;
+    // barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then the TMEM base address
+    auto full_bar = [&](int s) { return sBar + 8u * s; };
+    auto empty_bar = [&](int s) { return sBar + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int b) { return sBar + 8u * (2 * STAGES + b); };
+    auto tempty_bar = [&](int b) { return sBar + 8u * (2 * STAGES + 2 + b); };
+    const uint32_t sTmemPtr = sBar + 8u * (2 * STAGES + 4);
+    uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));   // generic pointer to smem_base
+    volatile uint32_t* tmem_ptr_generic =
+        reinterpret_cast<volatile uint32_t*>(gen_base + (sTmemPtr - smem_base));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull_bar(b), 1);
+            mbar_init(tempty_bar(b), 4);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&p.tm_in);
+        tma_prefetch_desc(&p.tm_w);
+        tma_prefetch_desc(&p.tm_out);
+    }
+    if (warp == 1) {
+        tmem_alloc(sTmemPtr, 2 * NT);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_generic;
+
+    const long long m_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
+    const long long total_tiles = m_tiles * p.n_tiles_n;
+    const int taps = p.fH * p.fW;
+    const int kiters = taps * p.kchunks;
+    const uint32_t stage_tx = (uint32_t)p.rows * 128u + (uint32_t)NT * 128u;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int nt = (int)(t % p.n_tiles_n);
+                long long mt = t / p.n_tiles_n;
+                const int tw = (int)(mt % p.tiles_w);
+                mt /= p.tiles_w;
+                const int th = (int)(mt % p.tiles_h);
+                const int tn = (int)(mt / p.tiles_h);
+                const int w0 = tw * p.BW, h0 = th * p.BH, n0 = tn * p.BN;
+                for (int tap = 0; tap < taps && ok; ++tap) {
+                    const int i = tap / p.fW, j = tap % p.fW;
+                    for (int kc = 0; kc < p.kchunks; ++kc, ++it) {
+                        const int s = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1u;
+                        if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) { ok = false; break; }
+                        mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                        tma_load_4d(sA + s * TILE_A_BYTES, &p.tm_in, full_bar(s), kc * KC, w0 + p.sgn * j + p.off_w,
+                                    h0 + p.sgn * i + p.off_h, n0);
+                        tma_load_2d(sB + s * Cfg::TILE_B_BYTES, &p.tm_w, full_bar(s), kc * KC,
+                                    tap * p.rows_per_tap + nt * NT);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (one thread)
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(TF32 ? 2u : 1u, 0u, 0u, 128u, (uint32_t)NT);
+            uint32_t it = 0;
+            uint32_t lt = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
+                const uint32_t buf = lt & 1u;
+                const uint32_t aph = (lt >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * NT;
+                for (int ki = 0; ki < kiters; ++ki, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(full_bar(s), ph, p.status, DS_TIMEOUT_FULL)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a0 = sA + s * TILE_A_BYTES;
+                    const uint32_t b0 = sB + s * Cfg::TILE_B_BYTES;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        umma<TF32>(d_tmem, make_smem_desc(a0 + k * 32, 16, 1024), make_smem_desc(b0 + k * 32, 16, 1024),
+                                   idesc, (ki > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(s));   // stage is free once these MMAs have read it
+                }
+                if (ok) umma_commit(tfull_bar(buf));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps, 128 rows)
+        const int q = warp & 3;                  // TMEM lane quarter this warp may access
+        const int row = q * 32 + lane;
+        const bool leader = (threadIdx.x == 64);
+        uint8_t* stage_gen = gen_base + (sStage - smem_base);
+        uint32_t lt = 0, chunk_ctr = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
+            const int nt = (int)(t % p.n_tiles_n);
+            long long mt = t / p.n_tiles_n;
+            const int tw = (int)(mt % p.tiles_w);
+            mt /= p.tiles_w;
+            const int th = (int)(mt % p.tiles_h);
+            const int tn = (int)(mt / p.tiles_h);
+            const int w0 = tw * p.BW, h0 = th * p.BH, n0 = tn * p.BN;
+            const uint32_t buf = lt & 1u;
+            const uint32_t aph = (lt >> 1) & 1u;
+            if (!mbar_wait(tfull_bar(buf), aph, p.status, DS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int ch = 0; ch < NT / 32; ++ch, ++chunk_ctr) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * NT + ch * 32, r);
+                tmem_ld_wait();
+                if (ch == NT / 32 - 1) {          // accumulator fully read: hand the buffer back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                }
+                const int c0 = nt * NT + ch * 32;
+                const uint32_t sb = chunk_ctr & 1u;
+                if (leader) tma_store_wait_read<1>();   // the store that last used this staging buffer is done
+                named_bar_sync(1, 128);
+                float4* dst_row = reinterpret_cast<float4*>(stage_gen + sb * STAGING_BYTES + row * 128);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    float4 v;
+                    v.x = __uint_as_float(r[4 * u + 0]);
+                    v.y = __uint_as_float(r[4 * u + 1]);
+                    v.z = __uint_as_float(r[4 * u + 2]);
+                    v.w = __uint_as_float(r[4 * u + 3]);
+                    if (p.bias) {
+                        const int c = c0 + 4 * u;
+                        if (c + 0 < p.n_out) v.x += __ldg(p.bias + c + 0);
+                        if (c + 1 < p.n_out) v.y += __ldg(p.bias + c + 1);
+                        if (c + 2 < p.n_out) v.z += __ldg(p.bias + c + 2);
+                        if (c + 3 < p.n_out) v.w += __ldg(p.bias + c + 3);
+                    }
+                    dst_row[u ^ (row & 7)] = v;      // 128-byte swizzle: 16-byte unit index XOR (row mod 8)
+                }
+                fence_proxy_async_smem();
+                named_bar_sync(1, 128);
+                if (leader && c0 < p.n_out) {
+                    tma_store_4d(&p.tm_out, sStage + sb * STAGING_BYTES, c0, w0, h0, n0);
+                    tma_store_commit();
+                }
+            }
+        }
+        if (leader) tma_store_wait_all<0>();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * NT);
+    }
+}
+
+// ====================================================================================== dW (filter gradient)
+struct DwParams {
+    CUtensorMap tm_x;    // (Cin_p, W, H, N), box (128 B of channels, BW, BH, BN)
+    CUtensorMap tm_dy;   // (Cout_p, Wo, Ho, N), same box
+    float* part;         // [splits][U][UC][ldn] partial sums
+    int* status;
+    int BW, BH, BN, rows;
+    int tiles_w, tiles_h, tiles_n;
+    int fH, fW, padH, padW;
+    int cblocks;         // 128-byte channel blocks of x
+    int U;               // fH*fW*cblocks units (one unit = one tap x one channel block)
+    int MG;              // M groups = ceil(U / MB)
+    int gpc;             // M groups per CTA
+    int n_tiles_n;
+    int ldn;
+};
+
+static constexpr int DW_THREADS = 192;
+
+template <bool TF32, int NB>
+struct DwCfg {
+    static constexpr int UC = TF32 ? 32 : 64;       // channels per 128-byte block
+    static constexpr int MB = 128 / UC;             // x blocks per M=128
+    static constexpr int NT = NB * UC;              // dy channels per CTA
+    static constexpr int STAGE_BYTES = (MB + NB) * TILE_A_BYTES;
+    static constexpr int STAGES = (200 * 1024) / STAGE_BYTES;
+    static constexpr int KROWS = TF32 ? 8 : 16;     // pixel rows per MMA
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+    static constexpr int MAX_GPC = 512 / NT;
+    static_assert(STAGES >= 2, "need at least two stages");
+};
+
+template <bool TF32, int NB>
+__global__ void __launch_bounds__(DW_THREADS, 1) dw_conv_kernel(const __grid_constant__ DwParams p) {
+    using Cfg = DwCfg<TF32, NB>;
+    constexpr int STAGES = Cfg::STAGES, MB = Cfg::MB, NT = Cfg::NT, UC = Cfg::UC;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t sBar = smem_base + STAGES * Cfg::STAGE_BYTES;
+    auto full_bar = [&](int s) { return sBar + 8u * s; };
+    auto empty_bar = [&](int s) { return sBar + 8u * (STAGES + s); };
+    const uint32_t done_bar = sBar + 8u * (2 * STAGES);
+    const uint32_t sTmemPtr = sBar + 8u * (2 * STAGES + 1);
+    volatile uint32_t* tmem_ptr_generic = reinterpret_cast<volatile uint32_t*>(gen_base + (sTmemPtr - smem_base));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // Rows past p.rows are never written by TMA but are read by the MMAs: keep them zero.
+    {
+        uint4* z = reinterpret_cast<uint4*>(gen_base);
+        const int n16 = STAGES * Cfg::STAGE_BYTES / 16;
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
+        fence_proxy_async_smem();
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(done_bar, 1);
+        mbar_fence_init();
+        tma_prefetch_desc(&p.tm_x);
+        tma_prefetch_desc(&p.tm_dy);
+    }
+    if (warp == 1) {
+        tmem_alloc(sTmemPtr, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_generic;
+
+    const int split = blockIdx.x, splits = gridDim.x;
+    const int gc = blockIdx.y / p.n_tiles_n;
+    const int nt = blockIdx.y % p.n_tiles_n;
+    const int g_begin = gc * p.gpc;
+    const int g_end = min(p.MG, g_begin + p.gpc);
+    const int ngroups = g_end - g_begin;
+    const long long total_ptiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
+    const uint32_t stage_tx = (uint32_t)(MB + NB) * (uint32_t)p.rows * 128u;
+    const int ksteps = (p.rows + Cfg::KROWS - 1) / Cfg::KROWS;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long pt = split; pt < total_ptiles && ok; pt += splits) {
+                long long r = pt;
+                const int tw = (int)(r % p.tiles_w);
+                r /= p.tiles_w;
+                const int th = (int)(r % p.tiles_h);
+                const int tn = (int)(r / p.tiles_h);
+                const int w0 = tw * p.BW, h0 = th * p.BH, n0 = tn * p.BN;
+                for (int g = g_begin; g < g_end; ++g, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) { ok = false; break; }
+                    mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                    const uint32_t st = smem_base + s * Cfg::STAGE_BYTES;
+                    for (int m = 0; m < MB; ++m) {
+                        int u = g * MB + m;
+                        if (u >= p.U) u = p.U - 1;       // padding unit of the last group: results are dropped
+                        const int tap = u / p.cblocks, cb = u % p.cblocks;
+                        const int i = tap / p.fW, j = tap % p.fW;
+                        tma_load_4d(st + m * TILE_A_BYTES, &p.tm_x, full_bar(s), cb * UC, w0 + j - p.padW,
+                                    h0 + i - p.padH, n0);
+                    }
+                    for (int nb = 0; nb < NB; ++nb)
+                        tma_load_4d(st + (MB + nb) * TILE_A_BYTES, &p.tm_dy, full_bar(s), (nt * NB + nb) * UC, w0, h0,
+                                    n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(TF32 ? 2u : 1u, 1u, 1u, 128u, (uint32_t)NT);
+            uint32_t it = 0;
+            bool ok = true;
+            bool first = true;
+            for (long long pt = split; pt < total_ptiles && ok; pt += splits, first = false) {
+                for (int g = 0; g < ngroups; ++g, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(full_bar(s), ph, p.status, DS_TIMEOUT_FULL)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a0 = smem_base + s * Cfg::STAGE_BYTES;
+                    const uint32_t b0 = a0 + MB * TILE_A_BYTES;
+                    const uint32_t d_tmem = tmem_base + g * NT;
+                    for (int kk = 0; kk < ksteps; ++kk) {
+                        const uint32_t koff = kk * Cfg::KROWS * 128;
+                        // MN-major operands: 16-bit types use the plain 128-byte swizzle (8-row K groups);
+                        // 32-bit types need the 32-byte-unit variant (4-row K groups).
+                        constexpr uint32_t LT = TF32 ? 1u : 2u;
+                        constexpr uint32_t SBO = TF32 ? 512u : 1024u;
+                        umma<TF32>(d_tmem, make_smem_desc(a0 + koff, TILE_A_BYTES, SBO, LT),
+                                   make_smem_desc(b0 + koff, TILE_A_BYTES, SBO, LT), idesc, (!first || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(s));
+                }
+            }
+            umma_commit(done_bar);
+        }
+    } else {
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const bool any_tiles = split < total_ptiles;
+        bool ok = true;
+        if (any_tiles) ok = mbar_wait(done_bar, 0, p.status, DS_TIMEOUT_TMEM_FULL);
+        tc_fence_after();
+        if (ok) {
+            const int m = row / UC, c_in = row % UC;
+            for (int g = 0; g < ngroups; ++g) {
+                const int u = (g_begin + g) * MB + m;
+#pragma unroll 1
+                for (int ch = 0; ch < NT / 32; ++ch) {
+                    uint32_t r[32];
+                    if (any_tiles) {
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + g * NT + ch * 32, r);
+                        tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 32; ++k) r[k] = 0u;
+                    }
+                    if (u < p.U) {
+                        float4* dst = reinterpret_cast<float4*>(
+                            p.part + (((size_t)split * p.U + u) * UC + c_in) * (size_t)p.ldn + nt * NT + ch * 32);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            dst[k] = make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]),
+                                                 __uint_as_float(r[4 * k + 2]), __uint_as_float(r[4 * k + 3]));
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// dW[tap][c][d] = sum over splits of part[split][tap*cblocks + c/UC][c%UC][d]
+__global__ void dw_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int splits, int U, int UC,
+                                 int ldn, int cblocks, int taps, int Cin, int Cout) {
+    const long long total = 1LL * taps * Cin * Cout;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int d = (int)(idx % Cout);
+        const long long tc = idx / Cout;
+        const int c = (int)(tc % Cin);
+        const int tap = (int)(tc / Cin);
+        const int u = tap * cblocks + c / UC;
+        const float* src = part + ((size_t)u * UC + (c % UC)) * (size_t)ldn + d;
+        const size_t split_stride = (size_t)U * UC * ldn;
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) acc += src[s * split_stride];
+        dw[idx] = acc;
+    }
+}
+
+// ====================================================================================== shadow copies
+// fp32 [rows][C] -> bf16 [rows][Cp] (zero padded channels).  Optionally also per-block column sums of the
+// fp32 input (for dB), written to colsum_part[block][C].
+template <bool COLSUM>
+__global__ void __launch_bounds__(256) cast_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                                        long long rows, int C, int Cp, float* __restrict__ colsum_part,
+                                                        long long rows_per_block) {
+    const int G = Cp / 8;                 // 8-channel groups per row
+    const long long r_begin = blockIdx.x * rows_per_block;
+    long long r_end = r_begin + rows_per_block;
+    if (r_end > rows) r_end = rows;
+    const bool vec = (C % 4) == 0;
+    __shared__ float red[COLSUM ? 256 * 8 : 8];
+    for (int gbase = 0; gbase < G; gbase += 256) {
+        const int Gc = (G - gbase) < 256 ? (G - gbase) : 256;   // groups handled in this pass
+        const int planes = 256 / Gc;                            // rows processed concurrently
+        const int g = gbase + threadIdx.x % Gc;
+        const int plane = threadIdx.x / Gc;
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+        if (plane < planes) {
+            const int c0 = g * 8;
+            for (long long r = r_begin + plane; r < r_end; r += planes) {
+                float v[8];
+                const float* s = src + r * C + c0;
+                if (vec && c0 + 8 <= C) {
+                    const float4 a = *reinterpret_cast<const float4*>(s);
+                    const float4 b = *reinterpret_cast<const float4*>(s + 4);
+                    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+                    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) v[k] = (c0 + k < C) ? s[k] : 0.f;
+                }
+                if (COLSUM) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[k] += v[k];
+                }
+                __nv_bfloat162 o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+                *reinterpret_cast<uint4*>(dst + r * Cp + c0) = *reinterpret_cast<uint4*>(o);
+            }
+        }
+        if (COLSUM) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) red[threadIdx.x * 8 + k] = acc[k];   // idle threads hold zeros
+            __syncthreads();
+            for (int cc = threadIdx.x; cc < Gc * 8; cc += blockDim.x) {
+                const int c = gbase * 8 + cc;
+                if (c < C) {
+                    const int gg = cc / 8, k = cc % 8;
+                    float s = 0.f;
+                    for (int pl = 0; pl < planes; ++pl) s += red[(pl * Gc + gg) * 8 + k];
+                    colsum_part[(size_t)blockIdx.x * C + c] = s;
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// Column sums of an fp32 [rows][C] matrix into part[block][C] (used for dB when no cast pass runs).
+__global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ src, long long rows, int C,
+                                                     float* __restrict__ part, long long rows_per_block) {
+    const long long r_begin = blockIdx.x * rows_per_block;
+    long long r_end = r_begin + rows_per_block;
+    if (r_end > rows) r_end = rows;
+    // thread -> (column group, row lane) so that a warp reads consecutive addresses when C <= 256
+    const int cols = C < 256 ? C : 256;
+    const int lanes = 256 / cols > 0 ? 256 / cols : 1;
+    __shared__ float red[256];
+    for (int cbase = 0; cbase < C; cbase += cols) {
+        const int c = cbase + threadIdx.x % cols;
+        const int rl = threadIdx.x / cols;
+        float acc = 0.f;
+        if (rl < lanes && c < C)
+            for (long long r = r_begin + rl; r < r_end; r += lanes) acc += src[r * C + c];
+        red[threadIdx.x] = acc;
+        __syncthreads();
+        if (threadIdx.x < cols && c < C) {
+            float s = 0.f;
+            for (int l = 0; l < lanes; ++l) s += red[l * cols + threadIdx.x];
+            part[(size_t)blockIdx.x * C + c] = s;
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void colsum_finish_kernel(const float* __restrict__ part, int nblocks, int C, float* __restrict__ out) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float s = 0.f;
+    for (int b = 0; b < nblocks; ++b) s += part[(size_t)b * C + c];
+    out[c] = s;
+}
+
+// Filter shadows.  w is (taps, Cin, Cout) fp32.
+//   transpose=1: out[tap][n < Np][k < Kp] = w[tap][k][n]   (forward B operand: K = Cin contiguous)
+//   transpose=0: out[tap][n < Np][k < Kp] = w[tap][n][k]   (dX B operand: rows = Cin, K = Cout contiguous)
+template <typename OutT>
+__global__ void filter_shadow_kernel(const float* __restrict__ w, OutT* __restrict__ out, int taps, int Cin, int Cout,
+                                     int Np, int Kp, int transpose) {
+    const long long total = 1LL * taps * Np * Kp;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int k = (int)(idx % Kp);
+        const long long tn = idx / Kp;
+        const int n = (int)(tn % Np);
+        const int tap = (int)(tn / Np);
+        float v = 0.f;
+        if (transpose) {
+            if (k < Cin && n < Cout) v = w[((size_t)tap * Cin + k) * Cout + n];
+        } else {
+            if (n < Cin && k < Cout) v = w[((size_t)tap * Cin + n) * Cout + k];
+        }
+        out[idx] = static_cast<OutT>(v);
+    }
+}
+
+// ====================================================================================== host side
+struct TcPlan {
+    bool tf32;
+    int Ho, Wo, taps;
+    int elt;          // operand element size
+    int KC;           // elements per 128-byte block
+    int Cin_p, Cout_p;
+    // workspace offsets (bytes)
+    size_t off_xsh, off_dysh, off_wf, off_wd, off_part, off_dbpart, total;
+    // dW decomposition
+    int dw_nb, dw_nt, dw_cblocks, dw_U, dw_MG, dw_gpc, dw_ngc, dw_ntn, dw_splits;
+    int db_blocks;
+    PixelTiling til_out;   // tiles over output pixels (forward, dW)
+    PixelTiling til_in;    // tiles over input pixels (dX)
+};
+
+static int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+static int num_sms() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+static TcPlan make_plan(const AetherConvDesc& d) {
+    TcPlan pl{};
+    pl.tf32 = (d.math_mode == AETHER_MATH_TF32);
+    conv_out_hw(d, pl.Ho, pl.Wo);
+    pl.taps = d.fH * d.fW;
+    pl.elt = pl.tf32 ? 4 : 2;
+    pl.KC = 128 / pl.elt;
+    pl.Cin_p = round_up(d.Cin, pl.KC);
+    pl.Cout_p = round_up(d.Cout, pl.KC);
+    pl.til_out = choose_tiling(d.S, pl.Ho, pl.Wo);
+    pl.til_in = choose_tiling(d.S, d.H, d.W);
+    // dW decomposition
+    const int UC = pl.KC;
+    const int MB = 128 / UC;
+    if (pl.tf32) pl.dw_nb = (pl.Cout_p % 64 == 0) ? 2 : 1;
+    else pl.dw_nb = (pl.Cout_p % 128 == 0) ? 2 : 1;
+    pl.dw_nt = pl.dw_nb * UC;
+    pl.dw_cblocks = pl.Cin_p / UC;
+    pl.dw_U = pl.taps * pl.dw_cblocks;
+    pl.dw_MG = ceil_div(pl.dw_U, MB);
+    const int max_gpc = 512 / pl.dw_nt;
+    pl.dw_ngc = ceil_div(pl.dw_MG, max_gpc);
+    pl.dw_gpc = ceil_div(pl.dw_MG, pl.dw_ngc);
+    pl.dw_ngc = ceil_div(pl.dw_MG, pl.dw_gpc);
+    pl.dw_ntn = pl.Cout_p / pl.dw_nt;
+    long long ptiles = pl.til_out.total();
+    long long want = num_sms() / (pl.dw_ngc * pl.dw_ntn);
+    if (want < 1) want = 1;
+    if (want > ptiles) want = ptiles;
+    pl.dw_splits = (int)want;
+    const long long out_rows = 1LL * d.S * pl.Ho * pl.Wo;
+    pl.db_blocks = (int)(out_rows < 4LL * num_sms() * 64 ? (out_rows + 63) / 64 : 4LL * num_sms());
+    if (pl.db_blocks < 1) pl.db_blocks = 1;
+    // workspace
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 1024); return o; };
+    const size_t in_rows = (size_t)d.S * d.H * d.W;
+    pl.off_xsh = take(pl.tf32 ? 0 : in_rows * pl.Cin_p * 2);
+    pl.off_dysh = take(pl.tf32 ? 0 : (size_t)out_rows * pl.Cout_p * 2);
+    pl.off_wf = take((size_t)pl.taps * pl.Cout_p * pl.Cin_p * pl.elt);
+    pl.off_wd = take(pl.tf32 ? 0 : (size_t)pl.taps * pl.Cin_p * pl.Cout_p * pl.elt);
+    pl.off_part = take((size_t)pl.dw_splits * pl.dw_U * UC * pl.Cout_p * 4);
+    pl.off_dbpart = take((size_t)pl.db_blocks * d.Cout * 4);
+    pl.total = off;
+    return pl;
+}
+
+bool tc_conv_eligible(const AetherConvDesc& d) {
+    if (d.math_mode != AETHER_MATH_BF16 && d.math_mode != AETHER_MATH_TF32) return false;
+    if (d.sH != 1 || d.sW != 1) return false;
+    if (d.Cin % 4 || d.Cout % 4) return false;           // 16-byte rows for the fp32 tensor maps
+    if (d.Cin < 16 || d.Cout < 16) return false;         // tiny channel counts: the CUDA-core kernel is used
+    if (d.fH * d.fW > 64) return false;
+    int Ho, Wo;
+    conv_out_hw(d, Ho, Wo);
+    if (Ho < 1 || Wo < 1) return false;
+    return true;
+}
+
+size_t tc_conv_workspace_bytes(const AetherConvDesc& d) { return make_plan(d).total; }
+
+template <typename K>
+static int set_smem(K kernel, int bytes) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(smem=%d): %s", bytes, cudaGetErrorString(e));
+    return AE_OK;
+}
+
+template <bool TF32, int NT>
+static int launch_igemm(const IgemmParams& p, cudaStream_t st) {
+    using Cfg = IgemmCfg<NT>;
+    static bool configured = false;
+    if (!configured) {
+        int rc = set_smem(igemm_conv_kernel<TF32, NT>, Cfg::SMEM_BYTES);
+        if (rc) return rc;
+        configured = true;
+    }
+    const long long total = 1LL * p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles_n;
+    int grid = (int)(total < num_sms() ? total : num_sms());
+    igemm_conv_kernel<TF32, NT><<<grid, IGEMM_THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    count_launch();
+    return check_launch("igemm_conv_kernel");
+}
+
+static int pick_nt(int n_padded) {
+    if (n_padded % 256 == 0) return 256;
+    if (n_padded % 128 == 0) return 128;
+    if (n_padded % 64 == 0) return 64;
+    return 32;
+}
+
+template <bool TF32>
+static int dispatch_igemm(IgemmParams& p, int nt, cudaStream_t st) {
+    switch (nt) {
+        case 256: return launch_igemm<TF32, 256>(p, st);
+        case 128: return launch_igemm<TF32, 128>(p, st);
+        case 64: return launch_igemm<TF32, 64>(p, st);
+        default: return launch_igemm<TF32, 32>(p, st);
+    }
+}
+
+// Runs out[p, n] = sum_{tap,k} in[p (+/-) tap, k] * Wm[tap][n][k] (+ bias).
+static int run_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
+                     int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, const PixelTiling& til,
+                     int n_padded, int fH, int fW, int sgn, int off_h, int off_w, const float* bias, cudaStream_t st) {
+    IgemmParams p;
+    memset(&p, 0, sizeof(p));
+    const int elt = tf32 ? 4 : 2;
+    const int KC = 128 / elt;
+    const CUtensorMapDataType dt = tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const int nt = pick_nt(n_padded);
+    int rc;
+    if ((rc = make_map_nhwc(&p.tm_in, in, dt, elt, in_C, in_W, in_H, S, KC, til.BW, til.BH, til.BN))) return rc;
+    if ((rc = make_map_2d(&p.tm_w, wmat, dt, elt, w_inner, 1LL * taps * rows_per_tap, KC, nt))) return rc;
+    if ((rc = make_map_nhwc(&p.tm_out, out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out_C, out_W, out_H, S, 32, til.BW,
+                            til.BH, til.BN)))
+        return rc;
+    p.bias = bias;
+    p.status = device_status_word();
+    p.n_out = out_C;
+    p.BW = til.BW; p.BH = til.BH; p.BN = til.BN; p.rows = til.rows;
+    p.tiles_w = til.tiles_w; p.tiles_h = til.tiles_h; p.tiles_n = til.tiles_n;
+    p.n_tiles_n = ceil_div(n_padded, nt);
+    p.rows_per_tap = rows_per_tap;
+    p.fH = fH; p.fW = fW; p.sgn = sgn; p.off_h = off_h; p.off_w = off_w;
+    p.kchunks = ceil_div(in_C, KC);
+    return tf32 ? dispatch_igemm<true>(p, nt, st) : dispatch_igemm<false>(p, nt, st);
+}
+
+static int launch_cast(const float* src, __nv_bfloat16* dst, long long rows, int C, int Cp, float* colsum_part,
+                       int colsum_blocks, cudaStream_t st) {
+    if (colsum_part) {
+        const long long rpb = (rows + colsum_blocks - 1) / colsum_blocks;
+        cast_bf16_kernel<true><<<colsum_blocks, 256, 0, st>>>(src, dst, rows, C, Cp, colsum_part, rpb);
+    } else {
+        long long blocks = 8LL * num_sms();
+        const int G = Cp / 8;
+        const int planes = G >= 256 ? 1 : 256 / G;
+        if (blocks * planes > rows) blocks = (rows + planes - 1) / planes;
+        if (blocks < 1) blocks = 1;
+        const long long rpb = (rows + blocks - 1) / blocks;
+        cast_bf16_kernel<false><<<(int)blocks, 256, 0, st>>>(src, dst, rows, C, Cp, nullptr, rpb);
+    }
+    count_launch();
+    return check_launch("cast_bf16_kernel");
+}
+
+int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, void* ws,
+                size_t ws_bytes, cudaStream_t st) {
+    const TcPlan pl = make_plan(d);
+    if (ws_bytes < pl.total || !ws) return set_error(AE_BAD_ARG, "conv workspace too small: %zu < %zu", ws_bytes, pl.total);
+    uint8_t* wsb = static_cast<uint8_t*>(ws);
+    int rc;
+    const int fblocks = 2 * num_sms();
+    if (pl.tf32) {
+        float* wf = reinterpret_cast<float*>(wsb + pl.off_wf);
+        filter_shadow_kernel<float><<<fblocks, 256, 0, st>>>(w, wf, pl.taps, d.Cin, d.Cout, pl.Cout_p, pl.Cin_p, 1);
+        count_launch();
+        if ((rc = check_launch("filter_shadow_kernel"))) return rc;
+        return run_igemm(true, x, d.Cin, d.H, d.W, d.S, wf, pl.Cin_p, pl.Cout_p, pl.taps, y, d.Cout, pl.Ho, pl.Wo,
+                         pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, st);
+    }
+    __nv_bfloat16* xsh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_xsh);
+    __nv_bfloat16* wf = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_wf);
+    if ((rc = launch_cast(x, xsh, 1LL * d.S * d.H * d.W, d.Cin, pl.Cin_p, nullptr, 0, st))) return rc;
+    filter_shadow_kernel<__nv_bfloat16><<<fblocks, 256, 0, st>>>(w, wf, pl.taps, d.Cin, d.Cout, pl.Cout_p, pl.Cin_p, 1);
+    count_launch();
+    if ((rc = check_launch("filter_shadow_kernel"))) return rc;
+    return run_igemm(false, xsh, pl.Cin_p, d.H, d.W, d.S, wf, pl.Cin_p, pl.Cout_p, pl.taps, y, d.Cout, pl.Ho, pl.Wo,
+                     pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, st);
+}
+
+template <bool TF32, int NB>
+static int launch_dw(const DwParams& p, int splits, int grid_y, cudaStream_t st) {
+    using Cfg = DwCfg<TF32, NB>;
+    static bool configured = false;
+    if (!configured) {
+        int rc = set_smem(dw_conv_kernel<TF32, NB>, Cfg::SMEM_BYTES);
+        if (rc) return rc;
+        configured = true;
+    }
+    dw_conv_kernel<TF32, NB><<<dim3(splits, grid_y), DW_THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    count_launch();
+    return check_launch("dw_conv_kernel");
+}
+
+int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const float* w, float* dx, float* dw,
+                float* db, void* ws, size_t ws_bytes, int x_shadow_valid, cudaStream_t st) {
+    const TcPlan pl = make_plan(d);
+    if (ws_bytes < pl.total || !ws) return set_error(AE_BAD_ARG, "conv workspace too small: %zu < %zu", ws_bytes, pl.total);
+    uint8_t* wsb = static_cast<uint8_t*>(ws);
+    int rc;
+    const long long out_rows = 1LL * d.S * pl.Ho * pl.Wo;
+    const long long in_rows = 1LL * d.S * d.H * d.W;
+    float* dbpart = reinterpret_cast<float*>(wsb + pl.off_dbpart);
+    const void* x_op = x;
+    const void* dy_op = dy;
+    const int fblocks = 2 * num_sms();
+
+    // ---- shadows + dB
+    if (pl.tf32) {
+        if (db) {
+            const long long rpb = (out_rows + pl.db_blocks - 1) / pl.db_blocks;
+            colsum_kernel<<<pl.db_blocks, 256, 0, st>>>(dy, out_rows, d.Cout, dbpart, rpb);
+            count_launch();
+            if ((rc = check_launch("colsum_kernel"))) return rc;
+        }
+    } else {
+        __nv_bfloat16* dysh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_dysh);
+        __nv_bfloat16* xsh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_xsh);
+        if ((rc = launch_cast(dy, dysh, out_rows, d.Cout, pl.Cout_p, dbpart, pl.db_blocks, st))) return rc;
+        if (dw && !x_shadow_valid)
+            if ((rc = launch_cast(x, xsh, in_rows, d.Cin, pl.Cin_p, nullptr, 0, st))) return rc;
+        x_op = xsh;
+        dy_op = dysh;
+    }
+    if (db) {
+        colsum_finish_kernel<<<ceil_div(d.Cout, 128), 128, 0, st>>>(dbpart, pl.db_blocks, d.Cout, db);
+        count_launch();
+        if ((rc = check_launch("colsum_finish_kernel"))) return rc;
+    }
+
+    // ---- dX: gather over dy with the filter read as (rows = Cin, K = Cout)
+    if (dx) {
+        if (pl.tf32) {
+            // the caller's (taps, Cin, Cout) array already is the K-major matrix needed here
+            rc = run_igemm(true, dy, d.Cout, pl.Ho, pl.Wo, d.S, w, d.Cout, d.Cin, pl.taps, dx, d.Cin, d.H, d.W,
+                           pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, st);
+        } else {
+            __nv_bfloat16* wd = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_wd);
+            filter_shadow_kernel<__nv_bfloat16><<<fblocks, 256, 0, st>>>(w, wd, pl.taps, d.Cin, d.Cout, pl.Cin_p,
+                                                                          pl.Cout_p, 0);
+            count_launch();
+            if ((rc = check_launch("filter_shadow_kernel"))) return rc;
+            rc = run_igemm(false, dy_op, pl.Cout_p, pl.Ho, pl.Wo, d.S, wd, pl.Cout_p, pl.Cin_p, pl.taps, dx, d.Cin, d.H,
+                           d.W, pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, st);
+        }
+        if (rc) return rc;
+    }
+
+    // ---- dW: split over pixel tiles, fixed-order reduction of the partials
+    if (dw) {
+        DwParams p;
+        memset(&p, 0, sizeof(p));
+        const CUtensorMapDataType dt = pl.tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        const PixelTiling& til = pl.til_out;
+        const int xC = pl.tf32 ? d.Cin : pl.Cin_p;
+        const int dyC = pl.tf32 ? d.Cout : pl.Cout_p;
+        const CUtensorMapSwizzle swz = pl.tf32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+        if ((rc = make_map_nhwc(&p.tm_x, x_op, dt, pl.elt, xC, d.W, d.H, d.S, pl.KC, til.BW, til.BH, til.BN, swz)))
+            return rc;
+        if ((rc = make_map_nhwc(&p.tm_dy, dy_op, dt, pl.elt, dyC, pl.Wo, pl.Ho, d.S, pl.KC, til.BW, til.BH, til.BN, swz)))
+            return rc;
+        p.part = reinterpret_cast<float*>(wsb + pl.off_part);
+        p.status = device_status_word();
+        p.BW = til.BW; p.BH = til.BH; p.BN = til.BN; p.rows = til.rows;
+        p.tiles_w = til.tiles_w; p.tiles_h = til.tiles_h; p.tiles_n = til.tiles_n;
+        p.fH = d.fH; p.fW = d.fW; p.padH = d.padH; p.padW = d.padW;
+        p.cblocks = pl.dw_cblocks; p.U = pl.dw_U; p.MG = pl.dw_MG; p.gpc = pl.dw_gpc;
+        p.n_tiles_n = pl.dw_ntn; p.ldn = pl.Cout_p;
+        const int gy = pl.dw_ngc * pl.dw_ntn;
+        if (pl.tf32) rc = (pl.dw_nb == 2) ? launch_dw<true, 2>(p, pl.dw_splits, gy, st) : launch_dw<true, 1>(p, pl.dw_splits, gy, st);
+        else rc = (pl.dw_nb == 2) ? launch_dw<false, 2>(p, pl.dw_splits, gy, st) : launch_dw<false, 1>(p, pl.dw_splits, gy, st);
+        if (rc) return rc;
+        dw_reduce_kernel<<<2 * num_sms(), 256, 0, st>>>(p.part, dw, pl.dw_splits, pl.dw_U, pl.KC, pl.Cout_p,
+                                                        pl.dw_cblocks, pl.taps, d.Cin, d.Cout);
+        count_launch();
+        if ((rc = check_launch("dw_reduce_kernel"))) return rc;
+    }
+    return AE_OK;
+}
+
+}  // namespace aether

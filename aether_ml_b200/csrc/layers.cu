@@ -1,0 +1,690 @@
+// Bandwidth-bound layers that sit next to the convolution in Aether-ML's networks
+// (CNN/models/CNN_classes_cupy.py): Batch_Norm :430-526, Pooling :204-312, ReLU :406-415,
+// Leaky_ReLU :417-428, Layer_Dropout_Spatial :384-404, Layer_Dropout :364-382, Optimizer_Adam
+// :685-736, SoftMax + categorical cross-entropy :541-680.  All arrays are fp32 with the channel
+// (last) axis contiguous; kernels use 128-bit accesses along it whenever the channel count allows.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace aether {
+
+static int blocks_for(long long items, int threads, int per_sm = 8) {
+    long long b = (items + threads - 1) / threads;
+    const long long cap = 148LL * per_sm;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+// ====================================================================================== batch norm
+// Per-channel reductions over a [rows][C] matrix.  Thread t of a block owns column (t % cols) and row
+// lane (t / cols); a block walks a contiguous slab of rows, so a warp reads consecutive addresses.
+// MODE 0: partial (count, mean, M2) of x         -> part[block][3][C]
+// MODE 1: partial sum(dy), sum(dy * xhat)        -> part[block][2][C]   (xhat from mean/inv_std)
+template <int MODE>
+__global__ void __launch_bounds__(256) bn_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                        const float* __restrict__ mean, const float* __restrict__ var,
+                                                        float eps, long long rows, int C, float* __restrict__ part,
+                                                        long long rows_per_block) {
+    const long long r0 = blockIdx.x * rows_per_block;
+    long long r1 = r0 + rows_per_block;
+    if (r1 > rows) r1 = rows;
+    const int cols = C < 256 ? C : 256;
+    const int lanes = 256 / cols;
+    __shared__ float sh_a[256], sh_b[256], sh_n[256];
+    constexpr int NOUT = MODE == 0 ? 3 : 2;
+    for (int cbase = 0; cbase < C; cbase += cols) {
+        const int c = cbase + threadIdx.x % cols;
+        const int rl = threadIdx.x / cols;
+        float a = 0.f, b = 0.f, n = 0.f;
+        if (rl < lanes && c < C) {
+            if (MODE == 0) {
+                // shifted sums: subtract the first element of the slab to avoid cancellation
+                const float shift = (r0 < r1) ? x[(size_t)r0 * C + c] : 0.f;
+                for (long long r = r0 + rl; r < r1; r += lanes) {
+                    const float v = x[(size_t)r * C + c] - shift;
+                    a += v;
+                    b = fmaf(v, v, b);
+                    n += 1.f;
+                }
+                // convert to (n, mean, M2) about the true local mean
+                if (n > 0.f) {
+                    const float m = a / n;
+                    b = b - a * m;
+                    a = m + shift;
+                }
+            } else {
+                const float mu = mean[c];
+                const float inv = rsqrtf(var[c] + eps);
+                for (long long r = r0 + rl; r < r1; r += lanes) {
+                    const float g = dy[(size_t)r * C + c];
+                    a += g;
+                    b = fmaf(g, (x[(size_t)r * C + c] - mu) * inv, b);
+                }
+            }
+        }
+        sh_a[threadIdx.x] = a;
+        sh_b[threadIdx.x] = b;
+        sh_n[threadIdx.x] = n;
+        __syncthreads();
+        if (threadIdx.x < cols && c < C) {
+            float* out = part + (size_t)blockIdx.x * NOUT * C;
+            if (MODE == 0) {
+                // Chan's parallel merge of the row lanes, in fixed order
+                float N = 0.f, M = 0.f, M2 = 0.f;
+                for (int l = 0; l < lanes; ++l) {
+                    const float nl = sh_n[l * cols + threadIdx.x];
+                    if (nl == 0.f) continue;
+                    const float ml = sh_a[l * cols + threadIdx.x], m2l = sh_b[l * cols + threadIdx.x];
+                    const float tot = N + nl;
+                    const float delta = ml - M;
+                    M2 += m2l + delta * delta * N * nl / tot;
+                    M += delta * nl / tot;
+                    N = tot;
+                }
+                out[c] = N;
+                out[C + c] = M;
+                out[2 * C + c] = M2;
+            } else {
+                float sa = 0.f, sb = 0.f;
+                for (int l = 0; l < lanes; ++l) {
+                    sa += sh_a[l * cols + threadIdx.x];
+                    sb += sh_b[l * cols + threadIdx.x];
+                }
+                out[c] = sa;
+                out[C + c] = sb;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Merges the per-block (n, mean, M2) triples in double precision, writes batch mean / biased variance,
+// updates the running statistics (momentum * old + (1 - momentum) * batch) and the affine
+// coefficients scale = gamma / sqrt(var + eps), shift = beta - mean * scale used by the apply kernel.
+__global__ void bn_finalize_fwd_kernel(const float* __restrict__ part, int nblocks, int C,
+                                       const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
+                                       float momentum, float* __restrict__ running_mean,
+                                       float* __restrict__ running_var, float* __restrict__ batch_mean,
+                                       float* __restrict__ batch_var, float* __restrict__ scale_shift) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    double N = 0.0, M = 0.0, M2 = 0.0;
+    for (int b = 0; b < nblocks; ++b) {
+        const float* p = part + (size_t)b * 3 * C;
+        const double nl = p[c];
+        if (nl == 0.0) continue;
+        const double ml = p[C + c], m2l = p[2 * C + c];
+        const double tot = N + nl, delta = ml - M;
+        M2 += m2l + delta * delta * N * nl / tot;
+        M += delta * nl / tot;
+        N = tot;
+    }
+    const double var = N > 0 ? M2 / N : 0.0;
+    batch_mean[c] = (float)M;
+    batch_var[c] = (float)var;
+    running_mean[c] = momentum * running_mean[c] + (1.f - momentum) * (float)M;
+    running_var[c] = momentum * running_var[c] + (1.f - momentum) * (float)var;
+    const double sc = (double)gamma[c] / sqrt(var + (double)eps);
+    scale_shift[c] = (float)sc;
+    scale_shift[C + c] = (float)((double)beta[c] - M * sc);
+}
+
+__global__ void bn_eval_coeff_kernel(int C, const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
+                                     const float* __restrict__ running_mean, const float* __restrict__ running_var,
+                                     float* __restrict__ scale_shift) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const float sc = gamma[c] / sqrtf(running_var[c] + eps);
+    scale_shift[c] = sc;
+    scale_shift[C + c] = beta[c] - running_mean[c] * sc;
+}
+
+// y = x * scale[c] + shift[c]
+__global__ void __launch_bounds__(256) affine_channels_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                              const float* __restrict__ scale,
+                                                              const float* __restrict__ shift, long long n, int C) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    if ((C & 3) == 0) {
+        const long long n4 = n >> 2;
+        const int C4 = C >> 2;
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        float4* y4 = reinterpret_cast<float4*>(y);
+        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += stride) {
+            const int c = (int)(i % C4) * 4;
+            const float4 v = x4[i];
+            const float4 s = *reinterpret_cast<const float4*>(scale + c);
+            float4 o;
+            if (shift) {
+                const float4 t = *reinterpret_cast<const float4*>(shift + c);
+                o = make_float4(fmaf(v.x, s.x, t.x), fmaf(v.y, s.y, t.y), fmaf(v.z, s.z, t.z), fmaf(v.w, s.w, t.w));
+            } else {
+                o = make_float4(v.x * s.x, v.y * s.y, v.z * s.z, v.w * s.w);
+            }
+            y4[i] = o;
+        }
+    } else {
+        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+            const int c = (int)(i % C);
+            y[i] = shift ? fmaf(x[i], scale[c], shift[c]) : x[i] * scale[c];
+        }
+    }
+}
+
+// dgamma = sum(dy * xhat), dbeta = sum(dy); coefficients for
+// dx = k1[c] * dy + k2[c] * x + k3[c]  with  k1 = gamma*inv, k2 = -gamma*inv^2*dgamma/N * ... (see below)
+__global__ void bn_finalize_bwd_kernel(const float* __restrict__ part, int nblocks, int C, long long rows,
+                                       const float* __restrict__ gamma, const float* __restrict__ mean,
+                                       const float* __restrict__ var, float eps, float* __restrict__ dgamma,
+                                       float* __restrict__ dbeta, float* __restrict__ coeff) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    double sdy = 0.0, sdyx = 0.0;
+    for (int b = 0; b < nblocks; ++b) {
+        sdy += part[(size_t)b * 2 * C + c];
+        sdyx += part[(size_t)b * 2 * C + C + c];
+    }
+    dgamma[c] = (float)sdyx;
+    dbeta[c] = (float)sdy;
+    // dx = gamma*inv/N * (N*dy - sum(dy) - xhat * sum(dy*xhat)),  xhat = (x - mean) * inv
+    //    = k1*dy + k2*x + k3
+    const double inv = 1.0 / sqrt((double)var[c] + (double)eps);
+    const double g = gamma[c], N = (double)rows, mu = mean[c];
+    const double k1 = g * inv;
+    const double k2 = -g * inv * inv * inv * sdyx / N;
+    const double k3 = -g * inv * sdy / N - k2 * mu;
+    coeff[c] = (float)k1;
+    coeff[C + c] = (float)k2;
+    coeff[2 * C + c] = (float)k3;
+}
+
+__global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                           float* __restrict__ dx, const float* __restrict__ coeff,
+                                                           long long n, int C) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    if ((C & 3) == 0) {
+        const long long n4 = n >> 2;
+        const int C4 = C >> 2;
+        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += stride) {
+            const int c = (int)(i % C4) * 4;
+            const float4 xv = reinterpret_cast<const float4*>(x)[i];
+            const float4 g = reinterpret_cast<const float4*>(dy)[i];
+            const float4 k1 = *reinterpret_cast<const float4*>(coeff + c);
+            const float4 k2 = *reinterpret_cast<const float4*>(coeff + C + c);
+            const float4 k3 = *reinterpret_cast<const float4*>(coeff + 2 * C + c);
+            float4 o;
+            o.x = fmaf(k1.x, g.x, fmaf(k2.x, xv.x, k3.x));
+            o.y = fmaf(k1.y, g.y, fmaf(k2.y, xv.y, k3.y));
+            o.z = fmaf(k1.z, g.z, fmaf(k2.z, xv.z, k3.z));
+            o.w = fmaf(k1.w, g.w, fmaf(k2.w, xv.w, k3.w));
+            reinterpret_cast<float4*>(dx)[i] = o;
+        }
+    } else {
+        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+            const int c = (int)(i % C);
+            dx[i] = fmaf(coeff[c], dy[i], fmaf(coeff[C + c], x[i], coeff[2 * C + c]));
+        }
+    }
+}
+
+static int bn_blocks(long long rows) {
+    long long nb = rows / 32;
+    if (nb > 148LL * 4) nb = 148LL * 4;
+    if (nb < 1) nb = 1;
+    return (int)nb;
+}
+
+}  // namespace aether
+
+using namespace aether;
+
+extern "C" size_t aether_bn_workspace_bytes(int64_t rows, int C) {
+    if (rows <= 0 || C <= 0) return 0;
+    return align_up(((size_t)bn_blocks(rows) * 3 + 3) * (size_t)C * sizeof(float), 256);
+}
+
+extern "C" int aether_bn_fwd_train(const float* x, const float* gamma, const float* beta, float* running_mean,
+                                   float* running_var, float* batch_mean, float* batch_var, float* y, int64_t rows,
+                                   int C, float eps, float momentum, void* ws, size_t ws_bytes, void* stream) {
+    if (!x || !gamma || !beta || !running_mean || !running_var || !batch_mean || !batch_var || !y || !ws)
+        return set_error(AE_BAD_ARG, "aether_bn_fwd_train: null pointer");
+    if (rows <= 0 || C <= 0) return set_error(AE_BAD_ARG, "aether_bn_fwd_train: rows=%lld C=%d", (long long)rows, C);
+    if (ws_bytes < aether_bn_workspace_bytes(rows, C)) return set_error(AE_BAD_ARG, "aether_bn_fwd_train: workspace too small");
+    if ((C & 3) == 0 && (!aligned16(x) || !aligned16(y))) return set_error(AE_BAD_ARG, "aether_bn_fwd_train: arrays must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int nb = bn_blocks(rows);
+    float* part = static_cast<float*>(ws);
+    float* coeff = part + (size_t)nb * 3 * C;
+    bn_reduce_kernel<0><<<nb, 256, 0, st>>>(x, nullptr, nullptr, nullptr, eps, rows, C, part, (rows + nb - 1) / nb);
+    bn_finalize_fwd_kernel<<<ceil_div(C, 128), 128, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
+                                                            running_var, batch_mean, batch_var, coeff);
+    const long long n = rows * C;
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C);
+    count_launch(3);
+    return check_launch("aether_bn_fwd_train");
+}
+
+extern "C" int aether_bn_fwd_eval(const float* x, const float* gamma, const float* beta, const float* running_mean,
+                                  const float* running_var, float* y, int64_t rows, int C, float eps, void* ws,
+                                  size_t ws_bytes, void* stream) {
+    if (!x || !gamma || !beta || !running_mean || !running_var || !y || !ws)
+        return set_error(AE_BAD_ARG, "aether_bn_fwd_eval: null pointer");
+    if (rows <= 0 || C <= 0) return set_error(AE_BAD_ARG, "aether_bn_fwd_eval: rows=%lld C=%d", (long long)rows, C);
+    if (ws_bytes < 2 * (size_t)C * sizeof(float)) return set_error(AE_BAD_ARG, "aether_bn_fwd_eval: workspace too small");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* coeff = static_cast<float*>(ws);
+    bn_eval_coeff_kernel<<<ceil_div(C, 128), 128, 0, st>>>(C, gamma, beta, eps, running_mean, running_var, coeff);
+    const long long n = rows * C;
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C);
+    count_launch(2);
+    return check_launch("aether_bn_fwd_eval");
+}
+
+extern "C" int aether_bn_bwd(const float* x, const float* dy, const float* gamma, const float* batch_mean,
+                             const float* batch_var, float* dx, float* dgamma, float* dbeta, int64_t rows, int C,
+                             float eps, void* ws, size_t ws_bytes, void* stream) {
+    if (!x || !dy || !gamma || !batch_mean || !batch_var || !dx || !dgamma || !dbeta || !ws)
+        return set_error(AE_BAD_ARG, "aether_bn_bwd: null pointer");
+    if (rows <= 0 || C <= 0) return set_error(AE_BAD_ARG, "aether_bn_bwd: rows=%lld C=%d", (long long)rows, C);
+    if (ws_bytes < aether_bn_workspace_bytes(rows, C)) return set_error(AE_BAD_ARG, "aether_bn_bwd: workspace too small");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int nb = bn_blocks(rows);
+    float* part = static_cast<float*>(ws);
+    float* coeff = part + (size_t)nb * 3 * C;
+    bn_reduce_kernel<1><<<nb, 256, 0, st>>>(x, dy, batch_mean, batch_var, eps, rows, C, part, (rows + nb - 1) / nb);
+    bn_finalize_bwd_kernel<<<ceil_div(C, 128), 128, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
+                                                            dbeta, coeff);
+    const long long n = rows * C;
+    bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C);
+    count_launch(3);
+    return check_launch("aether_bn_bwd");
+}
+
+namespace aether {
+// ====================================================================================== pooling
+// Forward: one thread per (output pixel, 4 channels).  The argmax code is the window-local index
+// i*fW + j of the FIRST maximum in row-major window order (ties keep the earlier cell).
+template <bool MAX>
+__global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                       uint8_t* __restrict__ arg, int S, int H, int W, int C, int fH,
+                                                       int fW, int sH, int sW, int Ho, int Wo, int vec) {
+    const int Cv = C / vec;
+    const long long total = 1LL * S * Ho * Wo * Cv;
+    const float inv = 1.f / (float)(fH * fW);
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int cv = (int)(idx % Cv);
+        long long pix = idx / Cv;
+        const int wo = (int)(pix % Wo);
+        pix /= Wo;
+        const int ho = (int)(pix % Ho);
+        const int s = (int)(pix / Ho);
+        const size_t obase = ((size_t)(((size_t)s * Ho + ho) * Wo + wo)) * C + (size_t)cv * vec;
+        if (vec == 4) {
+            float4 best = make_float4(0.f, 0.f, 0.f, 0.f);
+            uchar4 code = make_uchar4(0, 0, 0, 0);
+            for (int i = 0; i < fH; ++i)
+                for (int j = 0; j < fW; ++j) {
+                    const float4 v = *reinterpret_cast<const float4*>(
+                        x + (((size_t)s * H + ho * sH + i) * W + wo * sW + j) * C + cv * 4);
+                    const unsigned char k = (unsigned char)(i * fW + j);
+                    if (MAX) {
+                        if (k == 0) { best = v; }
+                        else {
+                            if (v.x > best.x) { best.x = v.x; code.x = k; }
+                            if (v.y > best.y) { best.y = v.y; code.y = k; }
+                            if (v.z > best.z) { best.z = v.z; code.z = k; }
+                            if (v.w > best.w) { best.w = v.w; code.w = k; }
+                        }
+                    } else {
+                        best.x += v.x; best.y += v.y; best.z += v.z; best.w += v.w;
+                    }
+                }
+            if (!MAX) { best.x *= inv; best.y *= inv; best.z *= inv; best.w *= inv; }
+            *reinterpret_cast<float4*>(y + obase) = best;
+            if (MAX) *reinterpret_cast<uchar4*>(arg + obase) = code;
+        } else {
+            float best = 0.f;
+            unsigned char code = 0;
+            for (int i = 0; i < fH; ++i)
+                for (int j = 0; j < fW; ++j) {
+                    const float v = x[(((size_t)s * H + ho * sH + i) * W + wo * sW + j) * C + cv];
+                    const unsigned char k = (unsigned char)(i * fW + j);
+                    if (MAX) {
+                        if (k == 0 || v > best) { best = v; code = k; }
+                    } else {
+                        best += v;
+                    }
+                }
+            y[obase] = MAX ? best : best * inv;
+            if (MAX) arg[obase] = code;
+        }
+    }
+}
+
+// Backward in gather form: each input cell sums the dy of every window that selected it (max) or
+// that covers it (average).  No atomics; cells outside every window get zero.
+template <bool MAX>
+__global__ void __launch_bounds__(256) pool_bwd_kernel(const float* __restrict__ dy, const uint8_t* __restrict__ arg,
+                                                       float* __restrict__ dx, int S, int H, int W, int C, int fH,
+                                                       int fW, int sH, int sW, int Ho, int Wo) {
+    const long long total = 1LL * S * H * W * C;
+    const float inv = 1.f / (float)(fH * fW);
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(idx % C);
+        long long pix = idx / C;
+        const int w = (int)(pix % W);
+        pix /= W;
+        const int h = (int)(pix % H);
+        const int s = (int)(pix / H);
+        float acc = 0.f;
+        // windows (ho, wo) with ho*sH <= h < ho*sH + fH
+        const int ho_hi = min(Ho - 1, h / sH);
+        const int wo_hi = min(Wo - 1, w / sW);
+        for (int ho = ho_hi; ho >= 0 && ho * sH + fH > h; --ho) {
+            const int i = h - ho * sH;
+            for (int wo = wo_hi; wo >= 0 && wo * sW + fW > w; --wo) {
+                const int j = w - wo * sW;
+                const size_t o = (((size_t)s * Ho + ho) * Wo + wo) * C + c;
+                if (MAX) {
+                    if (arg[o] == (uint8_t)(i * fW + j)) acc += dy[o];
+                } else {
+                    acc += dy[o] * inv;
+                }
+            }
+        }
+        dx[idx] = acc;
+    }
+}
+
+// ====================================================================================== activations
+// y = x > 0 ? x : alpha * x   (alpha = 0 gives ReLU)
+__global__ void __launch_bounds__(256) lrelu_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, long long n,
+                                                        float alpha) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long n4 = n >> 2;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 v = reinterpret_cast<const float4*>(x)[i];
+        v.x = v.x > 0.f ? v.x : alpha * v.x;
+        v.y = v.y > 0.f ? v.y : alpha * v.y;
+        v.z = v.z > 0.f ? v.z : alpha * v.z;
+        v.w = v.w > 0.f ? v.w : alpha * v.w;
+        reinterpret_cast<float4*>(y)[i] = v;
+    }
+    for (long long i = (n4 << 2) + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride)
+        y[i] = x[i] > 0.f ? x[i] : alpha * x[i];
+}
+// dx = x < 0 ? alpha * dy : dy   (the gradient passes where x == 0, as in the reference)
+__global__ void __launch_bounds__(256) lrelu_bwd_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                        float* __restrict__ dx, long long n, float alpha) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long n4 = n >> 2;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 v = reinterpret_cast<const float4*>(x)[i];
+        float4 g = reinterpret_cast<const float4*>(dy)[i];
+        g.x = v.x < 0.f ? alpha * g.x : g.x;
+        g.y = v.y < 0.f ? alpha * g.y : g.y;
+        g.z = v.z < 0.f ? alpha * g.z : g.z;
+        g.w = v.w < 0.f ? alpha * g.w : g.w;
+        reinterpret_cast<float4*>(dx)[i] = g;
+    }
+    for (long long i = (n4 << 2) + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride)
+        dx[i] = x[i] < 0.f ? alpha * dy[i] : dy[i];
+}
+
+// ====================================================================================== dropout
+// Counter-based generator (Philox-4x32-10, Salmon et al. 2011): 4 uniforms per (seed, index).
+__device__ __forceinline__ uint4 philox4x32_10(uint2 key, uint4 ctr) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const unsigned int hi0 = __umulhi(0xD2511F53u, ctr.x), lo0 = 0xD2511F53u * ctr.x;
+        const unsigned int hi1 = __umulhi(0xCD9E8D57u, ctr.z), lo1 = 0xCD9E8D57u * ctr.z;
+        ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+        key.x += 0x9E3779B9u;
+        key.y += 0xBB67AE85u;
+    }
+    return ctr;
+}
+// mask[i] = (u < keep) / keep ; y = x * mask.  4 elements per thread.
+__global__ void __launch_bounds__(256) dropout_fwd_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                          float* __restrict__ mask, long long n, float keep,
+                                                          unsigned long long seed, unsigned long long offset) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const float scale = 1.f / keep;
+    for (long long q = blockIdx.x * (long long)blockDim.x + threadIdx.x; q * 4 < n; q += stride) {
+        const unsigned long long ctr = (unsigned long long)q + offset;
+        const uint4 r = philox4x32_10(make_uint2((unsigned)seed, (unsigned)(seed >> 32)),
+                                      make_uint4((unsigned)ctr, (unsigned)(ctr >> 32), 0u, 0u));
+        const unsigned int rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const long long i = q * 4 + k;
+            if (i < n) {
+                const float u = (float)(rr[k] >> 8) * (1.0f / 16777216.0f);
+                const float m = u < keep ? scale : 0.f;
+                mask[i] = m;
+                y[i] = x[i] * m;
+            }
+        }
+    }
+}
+__global__ void __launch_bounds__(256) mul_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                  float* __restrict__ y, long long n) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) y[i] = a[i] * b[i];
+}
+
+// ====================================================================================== Adam
+// One launch updates a whole flat parameter buffer (Optimizer_Adam.update_parameters, :710-734):
+//   g' = g * gscale;  m = b1*m + (1-b1)*g';  v = b2*v + (1-b2)*g'^2
+//   p -= lr * (m / bc1) / (sqrt(v / bc2) + eps)        with bc = 1 - beta^(iterations+1)
+__global__ void __launch_bounds__(256) adam_kernel(float* __restrict__ p, const float* __restrict__ g,
+                                                   float* __restrict__ m, float* __restrict__ v, long long n, float lr,
+                                                   float b1, float b2, float eps, float inv_bc1, float inv_bc2,
+                                                   float gscale) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float gi = g[i] * gscale;
+        const float mi = b1 * m[i] + (1.f - b1) * gi;
+        const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        p[i] -= lr * (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
+    }
+}
+
+// g += l1 * sign(w) + 2 * l2 * w   (Layer_Dense.backward regulariser terms, :337-351; sign(0) = +1)
+__global__ void __launch_bounds__(256) reg_grad_kernel(const float* __restrict__ w, float* __restrict__ g, long long n,
+                                                       float l1, float l2) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float wi = w[i];
+        g[i] += l1 * (wi < 0.f ? -1.f : 1.f) + 2.f * l2 * wi;
+    }
+}
+
+// out[0] += l1 * sum|w| + l2 * sum w^2   (Loss.regularization_loss, :593-609); single block, fixed order.
+__global__ void __launch_bounds__(256) reg_loss_kernel(const float* __restrict__ w, long long n, float l1, float l2,
+                                                       float* __restrict__ out) {
+    __shared__ double sh[256];
+    double acc = 0.0;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+        const double wi = w[i];
+        acc += l1 * fabs(wi) + l2 * wi * wi;
+    }
+    sh[threadIdx.x] = acc;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s) sh[threadIdx.x] += sh[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[0] += (float)sh[0];
+}
+
+// ====================================================================================== softmax + CCE
+// One warp per sample: probabilities, clipped cross-entropy with label smoothing, the combined
+// gradient (p - y_smooth) / rows, and whether argmax(p) == label.
+__global__ void __launch_bounds__(256) softmax_cce_kernel(const float* __restrict__ z, const int* __restrict__ labels,
+                                                          float* __restrict__ prob, float* __restrict__ loss,
+                                                          float* __restrict__ dz, int* __restrict__ correct, int rows,
+                                                          int classes, float smooth_fwd, float smooth_bwd,
+                                                          int input_is_prob) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= rows) return;
+    const float* zr = z + (size_t)warp * classes;
+    float mx = -INFINITY;
+    int amax = 0;
+    for (int k = lane; k < classes; k += 32) {
+        const float v = zr[k];
+        if (v > mx) { mx = v; amax = k; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, mx, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, amax, o);
+        if (om > mx || (om == mx && oa < amax)) { mx = om; amax = oa; }
+    }
+    float sum = 0.f;
+    if (!input_is_prob) {
+        for (int k = lane; k < classes; k += 32) sum += expf(zr[k] - mx);
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    }
+    const int label = labels ? labels[warp] : -1;
+    const float inv_rows = 1.f / (float)rows;
+    float l = 0.f;
+    for (int k = lane; k < classes; k += 32) {
+        const float pk = input_is_prob ? zr[k] : expf(zr[k] - mx) / sum;
+        if (prob) prob[(size_t)warp * classes + k] = pk;
+        if (labels) {
+            const float onehot = (k == label) ? 1.f : 0.f;
+            const float tf = onehot * (1.f - smooth_fwd) + smooth_fwd / classes;
+            const float tb = onehot * (1.f - smooth_bwd) + smooth_bwd / classes;
+            const float pc = fminf(fmaxf(pk, 1e-7f), 1.f - 1e-7f);
+            l -= tf * logf(pc);
+            if (dz) dz[(size_t)warp * classes + k] = (pk - tb) * inv_rows;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) {
+        if (loss) loss[warp] = l;
+        if (correct) correct[warp] = (amax == label) ? 1 : 0;
+    }
+}
+
+}  // namespace aether
+
+// ====================================================================================== C ABI
+extern "C" int aether_pool_fwd(const float* x, float* y, uint8_t* argmax, int S, int H, int W, int C, int fH, int fW,
+                               int sH, int sW, int kind, void* stream) {
+    if (!x || !y || (kind == AETHER_POOL_MAX && !argmax)) return set_error(AE_BAD_ARG, "aether_pool_fwd: null pointer");
+    if (S <= 0 || C <= 0 || fH <= 0 || fW <= 0 || sH <= 0 || sW <= 0 || H < fH || W < fW || fH * fW > 255)
+        return set_error(AE_BAD_ARG, "aether_pool_fwd: bad shape S=%d H=%d W=%d C=%d f=%dx%d s=%dx%d", S, H, W, C, fH, fW, sH, sW);
+    if (kind != AETHER_POOL_MAX && kind != AETHER_POOL_AVG) return set_error(AE_UNSUPPORTED, "aether_pool_fwd: kind %d", kind);
+    const int Ho = (H - fH) / sH + 1, Wo = (W - fW) / sW + 1;
+    const int vec = ((C & 3) == 0 && aligned16(x) && aligned16(y) && (!argmax || (reinterpret_cast<uintptr_t>(argmax) & 3) == 0)) ? 4 : 1;
+    const long long total = 1LL * S * Ho * Wo * (C / vec);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (kind == AETHER_POOL_MAX)
+        pool_fwd_kernel<true><<<blocks_for(total, 256, 16), 256, 0, st>>>(x, y, argmax, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
+    else
+        pool_fwd_kernel<false><<<blocks_for(total, 256, 16), 256, 0, st>>>(x, y, nullptr, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
+    count_launch();
+    return check_launch("aether_pool_fwd");
+}
+
+extern "C" int aether_pool_bwd(const float* dy, const uint8_t* argmax, float* dx, int S, int H, int W, int C, int fH,
+                               int fW, int sH, int sW, int kind, void* stream) {
+    if (!dy || !dx || (kind == AETHER_POOL_MAX && !argmax)) return set_error(AE_BAD_ARG, "aether_pool_bwd: null pointer");
+    if (S <= 0 || C <= 0 || fH <= 0 || fW <= 0 || sH <= 0 || sW <= 0 || H < fH || W < fW || fH * fW > 255)
+        return set_error(AE_BAD_ARG, "aether_pool_bwd: bad shape");
+    if (kind != AETHER_POOL_MAX && kind != AETHER_POOL_AVG) return set_error(AE_UNSUPPORTED, "aether_pool_bwd: kind %d", kind);
+    const int Ho = (H - fH) / sH + 1, Wo = (W - fW) / sW + 1;
+    const long long total = 1LL * S * H * W * C;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (kind == AETHER_POOL_MAX)
+        pool_bwd_kernel<true><<<blocks_for(total, 256, 16), 256, 0, st>>>(dy, argmax, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
+    else
+        pool_bwd_kernel<false><<<blocks_for(total, 256, 16), 256, 0, st>>>(dy, nullptr, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
+    count_launch();
+    return check_launch("aether_pool_bwd");
+}
+
+extern "C" int aether_leaky_relu_fwd(const float* x, float* y, int64_t n, float alpha, void* stream) {
+    if (!x || !y || n <= 0) return set_error(AE_BAD_ARG, "aether_leaky_relu_fwd: bad argument");
+    if (!aligned16(x) || !aligned16(y)) return set_error(AE_BAD_ARG, "aether_leaky_relu_fwd: arrays must be 16-byte aligned");
+    lrelu_fwd_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, n, alpha);
+    count_launch();
+    return check_launch("aether_leaky_relu_fwd");
+}
+
+extern "C" int aether_leaky_relu_bwd(const float* x, const float* dy, float* dx, int64_t n, float alpha, void* stream) {
+    if (!x || !dy || !dx || n <= 0) return set_error(AE_BAD_ARG, "aether_leaky_relu_bwd: bad argument");
+    if (!aligned16(x) || !aligned16(dy) || !aligned16(dx)) return set_error(AE_BAD_ARG, "aether_leaky_relu_bwd: arrays must be 16-byte aligned");
+    lrelu_bwd_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, dy, dx, n, alpha);
+    count_launch();
+    return check_launch("aether_leaky_relu_bwd");
+}
+
+extern "C" int aether_channel_scale(const float* x, const float* scale, float* y, int64_t n, int C, void* stream) {
+    if (!x || !scale || !y || n <= 0 || C <= 0 || n % C) return set_error(AE_BAD_ARG, "aether_channel_scale: bad argument");
+    if ((C & 3) == 0 && (!aligned16(x) || !aligned16(y) || !aligned16(scale)))
+        return set_error(AE_BAD_ARG, "aether_channel_scale: arrays must be 16-byte aligned");
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, scale, nullptr, n, C);
+    count_launch();
+    return check_launch("aether_channel_scale");
+}
+
+extern "C" int aether_dropout_fwd(const float* x, float* y, float* mask, int64_t n, float keep_prob, uint64_t seed,
+                                  uint64_t offset, void* stream) {
+    if (!x || !y || !mask || n <= 0 || !(keep_prob > 0.f) || keep_prob > 1.f)
+        return set_error(AE_BAD_ARG, "aether_dropout_fwd: bad argument");
+    dropout_fwd_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, mask, n, keep_prob, seed, offset);
+    count_launch();
+    return check_launch("aether_dropout_fwd");
+}
+
+extern "C" int aether_mul(const float* a, const float* b, float* y, int64_t n, void* stream) {
+    if (!a || !b || !y || n <= 0) return set_error(AE_BAD_ARG, "aether_mul: bad argument");
+    mul_kernel<<<blocks_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(a, b, y, n);
+    count_launch();
+    return check_launch("aether_mul");
+}
+
+extern "C" int aether_adam_step(float* p, const float* g, float* m, float* v, int64_t n, float lr, float beta1,
+                                float beta2, float eps, float bias_corr1, float bias_corr2, float grad_scale,
+                                void* stream) {
+    if (!p || !g || !m || !v || n <= 0) return set_error(AE_BAD_ARG, "aether_adam_step: bad argument");
+    if (!(bias_corr1 > 0.f) || !(bias_corr2 > 0.f)) return set_error(AE_BAD_ARG, "aether_adam_step: bias corrections must be > 0");
+    adam_kernel<<<blocks_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(p, g, m, v, n, lr, beta1, beta2, eps, 1.f / bias_corr1,
+                                                                                   1.f / bias_corr2, grad_scale);
+    count_launch();
+    return check_launch("aether_adam_step");
+}
+
+extern "C" int aether_regularizer_grad(const float* w, float* g, int64_t n, float l1, float l2, void* stream) {
+    if (!w || !g || n <= 0) return set_error(AE_BAD_ARG, "aether_regularizer_grad: bad argument");
+    reg_grad_kernel<<<blocks_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(w, g, n, l1, l2);
+    count_launch();
+    return check_launch("aether_regularizer_grad");
+}
+
+extern "C" int aether_regularizer_loss(const float* w, int64_t n, float l1, float l2, float* out, void* stream) {
+    if (!w || !out || n <= 0) return set_error(AE_BAD_ARG, "aether_regularizer_loss: bad argument");
+    reg_loss_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(w, n, l1, l2, out);
+    count_launch();
+    return check_launch("aether_regularizer_loss");
+}
+
+extern "C" int aether_softmax_cce(const float* z, const int32_t* labels, float* prob, float* loss, float* dz,
+                                  int32_t* correct, int rows, int classes, float smooth_fwd, float smooth_bwd,
+                                  int input_is_prob, void* stream) {
+    if (!z || rows <= 0 || classes <= 0) return set_error(AE_BAD_ARG, "aether_softmax_cce: bad argument");
+    if (!labels && (loss || dz || correct)) return set_error(AE_BAD_ARG, "aether_softmax_cce: labels required for loss/gradient");
+    const int threads = 256;
+    const int blocks = ceil_div(rows * 32, threads);
+    softmax_cce_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(z, labels, prob, loss, dz, correct, rows, classes, smooth_fwd, smooth_bwd, input_is_prob);
+    count_launch();
+    return check_launch("aether_softmax_cce");
+}

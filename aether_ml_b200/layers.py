@@ -1,0 +1,707 @@
+"""Layer, loss and optimizer classes with the names, constructor arguments, methods and attributes of
+Aether-ML's ``CNN/models/CNN_classes_cupy.py``, computing on a B200 through libaether_b200.so.
+
+Every ``forward`` / ``backward`` below is a thin host-side wrapper: it validates shapes, owns the
+output / workspace buffers (torch CUDA tensors are used purely as device memory) and makes one or
+two C-ABI calls.  No arithmetic on activations happens in Python and there is no CPU fallback.
+
+Arrays: fp32, C-contiguous, NHWC activations, (fH, fW, Cin, Cout) filters -- the reference's layouts.
+Inputs may be torch CUDA tensors, objects exposing ``__cuda_array_interface__`` (CuPy arrays) or
+NumPy arrays (copied to the device).  Outputs are torch CUDA tensors.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import AetherConvDesc, check, lib
+
+DEFAULT_MATH_MODE = os.environ.get("AETHER_MATH_MODE", "bf16")
+
+
+def _device():
+    if not torch.cuda.is_available():
+        raise _lib.AetherError("aether_ml_b200 needs a CUDA device (no CPU fallback exists)")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def to_device(a, dtype=torch.float32):
+    """Return `a` as a contiguous CUDA tensor of `dtype` (no copy when it already is one)."""
+    if isinstance(a, torch.Tensor):
+        t = a
+    elif hasattr(a, "__cuda_array_interface__"):
+        t = torch.as_tensor(a, device=_device())
+    else:
+        t = torch.as_tensor(np.asarray(a))
+    if t.device.type != "cuda":
+        t = t.to(_device(), non_blocking=True)
+    if t.dtype != dtype:
+        t = t.to(dtype)
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _empty(shape, dtype=torch.float32):
+    return torch.empty(shape, dtype=dtype, device=_device())
+
+
+class _Workspace:
+    """Grow-only byte buffer owned by a layer and handed to the library as scratch."""
+
+    def __init__(self):
+        self.buf = None
+
+    def get(self, nbytes):
+        nbytes = max(int(nbytes), 256)
+        if self.buf is None or self.buf.numel() < nbytes:
+            self.buf = torch.empty(nbytes, dtype=torch.uint8, device=_device())
+        return self.buf
+
+
+# ------------------------------------------------------------------------------------- Conv_Layer
+class Conv_Layer:
+    """Drop-in for ``Conv_Layer`` (CNN_classes_cupy.py:37-161).
+
+    Same constructor arguments and attributes (``filter_weights``/``weights`` alias, ``biases``, the
+    four regularizer attributes; after ``forward``: ``output``, ``inputs``; after ``backward``:
+    ``dweights``, ``dbiases``, ``dinputs``).  ``dinputs`` is the scatter-ADD gradient that the
+    reference's CUDA scatter kernel produces (:4-35), returned contiguous instead of as a sliced view.
+    One extra keyword, ``math_mode`` in {"bf16", "tf32", "fp32"}, selects the operand precision of
+    the tensor-core kernels (default from $AETHER_MATH_MODE, else bf16)."""
+
+    def __init__(self, input_shape, num_filters=1, filter_size=(3, 3), strides=(1, 1), padding="same",
+                 math_mode=None):
+        self.input_shape = input_shape
+        self.num_filters = num_filters
+        self.filter_size = filter_size
+        self.strides = strides
+        self.padding = padding
+        self.math_mode = math_mode or DEFAULT_MATH_MODE
+        if self.math_mode not in _lib.MATH_MODES:
+            raise ValueError("math_mode must be one of %s" % sorted(_lib.MATH_MODES))
+        self.weight_regularizer_l1 = 0
+        self.weight_regularizer_l2 = 0
+        self.bias_regularizer_l1 = 0
+        self.bias_regularizer_l2 = 0
+        input_depth = input_shape[-1]
+        n = filter_size[0] * filter_size[1] * input_depth
+        std = np.float32(np.sqrt(np.float32(2.0 / n)))
+        # He-normal initialisation (:54-66), drawn on the host from NumPy's global generator
+        w = np.random.randn(filter_size[0], filter_size[1], input_depth, num_filters).astype(np.float32) * std
+        self.filter_weights = to_device(w)
+        self.biases = torch.zeros(num_filters, dtype=torch.float32, device=_device())
+        self._ws = _Workspace()
+        self._desc = None
+        self._fwd_input_ptr = None
+
+    # `weights` is the same array object as `filter_weights` (:68); in-place optimizer updates on
+    # either name are visible through both.
+    @property
+    def weights(self):
+        return self.filter_weights
+
+    @weights.setter
+    def weights(self, value):
+        self.filter_weights = value
+
+    def _make_desc(self, S, H, W, Cin):
+        fH, fW = self.filter_size
+        sH, sW = self.strides
+        P = (fH - 1) // 2 if self.padding == "same" else 0      # :78-81, same amount on both axes
+        Ho = int((H + 2 * P - fH) / sH + 1)
+        Wo = int((W + 2 * P - fW) / sW + 1)
+        d = AetherConvDesc(S, H, W, Cin, self.num_filters, fH, fW, sH, sW, P, P, _lib.MATH_MODES[self.math_mode])
+        return d, Ho, Wo
+
+    def forward(self, inputs, training):
+        x = to_device(inputs)
+        if x.ndim != 4:
+            raise ValueError(f"Expected a 4D tensor, got {x.ndim} instead.")
+        S, H, W, Cin = x.shape
+        if Cin != self.filter_weights.shape[2]:
+            raise ValueError(f"input has {Cin} channels, filters expect {self.filter_weights.shape[2]}")
+        d, Ho, Wo = self._make_desc(S, H, W, Cin)
+        if Ho < 1 or Wo < 1:
+            raise ValueError("filter larger than the padded input")
+        L = lib()
+        ws = self._ws.get(L.aether_conv2d_workspace_bytes(C.byref(d)))
+        y = _empty((S, Ho, Wo, self.num_filters))
+        check(L.aether_conv2d_fwd(C.byref(d), _ptr(x), _ptr(self.filter_weights), _ptr(self.biases), _ptr(y),
+                                  _ptr(ws), ws.numel(), _stream()), "aether_conv2d_fwd")
+        self.inputs = x
+        self.output = y
+        self._desc = d
+        self._fwd_input_ptr = x.data_ptr()
+        return self.output
+
+    def backward(self, dvalues, need_dinputs=True):
+        if self._desc is None:
+            raise RuntimeError("Conv_Layer.backward called before forward")
+        dy = to_device(dvalues)
+        d = self._desc
+        x = self.inputs
+        Ho = (d.H + 2 * d.padH - d.fH) // d.sH + 1
+        Wo = (d.W + 2 * d.padW - d.fW) // d.sW + 1
+        if tuple(dy.shape) != (d.S, Ho, Wo, d.Cout):
+            raise ValueError(f"dvalues has shape {tuple(dy.shape)}, expected {(d.S, Ho, Wo, d.Cout)}")
+        L = lib()
+        ws = self._ws.get(L.aether_conv2d_workspace_bytes(C.byref(d)))
+        if getattr(self, "_grad_views", None) is not None:
+            self.dweights, self.dbiases = self._grad_views
+        else:
+            self.dweights = _empty(tuple(self.filter_weights.shape))
+            self.dbiases = _empty((d.Cout,))
+        dx = _empty((d.S, d.H, d.W, d.Cin)) if need_dinputs else None
+        shadow_ok = 1 if self._fwd_input_ptr == x.data_ptr() else 0
+        check(L.aether_conv2d_bwd(C.byref(d), _ptr(x), _ptr(dy), _ptr(self.filter_weights), _ptr(dx),
+                                  _ptr(self.dweights), _ptr(self.dbiases), _ptr(ws), ws.numel(), shadow_ok,
+                                  _stream()), "aether_conv2d_bwd")
+        self.dinputs = dx
+        return self.dinputs
+
+    def get_parameters(self):
+        return self.filter_weights, self.biases
+
+    def set_parameters(self, weights, biases):
+        # copy into the existing arrays so `weights` stays the same object as `filter_weights`
+        w = to_device(weights)
+        b = to_device(biases).reshape(-1)
+        if tuple(w.shape) != tuple(self.filter_weights.shape) or b.numel() != self.biases.numel():
+            raise ValueError("parameter shapes do not match this layer")
+        self.filter_weights.copy_(w)
+        self.biases.copy_(b)
+
+
+# ------------------------------------------------------------------------------------- Pooling
+class Pooling:
+    """Drop-in for ``Pooling`` (CNN_classes_cupy.py:204-312), 'valid' padding, max or average.
+    The argmax is kept as one byte per output (window-local index of the first maximum);
+    ``max_indicies`` reconstructs the reference's (rows, cols) pair on demand."""
+
+    def __init__(self, filter_size=(2, 2), strides=(2, 2), padding="valid", pooling_type="max"):
+        self.filter_size = filter_size
+        self.strides = strides
+        self.padding = padding
+        self.pooling_type = pooling_type
+
+    def _kind(self):
+        if self.pooling_type == "max":
+            return _lib.POOL_MAX
+        if self.pooling_type == "average":
+            return _lib.POOL_AVG
+        raise ValueError(f"Expected pooling_type == max or average, recieved {self.pooling_type} instead")
+
+    def forward(self, inputs, training):
+        x = to_device(inputs)
+        if x.ndim != 4:
+            raise ValueError(f"Expected a 4D tensor, got {x.ndim} instead.")
+        if self.padding != "valid":
+            # the reference's "same" branch reads H_out before assigning it (:226-233) and cannot run
+            raise ValueError(f"Expected padding == valid, recieved {self.padding} instead")
+        S, H, W, Cc = x.shape
+        fH, fW = self.filter_size
+        sH, sW = self.strides
+        Ho = (H - fH) // sH + 1
+        Wo = (W - fW) // sW + 1
+        kind = self._kind()
+        y = _empty((S, Ho, Wo, Cc))
+        self._argmax = _empty((S, Ho, Wo, Cc), torch.uint8) if kind == _lib.POOL_MAX else None
+        check(lib().aether_pool_fwd(_ptr(x), _ptr(y), _ptr(self._argmax), S, H, W, Cc, fH, fW, sH, sW, kind,
+                                    _stream()), "aether_pool_fwd")
+        self.inputs = x
+        self.output = y
+        return self.output
+
+    @property
+    def max_indicies(self):
+        fW = self.filter_size[1]
+        code = self._argmax.to(torch.int64)
+        return code // fW, code % fW
+
+    def backward(self, dvalues):
+        dy = to_device(dvalues)
+        S, H, W, Cc = self.inputs.shape
+        fH, fW = self.filter_size
+        sH, sW = self.strides
+        dx = _empty((S, H, W, Cc))
+        check(lib().aether_pool_bwd(_ptr(dy), _ptr(self._argmax), _ptr(dx), S, H, W, Cc, fH, fW, sH, sW,
+                                    self._kind(), _stream()), "aether_pool_bwd")
+        self.dinputs = dx
+        return self.dinputs
+
+
+# ------------------------------------------------------------------------------------- activations
+class ReLU:
+    """Drop-in for ``ReLU`` (CNN_classes_cupy.py:406-415)."""
+    _alpha = 0.0
+
+    def forward(self, inputs, training):
+        x = to_device(inputs)
+        y = torch.empty_like(x)
+        check(lib().aether_leaky_relu_fwd(_ptr(x), _ptr(y), x.numel(), float(self._alpha), _stream()),
+              "aether_leaky_relu_fwd")
+        self.inputs = x
+        self.output = y
+        return self.output
+
+    def backward(self, dvalues):
+        dy = to_device(dvalues)
+        dx = torch.empty_like(dy)
+        check(lib().aether_leaky_relu_bwd(_ptr(self.inputs), _ptr(dy), _ptr(dx), dy.numel(), float(self._alpha),
+                                          _stream()), "aether_leaky_relu_bwd")
+        self.dinputs = dx
+        return self.dinputs
+
+
+class Leaky_ReLU(ReLU):
+    """Drop-in for ``Leaky_ReLU`` (CNN_classes_cupy.py:417-428)."""
+
+    def __init__(self, alpha=0.01):
+        self.alpha = alpha
+
+    @property
+    def _alpha(self):
+        return self.alpha
+
+
+# ------------------------------------------------------------------------------------- dropout
+class Layer_Dropout_Spatial:
+    """Drop-in for ``Layer_Dropout_Spatial`` (CNN_classes_cupy.py:384-404): one Bernoulli(keep) draw per
+    channel, shared by the whole batch, scaled by 1/keep.  The draw uses NumPy's global generator like
+    the reference's NumPy twin; ``channel_mask`` (1,1,1,C) may be overwritten before ``forward`` by
+    setting ``fixed_mask``.  Output stays fp32 (the reference promotes to fp64 through its mask)."""
+
+    def __init__(self, rate):
+        self.rate = rate
+        self.keep_prob = 1 - rate
+        self.fixed_mask = None
+
+    def forward(self, inputs, training):
+        x = to_device(inputs)
+        self.inputs = x
+        if not training:
+            self.output = x.clone()
+            return self.output
+        Cc = x.shape[-1]
+        if self.fixed_mask is not None:
+            mask = np.asarray(self.fixed_mask, dtype=np.float32).reshape(1, 1, 1, Cc)
+        else:
+            mask = (np.random.binomial(1, self.keep_prob, size=(1, 1, 1, Cc)) / self.keep_prob).astype(np.float32)
+        self.channel_mask = to_device(mask)
+        y = torch.empty_like(x)
+        check(lib().aether_channel_scale(_ptr(x), _ptr(self.channel_mask), _ptr(y), x.numel(), Cc, _stream()),
+              "aether_channel_scale")
+        self.output = y
+        return self.output
+
+    def backward(self, dvalues):
+        dy = to_device(dvalues)
+        dx = torch.empty_like(dy)
+        check(lib().aether_channel_scale(_ptr(dy), _ptr(self.channel_mask), _ptr(dx), dy.numel(), dy.shape[-1],
+                                         _stream()), "aether_channel_scale")
+        self.dinputs = dx
+        return self.dinputs
+
+
+class Layer_Dropout:
+    """Drop-in for ``Layer_Dropout`` (CNN_classes_cupy.py:364-382).  ``rate`` is the drop rate; the
+    element mask Bernoulli(1-rate)/(1-rate) is drawn on the device from a Philox stream keyed by
+    ``seed`` and a per-call offset (``rank_offset`` separates data-parallel ranks)."""
+    _next_seed = 0x5EED
+
+    def __init__(self, rate, seed=None, rank_offset=0):
+        self.rate = 1 - rate          # the reference stores the KEEP probability under this name (:367)
+        if seed is None:
+            seed = Layer_Dropout._next_seed
+            Layer_Dropout._next_seed += 1
+        self.seed = int(seed)
+        self.rank_offset = int(rank_offset)
+        self._calls = 0
+
+    def forward(self, inputs, training):
+        x = to_device(inputs)
+        self.inputs = x
+        if not training:
+            self.output = x.clone()
+            return self.output
+        y = torch.empty_like(x)
+        self.binary_mask = torch.empty_like(x)
+        offset = (self._calls << 40) + (self.rank_offset << 32)
+        self._calls += 1
+        check(lib().aether_dropout_fwd(_ptr(x), _ptr(y), _ptr(self.binary_mask), x.numel(), float(self.rate),
+                                       self.seed, offset, _stream()), "aether_dropout_fwd")
+        self.output = y
+        return self.output
+
+    def backward(self, dvalues):
+        dy = to_device(dvalues)
+        dx = torch.empty_like(dy)
+        check(lib().aether_mul(_ptr(dy), _ptr(self.binary_mask), _ptr(dx), dy.numel(), _stream()), "aether_mul")
+        self.dinputs = dx
+        return self.dinputs
+
+
+# ------------------------------------------------------------------------------------- Batch_Norm
+class Batch_Norm:
+    """Drop-in for ``Batch_Norm`` (CNN_classes_cupy.py:430-526) for 4-D (NHWC) and 2-D inputs.
+    ``gamma``/``beta`` (aliased as ``weights``/``biases``) have shape (C,); ``running_mean`` /
+    ``running_var`` / ``batch_mean`` / ``batch_var`` are exposed with the reference's keep-dims shape
+    ((1,1,1,C) or (1,C)) as views of flat (C,) storage.  ``normalized`` is not stored: the backward
+    kernel recomputes x-hat from the saved statistics."""
+
+    def __init__(self, epsilon=1e-5, momentum=0.9, n_features=None):
+        self.epsilon = epsilon
+        self.momentum = momentum
+        self.gamma = None
+        self.beta = None
+        self.running_mean = None
+        self.running_var = None
+        self.weight_regularizer_l1 = 0
+        self.weight_regularizer_l2 = 0
+        self.bias_regularizer_l1 = 0
+        self.bias_regularizer_l2 = 0
+        self._ws = _Workspace()
+        self._keep = None
+        if n_features is not None:
+            self._create(n_features)
+
+    def _create(self, Cc):
+        dev = _device()
+        self.gamma = torch.ones(Cc, dtype=torch.float32, device=dev)
+        self.beta = torch.zeros(Cc, dtype=torch.float32, device=dev)
+        self._rm = torch.zeros(Cc, dtype=torch.float32, device=dev)
+        self._rv = torch.ones(Cc, dtype=torch.float32, device=dev)
+        self.running_mean = self._rm
+        self.running_var = self._rv
+
+    @property
+    def weights(self):
+        return self.gamma
+
+    @weights.setter
+    def weights(self, v):
+        self.gamma = v
+
+    @property
+    def biases(self):
+        return self.beta
+
+    @biases.setter
+    def biases(self, v):
+        self.beta = v
+
+    def forward(self, inputs, training):
+        x = to_device(inputs)
+        if x.ndim not in (2, 4):
+            raise ValueError(f"Expected a 2D or 4D tensor, got {x.ndim} instead.")
+        Cc = x.shape[-1]
+        if self.gamma is None:
+            self._create(Cc)
+        rows = x.numel() // Cc
+        keep = (1,) * (x.ndim - 1) + (Cc,)
+        L = lib()
+        ws = self._ws.get(L.aether_bn_workspace_bytes(rows, Cc))
+        y = torch.empty_like(x)
+        if training:
+            self._bm = _empty((Cc,))
+            self._bv = _empty((Cc,))
+            check(L.aether_bn_fwd_train(_ptr(x), _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
+                                        _ptr(self._bm), _ptr(self._bv), _ptr(y), rows, Cc, float(self.epsilon),
+                                        float(self.momentum), _ptr(ws), ws.numel(), _stream()), "aether_bn_fwd_train")
+            self.batch_mean = self._bm.view(keep)
+            self.batch_var = self._bv.view(keep)
+            self.running_mean = self._rm.view(keep)       # the reference's stats pick up keep-dims here (:475-476)
+            self.running_var = self._rv.view(keep)
+        else:
+            check(L.aether_bn_fwd_eval(_ptr(x), _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
+                                       _ptr(y), rows, Cc, float(self.epsilon), _ptr(ws), ws.numel(), _stream()),
+                  "aether_bn_fwd_eval")
+        self.inputs = x
+        self.output = y
+        return self.output
+
+    def backward(self, dvalues):
+        dy = to_device(dvalues)
+        x = self.inputs
+        Cc = x.shape[-1]
+        rows = x.numel() // Cc
+        L = lib()
+        ws = self._ws.get(L.aether_bn_workspace_bytes(rows, Cc))
+        dx = torch.empty_like(x)
+        if getattr(self, "_grad_views", None) is not None:
+            self.dweights, self.dbiases = self._grad_views
+        else:
+            self.dweights = _empty((Cc,))
+            self.dbiases = _empty((Cc,))
+        check(L.aether_bn_bwd(_ptr(x), _ptr(dy), _ptr(self.gamma), _ptr(self._bm), _ptr(self._bv), _ptr(dx),
+                              _ptr(self.dweights), _ptr(self.dbiases), rows, Cc, float(self.epsilon), _ptr(ws),
+                              ws.numel(), _stream()), "aether_bn_bwd")
+        self.dinputs = dx
+        return self.dinputs
+
+    def get_parameters(self):
+        return self.gamma, self.beta, self.running_mean, self.running_var
+
+    def set_parameters(self, gamma, beta, running_mean, running_var):
+        g = to_device(gamma).reshape(-1)
+        if self.gamma is None:
+            self._create(g.numel())
+        self.gamma.copy_(g)
+        self.beta.copy_(to_device(beta).reshape(-1))
+        self._rm.copy_(to_device(running_mean).reshape(-1))
+        self._rv.copy_(to_device(running_var).reshape(-1))
+
+
+# ------------------------------------------------------------------------------------- Flatten / Dense
+class Flatten:
+    """Drop-in for ``Flatten`` (CNN_classes_cupy.py:528-539); a view, no kernel."""
+
+    def forward(self, inputs, training):
+        x = to_device(inputs)
+        self.inputs_shape = x.shape
+        self.output = x.reshape(x.shape[0], -1)
+        return self.output
+
+    def backward(self, dvalues):
+        self.dinputs = to_device(dvalues).reshape(self.inputs_shape)
+        return self.dinputs
+
+
+class Layer_Dense:
+    """Drop-in for ``Layer_Dense`` (CNN_classes_cupy.py:315-362).  The three products run through the
+    convolution kernels as a 1x1 convolution on a 1x1 image (x (S,n_in) is NHWC with H=W=1; weights
+    (n_in,n_out) are a (1,1,Cin,Cout) filter), so they use the same tensor-core path.  Parameters are
+    fp32 (the reference's are fp64 because ``randn`` is); biases keep the (1, n_out) shape."""
+
+    def __init__(self, n_inputs, n_neurons, weight_regularizer_l1=0, bias_regularizer_l1=0,
+                 weight_regularizer_l2=0, bias_regularizer_l2=0, math_mode=None):
+        w = 0.01 * np.random.randn(n_inputs, n_neurons) * np.sqrt(2.0 / n_inputs)       # :320-321
+        self.weights = to_device(w.astype(np.float32))
+        self.biases = torch.zeros((1, n_neurons), dtype=torch.float32, device=_device())
+        self.weight_regularizer_l1 = weight_regularizer_l1
+        self.weight_regularizer_l2 = weight_regularizer_l2
+        self.bias_regularizer_l1 = bias_regularizer_l1
+        self.bias_regularizer_l2 = bias_regularizer_l2
+        self.math_mode = math_mode or DEFAULT_MATH_MODE
+        self._ws = _Workspace()
+
+    def _desc(self, S):
+        n_in, n_out = self.weights.shape
+        return AetherConvDesc(S, 1, 1, n_in, n_out, 1, 1, 1, 1, 0, 0, _lib.MATH_MODES[self.math_mode])
+
+    def forward(self, inputs, training):
+        x = to_device(inputs)
+        if x.ndim != 2 or x.shape[1] != self.weights.shape[0]:
+            raise ValueError(f"Layer_Dense expects (samples, {self.weights.shape[0]}), got {tuple(x.shape)}")
+        d = self._desc(x.shape[0])
+        L = lib()
+        ws = self._ws.get(L.aether_conv2d_workspace_bytes(C.byref(d)))
+        y = _empty((x.shape[0], self.weights.shape[1]))
+        check(L.aether_conv2d_fwd(C.byref(d), _ptr(x), _ptr(self.weights), _ptr(self.biases), _ptr(y), _ptr(ws),
+                                  ws.numel(), _stream()), "aether_conv2d_fwd")
+        self.inputs = x
+        self.output = y
+        return self.output
+
+    def backward(self, dvalues):
+        dy = to_device(dvalues)
+        x = self.inputs
+        d = self._desc(x.shape[0])
+        L = lib()
+        ws = self._ws.get(L.aether_conv2d_workspace_bytes(C.byref(d)))
+        if getattr(self, "_grad_views", None) is not None:
+            self.dweights, self.dbiases = self._grad_views
+        else:
+            self.dweights = torch.empty_like(self.weights)
+            self.dbiases = torch.empty_like(self.biases)
+        dx = torch.empty_like(x)
+        check(L.aether_conv2d_bwd(C.byref(d), _ptr(x), _ptr(dy), _ptr(self.weights), _ptr(dx), _ptr(self.dweights),
+                                  _ptr(self.dbiases), _ptr(ws), ws.numel(), 1, _stream()), "aether_conv2d_bwd")
+        if self.weight_regularizer_l1 > 0 or self.weight_regularizer_l2 > 0:
+            check(L.aether_regularizer_grad(_ptr(self.weights), _ptr(self.dweights), self.weights.numel(),
+                                            float(self.weight_regularizer_l1), float(self.weight_regularizer_l2),
+                                            _stream()), "aether_regularizer_grad")
+        if self.bias_regularizer_l1 > 0 or self.bias_regularizer_l2 > 0:
+            check(L.aether_regularizer_grad(_ptr(self.biases), _ptr(self.dbiases), self.biases.numel(),
+                                            float(self.bias_regularizer_l1), float(self.bias_regularizer_l2),
+                                            _stream()), "aether_regularizer_grad")
+        self.dinputs = dx
+        return self.dinputs
+
+    def get_parameters(self):
+        return self.weights, self.biases
+
+    def set_parameters(self, weights, biases):
+        self.weights.copy_(to_device(weights))
+        self.biases.copy_(to_device(biases).reshape(1, -1))
+
+
+# ------------------------------------------------------------------------------------- softmax / loss
+def _labels_i32(y_true):
+    y = y_true if isinstance(y_true, torch.Tensor) else torch.as_tensor(np.asarray(y_true))
+    if y.ndim == 2:                   # one-hot rows -> class indices
+        y = y.argmax(dim=1)
+    return to_device(y, torch.int32)
+
+
+def _softmax_cce(z, labels, want_prob, want_loss, want_dz, want_correct, smooth_fwd, smooth_bwd, input_is_prob=False):
+    rows, classes = z.shape
+    prob = _empty((rows, classes)) if want_prob else None
+    loss = _empty((rows,)) if want_loss else None
+    dz = _empty((rows, classes)) if want_dz else None
+    correct = _empty((rows,), torch.int32) if want_correct else None
+    check(lib().aether_softmax_cce(_ptr(z), _ptr(labels), _ptr(prob), _ptr(loss), _ptr(dz), _ptr(correct), rows,
+                                   classes, float(smooth_fwd), float(smooth_bwd), 1 if input_is_prob else 0,
+                                   _stream()), "aether_softmax_cce")
+    return prob, loss, dz, correct
+
+
+class SoftMax:
+    """Drop-in for ``SoftMax`` (CNN_classes_cupy.py:541-563).  The standalone Jacobian ``backward`` of
+    the reference (:549-560) is not provided: every network in the reference ends in SoftMax +
+    categorical cross-entropy and takes the combined backward (:666-680)."""
+
+    def forward(self, inputs, training=True):
+        z = to_device(inputs)
+        self.inputs = z
+        self.output, _, _, _ = _softmax_cce(z, None, True, False, False, False, 0.0, 0.0)
+        return self.output
+
+    def predictions(self, outputs):
+        return to_device(outputs).argmax(dim=1)
+
+
+class Loss:
+    """Accumulating loss base class, ``Loss`` (CNN_classes_cupy.py:565-609)."""
+
+    def remember_trainable_layers(self, trainable_layers):
+        self.trainable_layers = trainable_layers
+
+    def calculate(self, output, y, *, include_regularization=False, training=True):
+        sample_losses = self.forward(output, y, training)
+        data_loss = sample_losses.mean()
+        self.accumulated_sum += sample_losses.sum()
+        self.accumulated_count += len(sample_losses)
+        if not include_regularization:
+            return data_loss
+        return data_loss, self.regularization_loss()
+
+    def calculate_accumulated(self, *, include_regularization=False):
+        data_loss = self.accumulated_sum / self.accumulated_count
+        if not include_regularization:
+            return data_loss
+        return data_loss, self.regularization_loss()
+
+    def new_pass(self):
+        self.accumulated_sum = 0
+        self.accumulated_count = 0
+
+    def regularization_loss(self):
+        out = None
+        L = lib()
+        for layer in self.trainable_layers:
+            for arr, l1, l2 in ((layer.weights, layer.weight_regularizer_l1, layer.weight_regularizer_l2),
+                                (layer.biases, layer.bias_regularizer_l1, layer.bias_regularizer_l2)):
+                if l1 > 0 or l2 > 0:
+                    if out is None:
+                        out = torch.zeros(1, dtype=torch.float32, device=_device())
+                    check(L.aether_regularizer_loss(_ptr(arr), arr.numel(), float(l1), float(l2), _ptr(out),
+                                                    _stream()), "aether_regularizer_loss")
+        return out[0] if out is not None else 0
+
+
+class Loss_CategoricalCrossEntropy(Loss):
+    """Drop-in for ``Loss_CategoricalCrossEntropy`` (CNN_classes_cupy.py:611-652); ``y_pred`` are
+    probabilities, ``y_true`` class indices or one-hot rows."""
+
+    def __init__(self, label_smoothing=0.0):
+        self.label_smoothing = label_smoothing
+
+    def forward(self, y_pred, y_true, training=True):
+        p = to_device(y_pred)
+        smooth = self.label_smoothing if training else 0.0
+        _, loss, _, _ = _softmax_cce(p, _labels_i32(y_true), False, True, False, False, smooth, 0.0, input_is_prob=True)
+        return loss
+
+    def backward(self, dvalues, y_true):
+        p = to_device(dvalues)
+        _, _, dz, _ = _softmax_cce(p, _labels_i32(y_true), False, False, True, False, 0.0, self.label_smoothing,
+                                   input_is_prob=True)
+        self.dinputs = dz
+        return self.dinputs
+
+
+class Activation_Softmax_Loss_CategoricalCrossEntropy:
+    """Drop-in for the combined class (CNN_classes_cupy.py:654-680); ``backward`` takes the softmax
+    OUTPUT and returns (p - y_smooth)/samples."""
+
+    def __init__(self, label_smoothing=0.0):
+        self.activation = SoftMax()
+        self.loss = Loss_CategoricalCrossEntropy(label_smoothing)
+        self.label_smoothing = label_smoothing
+
+    def forward(self, inputs, y_true, training=True):
+        self.activation.forward(inputs, training)
+        self.output = self.activation.output
+        return self.loss.calculate(self.output, y_true, training=training)
+
+    def backward(self, dvalues, y_true, training=True):
+        p = to_device(dvalues)
+        smooth = self.label_smoothing if training else 0.0
+        _, _, dz, _ = _softmax_cce(p, _labels_i32(y_true), False, False, True, False, 0.0, smooth, input_is_prob=True)
+        self.dinputs = dz
+        return self.dinputs
+
+
+# ------------------------------------------------------------------------------------- Adam
+class Optimizer_Adam:
+    """Drop-in for ``Optimizer_Adam`` (CNN_classes_cupy.py:685-736).  State lives on the layer under the
+    reference's attribute names (``weight_momentums``, ``weight_cache``, ``bias_momentums``,
+    ``bias_cache``) and parameters are updated in place.  ``grad_scale`` multiplies every gradient
+    first (1/world_size turns an all-reduced sum into the data-parallel average)."""
+
+    def __init__(self, learning_rate=.001, decay=0., epsilon=1e-7, beta_1=0.9, beta_2=.999):
+        self.learning_rate = learning_rate
+        self.current_learning_rate = learning_rate
+        self.decay = decay
+        self.iterations = 0
+        self.epsilon = epsilon
+        self.beta_1 = beta_1
+        self.beta_2 = beta_2
+        self.grad_scale = 1.0
+
+    def pre_update_parameters(self):
+        if self.decay:
+            self.current_learning_rate = self.learning_rate * (1. / (1. + self.decay * self.iterations))
+
+    def _step(self, p, g, m, v):
+        t = self.iterations + 1
+        check(lib().aether_adam_step(_ptr(p), _ptr(g), _ptr(m), _ptr(v), p.numel(), float(self.current_learning_rate),
+                                     float(self.beta_1), float(self.beta_2), float(self.epsilon),
+                                     float(1 - self.beta_1 ** t), float(1 - self.beta_2 ** t), float(self.grad_scale),
+                                     _stream()), "aether_adam_step")
+
+    def update_parameters(self, layer):
+        if not hasattr(layer, "weight_cache"):
+            layer.weight_momentums = torch.zeros_like(layer.weights)
+            layer.weight_cache = torch.zeros_like(layer.weights)
+            layer.bias_momentums = torch.zeros_like(layer.biases)
+            layer.bias_cache = torch.zeros_like(layer.biases)
+        self._step(layer.weights, layer.dweights, layer.weight_momentums, layer.weight_cache)
+        self._step(layer.biases, layer.dbiases, layer.bias_momentums, layer.bias_cache)
+
+    def update_flat(self, params, grads, m, v):
+        """One launch over a flat parameter buffer (used by the data-parallel trainer)."""
+        self._step(params, grads, m, v)
+
+    def post_update_parameters(self):
+        self.iterations += 1

@@ -1,0 +1,143 @@
+/* aether_b200.h -- C ABI of libaether_b200.so.
+ *
+ * A B200 (sm_100a) implementation of the convolution hot path of Aether-ML
+ * (https://github.com/AlexanderSoftCode/Aether-ML) and of the bandwidth-bound layers around it.
+ * Each entry point replaces the arithmetic of one method of the reference's layer classes in
+ * CNN/models/CNN_classes_cupy.py (cited per function as file:line); the Python classes of the same
+ * names in aether_ml_b200/layers.py call these through ctypes.
+ *
+ * Conventions
+ *   - Every pointer is a raw DEVICE address (e.g. arr.__cuda_array_interface__['data'][0], torch
+ *     tensor.data_ptr()) of a C-contiguous fp32 array unless stated otherwise.  Activations are NHWC,
+ *     filters are (fH, fW, Cin, Cout) -- the reference's own layouts.  Arrays must be 16-byte aligned.
+ *   - The caller owns every buffer, including workspaces (size them with the *_workspace_bytes query).
+ *     The library allocates nothing per call and frees nothing of the caller's.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream).  Calls only enqueue work;
+ *     they never synchronise.
+ *   - Return value: 0 on success, negative on failure (AETHER_E_*); aether_last_error() then holds a
+ *     message for the calling thread.  Nothing is launched when an argument check fails.
+ *   - Kernels that wait on hardware barriers give up after about two seconds and record a code that
+ *     aether_device_status() returns after the stream has been synchronised (0 = no such event).
+ */
+#ifndef AETHER_B200_H
+#define AETHER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AETHER_E_BAD_ARG (-1)
+#define AETHER_E_UNSUPPORTED (-2)
+#define AETHER_E_CUDA (-3)
+#define AETHER_E_DEVICE_TIMEOUT (-4)
+
+/* Operand precision of the convolution GEMMs (accumulation is always fp32). */
+#define AETHER_MATH_BF16 0 /* bf16 operands on the tensor cores (tcgen05 kind::f16)            */
+#define AETHER_MATH_TF32 1 /* tf32 operands on the tensor cores (tcgen05 kind::tf32)           */
+#define AETHER_MATH_FP32 2 /* fp32 FMA on the CUDA cores (also used for shapes the tensor path   */
+                           /* does not take: stride > 1, Cin or Cout < 16 or not a multiple of 4) */
+
+#define AETHER_POOL_MAX 0
+#define AETHER_POOL_AVG 1
+
+/* Geometry of one Conv_Layer (constructor arguments at CNN_classes_cupy.py:38-45 plus the batch).
+ * padH/padW are the zero padding on each side: (fH-1)/2 on BOTH axes for padding="same" (:78-81),
+ * 0 for "valid".  Output size is (H + 2*padH - fH)/sH + 1 (:84-85). */
+typedef struct AetherConvDesc {
+    int32_t S, H, W, Cin, Cout;
+    int32_t fH, fW, sH, sW, padH, padW;
+    int32_t math_mode; /* AETHER_MATH_* */
+} AetherConvDesc;
+
+int aether_version(void);
+/* Message of the last failed call on this thread ("" if none). */
+const char* aether_last_error(void);
+/* Number of kernels this library has launched since it was loaded (all threads). */
+uint64_t aether_launch_count(void);
+/* Code recorded by a kernel that abandoned a bounded wait (0 = none).  Read after synchronising. */
+int aether_device_status(void);
+void aether_device_status_clear(void);
+
+/* ---- Conv_Layer ------------------------------------------------------------------------------ */
+
+/* Bytes of scratch one layer needs for forward + backward (shadow copies of the operands in the MMA
+ * precision, split-K partial sums).  The same buffer should be passed to the forward and the
+ * backward call of a layer. */
+size_t aether_conv2d_workspace_bytes(const AetherConvDesc* desc);
+
+/* Conv_Layer.forward, CNN_classes_cupy.py:70-120: y = conv(x, w) + b with zero padding.
+ * x (S,H,W,Cin), w (fH,fW,Cin,Cout), b (Cout) or NULL, y (S,Ho,Wo,Cout). */
+int aether_conv2d_fwd(const AetherConvDesc* desc, const float* x, const float* w, const float* b, float* y, void* ws,
+                      size_t ws_bytes, void* stream);
+
+/* Conv_Layer.backward, CNN_classes_cupy.py:123-154: db = sum dy (:132), dw = windows^T dy (:134),
+ * dx = scatter-add of dy w^T (:138-146) with the padding border removed (:149-153; returned
+ * contiguous).  Any of dx, dw, db may be NULL to skip it.  x_shadow_valid != 0 tells the library that
+ * `ws` still holds the operand copy of the same x made by aether_conv2d_fwd (saves one pass). */
+int aether_conv2d_bwd(const AetherConvDesc* desc, const float* x, const float* dy, const float* w, float* dx, float* dw,
+                      float* db, void* ws, size_t ws_bytes, int x_shadow_valid, void* stream);
+
+/* ---- Batch_Norm (CNN_classes_cupy.py:430-526); x is [rows][C], rows = product of leading axes --- */
+size_t aether_bn_workspace_bytes(int64_t rows, int C);
+/* Training forward :467-476.  Writes batch_mean/batch_var (biased), y, and updates running_* in place
+ * as momentum*old + (1-momentum)*batch. */
+int aether_bn_fwd_train(const float* x, const float* gamma, const float* beta, float* running_mean, float* running_var,
+                        float* batch_mean, float* batch_var, float* y, int64_t rows, int C, float eps, float momentum,
+                        void* ws, size_t ws_bytes, void* stream);
+/* Inference forward :478-480 (ws: at least 2*C floats). */
+int aether_bn_fwd_eval(const float* x, const float* gamma, const float* beta, const float* running_mean,
+                       const float* running_var, float* y, int64_t rows, int C, float eps, void* ws, size_t ws_bytes,
+                       void* stream);
+/* Backward :484-508: dx, dgamma (= dweights), dbeta (= dbiases). */
+int aether_bn_bwd(const float* x, const float* dy, const float* gamma, const float* batch_mean, const float* batch_var,
+                  float* dx, float* dgamma, float* dbeta, int64_t rows, int C, float eps, void* ws, size_t ws_bytes,
+                  void* stream);
+
+/* ---- Pooling, 'valid' padding (CNN_classes_cupy.py:204-312) ---------------------------------- */
+/* Forward :212-273.  argmax (uint8, same shape as y; max pooling only) receives i*fW+j of the first
+ * maximum of each window in row-major order (:259-265). */
+int aether_pool_fwd(const float* x, float* y, uint8_t* argmax, int S, int H, int W, int C, int fH, int fW, int sH, int sW,
+                    int kind, void* stream);
+/* Backward :275-312 (max: routes dy to the argmax cell; average: dy/(fH*fW) to every cell, kernel :163-202). */
+int aether_pool_bwd(const float* dy, const uint8_t* argmax, float* dx, int S, int H, int W, int C, int fH, int fW, int sH,
+                    int sW, int kind, void* stream);
+
+/* ---- ReLU :406-415 (alpha = 0) and Leaky_ReLU :417-428 --------------------------------------- */
+int aether_leaky_relu_fwd(const float* x, float* y, int64_t n, float alpha, void* stream);
+/* dx = dy where x >= 0, alpha*dy where x < 0. */
+int aether_leaky_relu_bwd(const float* x, const float* dy, float* dx, int64_t n, float alpha, void* stream);
+
+/* ---- Layer_Dropout_Spatial :384-404: y = x * scale[c], scale = channel mask / keep_prob (C floats);
+ *      the same call with dy gives the backward. */
+int aether_channel_scale(const float* x, const float* scale, float* y, int64_t n, int C, void* stream);
+/* ---- Layer_Dropout :364-382: mask = Bernoulli(keep_prob)/keep_prob drawn from Philox(seed, offset),
+ *      y = x * mask; the mask is stored for the backward (aether_mul(dy, mask)). */
+int aether_dropout_fwd(const float* x, float* y, float* mask, int64_t n, float keep_prob, uint64_t seed, uint64_t offset,
+                       void* stream);
+int aether_mul(const float* a, const float* b, float* y, int64_t n, void* stream);
+
+/* ---- Optimizer_Adam.update_parameters :702-734 over one flat buffer.  bias_corr = 1 - beta^(it+1);
+ *      epsilon is added outside the square root; grad_scale multiplies g first (1/world for the
+ *      data-parallel average). */
+int aether_adam_step(float* p, const float* g, float* m, float* v, int64_t n, float lr, float beta1, float beta2,
+                     float eps, float bias_corr1, float bias_corr2, float grad_scale, void* stream);
+/* L1/L2 terms of Layer_Dense.backward :337-351: g += l1*sign(w) + 2*l2*w. */
+int aether_regularizer_grad(const float* w, float* g, int64_t n, float l1, float l2, void* stream);
+/* Loss.regularization_loss :593-609: out[0] += l1*sum|w| + l2*sum w^2. */
+int aether_regularizer_loss(const float* w, int64_t n, float l1, float l2, float* out, void* stream);
+
+/* ---- SoftMax.forward :542-547 + Loss_CategoricalCrossEntropy.forward :615-632 + combined backward
+ *      :666-680.  z [rows][classes]; labels int32 [rows] or NULL; any of prob, loss (per sample), dz,
+ *      correct (1 where argmax == label) may be NULL.  smooth_fwd / smooth_bwd are the label smoothing
+ *      applied to the loss and to the gradient.  input_is_prob != 0: z already holds probabilities
+ *      (the reference's loss classes take the softmax OUTPUT), so the softmax itself is skipped. */
+int aether_softmax_cce(const float* z, const int32_t* labels, float* prob, float* loss, float* dz, int32_t* correct,
+                       int rows, int classes, float smooth_fwd, float smooth_bwd, int input_is_prob, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AETHER_B200_H */

@@ -38,6 +38,9 @@ SIGNATURES = {
     "aether_launch_count": (_U64, []),
     "aether_device_status": (_I, []),
     "aether_device_status_clear": (None, []),
+    "aether_profile_enable": (_I, [_I]),
+    "aether_profile_read": (_I, [_I, C.POINTER(C.c_double), C.POINTER(C.c_int)]),
+    "aether_profile_reset": (None, []),
     "aether_conv2d_workspace_bytes": (_SZ, [_D]),
     "aether_conv2d_fwd": (_I, [_D, _P, _P, _P, _P, _P, _SZ, _P]),
     "aether_conv2d_bwd": (_I, [_D, _P, _P, _P, _P, _P, _P, _P, _SZ, _I, _P]),

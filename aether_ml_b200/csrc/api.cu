@@ -41,6 +41,30 @@ int check_launch(const char* what) {
     return AE_OK;
 }
 
+// ---- optional kernel timing ------------------------------------------------------------------
+static constexpr int PROF_MAX = 2048;          // event pairs per kind; further launches are not timed
+struct ProfSlot {
+    cudaEvent_t beg[PROF_MAX], end[PROF_MAX];
+    int used = 0;
+    bool created = false;
+};
+static ProfSlot g_prof[PK_COUNT];
+static bool g_prof_on = false;
+
+void prof_begin(int kind, cudaStream_t st) {
+    if (!g_prof_on) return;
+    ProfSlot& s = g_prof[kind];
+    if (s.used < PROF_MAX) cudaEventRecord(s.beg[s.used], st);
+}
+void prof_end(int kind, cudaStream_t st) {
+    if (!g_prof_on) return;
+    ProfSlot& s = g_prof[kind];
+    if (s.used < PROF_MAX) {
+        cudaEventRecord(s.end[s.used], st);
+        ++s.used;
+    }
+}
+
 static int validate_desc(const AetherConvDesc* d, const char* fn) {
     if (!d) return set_error(AE_BAD_ARG, "%s: null descriptor", fn);
     if (d->S <= 0 || d->H <= 0 || d->W <= 0 || d->Cin <= 0 || d->Cout <= 0 || d->fH <= 0 || d->fW <= 0 || d->sH <= 0 ||
@@ -73,6 +97,45 @@ extern "C" uint64_t aether_launch_count(void) { return g_launches.load(std::memo
 extern "C" int aether_device_status(void) { return g_status_host ? *reinterpret_cast<volatile int*>(g_status_host) : 0; }
 extern "C" void aether_device_status_clear(void) {
     if (g_status_host) *reinterpret_cast<volatile int*>(g_status_host) = 0;
+}
+
+extern "C" int aether_profile_enable(int on) {
+    if (on) {
+        for (int k = 0; k < PK_COUNT; ++k) {
+            ProfSlot& s = g_prof[k];
+            if (!s.created) {
+                for (int i = 0; i < PROF_MAX; ++i) {
+                    if (cudaEventCreate(&s.beg[i]) != cudaSuccess || cudaEventCreate(&s.end[i]) != cudaSuccess)
+                        return set_error(AE_CUDA, "aether_profile_enable: cudaEventCreate failed");
+                }
+                s.created = true;
+            }
+            s.used = 0;
+        }
+    }
+    g_prof_on = on != 0;
+    return AE_OK;
+}
+
+extern "C" int aether_profile_read(int kind, double* total_ms, int* launches) {
+    if (kind < 0 || kind >= PK_COUNT || !total_ms || !launches)
+        return set_error(AE_BAD_ARG, "aether_profile_read: bad argument");
+    ProfSlot& s = g_prof[kind];
+    double tot = 0.0;
+    for (int i = 0; i < s.used; ++i) {
+        float ms = 0.f;
+        cudaError_t e = cudaEventSynchronize(s.end[i]);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, s.beg[i], s.end[i]);
+        if (e != cudaSuccess) return set_error(AE_CUDA, "aether_profile_read: %s", cudaGetErrorString(e));
+        tot += ms;
+    }
+    *total_ms = tot;
+    *launches = s.used;
+    return AE_OK;
+}
+
+extern "C" void aether_profile_reset(void) {
+    for (int k = 0; k < PK_COUNT; ++k) g_prof[k].used = 0;
 }
 
 extern "C" size_t aether_conv2d_workspace_bytes(const AetherConvDesc* d) {

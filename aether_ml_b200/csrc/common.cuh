@@ -26,6 +26,12 @@ int* device_status_word();
 // Checks cudaGetLastError after a launch; returns AE_OK or AE_CUDA (with message).
 int check_launch(const char* what);
 
+// Optional per-kernel timing (off by default): CUDA events recorded around selected launches on the
+// launch stream, read back through aether_profile_read.
+enum ProfKind : int { PK_IGEMM_FWD = 0, PK_IGEMM_DX = 1, PK_DW = 2, PK_SHADOW = 3, PK_COUNT = 4 };
+void prof_begin(int kind, cudaStream_t st);
+void prof_end(int kind, cudaStream_t st);
+
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

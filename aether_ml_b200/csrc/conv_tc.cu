@@ -743,7 +743,10 @@ static int launch_igemm(const IgemmParams& p, cudaStream_t st) {
     }
     const long long total = 1LL * p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles_n;
     int grid = (int)(total < num_sms() ? total : num_sms());
+    const int pk = p.sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX;
+    prof_begin(pk, st);
     igemm_conv_kernel<TF32, NT><<<grid, IGEMM_THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    prof_end(pk, st);
     count_launch();
     return check_launch("igemm_conv_kernel");
 }
@@ -795,6 +798,7 @@ static int run_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, in
 
 static int launch_cast(const float* src, __nv_bfloat16* dst, long long rows, int C, int Cp, float* colsum_part,
                        int colsum_blocks, cudaStream_t st) {
+    prof_begin(PK_SHADOW, st);
     if (colsum_part) {
         const long long rpb = (rows + colsum_blocks - 1) / colsum_blocks;
         cast_bf16_kernel<true><<<colsum_blocks, 256, 0, st>>>(src, dst, rows, C, Cp, colsum_part, rpb);
@@ -807,6 +811,7 @@ static int launch_cast(const float* src, __nv_bfloat16* dst, long long rows, int
         const long long rpb = (rows + blocks - 1) / blocks;
         cast_bf16_kernel<false><<<(int)blocks, 256, 0, st>>>(src, dst, rows, C, Cp, nullptr, rpb);
     }
+    prof_end(PK_SHADOW, st);
     count_launch();
     return check_launch("cast_bf16_kernel");
 }
@@ -845,7 +850,9 @@ static int launch_dw(const DwParams& p, int splits, int grid_y, cudaStream_t st)
         if (rc) return rc;
         configured = true;
     }
+    prof_begin(PK_DW, st);
     dw_conv_kernel<TF32, NB><<<dim3(splits, grid_y), DW_THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    prof_end(PK_DW, st);
     count_launch();
     return check_launch("dw_conv_kernel");
 }

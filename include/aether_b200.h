@@ -61,6 +61,15 @@ uint64_t aether_launch_count(void);
 int aether_device_status(void);
 void aether_device_status_clear(void);
 
+/* Optional kernel timing for benchmarks (off by default).  aether_profile_enable(1) creates a fixed
+ * pool of CUDA events once and resets the counters; while enabled, events are recorded on the launch
+ * stream around each convolution kernel.  aether_profile_read waits for the recorded events and
+ * returns the summed duration and the number of timed launches of one kind:
+ * 0 = forward implicit GEMM, 1 = dX implicit GEMM, 2 = dW kernel, 3 = operand (bf16) cast kernels. */
+int aether_profile_enable(int on);
+int aether_profile_read(int kind, double* total_ms, int* launches);
+void aether_profile_reset(void);
+
 /* ---- Conv_Layer ------------------------------------------------------------------------------ */
 
 /* Bytes of scratch one layer needs for forward + backward (shadow copies of the operands in the MMA

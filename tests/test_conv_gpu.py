@@ -1,0 +1,199 @@
+"""GPU parity tests of Conv_Layer (through the C ABI) against the NumPy oracle and the golden vectors
+made by the reference's own classes.  Tolerances are relative L2: 1e-2 for bf16, 1e-3 for tf32,
+1e-5 for the fp32 CUDA-core path."""
+import numpy as np
+import pytest
+
+from oracle import aether_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = {"bf16": 1e-2, "tf32": 1e-3, "fp32": 1e-5}
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+    from aether_ml_b200 import _lib, layers
+    if not torch.cuda.is_available():
+        pytest.fail("CUDA device required for -m gpu tests")
+    return torch, _lib, layers
+
+
+def run_layer(env, mode, x, w, b, dy, f, st, pad):
+    torch, _lib, layers = env
+    np.random.seed(0)
+    layer = layers.Conv_Layer(x.shape[1:], w.shape[3], tuple(f), tuple(st), pad, math_mode=mode)
+    layer.set_parameters(w, b)
+    assert layer.weights is layer.filter_weights
+    y = layer.forward(x, True)
+    dx = layer.backward(dy)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    return (y.cpu().numpy(), dx.cpu().numpy(), layer.dweights.cpu().numpy(), layer.dbiases.cpu().numpy())
+
+
+GOLDEN = ["conv_same_3x3", "conv_valid_3x3", "conv_same_5x5", "conv_stride2_valid", "conv_tensor_path_small",
+          "conv_cfg1_tiny"]
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32", "fp32"])
+@pytest.mark.parametrize("name", GOLDEN)
+def test_golden_vectors(env, golden, name, mode):
+    g = golden(name)
+    st = tuple(int(v) for v in g["strides"]); f = tuple(int(v) for v in g["filter_size"]); pad = str(g["padding"])
+    y, dx, dw, db = run_layer(env, mode, g["x"], g["w"], g["b"], g["dy"], f, st, pad)
+    # shapes outside the tensor-core path run in fp32 whatever the requested mode
+    tensor_path = name == "conv_tensor_path_small" and mode != "fp32"
+    tol = TOL[mode] if tensor_path else TOL["fp32"]
+    assert y.shape == g["y"].shape and dx.shape == g["x"].shape and dw.shape == g["w"].shape
+    assert O.rel_l2(y, g["y"]) <= tol
+    assert O.rel_l2(dx, g["dx"]) <= tol
+    assert O.rel_l2(dw, g["dw"]) <= tol
+    assert O.rel_l2(db, g["db"]) <= tol
+
+
+def test_notebook_known_answers(env, golden):
+    g = golden("notebook_kat")
+    zeros = np.zeros(1, np.float32)
+    y, _, _, _ = run_layer(env, "fp32", g["image"][None, :, :, None], g["kernel"][:, :, None, None], zeros,
+                           np.zeros((1, 4, 4, 1), np.float32), (3, 3), (1, 1), "same")
+    assert np.array_equal(y[0, :, :, 0], g["expected"])
+    ones = np.ones((1, 5, 5, 3), np.float32)
+    y, _, _, _ = run_layer(env, "fp32", ones, np.ones((3, 3, 3, 1), np.float32), zeros,
+                           np.zeros((1, 3, 3, 1), np.float32), (3, 3), (1, 1), "valid")
+    assert y.shape == (1, 3, 3, 1) and np.all(y == 27)
+
+
+# (S, H, W, Cin, Cout, f, pad): tensor-core shapes incl. ragged tiles, padded channel counts, 1x1, 5x5
+SHAPES = [
+    (2, 8, 8, 64, 64, 3, "same"), (8, 16, 16, 128, 128, 3, "same"), (3, 56, 56, 64, 128, 3, "same"),
+    (16, 8, 8, 256, 256, 3, "same"), (4, 14, 14, 32, 64, 3, "same"), (5, 9, 7, 64, 64, 3, "valid"),
+    (3, 10, 10, 48, 80, 5, "same"), (200, 1, 1, 512, 128, 1, "valid"), (2, 33, 17, 16, 20, 3, "same"),
+    (1, 3, 3, 64, 192, 3, "same"), (130, 4, 4, 64, 64, 3, "same"), (2, 20, 150, 32, 32, 3, "same"),
+]
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_tensor_core_shapes(env, shape, mode):
+    S, H, W, Cin, Cout, f, pad = shape
+    rng = np.random.default_rng(hash(shape) % 2**32)
+    x = rng.standard_normal((S, H, W, Cin)).astype(np.float32)
+    w = (rng.standard_normal((f, f, Cin, Cout)) * np.sqrt(2.0 / (f * f * Cin))).astype(np.float32)
+    b = (rng.standard_normal(Cout) * 0.1).astype(np.float32)
+    Ho, Wo = O.conv_out_hw(H, W, (f, f), (1, 1), pad)
+    dy = rng.standard_normal((S, Ho, Wo, Cout)).astype(np.float32)
+    y, dx, dw, db = run_layer(env, mode, x, w, b, dy, (f, f), (1, 1), pad)
+    yo = O.conv_forward_blas(x, w, b, (1, 1), pad, dtype=np.float64)
+    dxo, dwo, dbo = O.conv_backward_blas(x, w, dy, (1, 1), pad, dtype=np.float64)
+    tol = TOL[mode]
+    assert O.rel_l2(y, yo) <= tol and O.rel_l2(dx, dxo) <= tol
+    assert O.rel_l2(dw, dwo) <= tol and O.rel_l2(db, dbo) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(3, 9, 9, 3, 8, 3, (2, 2), "valid"), (2, 12, 10, 5, 7, 3, (1, 1), "same"),
+                                   (4, 28, 28, 1, 32, 3, (1, 1), "same"), (2, 11, 11, 4, 6, 5, (2, 1), "same")])
+def test_cuda_core_shapes(env, shape):
+    S, H, W, Cin, Cout, f, st, pad = shape
+    rng = np.random.default_rng(3)
+    x = rng.random((S, H, W, Cin)).astype(np.float32)
+    w = rng.standard_normal((f, f, Cin, Cout)).astype(np.float32)
+    b = rng.standard_normal(Cout).astype(np.float32)
+    Ho, Wo = O.conv_out_hw(H, W, (f, f), st, pad)
+    dy = rng.standard_normal((S, Ho, Wo, Cout)).astype(np.float32)
+    y, dx, dw, db = run_layer(env, "bf16", x, w, b, dy, (f, f), st, pad)
+    yo = O.conv_forward(x, w, b, st, pad)
+    dxo, dwo, dbo = O.conv_backward(x, w, dy, st, pad)
+    for a, o in ((y, yo), (dx, dxo), (dw, dwo), (db, dbo)):
+        assert O.rel_l2(a, o) <= 1e-5
+
+
+def test_config1_full_size(env):
+    """First BASELINE config: (128,32,32,3) -> 32 filters, U[0,1) inputs, He-normal filters, zero bias."""
+    rng = np.random.default_rng(1235)
+    x = rng.random((128, 32, 32, 3)).astype(np.float32)
+    w = (rng.standard_normal((3, 3, 3, 32)) * np.sqrt(2.0 / 27)).astype(np.float32)
+    b = np.zeros(32, np.float32)
+    dy = rng.standard_normal((128, 32, 32, 32)).astype(np.float32)
+    y, dx, dw, db = run_layer(env, "bf16", x, w, b, dy, (3, 3), (1, 1), "same")
+    yo = O.conv_forward_blas(x, w, b, dtype=np.float64)
+    dxo, dwo, dbo = O.conv_backward_blas(x, w, dy, dtype=np.float64)
+    for a, o in ((y, yo), (dx, dxo), (dw, dwo), (db, dbo)):
+        assert O.rel_l2(a, o) <= 1e-5
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32"])
+@pytest.mark.parametrize("shape", [(256, 32, 32, 64, 64), (256, 16, 16, 128, 128), (256, 8, 8, 256, 256),
+                                   (256, 56, 56, 64, 128)])
+def test_sweep_shapes_full_size_properties(env, shape, mode):
+    """Full-size sweep shapes: size-independent checks instead of a full CPU recomputation.
+    (1) adjoint identities <conv(x;b=0), dy> = <x, dX> = <W, dW>; (2) a random sample of output
+    pixels, input pixels and filter taps recomputed exactly on the CPU; (3) dB = column sums;
+    (4) bit-identical results when run twice (fixed-order reductions)."""
+    torch, _lib, layers = env
+    S, H, W, Cin, Cout = shape
+    g = torch.Generator(device="cuda").manual_seed(7)
+    x = torch.randn((S, H, W, Cin), generator=g, device="cuda")
+    dy = torch.randn((S, H, W, Cout), generator=g, device="cuda")
+    np.random.seed(5)
+    layer = layers.Conv_Layer((H, W, Cin), Cout, (3, 3), (1, 1), "same", math_mode=mode)
+    y = layer.forward(x, True).clone()
+    dx = layer.backward(dy).clone()
+    dw = layer.dweights.clone(); db = layer.dbiases.clone()
+    y2 = layer.forward(x, True)
+    dx2 = layer.backward(dy)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert torch.equal(y, y2) and torch.equal(dx, dx2) and torch.equal(dw, layer.dweights) and torch.equal(db, layer.dbiases)
+    tol = TOL[mode]
+    a = float((y.double() * dy.double()).sum())            # bias is zero at construction
+    bx = float((x.double() * dx.double()).sum())
+    bw = float((layer.filter_weights.double() * dw.double()).sum())
+    scale = float(y.double().norm() * dy.double().norm())
+    assert abs(a - bx) <= tol * scale and abs(a - bw) <= tol * scale
+    assert O.rel_l2(db.cpu().numpy(), dy.double().sum(dim=(0, 1, 2)).cpu().numpy()) <= 1e-5
+    # sampled exact recomputation
+    rng = np.random.default_rng(11)
+    w = layer.filter_weights.cpu().numpy().astype(np.float64)
+    xs = x.cpu().numpy(); dys = dy.cpu().numpy()
+    ref, got = [], []
+    for _ in range(48):
+        s, h, ww = rng.integers(S), rng.integers(H), rng.integers(W)
+        acc = np.zeros(Cout); accx = np.zeros(Cin)
+        for i in range(3):
+            for j in range(3):
+                hi, wi = h + i - 1, ww + j - 1
+                if 0 <= hi < H and 0 <= wi < W:
+                    acc += xs[s, hi, wi].astype(np.float64) @ w[i, j]
+                ho, wo = h + 1 - i, ww + 1 - j
+                if 0 <= ho < H and 0 <= wo < W:
+                    accx += w[i, j] @ dys[s, ho, wo].astype(np.float64)
+        ref.append(np.concatenate([acc, accx])); got.append(np.concatenate([y[s, h, ww].cpu().numpy(), dx[s, h, ww].cpu().numpy()]))
+    assert O.rel_l2(np.stack(got), np.stack(ref)) <= tol
+    # a few filter taps of dW over the full reduction
+    for (i, j) in ((0, 0), (1, 1), (2, 1)):
+        xp = torch.nn.functional.pad(x, (0, 0, 1, 1, 1, 1))[:, i:i + H, j:j + W, :]
+        ref_tap = (xp.reshape(-1, Cin).double().T @ dy.reshape(-1, Cout).double()).cpu().numpy()
+        assert O.rel_l2(dw[i, j].cpu().numpy(), ref_tap) <= tol
+
+
+def test_edge_cases_and_errors(env):
+    torch, _lib, layers = env
+    layer = layers.Conv_Layer((8, 8, 64), 64, math_mode="bf16")
+    with pytest.raises(ValueError):
+        layer.forward(np.zeros((2, 8, 8), np.float32), True)                 # not 4-D
+    with pytest.raises(ValueError):
+        layer.forward(np.zeros((2, 8, 8, 32), np.float32), True)             # wrong channel count
+    with pytest.raises(RuntimeError):
+        layers.Conv_Layer((8, 8, 64), 64).backward(np.zeros((2, 8, 8, 64), np.float32))
+    layer.forward(np.zeros((2, 8, 8, 64), np.float32), True)
+    with pytest.raises(ValueError):
+        layer.backward(np.zeros((2, 8, 8, 32), np.float32))                  # wrong dvalues shape
+    small = layers.Conv_Layer((2, 2, 4), 4, filter_size=(5, 5), padding="valid")
+    with pytest.raises(ValueError):
+        small.forward(np.zeros((1, 2, 2, 4), np.float32), True)              # filter larger than input
+    # batch of one, single pixel
+    one = layers.Conv_Layer((1, 1, 64), 64, math_mode="bf16")
+    x = np.ones((1, 1, 1, 64), np.float32)
+    y = one.forward(x, True).cpu().numpy()
+    assert O.rel_l2(y, O.conv_forward(x, one.filter_weights.cpu().numpy(), np.zeros(64))) <= 1e-2

@@ -1,0 +1,205 @@
+"""GPU parity tests of the bandwidth-bound layers, Dense, softmax/loss and Adam (through the C ABI)
+against the golden vectors of the reference's classes and the NumPy oracle."""
+import numpy as np
+import pytest
+
+from oracle import aether_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+    from aether_ml_b200 import _lib, layers
+    if not torch.cuda.is_available():
+        pytest.fail("CUDA device required for -m gpu tests")
+    return torch, _lib, layers
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+@pytest.mark.parametrize("name", ["bn_4d", "bn_2d"])
+def test_batch_norm_golden(env, golden, name):
+    torch, _lib, layers = env
+    g = golden(name)
+    bn = layers.Batch_Norm(epsilon=1e-5, momentum=0.9)
+    bn.forward(g["x"], True)                               # first call creates gamma/beta/running stats
+    assert O.rel_l2(host(bn.output), g["y_first"]) <= 1e-5
+    bn.gamma.copy_(torch.from_numpy(g["gamma"])); bn.beta.copy_(torch.from_numpy(g["beta"]))
+    y = bn.forward(g["x"], True)
+    assert O.rel_l2(host(y), g["y"]) <= 1e-5
+    assert O.rel_l2(host(bn.batch_mean), g["mean"]) <= 1e-5 and O.rel_l2(host(bn.batch_var), g["var"]) <= 1e-5
+    assert host(bn.running_mean).shape == g["rm1"].shape
+    assert O.rel_l2(host(bn.running_mean), g["rm1"]) <= 1e-5 and O.rel_l2(host(bn.running_var), g["rv1"]) <= 1e-5
+    dx = bn.backward(g["dy"])
+    assert O.rel_l2(host(dx), g["dx"]) <= 1e-4
+    assert O.rel_l2(host(bn.dweights), g["dgamma"]) <= 1e-5 and O.rel_l2(host(bn.dbiases), g["dbeta"]) <= 1e-5
+    ye = bn.forward(g["x"], False)
+    assert O.rel_l2(host(ye), g["y_eval"]) <= 1e-5
+    assert bn.weights is bn.gamma and bn.biases is bn.beta
+    params = bn.get_parameters()
+    bn2 = layers.Batch_Norm()
+    bn2.set_parameters(*params)
+    assert O.rel_l2(host(bn2.forward(g["x"], False)), g["y_eval"]) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(128, 32, 32, 32), (64, 7, 7, 64), (37, 5, 3, 10), (512, 256), (3, 2, 2, 300)])
+def test_batch_norm_shapes(env, shape):
+    torch, _lib, layers = env
+    rng = np.random.default_rng(2)
+    x = (rng.standard_normal(shape) * 3 + 10).astype(np.float32)      # large mean: exercises the shifted sums
+    dy = rng.standard_normal(shape).astype(np.float32)
+    C = shape[-1]
+    gamma = (rng.standard_normal(C) + 1).astype(np.float32); beta = rng.standard_normal(C).astype(np.float32)
+    bn = layers.Batch_Norm(n_features=C)
+    bn.gamma.copy_(torch.from_numpy(gamma)); bn.beta.copy_(torch.from_numpy(beta))
+    y = bn.forward(x, True)
+    yo, _, mean, var, rm, rv = O.bn_forward_train(x, gamma, beta, np.zeros(C), np.ones(C))
+    assert O.rel_l2(host(y), yo) <= 2e-5
+    assert O.rel_l2(host(bn.batch_var), var) <= 1e-4
+    assert O.rel_l2(host(bn.running_var), rv) <= 1e-5
+    dx = bn.backward(dy)
+    dxo, dgo, dbo = O.bn_backward(x, dy, gamma, mean, var)
+    assert O.rel_l2(host(dx), dxo) <= 2e-4
+    assert O.rel_l2(host(bn.dweights), dgo) <= 1e-4 and O.rel_l2(host(bn.dbiases), dbo) <= 1e-4
+
+
+@pytest.mark.parametrize("name", ["pool_max_2x2", "pool_max_odd", "pool_max_overlap", "pool_avg_2x2"])
+def test_pooling_golden(env, golden, name):
+    torch, _lib, layers = env
+    g = golden(name)
+    f = tuple(int(v) for v in g["filter_size"]); st = tuple(int(v) for v in g["strides"]); kind = str(g["kind"])
+    pool = layers.Pooling(f, st, "valid", kind)
+    y = pool.forward(g["x"], True)
+    if kind == "max":
+        assert np.array_equal(host(y), g["y"])                         # bit exact
+        rows, cols = pool.max_indicies
+        assert np.array_equal(host(rows), g["arg_rows"]) and np.array_equal(host(cols), g["arg_cols"])
+    else:
+        assert O.rel_l2(host(y), g["y"]) <= 1e-6
+    dx = pool.backward(g["dy"])
+    assert dx.shape == g["x"].shape
+    assert O.rel_l2(host(dx), g["dx"]) <= 1e-6
+
+
+def test_pooling_notebook_example_and_shapes(env):
+    torch, _lib, layers = env
+    x = np.array([[1, 2, 3, 4], [4, 5, 6, 5], [7, 8, 9, 6], [8, 7, 6, 5]], np.float32)[None, :, :, None]
+    pool = layers.Pooling()
+    assert np.array_equal(host(pool.forward(x, True))[0, :, :, 0], [[5, 6], [8, 9]])
+    avg = layers.Pooling(pooling_type="average")
+    assert np.array_equal(host(avg.forward(x, True))[0, :, :, 0], [[3, 4.5], [7.5, 6.5]])
+    rng = np.random.default_rng(0)
+    for shape in [(128, 32, 32, 32), (16, 7, 7, 64), (3, 9, 11, 5)]:
+        xx = np.maximum(rng.standard_normal(shape), 0).astype(np.float32)    # post-ReLU: many all-zero windows
+        p = layers.Pooling()
+        y = p.forward(xx, True)
+        yo, arg = O.pool_forward(xx)
+        assert np.array_equal(host(y), yo.astype(np.float32))
+        dy = rng.standard_normal(yo.shape).astype(np.float32)
+        assert np.array_equal(host(p.backward(dy)), O.pool_backward(dy, shape, arg).astype(np.float32))
+    with pytest.raises(ValueError):
+        layers.Pooling().forward(np.zeros((4, 4, 4), np.float32), True)
+    with pytest.raises(ValueError):
+        layers.Pooling(padding="same").forward(np.zeros((1, 4, 4, 4), np.float32), True)
+
+
+def test_elementwise_golden(env, golden):
+    torch, _lib, layers = env
+    g = golden("elementwise")
+    relu = layers.ReLU()
+    assert np.array_equal(host(relu.forward(g["x"], True)), g["relu_y"])
+    assert np.array_equal(host(relu.backward(g["dy"])), g["relu_dx"])
+    lr = layers.Leaky_ReLU(0.01)
+    assert O.rel_l2(host(lr.forward(g["x"], True)), g["lrelu_y"]) <= 1e-6
+    assert O.rel_l2(host(lr.backward(g["dy"])), g["lrelu_dx"]) <= 1e-6
+    sd = layers.Layer_Dropout_Spatial(float(g["sd_rate"]))
+    sd.fixed_mask = g["sd_mask"]
+    assert O.rel_l2(host(sd.forward(g["x"], True)), g["sd_y"]) <= 1e-6
+    assert O.rel_l2(host(sd.backward(g["dy"])), g["sd_dx"]) <= 1e-6
+    assert np.array_equal(host(sd.forward(g["x"], False)), g["x"])
+    # odd sizes: vector body + scalar tail
+    x = np.random.default_rng(1).standard_normal(1003).astype(np.float32)
+    assert np.array_equal(host(layers.ReLU().forward(x, True)), np.maximum(x, 0))
+
+
+def test_dropout_statistics(env):
+    torch, _lib, layers = env
+    d = layers.Layer_Dropout(0.25, seed=9)
+    x = np.ones((512, 1024), np.float32)
+    y = host(d.forward(x, True))
+    keep = 0.75
+    assert set(np.unique(y)).issubset({0.0, np.float32(1 / keep)})
+    assert abs((y > 0).mean() - keep) < 5e-3
+    y2 = host(d.forward(x, True))
+    assert not np.array_equal(y, y2)                                   # a new mask every call
+    dy = np.full_like(x, 2.0)
+    assert np.array_equal(host(d.backward(dy)), y2 * 2.0)
+    assert np.array_equal(host(d.forward(x, False)), x)
+    spatial = layers.Layer_Dropout_Spatial(0.5)
+    ys = host(spatial.forward(np.ones((4, 3, 3, 64), np.float32), True))
+    assert np.all(ys == ys[0, 0, 0])                                   # one decision per channel for the whole batch
+
+
+@pytest.mark.parametrize("mode,tol", [("fp32", 1e-5), ("tf32", 1e-3), ("bf16", 1e-2)])
+def test_dense_softmax_loss_adam_golden(env, golden, mode, tol):
+    torch, _lib, layers = env
+    g = golden("dense_loss_adam")
+    dense = layers.Layer_Dense(12, 10, weight_regularizer_l2=2e-5, bias_regularizer_l2=1e-5, math_mode=mode)
+    dense.set_parameters(g["w0"], g["b0"])
+    z = dense.forward(g["x"], True)
+    assert O.rel_l2(host(z), g["z"]) <= 1e-5                             # 12 -> 10 always takes the fp32 kernel
+    sm = layers.SoftMax()
+    p = sm.forward(z, True)
+    assert O.rel_l2(host(p), g["p"]) <= 1e-5
+    loss = layers.Loss_CategoricalCrossEntropy(0.01)
+    assert O.rel_l2(host(loss.forward(p, g["labels"], True)), g["sample_losses"]) <= 1e-5
+    comb = layers.Activation_Softmax_Loss_CategoricalCrossEntropy(0.01)
+    dz = comb.backward(p, g["labels"], training=True)
+    assert O.rel_l2(host(dz), g["dz"]) <= 1e-5
+    onehot = np.eye(10, dtype=np.float32)[g["labels"]]
+    assert np.array_equal(host(comb.backward(p, onehot, training=True)), host(dz))
+    dense.backward(dz)
+    assert O.rel_l2(host(dense.dinputs), g["dx"]) <= 1e-5
+    assert O.rel_l2(host(dense.dweights), g["dw"]) <= 1e-5 and O.rel_l2(host(dense.dbiases), g["db"]) <= 1e-5
+    assert (sm.predictions(p).cpu().numpy() == g["p"].argmax(1)).all()
+    opt = layers.Optimizer_Adam(learning_rate=1e-3, decay=5e-5)
+    for it in range(3):
+        opt.pre_update_parameters()
+        opt.update_parameters(dense)
+        opt.post_update_parameters()
+        assert np.isclose(opt.current_learning_rate, g["lrs"][it])
+        assert O.rel_l2(host(dense.weights), g["w_hist"][it]) <= 1e-6
+        assert O.rel_l2(host(dense.biases), g["b_hist"][it]) <= 1e-6
+    assert O.rel_l2(host(dense.weight_momentums), g["m_w"]) <= 1e-5 and O.rel_l2(host(dense.weight_cache), g["v_w"]) <= 1e-5
+
+
+@pytest.mark.parametrize("mode,tol", [("tf32", 1e-3), ("bf16", 1e-2)])
+def test_dense_tensor_core(env, mode, tol):
+    torch, _lib, layers = env
+    rng = np.random.default_rng(8)
+    np.random.seed(8)
+    dense = layers.Layer_Dense(2048, 256, math_mode=mode)
+    w = (rng.standard_normal((2048, 256)) * 0.03).astype(np.float32); b = rng.standard_normal((1, 256)).astype(np.float32)
+    dense.set_parameters(w, b)
+    x = rng.standard_normal((128, 2048)).astype(np.float32); dy = rng.standard_normal((128, 256)).astype(np.float32)
+    y = dense.forward(x, True); dense.backward(dy)
+    dxo, dwo, dbo = O.dense_backward(x, w, b, dy)
+    assert O.rel_l2(host(y), O.dense_forward(x, w, b)) <= tol
+    assert O.rel_l2(host(dense.dinputs), dxo) <= tol and O.rel_l2(host(dense.dweights), dwo) <= tol
+    assert O.rel_l2(host(dense.dbiases), dbo) <= 1e-5 and dense.dbiases.shape == (1, 256)
+
+
+def test_regularization_loss(env):
+    torch, _lib, layers = env
+    np.random.seed(1)
+    d1 = layers.Layer_Dense(64, 32, weight_regularizer_l2=2e-5, bias_regularizer_l1=1e-3)
+    d1.biases.copy_(torch.randn(1, 32))
+    loss = layers.Loss_CategoricalCrossEntropy()
+    loss.remember_trainable_layers([d1])
+    w = host(d1.weights).astype(np.float64); b = host(d1.biases).astype(np.float64)
+    expect = 2e-5 * (w * w).sum() + 1e-3 * np.abs(b).sum()
+    assert np.isclose(float(loss.regularization_loss()), expect, rtol=1e-5)

@@ -605,12 +605,23 @@ __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ s
     }
 }
 
-__global__ void colsum_finish_kernel(const float* __restrict__ part, int nblocks, int C, float* __restrict__ out) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
+// out[c] = sum over blocks of part[block][C]: 32 columns x 8 row lanes per CTA, lanes combined in fixed order.
+__global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ part, int nblocks, int C,
+                                                            float* __restrict__ out) {
+    __shared__ float red[8][32];
+    const int cl = threadIdx.x & 31, lane = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cl;
     float s = 0.f;
-    for (int b = 0; b < nblocks; ++b) s += part[(size_t)b * C + c];
-    out[c] = s;
+    if (c < C)
+        for (int b = lane; b < nblocks; b += 8) s += part[(size_t)b * C + c];
+    red[lane][cl] = s;
+    __syncthreads();
+    if (lane == 0 && c < C) {
+        float t = 0.f;
+#pragma unroll
+        for (int l = 0; l < 8; ++l) t += red[l][cl];
+        out[c] = t;
+    }
 }
 
 // Filter shadows.  w is (taps, Cin, Cout) fp32.
@@ -888,7 +899,7 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
         dy_op = dysh;
     }
     if (db) {
-        colsum_finish_kernel<<<ceil_div(d.Cout, 128), 128, 0, st>>>(dbpart, pl.db_blocks, d.Cout, db);
+        colsum_finish_kernel<<<ceil_div(d.Cout, 32), 256, 0, st>>>(dbpart, pl.db_blocks, d.Cout, db);
         count_launch();
         if ((rc = check_launch("colsum_finish_kernel"))) return rc;
     }

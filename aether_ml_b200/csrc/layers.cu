@@ -192,7 +192,7 @@ __global__ void bn_finalize_bwd_kernel(const float* __restrict__ part, int nbloc
     const double inv = 1.0 / sqrt((double)var[c] + (double)eps);
     const double g = gamma[c], N = (double)rows, mu = mean[c];
     const double k1 = g * inv;
-    const double k2 = -g * inv * inv * inv * sdyx / N;
+    const double k2 = -g * inv * inv * sdyx / N;
     const double k3 = -g * inv * sdy / N - k2 * mu;
     coeff[c] = (float)k1;
     coeff[C + c] = (float)k2;

@@ -241,12 +241,12 @@ def run_gpu(args):
         dom_ms = kinds[dom][0] / max(kinds[dom][1], 1)
         achieved = per_gemm / (dom_ms * 1e-3) / 1e12 if dom_ms > 0 else None
         peak = pk["sustained"] if ms_total > 1500 else pk["burst"]
-        cpu_val, cpu_s = cpu_conv_sample(CPU_SAMPLE_IMAGES)
+        cpu_val, cpu_s = (None, 0.0) if args.skip_cpu_baseline else cpu_conv_sample(CPU_SAMPLE_IMAGES)
         out = {
             "metric": "conv_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": args.mode, "data": "synthetic",
-            "config": {"workload": WORKLOAD, "per_gpu_batch": S, "flops_per_step_per_gpu": fl_step,
+            "config": {"workload": WORKLOAD if S == 256 else WORKLOAD.replace("S=256", "S=%d" % S), "per_gpu_batch": S, "flops_per_step_per_gpu": fl_step,
                        "l2": "inputs (x 205 MB, dy 411 MB per step) exceed the 126 MB L2; no explicit flush",
                        "parallelism": "dp%d batch-sharded, one NCCL all-reduce of dW/dB per step" % world if world > 1 else "single GPU",
                        "pct_of_bf16_peak_burst": 100.0 * value / world / pk["burst"],
@@ -278,7 +278,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="bf16", choices=["bf16", "tf32"])
+    ap.add_argument("--batch", type=int, default=SHAPE["S"], help="per-GPU batch (smaller only for profiler captures)")
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU sample (profiler captures)")
     args = ap.parse_args()
+    SHAPE["S"] = args.batch
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -1,0 +1,176 @@
+"""GPU test of a whole training step through Model (conv blocks + dense head + Adam) against the
+same network evaluated with the NumPy oracle, for the two network topologies of the reference's
+example scripts (Fashion-MNIST-shaped and CIFAR-shaped, scaled down in batch)."""
+import os
+import pickle
+
+import numpy as np
+import pytest
+
+from oracle import aether_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+    from aether_ml_b200 import _lib, layers, model
+    if not torch.cuda.is_available():
+        pytest.fail("CUDA device required for -m gpu tests")
+    return torch, _lib, layers, model
+
+
+def host(t):
+    return t.detach().cpu().numpy().astype(np.float64)
+
+
+def build(env, topology, mode, flat):
+    torch, _lib, Ly, M = env
+    np.random.seed(42)
+    m = M.Model()
+    if topology == "fmnist":           # Conv 1->32, BN, ReLU, Pool, Conv 32->64, BN, ReLU, Pool, Flatten, Dense, Dense, SoftMax
+        shape, chans, dense = (28, 28, 1), (32, 64), (7 * 7 * 64, 128)
+        drop_sp, drop = (None, None), None
+    else:                              # CIFAR-shaped 3-block CNN with spatial dropout, LeakyReLU dense, dropout
+        shape, chans, dense = (32, 32, 3), (32, 64, 128), (4 * 4 * 128, 256)
+        drop_sp, drop = (0.075, 0.1, None), 0.075
+    h, w, c = shape
+    for k, co in enumerate(chans):
+        m.add(Ly.Conv_Layer((h, w, c), co, (3, 3), (1, 1), "same", math_mode=mode))
+        m.add(Ly.Batch_Norm(n_features=co))
+        m.add(Ly.ReLU())
+        if topology == "cifar" and drop_sp[k]:
+            m.add(Ly.Layer_Dropout_Spatial(drop_sp[k]))
+        m.add(Ly.Pooling((2, 2), (2, 2), "valid", "max"))
+        h, w, c = h // 2, w // 2, co
+    m.add(Ly.Flatten())
+    if topology == "cifar":
+        m.add(Ly.Layer_Dense(dense[0], dense[1], weight_regularizer_l2=2e-5, math_mode=mode))
+        m.add(Ly.Leaky_ReLU(0.01))
+        m.add(Ly.Layer_Dropout(drop, seed=77))
+    else:
+        m.add(Ly.Layer_Dense(dense[0], dense[1], math_mode=mode))
+    m.add(Ly.Layer_Dense(dense[1], 10, math_mode=mode))
+    m.add(Ly.SoftMax())
+    m.set(loss=Ly.Loss_CategoricalCrossEntropy(label_smoothing=0.01),
+          optimizer=Ly.Optimizer_Adam(learning_rate=1e-3, decay=5e-5), accuracy=M.Accuracy_Categorical())
+    m.finalize(flat=flat)
+    return m, shape
+
+
+def oracle_step(m, Ly, X, y):
+    """Replays forward/backward of the device model's layer list with the NumPy oracle, reading the
+    parameters (and the dropout masks the device drew) from the device layers.  Returns
+    (probabilities, {layer index: (dw, db)})."""
+    acts, ctx = [np.asarray(X, np.float64)], []
+    for l in m.layers:
+        a = acts[-1]
+        n = type(l).__name__
+        if n == "Conv_Layer":
+            out = O.conv_forward(a, host(l.weights), host(l.biases)); ctx.append(None)
+        elif n == "Batch_Norm":
+            C = a.shape[-1]
+            out, _, mean, var, _, _ = O.bn_forward_train(a, host(l.gamma), host(l.beta), np.zeros(C), np.ones(C)); ctx.append((mean, var))
+        elif n == "ReLU":
+            out = O.relu_forward(a); ctx.append(None)
+        elif n == "Leaky_ReLU":
+            out = O.leaky_relu_forward(a, l.alpha); ctx.append(None)
+        elif n == "Layer_Dropout_Spatial":
+            mask = host(l.channel_mask); out = a * mask; ctx.append(mask)
+        elif n == "Layer_Dropout":
+            mask = host(l.binary_mask); out = a * mask; ctx.append(mask)
+        elif n == "Pooling":
+            out, arg = O.pool_forward(a); ctx.append(arg)
+        elif n == "Flatten":
+            out = a.reshape(len(a), -1); ctx.append(a.shape)
+        elif n == "Layer_Dense":
+            out = O.dense_forward(a, host(l.weights), host(l.biases)); ctx.append(None)
+        elif n == "SoftMax":
+            out = O.softmax(a); ctx.append(None)
+        acts.append(out)
+    probs = acts[-1]
+    g = O.softmax_cce_backward(probs, y, 0.01)
+    grads = {}
+    for k in range(len(m.layers) - 2, -1, -1):
+        l, a, n = m.layers[k], acts[k], type(m.layers[k]).__name__
+        if n == "Conv_Layer":
+            g, dw, db = O.conv_backward(a, host(l.weights), g); grads[k] = (dw, db)
+        elif n == "Batch_Norm":
+            g, dg, dbeta = O.bn_backward(a, g, host(l.gamma), *ctx[k]); grads[k] = (dg, dbeta)
+        elif n == "ReLU":
+            g = O.relu_backward(a, g)
+        elif n == "Leaky_ReLU":
+            g = O.leaky_relu_backward(a, g, l.alpha)
+        elif n in ("Layer_Dropout_Spatial", "Layer_Dropout"):
+            g = g * ctx[k]
+        elif n == "Pooling":
+            g = O.pool_backward(g, a.shape, ctx[k])
+        elif n == "Flatten":
+            g = g.reshape(ctx[k])
+        elif n == "Layer_Dense":
+            g, dw, db = O.dense_backward(a, host(l.weights), host(l.biases), g, wl2=l.weight_regularizer_l2); grads[k] = (dw, db)
+    return probs, grads
+
+
+@pytest.mark.parametrize("topology,mode,flat,tol", [("fmnist", "tf32", False, 4e-3), ("cifar", "bf16", True, 4e-2),
+                                                   ("cifar", "fp32", False, 1e-4)])
+def test_train_step_matches_oracle(env, topology, mode, flat, tol):
+    torch, _lib, Ly, M = env
+    m, shape = build(env, topology, mode, flat)
+    rng = np.random.default_rng(9)
+    S = 16
+    X = rng.random((S,) + shape).astype(np.float32)
+    y = rng.integers(0, 10, S)
+    # randomise BN affine parameters and biases so every gradient path is exercised
+    for l in m.trainable_layers:
+        l.biases.copy_(torch.from_numpy((rng.standard_normal(tuple(l.biases.shape)) * 0.1).astype(np.float32)))
+    before = [(host(l.weights).copy(), host(l.biases).copy()) for l in m.trainable_layers]
+    out = m.forward(X, training=True)
+    data_loss, reg_loss = m.loss.calculate(out, y, include_regularization=True, training=True)
+    probs_o, grads_o = oracle_step(m, Ly, X, y)
+    m.backward(out, y)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert O.rel_l2(host(out), probs_o) <= tol
+    assert abs(float(data_loss) - O.cce_loss(probs_o, y, 0.01, True).mean()) <= tol * 3
+    # errors compound through the depth of the network: the tolerance is per network, not per layer
+    for k, (dw, db) in grads_o.items():
+        l = m.layers[k]
+        assert O.rel_l2(host(l.dweights), dw) <= tol * 5, (k, type(l).__name__)
+        assert O.rel_l2(host(l.dbiases).reshape(db.shape), db) <= tol * 5, (k, type(l).__name__)
+    if topology == "cifar":
+        w0 = before[m.trainable_layers.index(m.layers[-6])][0]
+        assert np.isclose(float(reg_loss), 2e-5 * (w0 ** 2).sum(), rtol=1e-4)
+    # optimizer: replay Adam on the DEVICE gradients so only the update rule is compared
+    dev_grads = [(host(l.dweights).copy(), host(l.dbiases).copy()) for l in m.trainable_layers]
+    m._apply_optimizer()
+    for (w0, b0), (gw, gb), l in zip(before, dev_grads, m.trainable_layers):
+        w1, _, _ = O.adam_step(w0, gw, 0, 0, 1e-3, 0)
+        b1, _, _ = O.adam_step(b0, gb.reshape(b0.shape), 0, 0, 1e-3, 0)
+        assert O.rel_l2(host(l.weights), w1) <= 1e-5 and O.rel_l2(host(l.biases), b1) <= 1e-4
+    assert m.optimizer.iterations == 1
+
+
+def test_train_loop_evaluate_predict_save_load(env, tmp_path, capsys):
+    torch, _lib, Ly, M = env
+    m, shape = build(env, "fmnist", "bf16", True)
+    rng = np.random.default_rng(3)
+    X = rng.random((64,) + shape).astype(np.float32)
+    y = (X.mean(axis=(1, 2, 3)) > np.median(X.mean(axis=(1, 2, 3)))).astype(np.int64)      # learnable 2-class target
+    m.train(X, y, epochs=6, batch_size=32, print_every=100, validation_data=(X, y))
+    printed = capsys.readouterr().out
+    assert "Training" in printed and "Valdiation" in printed
+    acc, loss = m.evaluate(X, y, batch_size=32)
+    assert acc > 0.6 and np.isfinite(loss)
+    pred = m.predict(X, batch_size=16)
+    assert tuple(pred.shape) == (64, 10)
+    path = os.path.join(tmp_path, "params")
+    m.save_parameters(path)
+    saved = pickle.load(open(path, "rb"))
+    assert len(saved) == len(m.trainable_layers) and saved[0][0].shape == (3, 3, 1, 32) and saved[1][2].shape == (1, 1, 1, 32)
+    m2, _ = build(env, "fmnist", "bf16", False)
+    m2.load_parameters(path)
+    assert O.rel_l2(host(m2.predict(X, batch_size=16)), host(pred)) <= 1e-6
+    conv = m2.layers[0]
+    assert conv.weights is conv.filter_weights

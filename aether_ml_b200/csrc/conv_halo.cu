@@ -1,0 +1,398 @@
+// Halo-reuse implicit GEMM for stride-1 convolutions on wide images (forward and dX).
+//
+// One tile = a strip of BH full-width output rows of one image.  Its input window -- (BH+fH-1) rows
+// by Wp = Wout+fW-1 columns, one 128-byte channel block per pixel -- is brought into shared memory
+// by ONE TMA box whose out-of-range coordinates are zero filled (that is the 'same' padding).
+// Shared-memory pixel q = hh*Wp + ww sits in row q of a 128-byte-swizzled K-major operand, so the A
+// operand of filter tap (i,j) is the SAME buffer read from row i*Wp + j on: the tensor core's
+// operand descriptor simply starts (i*Wp + j) * 128 bytes later (the swizzle is a function of the
+// absolute shared-memory address, so row-shifted starts address the data the TMA wrote).
+// Accumulator row r then holds output pixel (h_l, w) = (r / Wp, r % Wp); rows with w >= Wout or
+// h_l >= BH are by-products that are never stored.  The whole filter stays resident in shared
+// memory for the life of the CTA.  Compared with fetching one shifted tile per tap this cuts the
+// L2 -> shared-memory traffic per output pixel by roughly fH*fW.
+//
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer (the warp runs the loop so
+// that descriptor arithmetic is warp-uniform: 32-bit adds on the descriptors' low word; one elected
+// lane issues), warps 2..9 = epilogue.  Two epilogue warps share each 32-lane quarter of TMEM and
+// split its columns; they read the accumulator in the 16-lane x 256-bit shape, whose register
+// layout puts one 32-byte sector of an output row into four neighbouring threads, add the bias
+// (kept in shared memory) and write full sectors straight to global memory with streaming stores.
+// All TMEM loads of a tile are issued before the first wait.  No block-wide barrier is involved.
+#include <string.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "tc_host.cuh"
+
+namespace aether {
+
+struct HaloParams {
+    CUtensorMap tm_in;   // activations (C, W, H, N), box (128 B of channels, Wp, BH+fH-1, 1)
+    CUtensorMap tm_w;    // filter matrix (K, taps*rows_per_tap), box (128 B of K, NT)
+    float* out;          // (N, Hout, Wout, n_out) fp32
+    const float* bias;   // nullable
+    int* status;
+    int n_out;           // real output channels
+    int NT;              // accumulator columns (padded output channels), multiple of 32, <= 256
+    int Hout, Wout, Wp, BH;
+    int tiles_h, n_images;
+    int fH, fW, padT, padL, flip;
+    int kchunks, rows_per_tap;
+    int region_rows;     // (BH+fH-1) * Wp
+    int region_stride;   // bytes between stages (multiple of 1024)
+    int stages;
+    int w_bytes;         // resident filter bytes = taps * kchunks * NT * 128
+};
+
+#ifdef AETHER_KERNEL_TIMERS
+__device__ long long g_halo_timers[16];
+#define TIMER_ADD(slot, expr) do { if (blockIdx.x == 0) { long long _t0 = clock64(); expr; g_halo_timers[slot] += clock64() - _t0; } else { expr; } } while (0)
+#else
+#define TIMER_ADD(slot, expr) do { expr; } while (0)
+#endif
+
+static constexpr int HALO_EPI_WARPS = 8;
+static constexpr int HALO_THREADS = 64 + 32 * HALO_EPI_WARPS;
+static constexpr int HALO_STAGING = 0;
+static constexpr int HALO_TAIL = 2048;          // barriers, TMEM pointer, bias
+
+// MMA with descriptors given as (low word, shared high word); K-major 128-byte-swizzle operands.
+template <bool TF32>
+__device__ __forceinline__ void umma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                          uint32_t accumulate) {
+    if constexpr (TF32) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %3, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(hi), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(hi), "r"(accumulate)
+            : "memory");
+    }
+}
+
+template <bool TF32>
+__global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid_constant__ HaloParams p) {
+    constexpr int KC = TF32 ? 32 : 64;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t sW = smem_base;
+    const uint32_t sR = sW + ((p.w_bytes + 1023) & ~1023);
+    const uint32_t sStage = sR + p.stages * p.region_stride;
+    const uint32_t sBar = sStage + HALO_STAGING;
+    const int S = p.stages;
+    auto full_bar = [&](int s) { return sBar + 8u * s; };
+    auto empty_bar = [&](int s) { return sBar + 8u * (S + s); };
+    auto tfull_bar = [&](int b) { return sBar + 8u * (2 * S + b); };
+    auto tempty_bar = [&](int b) { return sBar + 8u * (2 * S + 2 + b); };
+    const uint32_t wfull_bar = sBar + 8u * (2 * S + 4);
+    const uint32_t sTmemPtr = sBar + 8u * (2 * S + 5);
+    volatile uint32_t* tmem_ptr_generic = reinterpret_cast<volatile uint32_t*>(gen_base + (sTmemPtr - smem_base));
+    float* bias_s = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + 256);     // NT floats
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int NT = p.NT;
+    const uint32_t tmem_cols = (2 * NT <= 32) ? 32u : (2 * NT <= 64) ? 64u : (2 * NT <= 128) ? 128u : (2 * NT <= 256) ? 256u : 512u;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull_bar(b), 1);
+            mbar_init(tempty_bar(b), HALO_EPI_WARPS);
+        }
+        mbar_init(wfull_bar, 1);
+        mbar_fence_init();
+        tma_prefetch_desc(&p.tm_in);
+        tma_prefetch_desc(&p.tm_w);
+    }
+    for (int i = threadIdx.x; i < NT; i += blockDim.x) bias_s[i] = (p.bias != nullptr && i < p.n_out) ? p.bias[i] : 0.f;
+    if (warp == 1) {
+        tmem_alloc(sTmemPtr, tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_generic;
+
+    const int taps = p.fH * p.fW;
+    const long long total_tiles = 1LL * p.tiles_h * p.n_images;
+    const uint32_t region_tx = (uint32_t)p.region_rows * 128u;
+    const uint32_t wtile_bytes = (uint32_t)NT * 128u;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(wfull_bar, (uint32_t)p.w_bytes);
+            for (int t = 0; t < taps; ++t)
+                for (int kc = 0; kc < p.kchunks; ++kc)
+                    tma_load_2d(sW + (uint32_t)(t * p.kchunks + kc) * wtile_bytes, &p.tm_w, wfull_bar, kc * KC,
+                                t * p.rows_per_tap);
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int th = (int)(t % p.tiles_h);
+                const int n = (int)(t / p.tiles_h);
+                const int h0 = th * p.BH;
+                for (int kc = 0; kc < p.kchunks; ++kc, ++it) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1u;
+                    bool w_ok;
+                    TIMER_ADD(0, w_ok = mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY));
+                    if (!w_ok) { ok = false; break; }
+                    mbar_arrive_expect_tx(full_bar(s), region_tx);
+                    tma_load_4d(sR + s * p.region_stride, &p.tm_in, full_bar(s), kc * KC, -p.padL, h0 - p.padT, n);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        // The whole warp runs the loop (so the descriptor arithmetic stays warp-uniform); one elected
+        // lane issues the MMAs and the commits.
+        {
+            const bool leader = elect_one();
+            const uint32_t idesc = make_idesc(TF32 ? 2u : 1u, 0u, 0u, 128u, (uint32_t)NT);
+            const uint64_t proto = make_smem_desc(0, 16, 1024);
+            const uint32_t hi = (uint32_t)(proto >> 32);
+            const uint32_t lo_proto = (uint32_t)proto;                         // LBO field; start address added below
+            const uint32_t wt16 = wtile_bytes >> 4;
+            const uint32_t bstep = wt16 * (uint32_t)p.kchunks;                 // one filter tap, in 16-byte units
+            const uint32_t w_lo = lo_proto + ((sW & 0x3FFFFu) >> 4);
+            const uint32_t row_step = (uint32_t)p.Wp * 8u;                     // one window row, in 16-byte units
+            uint32_t it = 0, lt = 0;
+            bool ok = __all_sync(0xffffffffu, mbar_wait(wfull_bar, 0, p.status, DS_TIMEOUT_FULL));
+            for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
+                const uint32_t buf = lt & 1u;
+                const uint32_t aph = (lt >> 1) & 1u;
+                bool w_ok;
+                if (lane == 0) { TIMER_ADD(1, w_ok = mbar_wait(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY)); }
+                else w_ok = mbar_wait(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY);
+                w_ok = __all_sync(0xffffffffu, w_ok);
+                if (!w_ok) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * NT;
+                uint32_t acc = 0;
+                for (int kc = 0; kc < p.kchunks; ++kc, ++it) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1u;
+                    bool f_ok;
+                    if (lane == 0) { TIMER_ADD(2, f_ok = mbar_wait(full_bar(s), ph, p.status, DS_TIMEOUT_FULL)); }
+                    else f_ok = mbar_wait(full_bar(s), ph, p.status, DS_TIMEOUT_FULL);
+                    f_ok = __all_sync(0xffffffffu, f_ok);
+                    if (!f_ok) { ok = false; break; }
+                    tc_fence_after();
+#ifdef AETHER_KERNEL_TIMERS
+                    const long long t_issue0 = clock64();
+#endif
+                    uint32_t a_row = lo_proto + (((sR + s * p.region_stride) & 0x3FFFFu) >> 4);
+                    // filter tap that multiplies window shift (ti,tj): the same index, or the mirrored one for dX
+                    uint32_t b_cur = w_lo + (uint32_t)kc * wt16 + (p.flip ? (uint32_t)(taps - 1) * bstep : 0u);
+                    for (int ti = 0; ti < p.fH; ++ti) {
+                        uint32_t a_tap = a_row;
+                        for (int tj = 0; tj < p.fW; ++tj) {
+                            if (leader) {
+                                umma_lohi<TF32>(d_tmem, a_tap, b_cur, hi, idesc, acc);
+                                umma_lohi<TF32>(d_tmem, a_tap + 2, b_cur + 2, hi, idesc, 1u);
+                                umma_lohi<TF32>(d_tmem, a_tap + 4, b_cur + 4, hi, idesc, 1u);
+                                umma_lohi<TF32>(d_tmem, a_tap + 6, b_cur + 6, hi, idesc, 1u);
+                            }
+                            acc = 1u;
+                            a_tap += 8u;
+                            b_cur = p.flip ? b_cur - bstep : b_cur + bstep;
+                        }
+                        a_row += row_step;
+                    }
+                    if (leader) umma_commit(empty_bar(s));
+#ifdef AETHER_KERNEL_TIMERS
+                    if (blockIdx.x == 0 && lane == 0) g_halo_timers[3] += clock64() - t_issue0;
+#endif
+                }
+                if (ok && leader) umma_commit(tfull_bar(buf));
+                __syncwarp();
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        // Warp (q, half): TMEM lanes [32q, 32q+32), columns [half*NT/2, (half+1)*NT/2).  Accumulators are read
+        // with the 16-lane x 256-bit shape: thread t receives, per 8-column group, columns 2*(t%4)+{0,1} of rows
+        // t/4 and t/4+8 of the 16-lane half -- i.e. four threads hold one 32-byte sector of an output row, so
+        // the registers go straight to global memory as full sectors (no shared-memory staging).
+        const int ew = warp - 2;
+        const int q = warp & 3;
+        const int half = ew >> 2;
+        const int ncols = NT >> 1;                 // columns this warp owns (multiple of 16)
+        const int col_begin = half * ncols;
+        const int trow = lane >> 2, tcol = (lane & 3) * 2;
+        uint32_t lt = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
+            const int th = (int)(t % p.tiles_h);
+            const int n = (int)(t / p.tiles_h);
+            const int h0 = th * p.BH;
+            // rows held by this thread: q*32 + 16*lh + trow + 8*k  (lh = lane half, k = 0/1)
+            float* rowp[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int r = q * 32 + (j >> 1) * 16 + trow + (j & 1) * 8;
+                const int hl = r / p.Wp, w = r - hl * p.Wp;
+                const bool valid = (w < p.Wout) && (hl < p.BH) && (h0 + hl < p.Hout);
+                rowp[j] = valid ? p.out + ((size_t)((size_t)n * p.Hout + h0 + hl) * p.Wout + w) * p.n_out : nullptr;
+            }
+            const uint32_t buf = lt & 1u;
+            const uint32_t aph = (lt >> 1) & 1u;
+            bool t_ok;
+#ifdef AETHER_KERNEL_TIMERS
+            if (warp == 2 && lane == 0) { TIMER_ADD(4, t_ok = mbar_wait(tfull_bar(buf), aph, p.status, DS_TIMEOUT_TMEM_FULL)); }
+            else
+#endif
+                t_ok = mbar_wait(tfull_bar(buf), aph, p.status, DS_TIMEOUT_TMEM_FULL);
+            if (!t_ok) { ok = false; break; }
+            tc_fence_after();
+#ifdef AETHER_KERNEL_TIMERS
+            const long long t_ep0 = clock64();
+#endif
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NT + col_begin;
+#pragma unroll 1
+            for (int cb = 0; cb < ncols; cb += 64) {            // batches of up to 64 columns: 8 loads in flight
+                uint32_t v[2][4][8];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (cb + u * 16 < ncols) {
+                        tmem_ld_16x256b_x2(taddr0 + cb + u * 16, v[0][u]);
+                        tmem_ld_16x256b_x2(taddr0 + (16u << 16) + cb + u * 16, v[1][u]);
+                    }
+                }
+                tmem_ld_wait();
+                if (cb + 64 >= ncols) {                          // accumulator fully read by this warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (cb + u * 16 < ncols) {
+#pragma unroll
+                        for (int g = 0; g < 2; ++g) {            // two 8-column groups per 16-column load
+                            const int c = col_begin + cb + u * 16 + g * 8 + tcol;
+                            const float2 b2 = *reinterpret_cast<const float2*>(bias_s + c);
+                            if (c < p.n_out) {
+#pragma unroll
+                                for (int lh = 0; lh < 2; ++lh) {
+#pragma unroll
+                                    for (int k = 0; k < 2; ++k) {
+                                        float* rp = rowp[lh * 2 + k];
+                                        if (rp != nullptr) {
+                                            float2 o;
+                                            o.x = __uint_as_float(v[lh][u][g * 4 + k * 2 + 0]) + b2.x;
+                                            o.y = __uint_as_float(v[lh][u][g * 4 + k * 2 + 1]) + b2.y;
+                                            __stcs(reinterpret_cast<float2*>(rp + c), o);
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+#ifdef AETHER_KERNEL_TIMERS
+            if (blockIdx.x == 0 && warp == 2 && lane == 0) { g_halo_timers[5] += clock64() - t_ep0; g_halo_timers[6] += 1; }
+#endif
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+// Decides whether the halo kernel takes this problem; if so launches it and sets *used.
+int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
+                   int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, int n_padded, int fH, int fW,
+                   int padT, int padL, int flip, const float* bias, int prof_kind, cudaStream_t st, bool* used) {
+    *used = false;
+    const int elt = tf32 ? 4 : 2;
+    const int KC = 128 / elt;
+    const int Wp = out_W + fW - 1;
+    if (n_padded > 256 || n_padded % 32 || out_C % 4) return AE_OK;
+    if (Wp > 256 || out_W > 128 || out_W < 12) return AE_OK;
+    int BH = (128 - out_W) / Wp + 1;
+    if (BH > out_H) BH = out_H;
+    if (BH + fH - 1 > 256) return AE_OK;
+    const int tiles_h = ceil_div(out_H, BH);
+    // useful fraction of the 128 accumulator rows, including the ragged last strip of each image
+    const double eff = (double)out_H * out_W / ((double)tiles_h * 128.0);
+    if (eff < 0.70) return AE_OK;
+    const int kchunks = ceil_div(in_C, KC);
+    const int w_bytes = taps * kchunks * n_padded * 128;
+    const int region_rows = (BH + fH - 1) * Wp;
+    const int region_stride = (int)align_up((size_t)region_rows * 128, 1024);
+    const int smem_max = 232448;
+    const int fixed = 1024 + (int)align_up(w_bytes, 1024) + HALO_STAGING + HALO_TAIL;
+    int stages = (smem_max - fixed) / region_stride;
+    if (stages > 4) stages = 4;
+    if (stages < 2) return AE_OK;
+    // every tap reads 128 rows from its shifted start; the furthest read must stay inside the allocation
+    const int overhang_rows = (fH - 1) * Wp + (fW - 1) + 128 - region_rows;
+    if (overhang_rows > 0 && overhang_rows * 128 > HALO_STAGING + HALO_TAIL + (region_stride - region_rows * 128)) return AE_OK;
+
+    HaloParams p;
+    memset(&p, 0, sizeof(p));
+    const CUtensorMapDataType dt = tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    int rc;
+    if ((rc = make_map_nhwc(&p.tm_in, in, dt, elt, in_C, in_W, in_H, S, KC, Wp, BH + fH - 1, 1))) return rc;
+    if ((rc = make_map_2d(&p.tm_w, wmat, dt, elt, w_inner, 1LL * taps * rows_per_tap, KC, n_padded))) return rc;
+    p.out = out;
+    p.bias = bias;
+    p.status = device_status_word();
+    p.n_out = out_C;
+    p.NT = n_padded;
+    p.Hout = out_H; p.Wout = out_W; p.Wp = Wp; p.BH = BH;
+    p.tiles_h = tiles_h; p.n_images = S;
+    p.fH = fH; p.fW = fW; p.padT = padT; p.padL = padL; p.flip = flip;
+    p.kchunks = kchunks; p.rows_per_tap = rows_per_tap;
+    p.region_rows = region_rows; p.region_stride = region_stride; p.stages = stages; p.w_bytes = w_bytes;
+    const int smem = fixed + stages * region_stride;
+
+    static bool configured[2] = {false, false};
+    if (!configured[tf32 ? 1 : 0]) {
+        cudaError_t e = tf32 ? cudaFuncSetAttribute(halo_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max)
+                             : cudaFuncSetAttribute(halo_conv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+        if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(halo, %d): %s", smem_max, cudaGetErrorString(e));
+        configured[tf32 ? 1 : 0] = true;
+    }
+    const long long total = 1LL * tiles_h * S;
+    const int grid = (int)(total < num_sms() ? total : num_sms());
+    prof_begin(prof_kind, st);
+    if (tf32) halo_conv_kernel<true><<<grid, HALO_THREADS, smem, st>>>(p);
+    else halo_conv_kernel<false><<<grid, HALO_THREADS, smem, st>>>(p);
+    prof_end(prof_kind, st);
+    count_launch();
+    *used = true;
+    return check_launch("halo_conv_kernel");
+}
+
+#ifdef AETHER_KERNEL_TIMERS
+extern "C" void aether_debug_halo_timers(long long* out, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_halo_timers, sizeof(long long) * 16);
+    if (reset) {
+        long long z[16] = {0};
+        cudaMemcpyToSymbol(g_halo_timers, z, sizeof(z));
+    }
+}
+#endif
+
+}  // namespace aether

@@ -19,6 +19,7 @@
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "tc_host.cuh"
 
 namespace aether {
 
@@ -69,8 +70,8 @@ static EncodeTiledFn encode_fn() {
 }
 
 // NHWC tensor seen as 4-D (C, W, H, N), 128-byte swizzle, box (box_c, BW, BH, BN).
-static int make_map_nhwc(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elt, int C, int W, int H, int N,
-                         int box_c, int BW, int BH, int BN, CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B) {
+int make_map_nhwc(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elt, int C, int W, int H, int N, int box_c,
+                  int BW, int BH, int BN, CUtensorMapSwizzle swz) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return set_error(AE_CUDA, "cuTensorMapEncodeTiled entry point not available");
     cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
@@ -85,8 +86,8 @@ static int make_map_nhwc(CUtensorMap* m, const void* base, CUtensorMapDataType d
     return AE_OK;
 }
 // Row-major matrix (inner = K elements contiguous, `rows` rows), box (box_k, box_rows).
-static int make_map_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elt, int inner, long long rows,
-                       int box_k, int box_rows) {
+int make_map_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elt, int inner, long long rows, int box_k,
+                int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return set_error(AE_CUDA, "cuTensorMapEncodeTiled entry point not available");
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
@@ -665,7 +666,7 @@ struct TcPlan {
 
 static int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
-static int num_sms() {
+int num_sms() {
     static int n = 0;
     if (!n) {
         int dev = 0;
@@ -783,6 +784,15 @@ static int dispatch_igemm(IgemmParams& p, int nt, cudaStream_t st) {
 static int run_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
                      int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, const PixelTiling& til,
                      int n_padded, int fH, int fW, int sgn, int off_h, int off_w, const float* bias, cudaStream_t st) {
+    {   // wide images with a filter that fits in shared memory: halo-reuse kernel
+        bool used = false;
+        const int padT = sgn > 0 ? -off_h : fH - 1 - off_h;
+        const int padL = sgn > 0 ? -off_w : fW - 1 - off_w;
+        int rc0 = run_halo_igemm(tf32, in, in_C, in_H, in_W, S, wmat, w_inner, rows_per_tap, taps, out, out_C, out_H, out_W,
+                                 n_padded, fH, fW, padT, padL, sgn > 0 ? 0 : 1, bias, sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX,
+                                 st, &used);
+        if (rc0 || used) return rc0;
+    }
     IgemmParams p;
     memset(&p, 0, sizeof(p));
     const int elt = tf32 ? 4 : 2;

@@ -1,0 +1,20 @@
+// Host-side helpers shared by the tensor-core convolution files.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace aether {
+
+int num_sms();
+// NHWC tensor seen as 4-D (C, W, H, N), box (box_c, BW, BH, BN); 128-byte swizzle unless told otherwise.
+int make_map_nhwc(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elt, int C, int W, int H, int N,
+                  int box_c, int BW, int BH, int BN, CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B);
+// Row-major matrix (inner = K elements contiguous, `rows` rows), box (box_k, box_rows), 128-byte swizzle.
+int make_map_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elt, int inner, long long rows, int box_k,
+                int box_rows);
+// Halo-reuse kernel (conv_halo.cu): launches and sets *used when the problem fits it, else leaves *used false.
+int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
+                   int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, int n_padded, int fH, int fW,
+                   int padT, int padL, int flip, const float* bias, int prof_kind, cudaStream_t st, bool* used);
+
+}  // namespace aether

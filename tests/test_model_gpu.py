@@ -126,6 +126,7 @@ def test_train_step_matches_oracle(env, topology, mode, flat, tol):
     for l in m.trainable_layers:
         l.biases.copy_(torch.from_numpy((rng.standard_normal(tuple(l.biases.shape)) * 0.1).astype(np.float32)))
     before = [(host(l.weights).copy(), host(l.biases).copy()) for l in m.trainable_layers]
+    m.loss.new_pass()
     out = m.forward(X, training=True)
     data_loss, reg_loss = m.loss.calculate(out, y, include_regularization=True, training=True)
     probs_o, grads_o = oracle_step(m, Ly, X, y)
@@ -138,7 +139,13 @@ def test_train_step_matches_oracle(env, topology, mode, flat, tol):
     for k, (dw, db) in grads_o.items():
         l = m.layers[k]
         assert O.rel_l2(host(l.dweights), dw) <= tol * 5, (k, type(l).__name__)
-        assert O.rel_l2(host(l.dbiases).reshape(db.shape), db) <= tol * 5, (k, type(l).__name__)
+        # a bias that feeds a Batch_Norm has an exactly zero gradient (the batch mean is subtracted):
+        # compare those on the scale of the weight gradient instead of relative to rounding noise
+        dbd = host(l.dbiases).reshape(db.shape)
+        if np.linalg.norm(db) > 1e-6 * np.linalg.norm(dw):
+            assert O.rel_l2(dbd, db) <= tol * 5, (k, type(l).__name__)
+        else:
+            assert np.linalg.norm(dbd - db) <= tol * np.linalg.norm(dw), (k, type(l).__name__)
     if topology == "cifar":
         w0 = before[m.trainable_layers.index(m.layers[-6])][0]
         assert np.isclose(float(reg_loss), 2e-5 * (w0 ** 2).sum(), rtol=1e-4)
@@ -156,13 +163,13 @@ def test_train_loop_evaluate_predict_save_load(env, tmp_path, capsys):
     torch, _lib, Ly, M = env
     m, shape = build(env, "fmnist", "bf16", True)
     rng = np.random.default_rng(3)
-    X = rng.random((64,) + shape).astype(np.float32)
-    y = (X.mean(axis=(1, 2, 3)) > np.median(X.mean(axis=(1, 2, 3)))).astype(np.int64)      # learnable 2-class target
-    m.train(X, y, epochs=6, batch_size=32, print_every=100, validation_data=(X, y))
+    y = rng.integers(0, 2, 64)                                                            # separable 2-class data:
+    X = (rng.random((64,) + shape) * 0.3 + 0.7 * y[:, None, None, None]).astype(np.float32)   # dark vs bright images
+    m.train(X, y, epochs=20, batch_size=32, print_every=100, validation_data=(X, y))
     printed = capsys.readouterr().out
     assert "Training" in printed and "Valdiation" in printed
     acc, loss = m.evaluate(X, y, batch_size=32)
-    assert acc > 0.6 and np.isfinite(loss)
+    assert acc > 0.9 and np.isfinite(loss)
     pred = m.predict(X, batch_size=16)
     assert tuple(pred.shape) == (64, 10)
     path = os.path.join(tmp_path, "params")

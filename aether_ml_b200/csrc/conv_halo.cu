@@ -47,7 +47,8 @@ struct HaloParams {
 
 #ifdef AETHER_KERNEL_TIMERS
 __device__ long long g_halo_timers[16];
-#define TIMER_ADD(slot, expr) do { if (blockIdx.x == 0) { long long _t0 = clock64(); expr; g_halo_timers[slot] += clock64() - _t0; } else { expr; } } while (0)
+#define TIMER_BLOCK 1
+#define TIMER_ADD(slot, expr) do { if (blockIdx.x == TIMER_BLOCK) { long long _t0 = clock64(); expr; s_timers[slot] += clock64() - _t0; } else { expr; } } while (0)
 #else
 #define TIMER_ADD(slot, expr) do { expr; } while (0)
 #endif
@@ -95,10 +96,17 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
     const uint32_t sTmemPtr = sBar + 8u * (2 * S + 5);
     volatile uint32_t* tmem_ptr_generic = reinterpret_cast<volatile uint32_t*>(gen_base + (sTmemPtr - smem_base));
     float* bias_s = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + 256);     // NT floats
+#ifdef AETHER_KERNEL_TIMERS
+    long long* s_timers = reinterpret_cast<long long*>(gen_base + (sBar - smem_base) + 1536);
+    if (threadIdx.x < 16) s_timers[threadIdx.x] = 0;
+#endif
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int NT = p.NT;
+#ifdef AETHER_KERNEL_TIMERS
+    const long long t_kernel0 = clock64();
+#endif
     const uint32_t tmem_cols = (2 * NT <= 32) ? 32u : (2 * NT <= 64) ? 64u : (2 * NT <= 128) ? 128u : (2 * NT <= 256) ? 256u : 512u;
 
     if (threadIdx.x == 0) {
@@ -170,13 +178,20 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
             const uint32_t w_lo = lo_proto + ((sW & 0x3FFFFu) >> 4);
             const uint32_t row_step = (uint32_t)p.Wp * 8u;                     // one window row, in 16-byte units
             uint32_t it = 0, lt = 0;
-            bool ok = __all_sync(0xffffffffu, mbar_wait(wfull_bar, 0, p.status, DS_TIMEOUT_FULL));
+#ifdef AETHER_KERNEL_TIMERS
+            if (blockIdx.x == TIMER_BLOCK && lane == 0) s_timers[7] = clock64() - t_kernel0;       // init done
+#endif
+            // every lane observes each barrier itself (non-suspending polls, so no lane lags behind)
+            bool ok = __all_sync(0xffffffffu, mbar_wait_spin(wfull_bar, 0, p.status, DS_TIMEOUT_FULL));
+#ifdef AETHER_KERNEL_TIMERS
+            if (blockIdx.x == TIMER_BLOCK && lane == 0) s_timers[8] = clock64() - t_kernel0;       // filter resident
+#endif
             for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
                 const uint32_t buf = lt & 1u;
                 const uint32_t aph = (lt >> 1) & 1u;
                 bool w_ok;
-                if (lane == 0) { TIMER_ADD(1, w_ok = mbar_wait(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY)); }
-                else w_ok = mbar_wait(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY);
+                if (lane == 0) { TIMER_ADD(1, w_ok = mbar_wait_spin(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY)); }
+                else w_ok = mbar_wait_spin(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY);
                 w_ok = __all_sync(0xffffffffu, w_ok);
                 if (!w_ok) { ok = false; break; }
                 tc_fence_after();
@@ -186,8 +201,8 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1u;
                     bool f_ok;
-                    if (lane == 0) { TIMER_ADD(2, f_ok = mbar_wait(full_bar(s), ph, p.status, DS_TIMEOUT_FULL)); }
-                    else f_ok = mbar_wait(full_bar(s), ph, p.status, DS_TIMEOUT_FULL);
+                    if (lane == 0) { TIMER_ADD(2, f_ok = mbar_wait_spin(full_bar(s), ph, p.status, DS_TIMEOUT_FULL)); }
+                    else f_ok = mbar_wait_spin(full_bar(s), ph, p.status, DS_TIMEOUT_FULL);
                     f_ok = __all_sync(0xffffffffu, f_ok);
                     if (!f_ok) { ok = false; break; }
                     tc_fence_after();
@@ -214,11 +229,14 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                     }
                     if (leader) umma_commit(empty_bar(s));
 #ifdef AETHER_KERNEL_TIMERS
-                    if (blockIdx.x == 0 && lane == 0) g_halo_timers[3] += clock64() - t_issue0;
+                    if (blockIdx.x == TIMER_BLOCK && lane == 0) s_timers[3] += clock64() - t_issue0;
 #endif
                 }
                 if (ok && leader) umma_commit(tfull_bar(buf));
                 __syncwarp();
+#ifdef AETHER_KERNEL_TIMERS
+                if (blockIdx.x == TIMER_BLOCK && lane == 0) { if (lt == 0) s_timers[9] = clock64() - t_kernel0; s_timers[10] = clock64() - t_kernel0; }
+#endif
             }
         }
     } else {
@@ -295,7 +313,11 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                                             float2 o;
                                             o.x = __uint_as_float(v[lh][u][g * 4 + k * 2 + 0]) + b2.x;
                                             o.y = __uint_as_float(v[lh][u][g * 4 + k * 2 + 1]) + b2.y;
+#ifdef AETHER_NO_STCS
+                                            *reinterpret_cast<float2*>(rp + c) = o;
+#else
                                             __stcs(reinterpret_cast<float2*>(rp + c), o);
+#endif
                                         }
                                     }
                                 }
@@ -305,13 +327,24 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                 }
             }
 #ifdef AETHER_KERNEL_TIMERS
-            if (blockIdx.x == 0 && warp == 2 && lane == 0) { g_halo_timers[5] += clock64() - t_ep0; g_halo_timers[6] += 1; }
+            if (blockIdx.x == TIMER_BLOCK && warp == 2 && lane == 0) { s_timers[5] += clock64() - t_ep0; s_timers[6] += 1; }
 #endif
         }
     }
 
     tc_fence_before();
     __syncthreads();
+#ifdef AETHER_KERNEL_TIMERS
+    if (threadIdx.x == 0) {
+        const long long dt = clock64() - t_kernel0;
+        if (blockIdx.x == TIMER_BLOCK) {
+            for (int i = 0; i < 12; ++i) g_halo_timers[i] = s_timers[i];
+            g_halo_timers[12] = dt;
+        }
+        atomicMax(reinterpret_cast<unsigned long long*>(&g_halo_timers[13]), (unsigned long long)dt);
+        atomicAdd(reinterpret_cast<unsigned long long*>(&g_halo_timers[14]), (unsigned long long)dt);
+    }
+#endif
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);

@@ -61,6 +61,31 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     return true;
 }
 
+// Non-suspending variant for warps whose lanes all poll the same barrier: test_wait returns at once, so no lane
+// sleeps past the completion (a suspended try_wait of one lane would hold back the whole converged warp).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, int* status, int code) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_test_wait(bar, parity)) {
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (status) atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+    return true;
+}
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

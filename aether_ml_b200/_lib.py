@@ -46,6 +46,7 @@ SIGNATURES = {
     "aether_conv2d_bwd": (_I, [_D, _P, _P, _P, _P, _P, _P, _P, _SZ, _I, _P]),
     "aether_bn_workspace_bytes": (_SZ, [_I64, _I]),
     "aether_bn_fwd_train": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _SZ, _P]),
+    "aether_bn_fwd_train_static": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P]),
     "aether_bn_fwd_eval": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I, _F, _P, _SZ, _P]),
     "aether_bn_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _P, _SZ, _P]),
     "aether_pool_fwd": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),

@@ -265,6 +265,66 @@ extern "C" int aether_bn_fwd_train(const float* x, const float* gamma, const flo
     return check_launch("aether_bn_fwd_train");
 }
 
+// ---- Batch_Norm training forward for callers that cannot hand over a workspace ---------------------------
+// Scratch lives in a fixed device array that is part of the library image: every GPU that loads the library
+// carries these AETHER_BN_STATIC_SCRATCH_FLOATS * 4 bytes (about 1.8 MB) until the process exits.
+// Layout per call: [blocks][3][C] partial (count, mean, M2) triples, then [3][C] coefficients.
+static constexpr int BN_STATIC_MAX_BLOCKS = 148;
+static constexpr size_t AETHER_BN_STATIC_SCRATCH_FLOATS = ((size_t)BN_STATIC_MAX_BLOCKS * 3 + 3) * AETHER_BN_STATIC_MAX_CHANNELS;
+static __device__ __align__(256) float g_bn_static_scratch[AETHER_BN_STATIC_SCRATCH_FLOATS];
+
+// Host code cannot use the array's name as a pointer (on the host it is only a handle for the symbol): the
+// device address is looked up once per device and cached here.
+static float* g_bn_static_ptr[64] = {nullptr};
+
+static int bn_static_scratch(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return set_error(AE_CUDA, "aether_bn_fwd_train_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return set_error(AE_UNSUPPORTED, "aether_bn_fwd_train_static: device ordinal %d out of range", dev);
+    if (g_bn_static_ptr[dev] == nullptr) {
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_bn_static_scratch);   // address on the CURRENT device
+        if (e != cudaSuccess || ptr == nullptr)
+            return set_error(AE_CUDA, "aether_bn_fwd_train_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_bn_static_ptr[dev] = ptr;
+    }
+    *out = g_bn_static_ptr[dev];
+    return AE_OK;
+}
+
+extern "C" int aether_bn_fwd_train_static(const float* x, const float* gamma, const float* beta, float* running_mean,
+                                          float* running_var, float* batch_mean, float* batch_var, float* y,
+                                          int64_t rows, int C, float eps, float momentum, void* stream) {
+    if (!x || !gamma || !beta || !running_mean || !running_var || !batch_mean || !batch_var || !y)
+        return set_error(AE_BAD_ARG, "aether_bn_fwd_train_static: null pointer");
+    if (rows <= 0 || C <= 0) return set_error(AE_BAD_ARG, "aether_bn_fwd_train_static: rows=%lld C=%d", (long long)rows, C);
+    if (C > AETHER_BN_STATIC_MAX_CHANNELS)
+        return set_error(AE_UNSUPPORTED,
+                         "aether_bn_fwd_train_static: C=%d exceeds the built-in scratch (at most %d channels); use "
+                         "aether_bn_fwd_train with a caller-provided workspace", C, AETHER_BN_STATIC_MAX_CHANNELS);
+    if ((C & 3) == 0 && (!aligned16(x) || !aligned16(y)))
+        return set_error(AE_BAD_ARG, "aether_bn_fwd_train_static: arrays must be 16-byte aligned");
+    float* scratch = nullptr;
+    int rc = bn_static_scratch(&scratch);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int nb = bn_blocks(rows);
+    if (nb > BN_STATIC_MAX_BLOCKS) nb = BN_STATIC_MAX_BLOCKS;
+    float* part = scratch;
+    float* coeff = scratch + (size_t)nb * 3 * C;
+    // Every scratch element read below is written earlier in this same call (each block stores all 3*C of its
+    // partials, the finalize kernel stores all coefficients), so stale contents of a previous call never matter
+    // and nothing has to be cleared.
+    bn_reduce_kernel<0><<<nb, 256, 0, st>>>(x, nullptr, nullptr, nullptr, eps, rows, C, part, (rows + nb - 1) / nb);
+    bn_finalize_fwd_kernel<<<ceil_div(C, 128), 128, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
+                                                            running_var, batch_mean, batch_var, coeff);
+    const long long n = rows * C;
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C);
+    count_launch(3);
+    return check_launch("aether_bn_fwd_train_static");
+}
+
 extern "C" int aether_bn_fwd_eval(const float* x, const float* gamma, const float* beta, const float* running_mean,
                                   const float* running_var, float* y, int64_t rows, int C, float eps, void* ws,
                                   size_t ws_bytes, void* stream) {

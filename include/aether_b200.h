@@ -96,6 +96,23 @@ size_t aether_bn_workspace_bytes(int64_t rows, int C);
 int aether_bn_fwd_train(const float* x, const float* gamma, const float* beta, float* running_mean, float* running_var,
                         float* batch_mean, float* batch_var, float* y, int64_t rows, int C, float eps, float momentum,
                         void* ws, size_t ws_bytes, void* stream);
+/* Same result as aether_bn_fwd_train, for callers that have no way to provide the workspace.  (No counterpart
+ * in the reference: its Batch_Norm lets CuPy allocate temporaries freely.)  Some hosts of this library must not
+ * or cannot allocate device memory around a call -- a process whose whole device-memory budget was handed to
+ * another pool at start-up, a plug-in that may touch only the arrays its host gave it, a step function that has
+ * to keep its memory footprint fixed -- so this variant keeps its scratch (per-block partial statistics and the
+ * per-channel coefficients) in a fixed array inside the library image, about 1.8 MB that every GPU loading the
+ * library holds until the process exits.  It performs no cudaMalloc/cudaFree and calls no allocating routine.
+ *   - Limit: C <= AETHER_BN_STATIC_MAX_CHANNELS; larger C is rejected with AETHER_E_UNSUPPORTED.
+ *   - The FIRST call on each device looks up the array's device address (the device must be current); make
+ *     that first call before any stream capture begins.
+ *   - All calls on a device share the one array and it keeps whatever the last call left there.  Nothing needs
+ *     clearing (every element is rewritten before it is read), but two calls whose kernels can overlap on the
+ *     GPU (different streams without ordering) race on it: serialise them. */
+#define AETHER_BN_STATIC_MAX_CHANNELS 1024
+int aether_bn_fwd_train_static(const float* x, const float* gamma, const float* beta, float* running_mean,
+                               float* running_var, float* batch_mean, float* batch_var, float* y, int64_t rows, int C,
+                               float eps, float momentum, void* stream);
 /* Inference forward :478-480 (ws: at least 2*C floats). */
 int aether_bn_fwd_eval(const float* x, const float* gamma, const float* beta, const float* running_mean,
                        const float* running_var, float* y, int64_t rows, int C, float eps, void* ws, size_t ws_bytes,

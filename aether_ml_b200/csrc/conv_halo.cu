@@ -12,13 +12,17 @@
 // memory for the life of the CTA.  Compared with fetching one shifted tile per tap this cuts the
 // L2 -> shared-memory traffic per output pixel by roughly fH*fW.
 //
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer (the warp runs the loop so
-// that descriptor arithmetic is warp-uniform: 32-bit adds on the descriptors' low word; one elected
-// lane issues), warps 2..9 = epilogue.  Two epilogue warps share each 32-lane quarter of TMEM and
-// split its columns; they read the accumulator in the 16-lane x 256-bit shape, whose register
-// layout puts one 32-byte sector of an output row into four neighbouring threads, add the bias
-// (kept in shared memory) and write full sectors straight to global memory with streaming stores.
-// All TMEM loads of a tile are issued before the first wait.  No block-wide barrier is involved.
+// Warp roles (320 threads): warp 0 = TMA producer (it also prefetches the window of the tile after
+// next into L2), warp 1 = MMA issuer (the warp runs the loop so that descriptor arithmetic is
+// warp-uniform: 32-bit adds on the descriptors' low word; one elected lane issues), warps 2..9 =
+// epilogue.  Up to four accumulators live in TMEM so the issuer can run ahead of the epilogue.  Two
+// epilogue warps share each 32-lane quarter of TMEM and split its columns; they read the accumulator
+// in the 16-lane x 256-bit shape, whose register layout spreads 16 columns of an output row over
+// four neighbouring threads; two butterfly shuffles inside the quad give every thread 4 consecutive
+// columns, the bias (kept in shared memory) is added and 64-byte row segments go straight to global
+// memory (the store path handles about one cache line per cycle, so fewer, wider segments matter).
+// Everything that does not change from tile to tile (row -> pixel mapping, column offsets) is
+// computed once per thread.
 #include <string.h>
 
 #include "common.cuh"
@@ -46,16 +50,16 @@ struct HaloParams {
 };
 
 #ifdef AETHER_KERNEL_TIMERS
+// Cycle counters of one CTA (TIMER_BLOCK), for tuning builds only.
 __device__ long long g_halo_timers[16];
 #define TIMER_BLOCK 1
-#define TIMER_ADD(slot, expr) do { if (blockIdx.x == TIMER_BLOCK) { long long _t0 = clock64(); expr; s_timers[slot] += clock64() - _t0; } else { expr; } } while (0)
+#define TSTAMP(accv) do { if (tmr) { const long long _n = clock64(); accv += _n - tm_prev; tm_prev = _n; } } while (0)
 #else
-#define TIMER_ADD(slot, expr) do { expr; } while (0)
+#define TSTAMP(accv) do { } while (0)
 #endif
 
 static constexpr int HALO_EPI_WARPS = 8;
 static constexpr int HALO_THREADS = 64 + 32 * HALO_EPI_WARPS;
-static constexpr int HALO_STAGING = 0;
 static constexpr int HALO_TAIL = 2048;          // barriers, TMEM pointer, bias
 
 // MMA with descriptors given as (low word, shared high word); K-major 128-byte-swizzle operands.
@@ -85,21 +89,16 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
     uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t sW = smem_base;
     const uint32_t sR = sW + ((p.w_bytes + 1023) & ~1023);
-    const uint32_t sStage = sR + p.stages * p.region_stride;
-    const uint32_t sBar = sStage + HALO_STAGING;
+    const uint32_t sBar = sR + p.stages * p.region_stride;
     const int S = p.stages;
     auto full_bar = [&](int s) { return sBar + 8u * s; };
     auto empty_bar = [&](int s) { return sBar + 8u * (S + s); };
     auto tfull_bar = [&](int b) { return sBar + 8u * (2 * S + b); };
-    auto tempty_bar = [&](int b) { return sBar + 8u * (2 * S + 2 + b); };
-    const uint32_t wfull_bar = sBar + 8u * (2 * S + 4);
-    const uint32_t sTmemPtr = sBar + 8u * (2 * S + 5);
+    auto tempty_bar = [&](int b) { return sBar + 8u * (2 * S + 4 + b); };
+    const uint32_t wfull_bar = sBar + 8u * (2 * S + 8);
+    const uint32_t sTmemPtr = sBar + 8u * (2 * S + 9);
     volatile uint32_t* tmem_ptr_generic = reinterpret_cast<volatile uint32_t*>(gen_base + (sTmemPtr - smem_base));
     float* bias_s = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + 256);     // NT floats
-#ifdef AETHER_KERNEL_TIMERS
-    long long* s_timers = reinterpret_cast<long long*>(gen_base + (sBar - smem_base) + 1536);
-    if (threadIdx.x < 16) s_timers[threadIdx.x] = 0;
-#endif
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -107,14 +106,17 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
 #ifdef AETHER_KERNEL_TIMERS
     const long long t_kernel0 = clock64();
 #endif
-    const uint32_t tmem_cols = (2 * NT <= 32) ? 32u : (2 * NT <= 64) ? 64u : (2 * NT <= 128) ? 128u : (2 * NT <= 256) ? 256u : 512u;
+    // up to four accumulators (the 512 TMEM columns allow it) so the MMA issuer can run ahead of the epilogue
+    const uint32_t NB = (4 * NT <= 512) ? 4u : (3 * NT <= 512) ? 3u : 2u;
+    const uint32_t need_cols = NB * (uint32_t)NT;
+    const uint32_t tmem_cols = (need_cols <= 32) ? 32u : (need_cols <= 64) ? 64u : (need_cols <= 128) ? 128u : (need_cols <= 256) ? 256u : 512u;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < 4; ++b) {
             mbar_init(tfull_bar(b), 1);
             mbar_init(tempty_bar(b), HALO_EPI_WARPS);
         }
@@ -134,7 +136,8 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
     const uint32_t tmem_base = *tmem_ptr_generic;
 
     const int taps = p.fH * p.fW;
-    const long long total_tiles = 1LL * p.tiles_h * p.n_images;
+    const int total_tiles = p.tiles_h * p.n_images;          // host guarantees it fits in 31 bits
+    const int grid = (int)gridDim.x;
     const uint32_t region_tx = (uint32_t)p.region_rows * 128u;
     const uint32_t wtile_bytes = (uint32_t)NT * 128u;
 
@@ -146,99 +149,94 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                 for (int kc = 0; kc < p.kchunks; ++kc)
                     tma_load_2d(sW + (uint32_t)(t * p.kchunks + kc) * wtile_bytes, &p.tm_w, wfull_bar, kc * KC,
                                 t * p.rows_per_tap);
-            uint32_t it = 0;
+            int s = 0;
+            uint32_t ph = 0;
             bool ok = true;
-            for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int th = (int)(t % p.tiles_h);
-                const int n = (int)(t / p.tiles_h);
-                const int h0 = th * p.BH;
-                for (int kc = 0; kc < p.kchunks; ++kc, ++it) {
-                    const int s = it % S;
-                    const uint32_t ph = (it / S) & 1u;
-                    bool w_ok;
-                    TIMER_ADD(0, w_ok = mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY));
-                    if (!w_ok) { ok = false; break; }
+            for (int t = blockIdx.x; t < total_tiles && ok; t += grid) {
+                const int n = t / p.tiles_h;
+                const int h0 = (t - n * p.tiles_h) * p.BH;
+                const int tp = t + 2 * grid;                       // tile after next: warm L2 with its window
+                const int np = tp / p.tiles_h;
+                const int hp = (tp - np * p.tiles_h) * p.BH;
+                for (int kc = 0; kc < p.kchunks; ++kc) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) { ok = false; break; }
                     mbar_arrive_expect_tx(full_bar(s), region_tx);
                     tma_load_4d(sR + s * p.region_stride, &p.tm_in, full_bar(s), kc * KC, -p.padL, h0 - p.padT, n);
+                    if (tp < total_tiles) tma_prefetch_l2_4d(&p.tm_in, kc * KC, -p.padL, hp - p.padT, np);
+                    if (++s == S) { s = 0; ph ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        // The whole warp runs the loop (so the descriptor arithmetic stays warp-uniform); one elected
-        // lane issues the MMAs and the commits.
-        {
-            const bool leader = elect_one();
-            const uint32_t idesc = make_idesc(TF32 ? 2u : 1u, 0u, 0u, 128u, (uint32_t)NT);
-            const uint64_t proto = make_smem_desc(0, 16, 1024);
-            const uint32_t hi = (uint32_t)(proto >> 32);
-            const uint32_t lo_proto = (uint32_t)proto;                         // LBO field; start address added below
-            const uint32_t wt16 = wtile_bytes >> 4;
-            const uint32_t bstep = wt16 * (uint32_t)p.kchunks;                 // one filter tap, in 16-byte units
-            const uint32_t w_lo = lo_proto + ((sW & 0x3FFFFu) >> 4);
-            const uint32_t row_step = (uint32_t)p.Wp * 8u;                     // one window row, in 16-byte units
-            uint32_t it = 0, lt = 0;
+        const bool leader = elect_one();
+        const uint32_t idesc = make_idesc(TF32 ? 2u : 1u, 0u, 0u, 128u, (uint32_t)NT);
+        const uint64_t proto = make_smem_desc(0, 16, 1024);
+        const uint32_t hi = (uint32_t)(proto >> 32);
+        const uint32_t lo_proto = (uint32_t)proto;                         // LBO field; start address added below
+        const uint32_t wt16 = wtile_bytes >> 4;
+        const uint32_t bstep = wt16 * (uint32_t)p.kchunks;                 // one filter tap, in 16-byte units
+        const uint32_t w_lo = lo_proto + ((sW & 0x3FFFFu) >> 4);
+        const uint32_t row_step = (uint32_t)p.Wp * 8u;                     // one window row, in 16-byte units
+        const uint32_t r_lo = lo_proto + ((sR & 0x3FFFFu) >> 4);
+        const uint32_t rs16 = (uint32_t)p.region_stride >> 4;
+        // every lane observes each barrier itself (non-suspending polls, so no lane lags behind)
+        bool ok = __all_sync(0xffffffffu, mbar_wait_spin(wfull_bar, 0, p.status, DS_TIMEOUT_FULL));
 #ifdef AETHER_KERNEL_TIMERS
-            if (blockIdx.x == TIMER_BLOCK && lane == 0) s_timers[7] = clock64() - t_kernel0;       // init done
+        const bool tmr = (blockIdx.x == TIMER_BLOCK && lane == 0);
+        long long tm_a = 0, tm_b = 0, tm_c = 0, tm_d = 0, tm_e = 0, tm_prev = clock64();
 #endif
-            // every lane observes each barrier itself (non-suspending polls, so no lane lags behind)
-            bool ok = __all_sync(0xffffffffu, mbar_wait_spin(wfull_bar, 0, p.status, DS_TIMEOUT_FULL));
-#ifdef AETHER_KERNEL_TIMERS
-            if (blockIdx.x == TIMER_BLOCK && lane == 0) s_timers[8] = clock64() - t_kernel0;       // filter resident
-#endif
-            for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
-                const uint32_t buf = lt & 1u;
-                const uint32_t aph = (lt >> 1) & 1u;
-                bool w_ok;
-                if (lane == 0) { TIMER_ADD(1, w_ok = mbar_wait_spin(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY)); }
-                else w_ok = mbar_wait_spin(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY);
-                w_ok = __all_sync(0xffffffffu, w_ok);
-                if (!w_ok) { ok = false; break; }
+        int s = 0;
+        uint32_t ph = 0, buf = 0, aph = 0;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += grid) {
+            TSTAMP(tm_e);                                              // loop overhead between tiles
+            bool w_ok = mbar_wait_spin(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY);
+            w_ok = __all_sync(0xffffffffu, w_ok);
+            if (!w_ok) { ok = false; break; }
+            tc_fence_after();
+            TSTAMP(tm_a);                                              // wait for a drained accumulator
+            const uint32_t d_tmem = tmem_base + buf * NT;
+            uint32_t acc = 0;
+            for (int kc = 0; kc < p.kchunks; ++kc) {
+                bool f_ok = mbar_wait_spin(full_bar(s), ph, p.status, DS_TIMEOUT_FULL);
+                f_ok = __all_sync(0xffffffffu, f_ok);
+                if (!f_ok) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * NT;
-                uint32_t acc = 0;
-                for (int kc = 0; kc < p.kchunks; ++kc, ++it) {
-                    const int s = it % S;
-                    const uint32_t ph = (it / S) & 1u;
-                    bool f_ok;
-                    if (lane == 0) { TIMER_ADD(2, f_ok = mbar_wait_spin(full_bar(s), ph, p.status, DS_TIMEOUT_FULL)); }
-                    else f_ok = mbar_wait_spin(full_bar(s), ph, p.status, DS_TIMEOUT_FULL);
-                    f_ok = __all_sync(0xffffffffu, f_ok);
-                    if (!f_ok) { ok = false; break; }
-                    tc_fence_after();
-#ifdef AETHER_KERNEL_TIMERS
-                    const long long t_issue0 = clock64();
-#endif
-                    uint32_t a_row = lo_proto + (((sR + s * p.region_stride) & 0x3FFFFu) >> 4);
-                    // filter tap that multiplies window shift (ti,tj): the same index, or the mirrored one for dX
-                    uint32_t b_cur = w_lo + (uint32_t)kc * wt16 + (p.flip ? (uint32_t)(taps - 1) * bstep : 0u);
-                    for (int ti = 0; ti < p.fH; ++ti) {
-                        uint32_t a_tap = a_row;
-                        for (int tj = 0; tj < p.fW; ++tj) {
-                            if (leader) {
-                                umma_lohi<TF32>(d_tmem, a_tap, b_cur, hi, idesc, acc);
-                                umma_lohi<TF32>(d_tmem, a_tap + 2, b_cur + 2, hi, idesc, 1u);
-                                umma_lohi<TF32>(d_tmem, a_tap + 4, b_cur + 4, hi, idesc, 1u);
-                                umma_lohi<TF32>(d_tmem, a_tap + 6, b_cur + 6, hi, idesc, 1u);
-                            }
-                            acc = 1u;
-                            a_tap += 8u;
-                            b_cur = p.flip ? b_cur - bstep : b_cur + bstep;
+                TSTAMP(tm_b);                                          // wait for the window
+                uint32_t a_row = r_lo + (uint32_t)s * rs16;
+                // filter tap that multiplies window shift (ti,tj): the same index, or the mirrored one for dX
+                uint32_t b_cur = w_lo + (uint32_t)kc * wt16 + (p.flip ? (uint32_t)(taps - 1) * bstep : 0u);
+                for (int ti = 0; ti < p.fH; ++ti) {
+                    uint32_t a_tap = a_row;
+                    for (int tj = 0; tj < p.fW; ++tj) {
+                        if (leader) {
+                            umma_lohi<TF32>(d_tmem, a_tap, b_cur, hi, idesc, acc);
+                            umma_lohi<TF32>(d_tmem, a_tap + 2, b_cur + 2, hi, idesc, 1u);
+                            umma_lohi<TF32>(d_tmem, a_tap + 4, b_cur + 4, hi, idesc, 1u);
+                            umma_lohi<TF32>(d_tmem, a_tap + 6, b_cur + 6, hi, idesc, 1u);
                         }
-                        a_row += row_step;
+                        acc = 1u;
+                        a_tap += 8u;
+                        b_cur = p.flip ? b_cur - bstep : b_cur + bstep;
                     }
-                    if (leader) umma_commit(empty_bar(s));
-#ifdef AETHER_KERNEL_TIMERS
-                    if (blockIdx.x == TIMER_BLOCK && lane == 0) s_timers[3] += clock64() - t_issue0;
-#endif
+                    a_row += row_step;
                 }
-                if (ok && leader) umma_commit(tfull_bar(buf));
-                __syncwarp();
-#ifdef AETHER_KERNEL_TIMERS
-                if (blockIdx.x == TIMER_BLOCK && lane == 0) { if (lt == 0) s_timers[9] = clock64() - t_kernel0; s_timers[10] = clock64() - t_kernel0; }
-#endif
+                TSTAMP(tm_c);                                          // MMA issue
+                if (leader) umma_commit(empty_bar(s));
+                if (++s == S) { s = 0; ph ^= 1u; }
+                TSTAMP(tm_d);                                          // commits
             }
+            if (ok && leader) umma_commit(tfull_bar(buf));
+            if (++buf == NB) { buf = 0; aph ^= 1u; }
+            __syncwarp();
+            TSTAMP(tm_d);
         }
+#ifdef AETHER_KERNEL_TIMERS
+        if (tmr) {
+            g_halo_timers[1] = tm_a; g_halo_timers[2] = tm_b; g_halo_timers[3] = tm_c; g_halo_timers[4] = tm_d;
+            g_halo_timers[5] = tm_e; g_halo_timers[0] = clock64() - t_kernel0;
+        }
+#endif
     } else {
         // ------------------------------------------------------------------ epilogue
         // Warp (q, half): TMEM lanes [32q, 32q+32), columns [half*NT/2, (half+1)*NT/2).  Accumulators are read
@@ -250,35 +248,39 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
         const int half = ew >> 2;
         const int ncols = NT >> 1;                 // columns this warp owns (multiple of 16)
         const int col_begin = half * ncols;
-        const int trow = lane >> 2, tcol = (lane & 3) * 2;
-        uint32_t lt = 0;
+        const int trow = lane >> 2, tcol4 = (lane & 3) * 4;   // after the quad exchange a lane owns 4 consecutive columns
+        const bool lo2 = (lane & 2) == 0, odd = (lane & 1) != 0;
+        const bool all_cols = (p.n_out == NT);     // no padded output channels: no per-column bound checks
+        // The four accumulator rows this thread holds map to fixed pixels of every strip: precompute their
+        // offsets (in floats, relative to the strip's first pixel, including this thread's column offset).
+        int row_off[4], row_hl[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = q * 32 + (j >> 1) * 16 + trow + (j & 1) * 8;      // rows: lane half j>>1, sub-row j&1
+            const int hl = r / p.Wp, w = r - hl * p.Wp;
+            row_hl[j] = (w < p.Wout && hl < p.BH) ? hl : (1 << 30);           // never valid
+            row_off[j] = (hl * p.Wout + w) * p.n_out + col_begin + tcol4;
+        }
+        const float* bias4 = bias_s + col_begin + tcol4;
+        const size_t strip_floats = (size_t)p.BH * p.Wout * p.n_out;
+        const size_t image_floats = (size_t)p.Hout * p.Wout * p.n_out;
+#ifdef AETHER_KERNEL_TIMERS
+        const bool tmr = (blockIdx.x == TIMER_BLOCK && warp == 2 && lane == 0);
+        long long tm_w = 0, tm_l = 0, tm_s = 0, tm_prev = clock64();
+#endif
+        uint32_t buf = 0, aph = 0;
         bool ok = true;
-        for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
-            const int th = (int)(t % p.tiles_h);
-            const int n = (int)(t / p.tiles_h);
-            const int h0 = th * p.BH;
-            // rows held by this thread: q*32 + 16*lh + trow + 8*k  (lh = lane half, k = 0/1)
+        for (int t = blockIdx.x; t < total_tiles && ok; t += grid) {
+            const int n = t / p.tiles_h;
+            const int th = t - n * p.tiles_h;
+            const int rows_left = p.Hout - th * p.BH;
+            float* tile_base = p.out + (size_t)n * image_floats + (size_t)th * strip_floats;
             float* rowp[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int r = q * 32 + (j >> 1) * 16 + trow + (j & 1) * 8;
-                const int hl = r / p.Wp, w = r - hl * p.Wp;
-                const bool valid = (w < p.Wout) && (hl < p.BH) && (h0 + hl < p.Hout);
-                rowp[j] = valid ? p.out + ((size_t)((size_t)n * p.Hout + h0 + hl) * p.Wout + w) * p.n_out : nullptr;
-            }
-            const uint32_t buf = lt & 1u;
-            const uint32_t aph = (lt >> 1) & 1u;
-            bool t_ok;
-#ifdef AETHER_KERNEL_TIMERS
-            if (warp == 2 && lane == 0) { TIMER_ADD(4, t_ok = mbar_wait(tfull_bar(buf), aph, p.status, DS_TIMEOUT_TMEM_FULL)); }
-            else
-#endif
-                t_ok = mbar_wait(tfull_bar(buf), aph, p.status, DS_TIMEOUT_TMEM_FULL);
-            if (!t_ok) { ok = false; break; }
+            for (int j = 0; j < 4; ++j) rowp[j] = (row_hl[j] < rows_left) ? tile_base + row_off[j] : nullptr;
+            if (!mbar_wait(tfull_bar(buf), aph, p.status, DS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
             tc_fence_after();
-#ifdef AETHER_KERNEL_TIMERS
-            const long long t_ep0 = clock64();
-#endif
+            TSTAMP(tm_w);                                              // wait for a finished accumulator
             const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NT + col_begin;
 #pragma unroll 1
             for (int cb = 0; cb < ncols; cb += 64) {            // batches of up to 64 columns: 8 loads in flight
@@ -296,55 +298,49 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(buf));
                 }
+                TSTAMP(tm_l);                                          // TMEM -> registers
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     if (cb + u * 16 < ncols) {
 #pragma unroll
-                        for (int g = 0; g < 2; ++g) {            // two 8-column groups per 16-column load
-                            const int c = col_begin + cb + u * 16 + g * 8 + tcol;
-                            const float2 b2 = *reinterpret_cast<const float2*>(bias_s + c);
-                            if (c < p.n_out) {
+                        // A quad holds 16 columns of a row as 2+2 columns per lane (groups 0 and 1).  Two
+                        // butterfly exchanges inside the quad turn that into 4 consecutive columns per lane,
+                        // so each store instruction writes 64 contiguous bytes per row instead of 32.
+                        const int cc = cb + u * 16;              // column relative to this thread's first column
+                        const float4 b4 = *reinterpret_cast<const float4*>(bias4 + cc);
+                        const bool cols_ok = all_cols || col_begin + tcol4 + cc < p.n_out;
 #pragma unroll
-                                for (int lh = 0; lh < 2; ++lh) {
-#pragma unroll
-                                    for (int k = 0; k < 2; ++k) {
-                                        float* rp = rowp[lh * 2 + k];
-                                        if (rp != nullptr) {
-                                            float2 o;
-                                            o.x = __uint_as_float(v[lh][u][g * 4 + k * 2 + 0]) + b2.x;
-                                            o.y = __uint_as_float(v[lh][u][g * 4 + k * 2 + 1]) + b2.y;
-#ifdef AETHER_NO_STCS
-                                            *reinterpret_cast<float2*>(rp + c) = o;
-#else
-                                            __stcs(reinterpret_cast<float2*>(rp + c), o);
-#endif
-                                        }
-                                    }
-                                }
-                            }
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t a0 = v[j >> 1][u][(j & 1) * 2 + 0], a1 = v[j >> 1][u][(j & 1) * 2 + 1];
+                            const uint32_t b0 = v[j >> 1][u][4 + (j & 1) * 2 + 0], b1 = v[j >> 1][u][4 + (j & 1) * 2 + 1];
+                            // step 1 (lane ^ 2): lanes 0,1 collect group 0, lanes 2,3 collect group 1
+                            const uint32_t s0 = lo2 ? b0 : a0, s1 = lo2 ? b1 : a1;
+                            const uint32_t r0 = __shfl_xor_sync(0xffffffffu, s0, 2), r1 = __shfl_xor_sync(0xffffffffu, s1, 2);
+                            const uint32_t x0 = lo2 ? a0 : r0, x1 = lo2 ? a1 : r1;       // piece from the even source lane
+                            const uint32_t y0 = lo2 ? r0 : b0, y1 = lo2 ? r1 : b1;       // piece from the source lane + 2
+                            // step 2 (lane ^ 1): even lanes keep the lower pair of pieces, odd lanes the upper pair
+                            const uint32_t t0 = odd ? x0 : y0, t1 = odd ? x1 : y1;
+                            const uint32_t q0 = __shfl_xor_sync(0xffffffffu, t0, 1), q1 = __shfl_xor_sync(0xffffffffu, t1, 1);
+                            float4 o;
+                            o.x = __uint_as_float(odd ? q0 : x0) + b4.x;
+                            o.y = __uint_as_float(odd ? q1 : x1) + b4.y;
+                            o.z = __uint_as_float(odd ? y0 : q0) + b4.z;
+                            o.w = __uint_as_float(odd ? y1 : q1) + b4.w;
+                            if (cols_ok && rowp[j] != nullptr) *reinterpret_cast<float4*>(rowp[j] + cc) = o;
                         }
                     }
                 }
             }
-#ifdef AETHER_KERNEL_TIMERS
-            if (blockIdx.x == TIMER_BLOCK && warp == 2 && lane == 0) { s_timers[5] += clock64() - t_ep0; s_timers[6] += 1; }
-#endif
+            if (++buf == NB) { buf = 0; aph ^= 1u; }
+            TSTAMP(tm_s);                                              // bias + stores
         }
+#ifdef AETHER_KERNEL_TIMERS
+        if (tmr) { g_halo_timers[8] = tm_w; g_halo_timers[9] = tm_l; g_halo_timers[10] = tm_s; }
+#endif
     }
 
     tc_fence_before();
     __syncthreads();
-#ifdef AETHER_KERNEL_TIMERS
-    if (threadIdx.x == 0) {
-        const long long dt = clock64() - t_kernel0;
-        if (blockIdx.x == TIMER_BLOCK) {
-            for (int i = 0; i < 12; ++i) g_halo_timers[i] = s_timers[i];
-            g_halo_timers[12] = dt;
-        }
-        atomicMax(reinterpret_cast<unsigned long long*>(&g_halo_timers[13]), (unsigned long long)dt);
-        atomicAdd(reinterpret_cast<unsigned long long*>(&g_halo_timers[14]), (unsigned long long)dt);
-    }
-#endif
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);
@@ -365,6 +361,7 @@ int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int 
     if (BH > out_H) BH = out_H;
     if (BH + fH - 1 > 256) return AE_OK;
     const int tiles_h = ceil_div(out_H, BH);
+    if (1LL * tiles_h * S > 0x3fffffffLL) return AE_OK;
     // useful fraction of the 128 accumulator rows, including the ragged last strip of each image
     const double eff = (double)out_H * out_W / ((double)tiles_h * 128.0);
     if (eff < 0.70) return AE_OK;
@@ -373,13 +370,13 @@ int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int 
     const int region_rows = (BH + fH - 1) * Wp;
     const int region_stride = (int)align_up((size_t)region_rows * 128, 1024);
     const int smem_max = 232448;
-    const int fixed = 1024 + (int)align_up(w_bytes, 1024) + HALO_STAGING + HALO_TAIL;
+    const int fixed = 1024 + (int)align_up(w_bytes, 1024) + HALO_TAIL;
     int stages = (smem_max - fixed) / region_stride;
     if (stages > 4) stages = 4;
     if (stages < 2) return AE_OK;
     // every tap reads 128 rows from its shifted start; the furthest read must stay inside the allocation
     const int overhang_rows = (fH - 1) * Wp + (fW - 1) + 128 - region_rows;
-    if (overhang_rows > 0 && overhang_rows * 128 > HALO_STAGING + HALO_TAIL + (region_stride - region_rows * 128)) return AE_OK;
+    if (overhang_rows > 0 && overhang_rows * 128 > HALO_TAIL + (region_stride - region_rows * 128)) return AE_OK;
 
     HaloParams p;
     memset(&p, 0, sizeof(p));

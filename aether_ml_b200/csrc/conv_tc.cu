@@ -933,7 +933,21 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
     }
 
     // ---- dW: split over pixel tiles, fixed-order reduction of the partials
-    if (dw) {
+    bool dw_done = false;
+    if (dw && !pl.tf32) {   // wide images: halo-reuse kernel (every tap re-reads one shared-memory window)
+        int splits = 0;
+        float* part = reinterpret_cast<float*>(wsb + pl.off_part);
+        if ((rc = run_halo_dw(x_op, pl.Cin_p, d.H, d.W, d.S, dy_op, pl.Cout_p, pl.Ho, pl.Wo, d.fH, d.fW, d.padH, d.padW, part,
+                              pl.dw_splits, &splits, st, &dw_done)))
+            return rc;
+        if (dw_done) {
+            dw_reduce_kernel<<<2 * num_sms(), 256, 0, st>>>(part, dw, splits, pl.dw_U, pl.KC, pl.Cout_p, pl.dw_cblocks,
+                                                            pl.taps, d.Cin, d.Cout);
+            count_launch();
+            if ((rc = check_launch("dw_reduce_kernel"))) return rc;
+        }
+    }
+    if (dw && !dw_done) {
         DwParams p;
         memset(&p, 0, sizeof(p));
         const CUtensorMapDataType dt = pl.tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;

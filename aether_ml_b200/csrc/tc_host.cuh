@@ -17,4 +17,9 @@ int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int 
                    int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, int n_padded, int fH, int fW,
                    int padT, int padL, int flip, const float* bias, int prof_kind, cudaStream_t st, bool* used);
 
+// Halo-reuse dW kernel (conv_halo_dw.cu), bf16 shadows with 64-channel blocks.  `part` must have room for
+// max_splits split slices; the split count actually used is returned in *splits_out.
+int run_halo_dw(const void* x_sh, int Cin_p, int H, int W, int S, const void* dy_sh, int Cout_p, int Ho, int Wo, int fH,
+                int fW, int padH, int padW, float* part, int max_splits, int* splits_out, cudaStream_t st, bool* used);
+
 }  // namespace aether

@@ -271,8 +271,122 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------------- training workload
+def build_cnn(widen, math_mode):
+    """The CIFAR-shaped 3-block CNN of the reference's README example (CNN/architectures/CNN_cifar1.py:16-55):
+    Conv 3->32->64->128 (3x3 same) each with Batch_Norm / ReLU / [spatial dropout] / 2x2 max pool, Dense
+    2048->256 LeakyReLU dropout, Dense 256->10, softmax + CCE (label smoothing 0.01), Adam lr 1e-3 decay 5e-5.
+    `widen`=4 gives the data-parallel configuration (channels 128/256/512, Dense 8192->1024->10)."""
+    from aether_ml_b200 import layers as Ly
+    from aether_ml_b200.model import Accuracy_Categorical, Model
+    m = Model()
+    c_in, hw = 3, 32
+    for k, (c_out, sd) in enumerate(((32 * widen, 0.075), (64 * widen, 0.1), (128 * widen, None))):
+        m.add(Ly.Conv_Layer((hw, hw, c_in), c_out, (3, 3), (1, 1), "same", math_mode=math_mode))
+        m.add(Ly.Batch_Norm(n_features=c_out))
+        m.add(Ly.ReLU())
+        if sd:
+            m.add(Ly.Layer_Dropout_Spatial(sd))
+        m.add(Ly.Pooling((2, 2), (2, 2), "valid", "max"))
+        c_in, hw = c_out, hw // 2
+    m.add(Ly.Flatten())
+    m.add(Ly.Layer_Dense(4 * 4 * c_in, 256 * widen, weight_regularizer_l2=2e-5, math_mode=math_mode))
+    m.add(Ly.Leaky_ReLU(0.01))
+    m.add(Ly.Layer_Dropout(0.075, seed=11))
+    m.add(Ly.Layer_Dense(256 * widen, 10, math_mode=math_mode))
+    m.add(Ly.SoftMax())
+    m.set(loss=Ly.Loss_CategoricalCrossEntropy(label_smoothing=0.01),
+          optimizer=Ly.Optimizer_Adam(learning_rate=1e-3, decay=5e-5), accuracy=Accuracy_Categorical())
+    m.finalize(flat=True)
+    return m
+
+
+def run_train(args):
+    """Training images/s of the 3-block CNN, batch-sharded over the ranks (global batch fixed: strong scaling);
+    one step = forward + loss gradient + backward + all-reduce of the flat gradient buffer + Adam."""
+    import torch
+    import torch.distributed as dist
+    from aether_ml_b200 import _lib, dp
+    world, rank, local = dp.init_from_env()
+    dev = torch.device("cuda", local)
+    widen = 4 if args.workload == "train_wide" else 1
+    global_batch = args.global_batch or (4096 if widen == 4 else 128)
+    lo, hi = dp.shard_bounds(global_batch, rank, world)
+    np.random.seed(7)                                   # same initial parameters on every rank
+    model = build_cnn(widen, args.mode)
+    dp.attach(model)
+    g = torch.Generator(device="cpu").manual_seed(3)
+    X_host = torch.rand((global_batch, 32, 32, 3), generator=g)[lo:hi].contiguous().pin_memory()
+    y_host = torch.randint(0, 10, (global_batch,), generator=g, dtype=torch.int32)[lo:hi].contiguous().pin_memory()
+    X, y = X_host.to(dev), y_host.to(dev)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        model.train_step(X, y)
+    sync_all()
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel abandoned a bounded wait: status %d" % _lib.device_status())
+    sampler = ClockSampler(local) if rank == 0 else None
+    launches0 = _lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    t_begin = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        model.train_step(X, y)
+    e1.record()
+    sync_all()
+    t_end = time.perf_counter()
+    launches = _lib.launch_count() - launches0
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = float(ms.item()) / args.steps
+    clocks = sampler.stop(t_begin, t_end) if sampler else None
+
+    def e2e_step():
+        out = model.train_step(X_host.to(dev, non_blocking=True), y_host.to(dev, non_blocking=True))
+        return out[:1].cpu()                             # read part of the step's result back every step
+
+    e2e_step()
+    sync_all()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_e2e = max(2, min(args.steps, 10))
+    f0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    f1.record()
+    sync_all()
+    ms2 = torch.tensor([f0.elapsed_time(f1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
+    e2e_ms = float(ms2.item()) / n_e2e
+    if rank == 0:
+        print(json.dumps({
+            "metric": "train_images_per_s", "value": global_batch / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": args.mode, "data": "synthetic",
+            "config": {"workload": "train step of the CIFAR-shaped 3-block CNN%s, global batch %d NHWC (32,32,3) ~ U[0,1), "
+                                   "Adam lr 1e-3 decay 5e-5" % (" widened 4x (128/256/512, Dense 8192->1024->10)" if widen == 4 else "", global_batch),
+                       "per_gpu_batch": hi - lo, "parallelism": "dp%d, one NCCL all-reduce of the flat gradient buffer per step" % world,
+                       "l2": "activations of a step (GBs) exceed the 126 MB L2", "params": int(model.flat_params.numel())},
+            "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": "images/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": (X_host.numel() * 4 + y_host.numel() * 4) * world, "d2h_bytes_per_step": 40 * world},
+            "gpu_launches": int(launches), "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="conv", choices=["conv", "train", "train_wide"],
+                    help="conv = isolated Conv_Layer fwd+bwd (default, the headline metric); train / train_wide = "
+                         "training images/s of the 3-block CNN (README size / widened 4x, global batch 4096)")
+    ap.add_argument("--global-batch", type=int, default=0)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
@@ -284,8 +398,10 @@ def main():
     SHAPE["S"] = args.batch
     if args.impl == "reference":
         run_reference(args)
-    else:
+    elif args.workload == "conv":
         run_gpu(args)
+    else:
+        run_train(args)
 
 
 if __name__ == "__main__":

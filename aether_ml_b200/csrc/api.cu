@@ -141,6 +141,10 @@ extern "C" void aether_profile_reset(void) {
 extern "C" size_t aether_conv2d_workspace_bytes(const AetherConvDesc* d) {
     if (validate_desc(d, "aether_conv2d_workspace_bytes")) return 0;
     size_t g = generic_conv_workspace_bytes(*d);
+    if (smallc_conv_eligible(*d)) {
+        size_t s = smallc_conv_workspace_bytes(*d);
+        if (s > g) g = s;
+    }
     if (tc_conv_eligible(*d)) {
         size_t t = tc_conv_workspace_bytes(*d);
         return t > g ? t : g;
@@ -158,6 +162,7 @@ extern "C" int aether_conv2d_fwd(const AetherConvDesc* d, const float* x, const 
     if ((rc = pending_timeout("aether_conv2d_fwd"))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, ws, ws_bytes, st);
+    if (smallc_conv_eligible(*d) && (!b || aligned16(b))) return smallc_conv_fwd(*d, x, w, b, y, st);
     return generic_conv_fwd(*d, x, w, b, y, st);
 }
 
@@ -172,6 +177,8 @@ extern "C" int aether_conv2d_bwd(const AetherConvDesc* d, const float* x, const 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (tc_conv_eligible(*d)) return tc_conv_bwd(*d, x, dy, w, dx, dw, db, ws, ws_bytes, x_shadow_valid, st);
     if (dx && (rc = generic_conv_bwd_data(*d, dy, w, dx, st))) return rc;
+    if ((dw || db) && smallc_conv_eligible(*d) && (!db || aligned16(db)))
+        return smallc_conv_bwd_filter(*d, x, dy, dw, db, ws, ws_bytes, st);
     if (dw || db) return generic_conv_bwd_filter(*d, x, dy, dw, db, ws, ws_bytes, st);
     return AE_OK;
 }

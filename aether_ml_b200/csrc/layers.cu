@@ -108,19 +108,40 @@ __global__ void bn_finalize_fwd_kernel(const float* __restrict__ part, int nbloc
                                        float momentum, float* __restrict__ running_mean,
                                        float* __restrict__ running_var, float* __restrict__ batch_mean,
                                        float* __restrict__ batch_var, float* __restrict__ scale_shift) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    double N = 0.0, M = 0.0, M2 = 0.0;
-    for (int b = 0; b < nblocks; ++b) {
-        const float* p = part + (size_t)b * 3 * C;
-        const double nl = p[c];
-        if (nl == 0.0) continue;
-        const double ml = p[C + c], m2l = p[2 * C + c];
-        const double tot = N + nl, delta = ml - M;
-        M2 += m2l + delta * delta * N * nl / tot;
-        M += delta * nl / tot;
-        N = tot;
-    }
+    // 32 channels x 8 lanes per CTA (launch with 256 threads).  Two division-free passes over the per-block
+    // triples: total count and sum first, then M2 about the global mean; lanes are combined in fixed order.
+    __shared__ double red_a[8][32], red_b[8][32];
+    const int cl = threadIdx.x & 31, ln = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cl;
+    double n_sum = 0.0, s_sum = 0.0;
+    if (c < C)
+        for (int b = ln; b < nblocks; b += 8) {
+            const float* p = part + (size_t)b * 3 * C;
+            const double nl = p[c];
+            n_sum += nl;
+            s_sum += nl * (double)p[C + c];
+        }
+    red_a[ln][cl] = n_sum;
+    red_b[ln][cl] = s_sum;
+    __syncthreads();
+    double N = 0.0, S1 = 0.0;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) { N += red_a[l][cl]; S1 += red_b[l][cl]; }
+    const double M = N > 0 ? S1 / N : 0.0;
+    __syncthreads();
+    double m2 = 0.0;
+    if (c < C)
+        for (int b = ln; b < nblocks; b += 8) {
+            const float* p = part + (size_t)b * 3 * C;
+            const double d = (double)p[C + c] - M;
+            m2 += (double)p[2 * C + c] + (double)p[c] * d * d;
+        }
+    red_a[ln][cl] = m2;
+    __syncthreads();
+    if (ln != 0 || c >= C) return;
+    double M2 = 0.0;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) M2 += red_a[l][cl];
     const double var = N > 0 ? M2 / N : 0.0;
     batch_mean[c] = (float)M;
     batch_var[c] = (float)var;
@@ -178,13 +199,22 @@ __global__ void bn_finalize_bwd_kernel(const float* __restrict__ part, int nbloc
                                        const float* __restrict__ gamma, const float* __restrict__ mean,
                                        const float* __restrict__ var, float eps, float* __restrict__ dgamma,
                                        float* __restrict__ dbeta, float* __restrict__ coeff) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
+    __shared__ double red_a[8][32], red_b[8][32];
+    const int cl = threadIdx.x & 31, ln = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cl;
+    double pa = 0.0, pb = 0.0;
+    if (c < C)
+        for (int b = ln; b < nblocks; b += 8) {
+            pa += part[(size_t)b * 2 * C + c];
+            pb += part[(size_t)b * 2 * C + C + c];
+        }
+    red_a[ln][cl] = pa;
+    red_b[ln][cl] = pb;
+    __syncthreads();
+    if (ln != 0 || c >= C) return;
     double sdy = 0.0, sdyx = 0.0;
-    for (int b = 0; b < nblocks; ++b) {
-        sdy += part[(size_t)b * 2 * C + c];
-        sdyx += part[(size_t)b * 2 * C + C + c];
-    }
+#pragma unroll
+    for (int l = 0; l < 8; ++l) { sdy += red_a[l][cl]; sdyx += red_b[l][cl]; }
     dgamma[c] = (float)sdyx;
     dbeta[c] = (float)sdy;
     // dx = gamma*inv/N * (N*dy - sum(dy) - xhat * sum(dy*xhat)),  xhat = (x - mean) * inv
@@ -257,7 +287,7 @@ extern "C" int aether_bn_fwd_train(const float* x, const float* gamma, const flo
     float* part = static_cast<float*>(ws);
     float* coeff = part + (size_t)nb * 3 * C;
     bn_reduce_kernel<0><<<nb, 256, 0, st>>>(x, nullptr, nullptr, nullptr, eps, rows, C, part, (rows + nb - 1) / nb);
-    bn_finalize_fwd_kernel<<<ceil_div(C, 128), 128, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
+    bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
                                                             running_var, batch_mean, batch_var, coeff);
     const long long n = rows * C;
     affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C);
@@ -317,7 +347,7 @@ extern "C" int aether_bn_fwd_train_static(const float* x, const float* gamma, co
     // partials, the finalize kernel stores all coefficients), so stale contents of a previous call never matter
     // and nothing has to be cleared.
     bn_reduce_kernel<0><<<nb, 256, 0, st>>>(x, nullptr, nullptr, nullptr, eps, rows, C, part, (rows + nb - 1) / nb);
-    bn_finalize_fwd_kernel<<<ceil_div(C, 128), 128, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
+    bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
                                                             running_var, batch_mean, batch_var, coeff);
     const long long n = rows * C;
     affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C);
@@ -353,7 +383,7 @@ extern "C" int aether_bn_bwd(const float* x, const float* dy, const float* gamma
     float* part = static_cast<float*>(ws);
     float* coeff = part + (size_t)nb * 3 * C;
     bn_reduce_kernel<1><<<nb, 256, 0, st>>>(x, dy, batch_mean, batch_var, eps, rows, C, part, (rows + nb - 1) / nb);
-    bn_finalize_bwd_kernel<<<ceil_div(C, 128), 128, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
+    bn_finalize_bwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
                                                             dbeta, coeff);
     const long long n = rows * C;
     bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C);
@@ -425,21 +455,24 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__
 
 // Backward in gather form: each input cell sums the dy of every window that selected it (max) or
 // that covers it (average).  No atomics; cells outside every window get zero.
-template <bool MAX>
+template <bool MAX, int VEC>
 __global__ void __launch_bounds__(256) pool_bwd_kernel(const float* __restrict__ dy, const uint8_t* __restrict__ arg,
                                                        float* __restrict__ dx, int S, int H, int W, int C, int fH,
                                                        int fW, int sH, int sW, int Ho, int Wo) {
-    const long long total = 1LL * S * H * W * C;
+    const int Cv = C / VEC;
+    const long long total = 1LL * S * H * W * Cv;
     const float inv = 1.f / (float)(fH * fW);
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
-        const int c = (int)(idx % C);
-        long long pix = idx / C;
+        const int cv = (int)(idx % Cv);
+        long long pix = idx / Cv;
         const int w = (int)(pix % W);
         pix /= W;
         const int h = (int)(pix % H);
         const int s = (int)(pix / H);
-        float acc = 0.f;
+        float acc[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[k] = 0.f;
         // windows (ho, wo) with ho*sH <= h < ho*sH + fH
         const int ho_hi = min(Ho - 1, h / sH);
         const int wo_hi = min(Wo - 1, w / sW);
@@ -447,15 +480,30 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const float* __restrict__
             const int i = h - ho * sH;
             for (int wo = wo_hi; wo >= 0 && wo * sW + fW > w; --wo) {
                 const int j = w - wo * sW;
-                const size_t o = (((size_t)s * Ho + ho) * Wo + wo) * C + c;
-                if (MAX) {
-                    if (arg[o] == (uint8_t)(i * fW + j)) acc += dy[o];
+                const size_t o = (((size_t)s * Ho + ho) * Wo + wo) * C + (size_t)cv * VEC;
+                const unsigned char code = (unsigned char)(i * fW + j);
+                if (VEC == 4) {
+                    const float4 g = *reinterpret_cast<const float4*>(dy + o);
+                    if (MAX) {
+                        const uchar4 a = *reinterpret_cast<const uchar4*>(arg + o);
+                        if (a.x == code) acc[0] += g.x;
+                        if (a.y == code) acc[1] += g.y;
+                        if (a.z == code) acc[2] += g.z;
+                        if (a.w == code) acc[3] += g.w;
+                    } else {
+                        acc[0] += g.x * inv; acc[1] += g.y * inv; acc[2] += g.z * inv; acc[3] += g.w * inv;
+                    }
                 } else {
-                    acc += dy[o] * inv;
+                    if (MAX) {
+                        if (arg[o] == code) acc[0] += dy[o];
+                    } else {
+                        acc[0] += dy[o] * inv;
+                    }
                 }
             }
         }
-        dx[idx] = acc;
+        if (VEC == 4) *reinterpret_cast<float4*>(dx + idx * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        else dx[idx] = acc[0];
     }
 }
 
@@ -661,12 +709,17 @@ extern "C" int aether_pool_bwd(const float* dy, const uint8_t* argmax, float* dx
         return set_error(AE_BAD_ARG, "aether_pool_bwd: bad shape");
     if (kind != AETHER_POOL_MAX && kind != AETHER_POOL_AVG) return set_error(AE_UNSUPPORTED, "aether_pool_bwd: kind %d", kind);
     const int Ho = (H - fH) / sH + 1, Wo = (W - fW) / sW + 1;
-    const long long total = 1LL * S * H * W * C;
+    const bool vec = (C & 3) == 0 && aligned16(dy) && aligned16(dx) && (!argmax || (reinterpret_cast<uintptr_t>(argmax) & 3) == 0);
+    const long long total = 1LL * S * H * W * (vec ? C / 4 : C);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (kind == AETHER_POOL_MAX)
-        pool_bwd_kernel<true><<<blocks_for(total, 256, 16), 256, 0, st>>>(dy, argmax, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
-    else
-        pool_bwd_kernel<false><<<blocks_for(total, 256, 16), 256, 0, st>>>(dy, nullptr, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
+    const int nb = blocks_for(total, 256, 16);
+    if (kind == AETHER_POOL_MAX) {
+        if (vec) pool_bwd_kernel<true, 4><<<nb, 256, 0, st>>>(dy, argmax, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
+        else pool_bwd_kernel<true, 1><<<nb, 256, 0, st>>>(dy, argmax, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
+    } else {
+        if (vec) pool_bwd_kernel<false, 4><<<nb, 256, 0, st>>>(dy, nullptr, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
+        else pool_bwd_kernel<false, 1><<<nb, 256, 0, st>>>(dy, nullptr, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
+    }
     count_launch();
     return check_launch("aether_pool_bwd");
 }

@@ -92,7 +92,11 @@ def test_tensor_core_shapes(env, shape, mode):
 
 
 @pytest.mark.parametrize("shape", [(3, 9, 9, 3, 8, 3, (2, 2), "valid"), (2, 12, 10, 5, 7, 3, (1, 1), "same"),
-                                   (4, 28, 28, 1, 32, 3, (1, 1), "same"), (2, 11, 11, 4, 6, 5, (2, 1), "same")])
+                                   (4, 28, 28, 1, 32, 3, (1, 1), "same"), (2, 11, 11, 4, 6, 5, (2, 1), "same"),
+                                   # first-layer kernels (1..4 input channels, power-of-two filter count 16..256)
+                                   (5, 17, 13, 3, 128, 3, (1, 1), "same"), (3, 20, 20, 1, 64, 5, (2, 2), "valid"),
+                                   (2, 9, 9, 3, 256, 3, (1, 2), "same"), (6, 14, 14, 2, 16, 3, (1, 1), "same"),
+                                   (70, 32, 32, 3, 128, 3, (1, 1), "same")])
 def test_cuda_core_shapes(env, shape):
     S, H, W, Cin, Cout, f, st, pad = shape
     rng = np.random.default_rng(3)

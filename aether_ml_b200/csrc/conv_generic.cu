@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(256) gen_dx_kernel(const float* __restrict__ d
 // ---------------------------------------------------------------------------------- dW, dB
 // Block b owns a contiguous chunk of output pixels; thread t accumulates filter entries t, t+256, ...
 // over that chunk and writes them to part[b][entry].  A second kernel adds the chunks in fixed order.
+static constexpr int GEN_DW_CHUNK = 256;
 __global__ void __launch_bounds__(256) gen_dw_partial_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                                                              float* __restrict__ part, int S, int H, int W, int Cin,
                                                              int Cout, int fH, int fW, int sH, int sW, int pH, int pW,
@@ -94,28 +95,41 @@ __global__ void __launch_bounds__(256) gen_dw_partial_kernel(const float* __rest
     long long p1 = p0 + pix_per_block;
     if (p1 > npix) p1 = npix;
     const int entries = fH * fW * Cin * Cout;
-    for (int e = threadIdx.x; e < entries + Cout; e += blockDim.x) {
+    // Pixel coordinates are decoded once per chunk of GEN_DW_CHUNK pixels into shared memory
+    // (sample row base s*H, top-left input row, top-left input column), not once per (entry, pixel).
+    __shared__ int pix_s[GEN_DW_CHUNK], pix_h[GEN_DW_CHUNK], pix_w[GEN_DW_CHUNK];
+    for (int e0 = 0; e0 < entries + Cout; e0 += blockDim.x) {
+        const int e = e0 + threadIdx.x;
+        const bool is_w = e < entries && x != nullptr;
+        const bool is_b = e >= entries && e < entries + Cout;
+        const int d = is_b ? e - entries : e % Cout;
+        const int c = (e / Cout) % Cin;
+        const int tap = e / (Cout * Cin);
+        const int i = tap / fW, j = tap % fW;
         float acc = 0.f;
-        if (e < entries && x == nullptr) {
-            acc = 0.f;                             // only dB was requested
-        } else if (e < entries) {
-            const int d = e % Cout;
-            const int c = (e / Cout) % Cin;
-            const int tap = e / (Cout * Cin);
-            const int i = tap / fW, j = tap % fW;
-            for (long long p = p0; p < p1; ++p) {
+        for (long long c0 = p0; c0 < p1; c0 += GEN_DW_CHUNK) {
+            const int n = (int)((p1 - c0 < GEN_DW_CHUNK) ? (p1 - c0) : GEN_DW_CHUNK);
+            __syncthreads();
+            for (int q = threadIdx.x; q < n; q += blockDim.x) {
+                const long long p = c0 + q;
                 const int wo = (int)(p % Wo);
-                const int ho = (int)((p / Wo) % Ho);
-                const int s = (int)(p / ((long long)Wo * Ho));
-                const int hi = ho * sH + i - pH, wi = wo * sW + j - pW;
-                if (hi < 0 || hi >= H || wi < 0 || wi >= W) continue;
-                acc = fmaf(x[(((size_t)s * H + hi) * W + wi) * Cin + c], dy[(size_t)p * Cout + d], acc);
+                const long long r = p / Wo;
+                pix_w[q] = wo * sW - pW;
+                pix_h[q] = (int)(r % Ho) * sH - pH;
+                pix_s[q] = (int)(r / Ho) * H;
             }
-        } else {                                   // trailing Cout entries: dB
-            const int d = e - entries;
-            for (long long p = p0; p < p1; ++p) acc += dy[(size_t)p * Cout + d];
+            __syncthreads();
+            if (is_w) {
+                for (int q = 0; q < n; ++q) {
+                    const int hi = pix_h[q] + i, wi = pix_w[q] + j;
+                    if (hi < 0 || hi >= H || wi < 0 || wi >= W) continue;
+                    acc = fmaf(x[((size_t)(pix_s[q] + hi) * W + wi) * Cin + c], dy[(size_t)(c0 + q) * Cout + d], acc);
+                }
+            } else if (is_b) {                     // trailing Cout entries: dB
+                for (int q = 0; q < n; ++q) acc += dy[(size_t)(c0 + q) * Cout + d];
+            }
         }
-        part[(size_t)blockIdx.x * (entries + Cout) + e] = acc;
+        if (e < entries + Cout) part[(size_t)blockIdx.x * (entries + Cout) + e] = acc;
     }
 }
 
@@ -171,7 +185,7 @@ static int gen_dw_blocks(const AetherConvDesc& d) {
     int Ho, Wo;
     conv_out_hw(d, Ho, Wo);
     const long long npix = 1LL * d.S * Ho * Wo;
-    long long nb = npix / 64;
+    long long nb = npix / 32;
     if (nb > 148LL * 4) nb = 148LL * 4;
     if (nb < 1) nb = 1;
     return (int)nb;

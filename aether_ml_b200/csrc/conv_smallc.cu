@@ -8,81 +8,113 @@
 //
 // A CTA stages the im2col values of a tile of pixels (transposed, [K][TP]) in shared memory; a thread owns
 // four consecutive output channels and works on four pixels at a time, so each shared-memory read feeds
-// eight or more FMAs.  dW keeps its accumulators in registers across all tiles of the CTA and writes one
-// partial per CTA; a second kernel adds the partials in fixed order (bit-reproducible, no atomics).
+// eight or more FMAs.  Pixel and filter-entry coordinates are decoded once into small shared tables, so the
+// gather itself has no divisions.  dW keeps its accumulators in registers across all tiles of the CTA and
+// writes one partial per CTA; a second kernel adds the partials in fixed order (bit-reproducible, no atomics).
 #include "common.cuh"
 
 namespace aether {
 
 static constexpr int SC_THREADS = 256;
 static constexpr int SC_MAX_K = 64;
+static constexpr int SC_MAX_TP = 256;
 
 struct SmallcGeom {
     int S, H, W, Cin, Cout, fH, fW, sH, sW, pH, pW, Ho, Wo, K;
     long long P;      // output pixels
     int lanes;        // thread groups along pixels (forward) / along K (dW) = 256 / (Cout/4)
-    int TP;           // pixels per tile
+    int TP;           // pixels per tile (power of two)
+    int tp_shift;     // log2(TP)
+    int cg_shift;     // log2(Cout/4)
     int R;            // 4-pixel groups per thread and tile (forward)
     int KPG;          // filter entries per thread (dW)
 };
 
-// Gathers col^T for the tile starting at pixel p0 into colT[K][TP] (zero outside the image / past the end).
-__device__ __forceinline__ void stage_colT(const SmallcGeom& g, const float* __restrict__ x, long long p0, float* colT) {
-    for (int e = threadIdx.x; e < g.K * g.TP; e += SC_THREADS) {
-        const int k = e / g.TP, pl = e - k * g.TP;
-        const long long p = p0 + pl;
-        float v = 0.f;
-        if (p < g.P) {
-            const int wo = (int)(p % g.Wo);
-            const long long q = p / g.Wo;
-            const int ho = (int)(q % g.Ho);
-            const int s = (int)(q / g.Ho);
-            const int c = k % g.Cin;
-            const int tap = k / g.Cin;
-            const int i = tap / g.fW, j = tap - i * g.fW;
-            const int hi = ho * g.sH + i - g.pH, wi = wo * g.sW + j - g.pW;
-            if (hi >= 0 && hi < g.H && wi >= 0 && wi < g.W) v = x[(((size_t)s * g.H + hi) * g.W + wi) * g.Cin + c];
-        }
-        colT[e] = v;
+struct SmallcTables {
+    int k_i[SC_MAX_K], k_j[SC_MAX_K], k_c[SC_MAX_K];            // filter entry k -> (row, column, channel)
+    int pix_s[SC_MAX_TP], pix_h[SC_MAX_TP], pix_w[SC_MAX_TP];   // tile pixel -> (sample*H, top input row, left input column)
+};
+
+__device__ __forceinline__ void fill_ktab(const SmallcGeom& g, SmallcTables& t) {
+    for (int k = threadIdx.x; k < g.K; k += SC_THREADS) {
+        const int tap = k / g.Cin;
+        t.k_c[k] = k - tap * g.Cin;
+        t.k_i[k] = tap / g.fW;
+        t.k_j[k] = tap - (tap / g.fW) * g.fW;
     }
 }
 
+// Gathers col^T for the tile starting at pixel p0 into colT[K][TP] (zero outside the image / past the end).
+// Contains two block barriers; every thread of the CTA must call it.
+__device__ __forceinline__ void stage_colT(const SmallcGeom& g, SmallcTables& t, const float* __restrict__ x, long long p0,
+                                           float* colT) {
+    for (int q = threadIdx.x; q < g.TP; q += SC_THREADS) {
+        const long long p = p0 + q;
+        if (p < g.P) {
+            const int wo = (int)(p % g.Wo);
+            const long long r = p / g.Wo;
+            t.pix_w[q] = wo * g.sW - g.pW;
+            t.pix_h[q] = (int)(r % g.Ho) * g.sH - g.pH;
+            t.pix_s[q] = (int)(r / g.Ho) * g.H;
+        } else {
+            t.pix_w[q] = 0; t.pix_h[q] = -(1 << 20); t.pix_s[q] = 0;   // fails the row test below
+        }
+    }
+    __syncthreads();
+    const int n = g.K << g.tp_shift;
+    for (int e = threadIdx.x; e < n; e += SC_THREADS) {
+        const int k = e >> g.tp_shift, pl = e & (g.TP - 1);
+        const int hi = t.pix_h[pl] + t.k_i[k], wi = t.pix_w[pl] + t.k_j[k];
+        float v = 0.f;
+        if (hi >= 0 && hi < g.H && wi >= 0 && wi < g.W) v = x[((size_t)(t.pix_s[pl] + hi) * g.W + wi) * g.Cin + t.k_c[k]];
+        colT[e] = v;
+    }
+    __syncthreads();
+}
+
+#define SC_FMA4(A, S, V)                                                                  \
+    A.x = fmaf(S, V.x, A.x); A.y = fmaf(S, V.y, A.y); A.z = fmaf(S, V.z, A.z); A.w = fmaf(S, V.w, A.w)
+
+template <int R>
 __global__ void __launch_bounds__(SC_THREADS) smallc_fwd_kernel(const SmallcGeom g, const float* __restrict__ x,
                                                                 const float* __restrict__ w, const float* __restrict__ b,
                                                                 float* __restrict__ y, long long ntiles) {
     extern __shared__ float sm[];
+    __shared__ SmallcTables tab;
     float* wsm = sm;                          // [K][Cout]
     float* colT = sm + g.K * g.Cout;          // [K][TP]
     for (int e = threadIdx.x; e < g.K * g.Cout; e += SC_THREADS) wsm[e] = w[e];
-    const int cgs = g.Cout >> 2;
-    const int cg = threadIdx.x % cgs, pl = threadIdx.x / cgs;
+    fill_ktab(g, tab);
+    const int cg = threadIdx.x & ((1 << g.cg_shift) - 1), pl = threadIdx.x >> g.cg_shift;
     const float4 bias = b ? *reinterpret_cast<const float4*>(b + cg * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    __syncthreads();
     for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const long long p0 = tile * g.TP;
-        __syncthreads();                      // previous tile's readers are done (and weights are staged)
-        stage_colT(g, x, p0, colT);
-        __syncthreads();
-        for (int r = 0; r < g.R; ++r) {
-            const int pb = (r * g.lanes + pl) * 4;            // first of this thread's 4 pixels in the tile
-            float4 acc[4] = {bias, bias, bias, bias};
-            for (int k = 0; k < g.K; ++k) {
-                const float4 wv = *reinterpret_cast<const float4*>(wsm + k * g.Cout + cg * 4);
-                const float4 cv = *reinterpret_cast<const float4*>(colT + k * g.TP + pb);
-                acc[0].x = fmaf(cv.x, wv.x, acc[0].x); acc[0].y = fmaf(cv.x, wv.y, acc[0].y);
-                acc[0].z = fmaf(cv.x, wv.z, acc[0].z); acc[0].w = fmaf(cv.x, wv.w, acc[0].w);
-                acc[1].x = fmaf(cv.y, wv.x, acc[1].x); acc[1].y = fmaf(cv.y, wv.y, acc[1].y);
-                acc[1].z = fmaf(cv.y, wv.z, acc[1].z); acc[1].w = fmaf(cv.y, wv.w, acc[1].w);
-                acc[2].x = fmaf(cv.z, wv.x, acc[2].x); acc[2].y = fmaf(cv.z, wv.y, acc[2].y);
-                acc[2].z = fmaf(cv.z, wv.z, acc[2].z); acc[2].w = fmaf(cv.z, wv.w, acc[2].w);
-                acc[3].x = fmaf(cv.w, wv.x, acc[3].x); acc[3].y = fmaf(cv.w, wv.y, acc[3].y);
-                acc[3].z = fmaf(cv.w, wv.z, acc[3].z); acc[3].w = fmaf(cv.w, wv.w, acc[3].w);
-            }
+        const long long p0 = tile << g.tp_shift;
+        stage_colT(g, tab, x, p0, colT);
+        float4 acc[R][4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const long long p = p0 + pb + q;
-                if (p < g.P) *reinterpret_cast<float4*>(y + (size_t)p * g.Cout + cg * 4) = acc[q];
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[r][q] = bias;
+        for (int k = 0; k < g.K; ++k) {
+            const float4 wv = *reinterpret_cast<const float4*>(wsm + k * g.Cout + cg * 4);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float4 cv = *reinterpret_cast<const float4*>(colT + (k << g.tp_shift) + (r * g.lanes + pl) * 4);
+                SC_FMA4(acc[r][0], cv.x, wv);
+                SC_FMA4(acc[r][1], cv.y, wv);
+                SC_FMA4(acc[r][2], cv.z, wv);
+                SC_FMA4(acc[r][3], cv.w, wv);
             }
         }
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const long long p = p0 + (r * g.lanes + pl) * 4 + q;
+                if (p < g.P) __stcs(reinterpret_cast<float4*>(y + (size_t)p * g.Cout + cg * 4), acc[r][q]);
+            }
+        __syncthreads();                      // colT is rewritten by the next tile's gather
     }
 }
 
@@ -92,26 +124,28 @@ __global__ void __launch_bounds__(SC_THREADS) smallc_dw_kernel(const SmallcGeom 
                                                                const float* __restrict__ dy, float* __restrict__ part,
                                                                long long ntiles) {
     extern __shared__ float sm[];
+    __shared__ SmallcTables tab;
     float* colT = sm;                         // [K][TP]
-    float* dys = sm + g.K * g.TP;             // [TP][Cout]
-    const int cgs = g.Cout >> 2;
-    const int cg = threadIdx.x % cgs, kg = threadIdx.x / cgs;      // this thread's filter entries: kg, kg+lanes, ...
+    float* dys = sm + (g.K << g.tp_shift);    // [TP][Cout]
+    const int cgs = 1 << g.cg_shift;
+    const int cg = threadIdx.x & (cgs - 1), kg = threadIdx.x >> g.cg_shift;   // filter entries kg, kg+lanes, ...
     float4 acc[KPG];
 #pragma unroll
     for (int a = 0; a < KPG; ++a) acc[a] = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 bsum = make_float4(0.f, 0.f, 0.f, 0.f);
     const bool want_x = (x != nullptr);
+    fill_ktab(g, tab);
+    __syncthreads();
     for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const long long p0 = tile * g.TP;
-        __syncthreads();
-        if (want_x) stage_colT(g, x, p0, colT);
-        for (int e = threadIdx.x; e < g.TP * cgs; e += SC_THREADS) {
-            const int pl = e / cgs, c4 = e - pl * cgs;
-            const long long p = p0 + pl;
+        const long long p0 = tile << g.tp_shift;
+        for (int e = threadIdx.x; e < (g.TP << g.cg_shift); e += SC_THREADS) {
+            const long long p = p0 + (e >> g.cg_shift);
             reinterpret_cast<float4*>(dys)[e] =
-                (p < g.P) ? *reinterpret_cast<const float4*>(dy + (size_t)p * g.Cout + c4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                (p < g.P) ? __ldcs(reinterpret_cast<const float4*>(dy + (size_t)p * g.Cout) + (e & (cgs - 1)))
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        __syncthreads();
+        if (want_x) stage_colT(g, tab, x, p0, colT);
+        else __syncthreads();
         for (int pb = 0; pb < g.TP; pb += 4) {
             const float4 d0 = *reinterpret_cast<const float4*>(dys + (size_t)(pb + 0) * g.Cout + cg * 4);
             const float4 d1 = *reinterpret_cast<const float4*>(dys + (size_t)(pb + 1) * g.Cout + cg * 4);
@@ -126,19 +160,16 @@ __global__ void __launch_bounds__(SC_THREADS) smallc_dw_kernel(const SmallcGeom 
                 for (int a = 0; a < KPG; ++a) {
                     const int k = kg + a * g.lanes;
                     if (k < g.K) {
-                        const float4 cv = *reinterpret_cast<const float4*>(colT + k * g.TP + pb);
-                        acc[a].x = fmaf(cv.x, d0.x, acc[a].x); acc[a].y = fmaf(cv.x, d0.y, acc[a].y);
-                        acc[a].z = fmaf(cv.x, d0.z, acc[a].z); acc[a].w = fmaf(cv.x, d0.w, acc[a].w);
-                        acc[a].x = fmaf(cv.y, d1.x, acc[a].x); acc[a].y = fmaf(cv.y, d1.y, acc[a].y);
-                        acc[a].z = fmaf(cv.y, d1.z, acc[a].z); acc[a].w = fmaf(cv.y, d1.w, acc[a].w);
-                        acc[a].x = fmaf(cv.z, d2.x, acc[a].x); acc[a].y = fmaf(cv.z, d2.y, acc[a].y);
-                        acc[a].z = fmaf(cv.z, d2.z, acc[a].z); acc[a].w = fmaf(cv.z, d2.w, acc[a].w);
-                        acc[a].x = fmaf(cv.w, d3.x, acc[a].x); acc[a].y = fmaf(cv.w, d3.y, acc[a].y);
-                        acc[a].z = fmaf(cv.w, d3.z, acc[a].z); acc[a].w = fmaf(cv.w, d3.w, acc[a].w);
+                        const float4 cv = *reinterpret_cast<const float4*>(colT + (k << g.tp_shift) + pb);
+                        SC_FMA4(acc[a], cv.x, d0);
+                        SC_FMA4(acc[a], cv.y, d1);
+                        SC_FMA4(acc[a], cv.z, d2);
+                        SC_FMA4(acc[a], cv.w, d3);
                     }
                 }
             }
         }
+        __syncthreads();                      // dys / colT are rewritten by the next tile
     }
     float* out = part + (size_t)blockIdx.x * (g.K + 1) * g.Cout;
 #pragma unroll
@@ -174,6 +205,12 @@ __global__ void __launch_bounds__(256) smallc_reduce_kernel(const float* __restr
 }
 
 // ---------------------------------------------------------------------------------- host
+static int ilog2(int v) {
+    int s = 0;
+    while ((1 << s) < v) ++s;
+    return s;
+}
+
 static bool smallc_geom(const AetherConvDesc& d, SmallcGeom& g) {
     g.K = d.fH * d.fW * d.Cin;
     if (g.K > SC_MAX_K || d.Cin > 4) return false;
@@ -182,11 +219,13 @@ static bool smallc_geom(const AetherConvDesc& d, SmallcGeom& g) {
     g.sH = d.sH; g.sW = d.sW; g.pH = d.padH; g.pW = d.padW;
     conv_out_hw(d, g.Ho, g.Wo);
     g.P = 1LL * d.S * g.Ho * g.Wo;
-    g.lanes = SC_THREADS / (d.Cout >> 2);
+    g.cg_shift = ilog2(d.Cout >> 2);
+    g.lanes = SC_THREADS >> g.cg_shift;
     g.R = 64 / (g.lanes * 4) > 1 ? 64 / (g.lanes * 4) : 1;
     g.TP = g.lanes * 4 * g.R;
+    g.tp_shift = ilog2(g.TP);
     g.KPG = ceil_div(g.K, g.lanes);
-    return g.KPG <= 16;
+    return g.KPG <= 16 && g.TP <= SC_MAX_TP && g.R <= 4;
 }
 
 bool smallc_conv_eligible(const AetherConvDesc& d) {
@@ -196,7 +235,7 @@ bool smallc_conv_eligible(const AetherConvDesc& d) {
 
 static int smallc_blocks(const SmallcGeom& g) {
     const long long ntiles = (g.P + g.TP - 1) / g.TP;
-    long long nb = 2LL * 148;
+    long long nb = 4LL * 148;                 // four resident CTAs per SM hide each other's staging latency
     if (nb > ntiles) nb = ntiles;
     return (int)(nb < 1 ? 1 : nb);
 }
@@ -207,33 +246,45 @@ size_t smallc_conv_workspace_bytes(const AetherConvDesc& d) {
     return align_up((size_t)smallc_blocks(g) * (g.K + 1) * g.Cout * sizeof(float), 1024);
 }
 
+template <typename Kern>
+static int smallc_smem(Kern kernel, size_t smem, size_t& configured, const char* what) {
+    if (smem > 40 * 1024 && smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(%s): %s", what, cudaGetErrorString(e));
+        configured = smem;
+    }
+    return AE_OK;
+}
+
+template <int R>
+static int launch_smallc_fwd(const SmallcGeom& g, const float* x, const float* w, const float* b, float* y, int nb,
+                             long long ntiles, size_t smem, cudaStream_t st) {
+    static size_t configured = 0;
+    int rc = smallc_smem(smallc_fwd_kernel<R>, smem, configured, "smallc_fwd");
+    if (rc) return rc;
+    smallc_fwd_kernel<R><<<nb, SC_THREADS, smem, st>>>(g, x, w, b, y, ntiles);
+    count_launch();
+    return check_launch("smallc_fwd_kernel");
+}
+
 int smallc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, cudaStream_t st) {
     SmallcGeom g;
     if (!smallc_geom(d, g)) return set_error(AE_UNSUPPORTED, "smallc_conv_fwd: shape not supported");
     const long long ntiles = (g.P + g.TP - 1) / g.TP;
     const size_t smem = (size_t)(g.K * g.Cout + g.K * g.TP) * sizeof(float);
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(smallc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(smallc_fwd): %s", cudaGetErrorString(e));
-        configured = smem;
-    }
     long long nb = 4LL * 148;
     if (nb > ntiles) nb = ntiles;
-    smallc_fwd_kernel<<<(int)nb, SC_THREADS, smem, st>>>(g, x, w, b, y, ntiles);
-    count_launch();
-    return check_launch("smallc_fwd_kernel");
+    if (g.R == 1) return launch_smallc_fwd<1>(g, x, w, b, y, (int)nb, ntiles, smem, st);
+    if (g.R == 2) return launch_smallc_fwd<2>(g, x, w, b, y, (int)nb, ntiles, smem, st);
+    return launch_smallc_fwd<4>(g, x, w, b, y, (int)nb, ntiles, smem, st);
 }
 
 template <int KPG>
 static int launch_smallc_dw(const SmallcGeom& g, const float* x, const float* dy, float* part, int nb, long long ntiles,
                             size_t smem, cudaStream_t st) {
     static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(smallc_dw_kernel<KPG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(smallc_dw): %s", cudaGetErrorString(e));
-        configured = smem;
-    }
+    int rc = smallc_smem(smallc_dw_kernel<KPG>, smem, configured, "smallc_dw");
+    if (rc) return rc;
     smallc_dw_kernel<KPG><<<nb, SC_THREADS, smem, st>>>(g, x, dy, part, ntiles);
     count_launch();
     return check_launch("smallc_dw_kernel");

@@ -100,6 +100,113 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(const float* __restrict_
     }
 }
 
+// The same reductions with four consecutive channels per thread (C % 4 == 0, 16-byte aligned rows):
+// float4 loads keep four times the bytes in flight per thread, which is what the HBM latency needs.
+template <int MODE>
+__global__ void __launch_bounds__(256) bn_reduce_vec4_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                             const float* __restrict__ mean, const float* __restrict__ var,
+                                                             float eps, long long rows, int C, float* __restrict__ part,
+                                                             long long rows_per_block) {
+    const long long r0 = blockIdx.x * rows_per_block;
+    long long r1 = r0 + rows_per_block;
+    if (r1 > rows) r1 = rows;
+    const int CV = C >> 2;
+    const int cols = CV < 256 ? CV : 256;
+    const int lanes = 256 / cols;
+    __shared__ float4 sh_a4[256], sh_b4[256];
+    __shared__ float sh_n[256];
+    constexpr int NOUT = MODE == 0 ? 3 : 2;
+    for (int cbase = 0; cbase < CV; cbase += cols) {
+        const int cv = cbase + threadIdx.x % cols;
+        const int rl = threadIdx.x / cols;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        float n = 0.f;
+        if (rl < lanes && cv < CV) {
+            const float4* xr = reinterpret_cast<const float4*>(x) + cv;          // row r is xr[r * CV]
+            if (MODE == 0) {
+                const float4 sh = (r0 < r1) ? xr[(size_t)r0 * CV] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                for (long long r = r0 + rl; r < r1; r += lanes) {
+                    float4 v = xr[(size_t)r * CV];
+                    v.x -= sh.x; v.y -= sh.y; v.z -= sh.z; v.w -= sh.w;
+                    a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+                    b.x = fmaf(v.x, v.x, b.x); b.y = fmaf(v.y, v.y, b.y);
+                    b.z = fmaf(v.z, v.z, b.z); b.w = fmaf(v.w, v.w, b.w);
+                    n += 1.f;
+                }
+                if (n > 0.f) {
+                    float m;
+                    m = a.x / n; b.x -= a.x * m; a.x = m + sh.x;
+                    m = a.y / n; b.y -= a.y * m; a.y = m + sh.y;
+                    m = a.z / n; b.z -= a.z * m; a.z = m + sh.z;
+                    m = a.w / n; b.w -= a.w * m; a.w = m + sh.w;
+                }
+            } else {
+                const int c = cv * 4;
+                const float4 mu = make_float4(mean[c], mean[c + 1], mean[c + 2], mean[c + 3]);
+                const float4 inv = make_float4(rsqrtf(var[c] + eps), rsqrtf(var[c + 1] + eps), rsqrtf(var[c + 2] + eps),
+                                               rsqrtf(var[c + 3] + eps));
+                const float4* gr = reinterpret_cast<const float4*>(dy) + cv;
+#pragma unroll 4
+                for (long long r = r0 + rl; r < r1; r += lanes) {
+                    const float4 g = gr[(size_t)r * CV];
+                    const float4 v = xr[(size_t)r * CV];
+                    a.x += g.x; a.y += g.y; a.z += g.z; a.w += g.w;
+                    b.x = fmaf(g.x, (v.x - mu.x) * inv.x, b.x); b.y = fmaf(g.y, (v.y - mu.y) * inv.y, b.y);
+                    b.z = fmaf(g.z, (v.z - mu.z) * inv.z, b.z); b.w = fmaf(g.w, (v.w - mu.w) * inv.w, b.w);
+                }
+            }
+        }
+        sh_a4[threadIdx.x] = a;
+        sh_b4[threadIdx.x] = b;
+        sh_n[threadIdx.x] = n;
+        __syncthreads();
+        if (threadIdx.x < cols && cv < CV) {
+            float* out = part + (size_t)blockIdx.x * NOUT * C + cv * 4;
+            const float* pa = reinterpret_cast<const float*>(sh_a4);
+            const float* pb = reinterpret_cast<const float*>(sh_b4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (MODE == 0) {
+                    float N = 0.f, M = 0.f, M2 = 0.f;          // Chan's merge of the row lanes, in fixed order
+                    for (int l = 0; l < lanes; ++l) {
+                        const int t = l * cols + threadIdx.x;
+                        const float nl = sh_n[t];
+                        if (nl == 0.f) continue;
+                        const float tot = N + nl;
+                        const float delta = pa[t * 4 + k] - M;
+                        M2 += pb[t * 4 + k] + delta * delta * N * nl / tot;
+                        M += delta * nl / tot;
+                        N = tot;
+                    }
+                    out[k] = N;
+                    out[C + k] = M;
+                    out[2 * C + k] = M2;
+                } else {
+                    float sa = 0.f, sb = 0.f;
+                    for (int l = 0; l < lanes; ++l) {
+                        sa += pa[(l * cols + threadIdx.x) * 4 + k];
+                        sb += pb[(l * cols + threadIdx.x) * 4 + k];
+                    }
+                    out[k] = sa;
+                    out[C + k] = sb;
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <int MODE>
+static void launch_bn_reduce(int nb, cudaStream_t st, const float* x, const float* dy, const float* mean, const float* var,
+                             float eps, long long rows, int C, float* part) {
+    const long long rpb = (rows + nb - 1) / nb;
+    const bool vec = (C & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+                     (MODE == 0 || (reinterpret_cast<uintptr_t>(dy) & 15u) == 0);
+    if (vec) bn_reduce_vec4_kernel<MODE><<<nb, 256, 0, st>>>(x, dy, mean, var, eps, rows, C, part, rpb);
+    else bn_reduce_kernel<MODE><<<nb, 256, 0, st>>>(x, dy, mean, var, eps, rows, C, part, rpb);
+}
+
 // Merges the per-block (n, mean, M2) triples in double precision, writes batch mean / biased variance,
 // updates the running statistics (momentum * old + (1 - momentum) * batch) and the affine
 // coefficients scale = gamma / sqrt(var + eps), shift = beta - mean * scale used by the apply kernel.
@@ -172,8 +279,13 @@ __global__ void __launch_bounds__(256) affine_channels_kernel(const float* __res
         const int C4 = C >> 2;
         const float4* x4 = reinterpret_cast<const float4*>(x);
         float4* y4 = reinterpret_cast<float4*>(y);
-        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += stride) {
-            const int c = (int)(i % C4) * 4;
+        const long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+        const int cstep = (int)(stride % C4);          // the channel group advances by this much per iteration
+        int cq = (int)(i0 % C4);
+        for (long long i = i0; i < n4; i += stride) {
+            const int c = cq * 4;
+            cq += cstep;
+            if (cq >= C4) cq -= C4;
             const float4 v = x4[i];
             const float4 s = *reinterpret_cast<const float4*>(scale + c);
             float4 o;
@@ -236,8 +348,13 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const float* __restri
     if ((C & 3) == 0) {
         const long long n4 = n >> 2;
         const int C4 = C >> 2;
-        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += stride) {
-            const int c = (int)(i % C4) * 4;
+        const long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+        const int cstep = (int)(stride % C4);
+        int cq = (int)(i0 % C4);
+        for (long long i = i0; i < n4; i += stride) {
+            const int c = cq * 4;
+            cq += cstep;
+            if (cq >= C4) cq -= C4;
             const float4 xv = reinterpret_cast<const float4*>(x)[i];
             const float4 g = reinterpret_cast<const float4*>(dy)[i];
             const float4 k1 = *reinterpret_cast<const float4*>(coeff + c);
@@ -286,7 +403,7 @@ extern "C" int aether_bn_fwd_train(const float* x, const float* gamma, const flo
     const int nb = bn_blocks(rows);
     float* part = static_cast<float*>(ws);
     float* coeff = part + (size_t)nb * 3 * C;
-    bn_reduce_kernel<0><<<nb, 256, 0, st>>>(x, nullptr, nullptr, nullptr, eps, rows, C, part, (rows + nb - 1) / nb);
+    launch_bn_reduce<0>(nb, st, x, nullptr, nullptr, nullptr, eps, rows, C, part);
     bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
                                                             running_var, batch_mean, batch_var, coeff);
     const long long n = rows * C;
@@ -346,7 +463,7 @@ extern "C" int aether_bn_fwd_train_static(const float* x, const float* gamma, co
     // Every scratch element read below is written earlier in this same call (each block stores all 3*C of its
     // partials, the finalize kernel stores all coefficients), so stale contents of a previous call never matter
     // and nothing has to be cleared.
-    bn_reduce_kernel<0><<<nb, 256, 0, st>>>(x, nullptr, nullptr, nullptr, eps, rows, C, part, (rows + nb - 1) / nb);
+    launch_bn_reduce<0>(nb, st, x, nullptr, nullptr, nullptr, eps, rows, C, part);
     bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
                                                             running_var, batch_mean, batch_var, coeff);
     const long long n = rows * C;
@@ -378,11 +495,13 @@ extern "C" int aether_bn_bwd(const float* x, const float* dy, const float* gamma
         return set_error(AE_BAD_ARG, "aether_bn_bwd: null pointer");
     if (rows <= 0 || C <= 0) return set_error(AE_BAD_ARG, "aether_bn_bwd: rows=%lld C=%d", (long long)rows, C);
     if (ws_bytes < aether_bn_workspace_bytes(rows, C)) return set_error(AE_BAD_ARG, "aether_bn_bwd: workspace too small");
+    if ((C & 3) == 0 && (!aligned16(x) || !aligned16(dy) || !aligned16(dx)))
+        return set_error(AE_BAD_ARG, "aether_bn_bwd: arrays must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int nb = bn_blocks(rows);
     float* part = static_cast<float*>(ws);
     float* coeff = part + (size_t)nb * 3 * C;
-    bn_reduce_kernel<1><<<nb, 256, 0, st>>>(x, dy, batch_mean, batch_var, eps, rows, C, part, (rows + nb - 1) / nb);
+    launch_bn_reduce<1>(nb, st, x, dy, batch_mean, batch_var, eps, rows, C, part);
     bn_finalize_bwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
                                                             dbeta, coeff);
     const long long n = rows * C;
@@ -395,17 +514,18 @@ namespace aether {
 // ====================================================================================== pooling
 // Forward: one thread per (output pixel, 4 channels).  The argmax code is the window-local index
 // i*fW + j of the FIRST maximum in row-major window order (ties keep the earlier cell).
-template <bool MAX>
+// I is the flat-index type: unsigned int whenever the element count fits (32-bit divisions are several times
+// cheaper than 64-bit ones and the index decode is most of the kernel's instructions), else long long.
+template <bool MAX, typename I>
 __global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                        uint8_t* __restrict__ arg, int S, int H, int W, int C, int fH,
                                                        int fW, int sH, int sW, int Ho, int Wo, int vec) {
     const int Cv = C / vec;
-    const long long total = 1LL * S * Ho * Wo * Cv;
+    const I total = (I)(1LL * S * Ho * Wo * Cv);
     const float inv = 1.f / (float)(fH * fW);
-    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-         idx += (long long)gridDim.x * blockDim.x) {
-        const int cv = (int)(idx % Cv);
-        long long pix = idx / Cv;
+    for (I idx = blockIdx.x * (I)blockDim.x + threadIdx.x; idx < total; idx += (I)gridDim.x * (I)blockDim.x) {
+        const int cv = (int)(idx % (I)Cv);
+        I pix = idx / (I)Cv;
         const int wo = (int)(pix % Wo);
         pix /= Wo;
         const int ho = (int)(pix % Ho);
@@ -455,17 +575,16 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__
 
 // Backward in gather form: each input cell sums the dy of every window that selected it (max) or
 // that covers it (average).  No atomics; cells outside every window get zero.
-template <bool MAX, int VEC>
+template <bool MAX, int VEC, typename I>
 __global__ void __launch_bounds__(256) pool_bwd_kernel(const float* __restrict__ dy, const uint8_t* __restrict__ arg,
                                                        float* __restrict__ dx, int S, int H, int W, int C, int fH,
                                                        int fW, int sH, int sW, int Ho, int Wo) {
     const int Cv = C / VEC;
-    const long long total = 1LL * S * H * W * Cv;
+    const I total = (I)(1LL * S * H * W * Cv);
     const float inv = 1.f / (float)(fH * fW);
-    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-         idx += (long long)gridDim.x * blockDim.x) {
-        const int cv = (int)(idx % Cv);
-        long long pix = idx / Cv;
+    for (I idx = blockIdx.x * (I)blockDim.x + threadIdx.x; idx < total; idx += (I)gridDim.x * (I)blockDim.x) {
+        const int cv = (int)(idx % (I)Cv);
+        I pix = idx / (I)Cv;
         const int w = (int)(pix % W);
         pix /= W;
         const int h = (int)(pix % H);
@@ -502,7 +621,7 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const float* __restrict__
                 }
             }
         }
-        if (VEC == 4) *reinterpret_cast<float4*>(dx + idx * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        if (VEC == 4) *reinterpret_cast<float4*>(dx + (size_t)idx * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
         else dx[idx] = acc[0];
     }
 }
@@ -694,10 +813,15 @@ extern "C" int aether_pool_fwd(const float* x, float* y, uint8_t* argmax, int S,
     const int vec = ((C & 3) == 0 && aligned16(x) && aligned16(y) && (!argmax || (reinterpret_cast<uintptr_t>(argmax) & 3) == 0)) ? 4 : 1;
     const long long total = 1LL * S * Ho * Wo * (C / vec);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (kind == AETHER_POOL_MAX)
-        pool_fwd_kernel<true><<<blocks_for(total, 256, 16), 256, 0, st>>>(x, y, argmax, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
-    else
-        pool_fwd_kernel<false><<<blocks_for(total, 256, 16), 256, 0, st>>>(x, y, nullptr, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
+    const int nb = blocks_for(total, 256, 16);
+    const bool small = total < (1LL << 31);
+    if (kind == AETHER_POOL_MAX) {
+        if (small) pool_fwd_kernel<true, unsigned><<<nb, 256, 0, st>>>(x, y, argmax, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
+        else pool_fwd_kernel<true, long long><<<nb, 256, 0, st>>>(x, y, argmax, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
+    } else {
+        if (small) pool_fwd_kernel<false, unsigned><<<nb, 256, 0, st>>>(x, y, nullptr, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
+        else pool_fwd_kernel<false, long long><<<nb, 256, 0, st>>>(x, y, nullptr, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
+    }
     count_launch();
     return check_launch("aether_pool_fwd");
 }
@@ -713,13 +837,21 @@ extern "C" int aether_pool_bwd(const float* dy, const uint8_t* argmax, float* dx
     const long long total = 1LL * S * H * W * (vec ? C / 4 : C);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int nb = blocks_for(total, 256, 16);
+#define AETHER_POOL_BWD(MAXK, V, I, ARG) \
+    pool_bwd_kernel<MAXK, V, I><<<nb, 256, 0, st>>>(dy, ARG, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo)
+    const bool small = total < (1LL << 31);
     if (kind == AETHER_POOL_MAX) {
-        if (vec) pool_bwd_kernel<true, 4><<<nb, 256, 0, st>>>(dy, argmax, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
-        else pool_bwd_kernel<true, 1><<<nb, 256, 0, st>>>(dy, argmax, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
+        if (vec && small) AETHER_POOL_BWD(true, 4, unsigned, argmax);
+        else if (vec) AETHER_POOL_BWD(true, 4, long long, argmax);
+        else if (small) AETHER_POOL_BWD(true, 1, unsigned, argmax);
+        else AETHER_POOL_BWD(true, 1, long long, argmax);
     } else {
-        if (vec) pool_bwd_kernel<false, 4><<<nb, 256, 0, st>>>(dy, nullptr, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
-        else pool_bwd_kernel<false, 1><<<nb, 256, 0, st>>>(dy, nullptr, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo);
+        if (vec && small) AETHER_POOL_BWD(false, 4, unsigned, nullptr);
+        else if (vec) AETHER_POOL_BWD(false, 4, long long, nullptr);
+        else if (small) AETHER_POOL_BWD(false, 1, unsigned, nullptr);
+        else AETHER_POOL_BWD(false, 1, long long, nullptr);
     }
+#undef AETHER_POOL_BWD
     count_launch();
     return check_launch("aether_pool_bwd");
 }

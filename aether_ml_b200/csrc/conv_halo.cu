@@ -58,7 +58,12 @@ __device__ long long g_halo_timers[16];
 #define TSTAMP(accv) do { } while (0)
 #endif
 
-static constexpr int HALO_EPI_WARPS = 8;
+#ifndef AETHER_HALO_EPI_WARPS
+#define AETHER_HALO_EPI_WARPS 8
+#endif
+static constexpr int HALO_EPI_WARPS = AETHER_HALO_EPI_WARPS;      // 4 lane quadrants x HALO_EPI_PARTS column parts
+static constexpr int HALO_EPI_PARTS = HALO_EPI_WARPS / 4;
+static constexpr int HALO_EPI_UB = 8 / HALO_EPI_PARTS;            // 16-column TMEM loads in flight per batch
 static constexpr int HALO_THREADS = 64 + 32 * HALO_EPI_WARPS;
 static constexpr int HALO_TAIL = 2048;          // barriers, TMEM pointer, bias
 
@@ -245,9 +250,9 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
         // the registers go straight to global memory as full sectors (no shared-memory staging).
         const int ew = warp - 2;
         const int q = warp & 3;
-        const int half = ew >> 2;
-        const int ncols = NT >> 1;                 // columns this warp owns (multiple of 16)
-        const int col_begin = half * ncols;
+        const int part = ew >> 2;
+        const int ncols = NT / HALO_EPI_PARTS;     // columns this warp owns (multiple of 16)
+        const int col_begin = part * ncols;
         const int trow = lane >> 2, tcol4 = (lane & 3) * 4;   // after the quad exchange a lane owns 4 consecutive columns
         const bool lo2 = (lane & 2) == 0, odd = (lane & 1) != 0;
         const bool all_cols = (p.n_out == NT);     // no padded output channels: no per-column bound checks
@@ -283,24 +288,24 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
             TSTAMP(tm_w);                                              // wait for a finished accumulator
             const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NT + col_begin;
 #pragma unroll 1
-            for (int cb = 0; cb < ncols; cb += 64) {            // batches of up to 64 columns: 8 loads in flight
-                uint32_t v[2][4][8];
+            for (int cb = 0; cb < ncols; cb += 16 * HALO_EPI_UB) {   // batches of HALO_EPI_UB x 16 columns
+                uint32_t v[2][HALO_EPI_UB][8];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < HALO_EPI_UB; ++u) {
                     if (cb + u * 16 < ncols) {
                         tmem_ld_16x256b_x2(taddr0 + cb + u * 16, v[0][u]);
                         tmem_ld_16x256b_x2(taddr0 + (16u << 16) + cb + u * 16, v[1][u]);
                     }
                 }
                 tmem_ld_wait();
-                if (cb + 64 >= ncols) {                          // accumulator fully read by this warp
+                if (cb + 16 * HALO_EPI_UB >= ncols) {            // accumulator fully read by this warp
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(buf));
                 }
                 TSTAMP(tm_l);                                          // TMEM -> registers
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < HALO_EPI_UB; ++u) {
                     if (cb + u * 16 < ncols) {
 #pragma unroll
                         // A quad holds 16 columns of a row as 2+2 columns per lane (groups 0 and 1).  Two
@@ -326,7 +331,7 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                             o.y = __uint_as_float(odd ? q1 : x1) + b4.y;
                             o.z = __uint_as_float(odd ? y0 : q0) + b4.z;
                             o.w = __uint_as_float(odd ? y1 : q1) + b4.w;
-                            if (cols_ok && rowp[j] != nullptr) *reinterpret_cast<float4*>(rowp[j] + cc) = o;
+                            if (cols_ok && rowp[j] != nullptr) __stcs(reinterpret_cast<float4*>(rowp[j] + cc), o);
                         }
                     }
                 }
@@ -355,7 +360,7 @@ int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int 
     const int elt = tf32 ? 4 : 2;
     const int KC = 128 / elt;
     const int Wp = out_W + fW - 1;
-    if (n_padded > 256 || n_padded % 32 || out_C % 4) return AE_OK;
+    if (n_padded > 256 || n_padded % (16 * HALO_EPI_PARTS) || out_C % 4) return AE_OK;
     if (Wp > 256 || out_W > 128 || out_W < 12) return AE_OK;
     int BH = (128 - out_W) / Wp + 1;
     if (BH > out_H) BH = out_H;

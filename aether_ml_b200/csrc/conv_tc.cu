@@ -498,8 +498,9 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_conv_kernel(const __grid_con
 }
 
 // dW[tap][c][d] = sum over splits of part[split][tap*cblocks + c/UC][c%UC][d]
+// Taps from tap_split on have splits2 partials instead of splits (kernels whose CTA classes differ in number).
 __global__ void dw_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int splits, int U, int UC,
-                                 int ldn, int cblocks, int taps, int Cin, int Cout) {
+                                 int ldn, int cblocks, int taps, int Cin, int Cout, int tap_split, int splits2) {
     const long long total = 1LL * taps * Cin * Cout;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -511,7 +512,8 @@ __global__ void dw_reduce_kernel(const float* __restrict__ part, float* __restri
         const float* src = part + ((size_t)u * UC + (c % UC)) * (size_t)ldn + d;
         const size_t split_stride = (size_t)U * UC * ldn;
         float acc = 0.f;
-        for (int s = 0; s < splits; ++s) acc += src[s * split_stride];
+        const int ns = tap < tap_split ? splits : splits2;
+        for (int s = 0; s < ns; ++s) acc += src[s * split_stride];
         dw[idx] = acc;
     }
 }
@@ -543,8 +545,10 @@ __global__ void __launch_bounds__(256) cast_bf16_kernel(const float* __restrict_
                 float v[8];
                 const float* s = src + r * C + c0;
                 if (vec && c0 + 8 <= C) {
-                    const float4 a = *reinterpret_cast<const float4*>(s);
-                    const float4 b = *reinterpret_cast<const float4*>(s + 4);
+                    // streaming (evict-first) reads: the fp32 source is not needed again soon, the bf16 copy
+                    // written below is, so it should be what stays in L2
+                    const float4 a = __ldcs(reinterpret_cast<const float4*>(s));
+                    const float4 b = __ldcs(reinterpret_cast<const float4*>(s + 4));
                     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
                     v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
                 } else {
@@ -717,7 +721,12 @@ static TcPlan make_plan(const AetherConvDesc& d) {
     pl.off_dysh = take(pl.tf32 ? 0 : (size_t)out_rows * pl.Cout_p * 2);
     pl.off_wf = take((size_t)pl.taps * pl.Cout_p * pl.Cin_p * pl.elt);
     pl.off_wd = take(pl.tf32 ? 0 : (size_t)pl.taps * pl.Cin_p * pl.Cout_p * pl.elt);
-    pl.off_part = take((size_t)pl.dw_splits * pl.dw_U * UC * pl.Cout_p * 4);
+    int part_splits = pl.dw_splits;
+    if (!pl.tf32) {
+        const int rs = rows_dw_max_splits(pl.Cin_p, pl.Cout_p, pl.Ho, pl.Wo, d.S, d.fH, d.fW);
+        if (rs > part_splits) part_splits = rs;
+    }
+    pl.off_part = take((size_t)part_splits * pl.dw_U * UC * pl.Cout_p * 4);
     pl.off_dbpart = take((size_t)pl.db_blocks * d.Cout * 4);
     pl.total = off;
     return pl;
@@ -937,14 +946,26 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
     if (dw && !pl.tf32) {   // wide images: halo-reuse kernel (every tap re-reads one shared-memory window)
         int splits = 0;
         float* part = reinterpret_cast<float*>(wsb + pl.off_part);
-        if ((rc = run_halo_dw(x_op, pl.Cin_p, d.H, d.W, d.S, dy_op, pl.Cout_p, pl.Ho, pl.Wo, d.fH, d.fW, d.padH, d.padW, part,
-                              pl.dw_splits, &splits, st, &dw_done)))
+        int sa = 0, sb = 0, tap_split = 0;
+        if ((rc = run_rows_dw(x_op, pl.Cin_p, d.H, d.W, d.S, dy_op, pl.Cout_p, pl.Ho, pl.Wo, d.fH, d.fW, d.padH, d.padW, part,
+                              &sa, &sb, &tap_split, st, &dw_done)))
             return rc;
         if (dw_done) {
-            dw_reduce_kernel<<<2 * num_sms(), 256, 0, st>>>(part, dw, splits, pl.dw_U, pl.KC, pl.Cout_p, pl.dw_cblocks,
-                                                            pl.taps, d.Cin, d.Cout);
+            dw_reduce_kernel<<<2 * num_sms(), 256, 0, st>>>(part, dw, sa, pl.dw_U, pl.KC, pl.Cout_p, pl.dw_cblocks, pl.taps,
+                                                            d.Cin, d.Cout, tap_split, sb);
             count_launch();
             if ((rc = check_launch("dw_reduce_kernel"))) return rc;
+        }
+        if (!dw_done) {
+            if ((rc = run_halo_dw(x_op, pl.Cin_p, d.H, d.W, d.S, dy_op, pl.Cout_p, pl.Ho, pl.Wo, d.fH, d.fW, d.padH, d.padW,
+                                  part, pl.dw_splits, &splits, st, &dw_done)))
+                return rc;
+            if (dw_done) {
+                dw_reduce_kernel<<<2 * num_sms(), 256, 0, st>>>(part, dw, splits, pl.dw_U, pl.KC, pl.Cout_p, pl.dw_cblocks,
+                                                                pl.taps, d.Cin, d.Cout, pl.taps, splits);
+                count_launch();
+                if ((rc = check_launch("dw_reduce_kernel"))) return rc;
+            }
         }
     }
     if (dw && !dw_done) {
@@ -971,7 +992,7 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
         else rc = (pl.dw_nb == 2) ? launch_dw<false, 2>(p, pl.dw_splits, gy, st) : launch_dw<false, 1>(p, pl.dw_splits, gy, st);
         if (rc) return rc;
         dw_reduce_kernel<<<2 * num_sms(), 256, 0, st>>>(p.part, dw, pl.dw_splits, pl.dw_U, pl.KC, pl.Cout_p,
-                                                        pl.dw_cblocks, pl.taps, d.Cin, d.Cout);
+                                                        pl.dw_cblocks, pl.taps, d.Cin, d.Cout, pl.taps, pl.dw_splits);
         count_launch();
         if ((rc = check_launch("dw_reduce_kernel"))) return rc;
     }

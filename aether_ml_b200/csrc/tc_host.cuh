@@ -22,4 +22,10 @@ int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int 
 int run_halo_dw(const void* x_sh, int Cin_p, int H, int W, int S, const void* dy_sh, int Cout_p, int Ho, int Wo, int fH,
                 int fW, int padH, int padW, float* part, int max_splits, int* splits_out, cudaStream_t st, bool* used);
 
+// conv_dw_rows.cu: dW with dy as the M operand and the taps of a filter row as N (3-row filters, bf16).
+int rows_dw_max_splits(int Cin_p, int Cout_p, int Ho, int Wo, int S, int fH, int fW);
+int run_rows_dw(const void* x_sh, int Cin_p, int H, int W, int S, const void* dy_sh, int Cout_p, int Ho, int Wo, int fH,
+                int fW, int padH, int padW, float* part, int* splits_a, int* splits_b, int* tap_split, cudaStream_t st,
+                bool* used);
+
 }  // namespace aether

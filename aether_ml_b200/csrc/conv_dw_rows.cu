@@ -60,10 +60,18 @@ __global__ void __launch_bounds__(DWR_THREADS, 1) dw_rows_kernel(const __grid_co
     const int lane = threadIdx.x & 31;
 
     // Rows that no TMA box writes (the tails of the regions) are read by the MMAs and must be zero.
+    // Only those tails are cleared (a few KB), not the whole 220 KB of stages.
     {
-        uint4* z = reinterpret_cast<uint4*>(gen_base);
-        const int n16 = S * p.stage_bytes / 16;
-        for (int i = threadIdx.x; i < n16; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
+        const int dy_tail0 = p.dy_box_rows * 128, x_tail0 = 2 * p.dyr_bytes + p.x_box_rows * 128;
+        for (int s = 0; s < S; ++s) {
+            uint8_t* st = gen_base + (size_t)s * p.stage_bytes;
+            for (int o = dy_tail0 + threadIdx.x * 16; o < p.dyr_bytes; o += blockDim.x * 16) {
+                *reinterpret_cast<uint4*>(st + o) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(st + p.dyr_bytes + o) = make_uint4(0, 0, 0, 0);
+            }
+            for (int o = x_tail0 + threadIdx.x * 16; o < p.stage_bytes; o += blockDim.x * 16)
+                *reinterpret_cast<uint4*>(st + o) = make_uint4(0, 0, 0, 0);
+        }
         fence_proxy_async_smem();
     }
     if (threadIdx.x == 0) {

@@ -499,23 +499,77 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_conv_kernel(const __grid_con
 
 // dW[tap][c][d] = sum over splits of part[split][tap*cblocks + c/UC][c%UC][d]
 // Taps from tap_split on have splits2 partials instead of splits (kernels whose CTA classes differ in number).
-__global__ void dw_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int splits, int U, int UC,
-                                 int ldn, int cblocks, int taps, int Cin, int Cout, int tap_split, int splits2) {
+// A block of 256 threads handles 32 consecutive outputs with 8 lanes each: lane l adds splits l, l+8, ... and the
+// lanes are combined in fixed order through shared memory (bit-reproducible; many loads in flight per output).
+__global__ void __launch_bounds__(256) dw_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int splits,
+                                                        int U, int UC, int ldn, int cblocks, int taps, int Cin, int Cout,
+                                                        int tap_split, int splits2) {
+    __shared__ float red[8][32];
+    __shared__ float4 red4[8][32];
+    const int el = threadIdx.x & 31, ln = threadIdx.x >> 5;
     const long long total = 1LL * taps * Cin * Cout;
-    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-         idx += (long long)gridDim.x * blockDim.x) {
-        const int d = (int)(idx % Cout);
-        const long long tc = idx / Cout;
-        const int c = (int)(tc % Cin);
-        const int tap = (int)(tc / Cin);
-        const int u = tap * cblocks + c / UC;
-        const float* src = part + ((size_t)u * UC + (c % UC)) * (size_t)ldn + d;
-        const size_t split_stride = (size_t)U * UC * ldn;
-        float acc = 0.f;
-        const int ns = tap < tap_split ? splits : splits2;
-        for (int s = 0; s < ns; ++s) acc += src[s * split_stride];
-        dw[idx] = acc;
+    const size_t split_stride = (size_t)U * UC * ldn;
+    if ((Cout & 3) == 0 && (ldn & 3) == 0) {           // four consecutive output channels per thread
+        const int Cq = Cout >> 2;
+        const long long total4 = total >> 2;
+        for (long long base = blockIdx.x * 32LL; base < total4; base += gridDim.x * 32LL) {
+            const long long i4 = base + el;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i4 < total4) {
+                const int d = (int)(i4 % Cq) * 4;
+                const long long tc = i4 / Cq;
+                const int c = (int)(tc % Cin);
+                const int tap = (int)(tc / Cin);
+                const int u = tap * cblocks + c / UC;
+                const float* src = part + ((size_t)u * UC + (c % UC)) * (size_t)ldn + d;
+                const int ns = tap < tap_split ? splits : splits2;
+#pragma unroll 4
+                for (int s = ln; s < ns; s += 8) {
+                    const float4 v = *reinterpret_cast<const float4*>(src + s * split_stride);
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+            }
+            red4[ln][el] = acc;
+            __syncthreads();
+            if (ln == 0 && i4 < total4) {
+                float4 t = red4[0][el];
+#pragma unroll
+                for (int l = 1; l < 8; ++l) { const float4 v = red4[l][el]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+                *reinterpret_cast<float4*>(dw + i4 * 4) = t;
+            }
+            __syncthreads();
+        }
+        return;
     }
+    for (long long base = blockIdx.x * 32LL; base < total; base += gridDim.x * 32LL) {
+        const long long idx = base + el;
+        float acc = 0.f;
+        if (idx < total) {
+            const int d = (int)(idx % Cout);
+            const long long tc = idx / Cout;
+            const int c = (int)(tc % Cin);
+            const int tap = (int)(tc / Cin);
+            const int u = tap * cblocks + c / UC;
+            const float* src = part + ((size_t)u * UC + (c % UC)) * (size_t)ldn + d;
+            const int ns = tap < tap_split ? splits : splits2;
+            for (int s = ln; s < ns; s += 8) acc += src[s * split_stride];
+        }
+        red[ln][el] = acc;
+        __syncthreads();
+        if (ln == 0 && idx < total) {
+            float t = 0.f;
+#pragma unroll
+            for (int l = 0; l < 8; ++l) t += red[l][el];
+            dw[idx] = t;
+        }
+        __syncthreads();
+    }
+}
+
+static int dw_reduce_grid(int taps, int Cin, int Cout) {
+    const long long groups = (1LL * taps * Cin * Cout + 31) / 32;
+    const long long cap = 8LL * 148;
+    return (int)(groups < cap ? (groups < 1 ? 1 : groups) : cap);
 }
 
 // ====================================================================================== shadow copies
@@ -613,18 +667,19 @@ __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ s
 // out[c] = sum over blocks of part[block][C]: 32 columns x 8 row lanes per CTA, lanes combined in fixed order.
 __global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ part, int nblocks, int C,
                                                             float* __restrict__ out) {
-    __shared__ float red[8][32];
-    const int cl = threadIdx.x & 31, lane = threadIdx.x >> 5;
-    const int c = blockIdx.x * 32 + cl;
+    // 8 columns x 32 lanes per CTA: short serial chains, lanes combined in fixed order
+    __shared__ float red[32][8];
+    const int cl = threadIdx.x & 7, lane = threadIdx.x >> 3;
+    const int c = blockIdx.x * 8 + cl;
     float s = 0.f;
     if (c < C)
-        for (int b = lane; b < nblocks; b += 8) s += part[(size_t)b * C + c];
+        for (int b = lane; b < nblocks; b += 32) s += part[(size_t)b * C + c];
     red[lane][cl] = s;
     __syncthreads();
     if (lane == 0 && c < C) {
         float t = 0.f;
 #pragma unroll
-        for (int l = 0; l < 8; ++l) t += red[l][cl];
+        for (int l = 0; l < 32; ++l) t += red[l][cl];
         out[c] = t;
     }
 }
@@ -918,7 +973,7 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
         dy_op = dysh;
     }
     if (db) {
-        colsum_finish_kernel<<<ceil_div(d.Cout, 32), 256, 0, st>>>(dbpart, pl.db_blocks, d.Cout, db);
+        colsum_finish_kernel<<<ceil_div(d.Cout, 8), 256, 0, st>>>(dbpart, pl.db_blocks, d.Cout, db);
         count_launch();
         if ((rc = check_launch("colsum_finish_kernel"))) return rc;
     }
@@ -951,7 +1006,7 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
                               &sa, &sb, &tap_split, st, &dw_done)))
             return rc;
         if (dw_done) {
-            dw_reduce_kernel<<<2 * num_sms(), 256, 0, st>>>(part, dw, sa, pl.dw_U, pl.KC, pl.Cout_p, pl.dw_cblocks, pl.taps,
+            dw_reduce_kernel<<<dw_reduce_grid(pl.taps, d.Cin, d.Cout), 256, 0, st>>>(part, dw, sa, pl.dw_U, pl.KC, pl.Cout_p, pl.dw_cblocks, pl.taps,
                                                             d.Cin, d.Cout, tap_split, sb);
             count_launch();
             if ((rc = check_launch("dw_reduce_kernel"))) return rc;
@@ -961,7 +1016,7 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
                                   part, pl.dw_splits, &splits, st, &dw_done)))
                 return rc;
             if (dw_done) {
-                dw_reduce_kernel<<<2 * num_sms(), 256, 0, st>>>(part, dw, splits, pl.dw_U, pl.KC, pl.Cout_p, pl.dw_cblocks,
+                dw_reduce_kernel<<<dw_reduce_grid(pl.taps, d.Cin, d.Cout), 256, 0, st>>>(part, dw, splits, pl.dw_U, pl.KC, pl.Cout_p, pl.dw_cblocks,
                                                                 pl.taps, d.Cin, d.Cout, pl.taps, splits);
                 count_launch();
                 if ((rc = check_launch("dw_reduce_kernel"))) return rc;
@@ -991,7 +1046,7 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
         if (pl.tf32) rc = (pl.dw_nb == 2) ? launch_dw<true, 2>(p, pl.dw_splits, gy, st) : launch_dw<true, 1>(p, pl.dw_splits, gy, st);
         else rc = (pl.dw_nb == 2) ? launch_dw<false, 2>(p, pl.dw_splits, gy, st) : launch_dw<false, 1>(p, pl.dw_splits, gy, st);
         if (rc) return rc;
-        dw_reduce_kernel<<<2 * num_sms(), 256, 0, st>>>(p.part, dw, pl.dw_splits, pl.dw_U, pl.KC, pl.Cout_p,
+        dw_reduce_kernel<<<dw_reduce_grid(pl.taps, d.Cin, d.Cout), 256, 0, st>>>(p.part, dw, pl.dw_splits, pl.dw_U, pl.KC, pl.Cout_p,
                                                         pl.dw_cblocks, pl.taps, d.Cin, d.Cout, pl.taps, pl.dw_splits);
         count_launch();
         if ((rc = check_launch("dw_reduce_kernel"))) return rc;

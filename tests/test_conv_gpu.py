@@ -91,6 +91,32 @@ def test_tensor_core_shapes(env, shape, mode):
     assert O.rel_l2(dw, dwo) <= tol and O.rel_l2(db, dbo) <= 1e-5
 
 
+@pytest.mark.parametrize("shape", [(4, 20, 24, 64, 128, (3, 4), "same"), (3, 16, 30, 64, 128, (3, 2), "valid"),
+                                   (2, 14, 40, 128, 256, (3, 3), "same"), (5, 13, 19, 64, 128, (3, 3), "valid"),
+                                   (2, 15, 15, 64, 128, (5, 3), "same")])
+def test_filter_row_dw_shapes(env, shape):
+    """Three-row filters of width 2..4 on >= 12-pixel-wide images with 128-multiple output channels take the
+    dW kernel that stacks a filter row's taps along N (two CTA classes); rectangular filters, ragged strips,
+    several channel blocks.  The (5, 3) filter is a neighbour that must fall back to the other dW kernels."""
+    S, H, W, Cin, Cout, f, pad = shape
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((S, H, W, Cin)).astype(np.float32)
+    w = (rng.standard_normal((f[0], f[1], Cin, Cout)) * np.sqrt(2.0 / (f[0] * f[1] * Cin))).astype(np.float32)
+    b = (rng.standard_normal(Cout) * 0.1).astype(np.float32)
+    Ho, Wo = O.conv_out_hw(H, W, f, (1, 1), pad)
+    dy = rng.standard_normal((S, Ho, Wo, Cout)).astype(np.float32)
+    y, dx, dw, db = run_layer(env, "bf16", x, w, b, dy, f, (1, 1), pad)
+    yo = O.conv_forward_blas(x, w, b, (1, 1), pad, dtype=np.float64)
+    dxo, dwo, dbo = O.conv_backward_blas(x, w, dy, (1, 1), pad, dtype=np.float64)
+    tol = TOL["bf16"]
+    assert O.rel_l2(y, yo) <= tol and O.rel_l2(dx, dxo) <= tol
+    assert O.rel_l2(dw, dwo) <= tol and O.rel_l2(db, dbo) <= 1e-5
+    # every tap's gradient on its own (a tap dropped or doubled by a kernel barely moves the global norm)
+    for i in range(f[0]):
+        for j in range(f[1]):
+            assert O.rel_l2(dw[i, j], dwo[i, j]) <= 2 * tol, (i, j)
+
+
 @pytest.mark.parametrize("shape", [(3, 9, 9, 3, 8, 3, (2, 2), "valid"), (2, 12, 10, 5, 7, 3, (1, 1), "same"),
                                    (4, 28, 28, 1, 32, 3, (1, 1), "same"), (2, 11, 11, 4, 6, 5, (2, 1), "same"),
                                    # first-layer kernels (1..4 input channels, power-of-two filter count 16..256)

@@ -30,6 +30,10 @@ sys.path.insert(0, ROOT)
 SHAPE = dict(S=256, H=56, W=56, Cin=64, Cout=128, f=3)
 WORKLOAD = "conv_fwd_bwd S=256 NHWC 56x56 Cin=64 Cout=128 3x3 stride1 same (largest shape of the isolated sweep)"
 CPU_SAMPLE_IMAGES = 24       # images of the same shape per CPU-baseline sample
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the three GEMM kernels on this workload (bf16, batch 256),
+# from the one-pass ncu capture summarised in profiles/conv_fwd_bwd_56x56_64to128_dram_traffic.txt.  Part of each
+# kernel's output is still dirty in L2 when it ends, so the written bytes are below the algorithmic 411 / 205 MB.
+DRAM_TRAFFIC_S256 = {"igemm_fwd": 102975744 + 353941760, "igemm_dx": 205719808 + 155275776, "dw": 308393216 + 356096}
 REF_STEP_IMAGES = 2          # images per step of the --impl reference arm
 
 
@@ -284,7 +288,9 @@ def run_gpu(args):
                     "d2h_bytes_per_step": (y_out.numel() + dx_out.numel() + g_out.numel()) * 4},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": (achieved / peak) if achieved else None, "traffic": None,
+                         "frac": (achieved / peak) if achieved else None,
+                         "traffic": DRAM_TRAFFIC_S256.get(dom) if (S == 256 and args.mode == "bf16") else None,
+                         "traffic_unit": "bytes per launch (dram read + write, ncu, full-size workload)",
                          "peak_source": "%s (%s bf16 figure of MEASURED_PEAKS.json)" % (pk["source"], "sustained" if ms_total > 1500 else "burst"),
                          "launch_ms": dom_ms, "flops_per_launch": per_gemm},
             "kernels": {k: {"total_ms": v[0], "launches": v[1], "avg_ms": v[0] / max(v[1], 1),

@@ -161,9 +161,36 @@ extern "C" int aether_conv2d_fwd(const AetherConvDesc* d, const float* x, const 
         return set_error(AE_BAD_ARG, "aether_conv2d_fwd: arrays must be 16-byte aligned");
     if ((rc = pending_timeout("aether_conv2d_fwd"))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, ws, ws_bytes, st);
-    if (smallc_conv_eligible(*d) && (!b || aligned16(b))) return smallc_conv_fwd(*d, x, w, b, y, st);
+    if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, nullptr, ws, ws_bytes, st);
+    if (smallc_conv_eligible(*d) && (!b || aligned16(b))) return smallc_conv_fwd(*d, x, w, b, y, nullptr, st);
     return generic_conv_fwd(*d, x, w, b, y, st);
+}
+
+extern "C" int64_t aether_conv2d_bnstats_blocks(const AetherConvDesc* d) {
+    if (validate_desc(d, "aether_conv2d_bnstats_blocks")) return 0;
+    if (tc_conv_eligible(*d)) return tc_conv_stats_blocks(*d);
+    if (smallc_conv_eligible(*d)) return smallc_conv_stats_blocks(*d);
+    return 0;
+}
+
+extern "C" int aether_conv2d_fwd_bnstats(const AetherConvDesc* d, const float* x, const float* w, const float* b, float* y,
+                                         float* stats, size_t stats_bytes, void* ws, size_t ws_bytes, void* stream) {
+    int rc = validate_desc(d, "aether_conv2d_fwd_bnstats");
+    if (rc) return rc;
+    if (!x || !w || !y || !stats) return set_error(AE_BAD_ARG, "aether_conv2d_fwd_bnstats: null pointer");
+    if (!aligned16(x) || !aligned16(w) || !aligned16(y) || !aligned16(stats) || (b && !aligned16(b)) || (ws && !aligned16(ws)))
+        return set_error(AE_BAD_ARG, "aether_conv2d_fwd_bnstats: arrays must be 16-byte aligned");
+    const int64_t blocks = aether_conv2d_bnstats_blocks(d);
+    if (blocks <= 0)
+        return set_error(AE_UNSUPPORTED, "aether_conv2d_fwd_bnstats: the forward kernel of this shape does not emit statistics "
+                                         "(aether_conv2d_bnstats_blocks returned 0); use aether_conv2d_fwd");
+    if (stats_bytes < (size_t)blocks * 3 * d->Cout * sizeof(float))
+        return set_error(AE_BAD_ARG, "aether_conv2d_fwd_bnstats: statistics buffer too small: %zu < %zu", stats_bytes,
+                         (size_t)blocks * 3 * d->Cout * sizeof(float));
+    if ((rc = pending_timeout("aether_conv2d_fwd_bnstats"))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, stats, ws, ws_bytes, st);
+    return smallc_conv_fwd(*d, x, w, b, y, stats, st);
 }
 
 extern "C" int aether_conv2d_bwd(const AetherConvDesc* d, const float* x, const float* dy, const float* w, float* dx,

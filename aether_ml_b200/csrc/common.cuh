@@ -46,15 +46,19 @@ size_t generic_conv_workspace_bytes(const AetherConvDesc& d);
 // ---- conv_smallc.cu : fp32 first-layer convolution (1..4 input channels, fH*fW*Cin <= 64): forward, dW, dB
 bool smallc_conv_eligible(const AetherConvDesc& d);
 size_t smallc_conv_workspace_bytes(const AetherConvDesc& d);
-int smallc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, cudaStream_t st);
+int smallc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, float* stats,
+                    cudaStream_t st);
+long long smallc_conv_stats_blocks(const AetherConvDesc& d);
 int smallc_conv_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy, float* dw, float* db, void* ws,
                            size_t ws_bytes, cudaStream_t st);
 
 // ---- conv_tc.cu : tcgen05 implicit-GEMM convolution (stride 1)
 bool tc_conv_eligible(const AetherConvDesc& d);
 size_t tc_conv_workspace_bytes(const AetherConvDesc& d);
-int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, void* ws,
+// `stats` (nullable): per-block (count, mean, M2) of every output channel, tc_conv_stats_blocks(d) blocks of [3][Cout]
+int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, float* stats, void* ws,
                 size_t ws_bytes, cudaStream_t st);
+long long tc_conv_stats_blocks(const AetherConvDesc& d);
 int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const float* w, float* dx, float* dw,
                 float* db, void* ws, size_t ws_bytes, int x_shadow_valid, cudaStream_t st);
 

@@ -36,6 +36,8 @@ struct HaloParams {
     CUtensorMap tm_w;    // filter matrix (K, taps*rows_per_tap), box (128 B of K, NT)
     float* out;          // (N, Hout, Wout, n_out) fp32
     const float* bias;   // nullable
+    float* stats;        // nullable: per CTA and 32-row quarter (count, mean, M2) of every output channel,
+                         // [cta][4][3][n_out] -- the partials Batch_Norm's statistics are merged from
     int* status;
     int n_out;           // real output channels
     int NT;              // accumulator columns (padded output channels), multiple of 32, <= 256
@@ -66,6 +68,7 @@ static constexpr int HALO_EPI_PARTS = HALO_EPI_WARPS / 4;
 static constexpr int HALO_EPI_UB = 8 / HALO_EPI_PARTS;            // 16-column TMEM loads in flight per batch
 static constexpr int HALO_THREADS = 64 + 32 * HALO_EPI_WARPS;
 static constexpr int HALO_TAIL = 2048;          // barriers, TMEM pointer, bias
+static constexpr int HALO_STATS_BYTES = HALO_EPI_WARPS * 2 * 128 * 4;   // per-warp running column sums (statistics)
 
 // MMA with descriptors given as (low word, shared high word); K-major 128-byte-swizzle operands.
 template <bool TF32>
@@ -86,7 +89,8 @@ __device__ __forceinline__ void umma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32
     }
 }
 
-template <bool TF32>
+// STATS: the epilogue also accumulates per-channel statistics of the output (p.stats must be set).
+template <bool TF32, bool STATS>
 __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid_constant__ HaloParams p) {
     constexpr int KC = TF32 ? 32 : 64;
     extern __shared__ uint8_t smem_raw[];
@@ -256,6 +260,14 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
         const int trow = lane >> 2, tcol4 = (lane & 3) * 4;   // after the quad exchange a lane owns 4 consecutive columns
         const bool lo2 = (lane & 2) == 0, odd = (lane & 1) != 0;
         const bool all_cols = (p.n_out == NT);     // no padded output channels: no per-column bound checks
+        constexpr bool do_stats = STATS;
+        // running per-column sums of this warp over all its tiles: [2][128] floats of warp-private shared memory
+        float* stat_w = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + HALO_TAIL) + ew * 256;
+        float st_rows = 0.f;                       // rows (pixels) summed so far, identical in every lane
+        if (do_stats) {
+            for (int i = lane; i < 256; i += 32) stat_w[i] = 0.f;
+            __syncwarp();
+        }
         // The four accumulator rows this thread holds map to fixed pixels of every strip: precompute their
         // offsets (in floats, relative to the strip's first pixel, including this thread's column offset).
         int row_off[4], row_hl[4];
@@ -290,6 +302,9 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
 #pragma unroll 1
             for (int cb = 0; cb < ncols; cb += 16 * HALO_EPI_UB) {   // batches of HALO_EPI_UB x 16 columns
                 uint32_t v[2][HALO_EPI_UB][8];
+                float4 st_s[HALO_EPI_UB], st_q[HALO_EPI_UB];         // per-column sum / sum of squares of this tile's rows
+#pragma unroll
+                for (int u = 0; u < HALO_EPI_UB; ++u) st_s[u] = st_q[u] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int u = 0; u < HALO_EPI_UB; ++u) {
                     if (cb + u * 16 < ncols) {
@@ -326,18 +341,85 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                             // step 2 (lane ^ 1): even lanes keep the lower pair of pieces, odd lanes the upper pair
                             const uint32_t t0 = odd ? x0 : y0, t1 = odd ? x1 : y1;
                             const uint32_t q0 = __shfl_xor_sync(0xffffffffu, t0, 1), q1 = __shfl_xor_sync(0xffffffffu, t1, 1);
-                            float4 o;
-                            o.x = __uint_as_float(odd ? q0 : x0) + b4.x;
-                            o.y = __uint_as_float(odd ? q1 : x1) + b4.y;
-                            o.z = __uint_as_float(odd ? y0 : q0) + b4.z;
-                            o.w = __uint_as_float(odd ? y1 : q1) + b4.w;
-                            if (cols_ok && rowp[j] != nullptr) __stcs(reinterpret_cast<float4*>(rowp[j] + cc), o);
+                            float4 a;                                                     // accumulator values (before the bias)
+                            a.x = __uint_as_float(odd ? q0 : x0);
+                            a.y = __uint_as_float(odd ? q1 : x1);
+                            a.z = __uint_as_float(odd ? y0 : q0);
+                            a.w = __uint_as_float(odd ? y1 : q1);
+                            const bool wr = cols_ok && rowp[j] != nullptr;
+                            if (wr)
+                                __stcs(reinterpret_cast<float4*>(rowp[j] + cc),
+                                       make_float4(a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w));
+                            if (do_stats) {                                  // branch-free: by-product rows count as zero
+                                a.x = wr ? a.x : 0.f; a.y = wr ? a.y : 0.f;  // selects, not products: a by-product may be NaN
+                                a.z = wr ? a.z : 0.f; a.w = wr ? a.w : 0.f;
+                                st_s[u].x += a.x; st_s[u].y += a.y; st_s[u].z += a.z; st_s[u].w += a.w;
+                                st_q[u].x = fmaf(a.x, a.x, st_q[u].x); st_q[u].y = fmaf(a.y, a.y, st_q[u].y);
+                                st_q[u].z = fmaf(a.z, a.z, st_q[u].z); st_q[u].w = fmaf(a.w, a.w, st_q[u].w);
+                            }
+                        }
+                    }
+                }
+                if (do_stats) {
+                    // Lanes with equal lane%4 hold the same 4 columns of 8 different row groups: add them up
+                    // (xor 4, 8, 16); lanes 0..3 then add the tile's sums to this warp's running sums in
+                    // shared memory.  The sums are taken about the bias (the channel's expected offset).
+                    if (cb == 0) {
+                        float nrows = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) nrows += (rowp[j] != nullptr) ? 1.f : 0.f;
+                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 4);
+                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 8);
+                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 16);
+                        st_rows += nrows;
+                    }
+#pragma unroll
+                    for (int m = 4; m <= 16; m <<= 1) {
+#pragma unroll
+                        for (int u = 0; u < HALO_EPI_UB; ++u) {
+                            st_s[u].x += __shfl_xor_sync(0xffffffffu, st_s[u].x, m); st_s[u].y += __shfl_xor_sync(0xffffffffu, st_s[u].y, m);
+                            st_s[u].z += __shfl_xor_sync(0xffffffffu, st_s[u].z, m); st_s[u].w += __shfl_xor_sync(0xffffffffu, st_s[u].w, m);
+                            st_q[u].x += __shfl_xor_sync(0xffffffffu, st_q[u].x, m); st_q[u].y += __shfl_xor_sync(0xffffffffu, st_q[u].y, m);
+                            st_q[u].z += __shfl_xor_sync(0xffffffffu, st_q[u].z, m); st_q[u].w += __shfl_xor_sync(0xffffffffu, st_q[u].w, m);
+                        }
+                    }
+                    if (lane < 4) {
+#pragma unroll
+                        for (int u = 0; u < HALO_EPI_UB; ++u) {
+                            const int cc = cb + u * 16;
+                            if (cc < ncols) {
+                                float4* ps = reinterpret_cast<float4*>(stat_w + cc + tcol4);
+                                float4* pq = reinterpret_cast<float4*>(stat_w + 128 + cc + tcol4);
+                                float4 s = *ps, qq = *pq;
+                                s.x += st_s[u].x; s.y += st_s[u].y; s.z += st_s[u].z; s.w += st_s[u].w;
+                                qq.x += st_q[u].x; qq.y += st_q[u].y; qq.z += st_q[u].z; qq.w += st_q[u].w;
+                                *ps = s;
+                                *pq = qq;
+                            }
                         }
                     }
                 }
             }
             if (++buf == NB) { buf = 0; aph ^= 1u; }
             TSTAMP(tm_s);                                              // bias + stores
+        }
+        if (do_stats && lane < 4) {
+            // (count, mean, M2) of this warp's rows over all tiles of the CTA: block blockIdx.x*4 + q of [3][n_out]
+            float* sp = p.stats + ((size_t)blockIdx.x * 4 + q) * 3 * (size_t)p.n_out;
+            const float inv_n = st_rows > 0.f ? 1.f / st_rows : 0.f;
+            for (int cc = 0; cc < ncols; cc += 16) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int col = col_begin + tcol4 + cc + k;
+                    if (col < p.n_out) {
+                        const float s = stat_w[cc + tcol4 + k], qq = stat_w[128 + cc + tcol4 + k];
+                        const float m = s * inv_n;
+                        sp[col] = st_rows;
+                        sp[p.n_out + col] = m + bias_s[col];
+                        sp[2 * p.n_out + col] = fmaxf(qq - s * m, 0.f);
+                    }
+                }
+            }
         }
 #ifdef AETHER_KERNEL_TIMERS
         if (tmr) { g_halo_timers[8] = tm_w; g_halo_timers[9] = tm_l; g_halo_timers[10] = tm_s; }
@@ -353,35 +435,64 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
 }
 
 // Decides whether the halo kernel takes this problem; if so launches it and sets *used.
+struct HaloGeom {
+    int Wp, BH, tiles_h, kchunks, w_bytes, region_rows, region_stride, stages, fixed;
+};
+static constexpr int HALO_SMEM_MAX = 232448;
+
+// Decides whether the halo kernel takes the problem and, if so, its tiling.
+static bool halo_geometry(bool tf32, int in_C, int S, int taps, int out_C, int out_H, int out_W, int n_padded, int fH,
+                          int fW, HaloGeom& g) {
+    const int KC = tf32 ? 32 : 64;
+    g.Wp = out_W + fW - 1;
+    if (n_padded > 256 || n_padded % (16 * HALO_EPI_PARTS) || out_C % 4) return false;
+    if (g.Wp > 256 || out_W > 128 || out_W < 12) return false;
+    g.BH = (128 - out_W) / g.Wp + 1;
+    if (g.BH > out_H) g.BH = out_H;
+    if (g.BH + fH - 1 > 256) return false;
+    g.tiles_h = ceil_div(out_H, g.BH);
+    if (1LL * g.tiles_h * S > 0x3fffffffLL) return false;
+    // useful fraction of the 128 accumulator rows, including the ragged last strip of each image
+    const double eff = (double)out_H * out_W / ((double)g.tiles_h * 128.0);
+    if (eff < 0.70) return false;
+    g.kchunks = ceil_div(in_C, KC);
+    g.w_bytes = taps * g.kchunks * n_padded * 128;
+    g.region_rows = (g.BH + fH - 1) * g.Wp;
+    g.region_stride = (int)align_up((size_t)g.region_rows * 128, 1024);
+    g.fixed = 1024 + (int)align_up(g.w_bytes, 1024) + HALO_TAIL + HALO_STATS_BYTES;
+    g.stages = (HALO_SMEM_MAX - g.fixed) / g.region_stride;
+    if (g.stages > 4) g.stages = 4;
+    if (g.stages < 2) return false;
+    // every tap reads 128 rows from its shifted start; the furthest read must stay inside the allocation
+    const int overhang_rows = (fH - 1) * g.Wp + (fW - 1) + 128 - g.region_rows;
+    // (what the last stage reads past its region -- barriers, bias, statistics -- only feeds by-product rows)
+    if (overhang_rows > 0 && overhang_rows * 128 > HALO_TAIL + HALO_STATS_BYTES + (g.region_stride - g.region_rows * 128))
+        return false;
+    return true;
+}
+
+// Number of (count, mean, M2) partial blocks the kernel writes per output channel when asked for statistics
+// (4 per tile), or 0 when the halo kernel does not take this problem.
+long long halo_igemm_stats_blocks(bool tf32, int in_C, int S, int taps, int out_C, int out_H, int out_W, int n_padded,
+                                  int fH, int fW) {
+    HaloGeom g;
+    if (!halo_geometry(tf32, in_C, S, taps, out_C, out_H, out_W, n_padded, fH, fW, g)) return 0;
+    const long long total = 1LL * g.tiles_h * S;
+    return 4LL * (total < num_sms() ? total : num_sms());       // one block per CTA and 32-row quarter
+}
+
 int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
                    int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, int n_padded, int fH, int fW,
-                   int padT, int padL, int flip, const float* bias, int prof_kind, cudaStream_t st, bool* used) {
+                   int padT, int padL, int flip, const float* bias, float* stats, int prof_kind, cudaStream_t st,
+                   bool* used) {
     *used = false;
     const int elt = tf32 ? 4 : 2;
     const int KC = 128 / elt;
-    const int Wp = out_W + fW - 1;
-    if (n_padded > 256 || n_padded % (16 * HALO_EPI_PARTS) || out_C % 4) return AE_OK;
-    if (Wp > 256 || out_W > 128 || out_W < 12) return AE_OK;
-    int BH = (128 - out_W) / Wp + 1;
-    if (BH > out_H) BH = out_H;
-    if (BH + fH - 1 > 256) return AE_OK;
-    const int tiles_h = ceil_div(out_H, BH);
-    if (1LL * tiles_h * S > 0x3fffffffLL) return AE_OK;
-    // useful fraction of the 128 accumulator rows, including the ragged last strip of each image
-    const double eff = (double)out_H * out_W / ((double)tiles_h * 128.0);
-    if (eff < 0.70) return AE_OK;
-    const int kchunks = ceil_div(in_C, KC);
-    const int w_bytes = taps * kchunks * n_padded * 128;
-    const int region_rows = (BH + fH - 1) * Wp;
-    const int region_stride = (int)align_up((size_t)region_rows * 128, 1024);
-    const int smem_max = 232448;
-    const int fixed = 1024 + (int)align_up(w_bytes, 1024) + HALO_TAIL;
-    int stages = (smem_max - fixed) / region_stride;
-    if (stages > 4) stages = 4;
-    if (stages < 2) return AE_OK;
-    // every tap reads 128 rows from its shifted start; the furthest read must stay inside the allocation
-    const int overhang_rows = (fH - 1) * Wp + (fW - 1) + 128 - region_rows;
-    if (overhang_rows > 0 && overhang_rows * 128 > HALO_TAIL + (region_stride - region_rows * 128)) return AE_OK;
+    HaloGeom g;
+    if (!halo_geometry(tf32, in_C, S, taps, out_C, out_H, out_W, n_padded, fH, fW, g)) return AE_OK;
+    const int Wp = g.Wp, BH = g.BH, tiles_h = g.tiles_h, kchunks = g.kchunks, w_bytes = g.w_bytes;
+    const int region_rows = g.region_rows, region_stride = g.region_stride, stages = g.stages, fixed = g.fixed;
+    const int smem_max = HALO_SMEM_MAX;
 
     HaloParams p;
     memset(&p, 0, sizeof(p));
@@ -391,6 +502,7 @@ int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int 
     if ((rc = make_map_2d(&p.tm_w, wmat, dt, elt, w_inner, 1LL * taps * rows_per_tap, KC, n_padded))) return rc;
     p.out = out;
     p.bias = bias;
+    p.stats = stats;
     p.status = device_status_word();
     p.n_out = out_C;
     p.NT = n_padded;
@@ -401,18 +513,21 @@ int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int 
     p.region_rows = region_rows; p.region_stride = region_stride; p.stages = stages; p.w_bytes = w_bytes;
     const int smem = fixed + stages * region_stride;
 
-    static bool configured[2] = {false, false};
-    if (!configured[tf32 ? 1 : 0]) {
-        cudaError_t e = tf32 ? cudaFuncSetAttribute(halo_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max)
-                             : cudaFuncSetAttribute(halo_conv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+    // four instantiations: operand type x (with / without the statistics epilogue)
+    using KernelFn = void (*)(const HaloParams);
+    static const KernelFn kernels[4] = {halo_conv_kernel<false, false>, halo_conv_kernel<true, false>,
+                                        halo_conv_kernel<false, true>, halo_conv_kernel<true, true>};
+    static bool configured[4] = {false, false, false, false};
+    const int ki = (tf32 ? 1 : 0) + (stats ? 2 : 0);
+    if (!configured[ki]) {
+        cudaError_t e = cudaFuncSetAttribute(kernels[ki], cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
         if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(halo, %d): %s", smem_max, cudaGetErrorString(e));
-        configured[tf32 ? 1 : 0] = true;
+        configured[ki] = true;
     }
     const long long total = 1LL * tiles_h * S;
     const int grid = (int)(total < num_sms() ? total : num_sms());
     prof_begin(prof_kind, st);
-    if (tf32) halo_conv_kernel<true><<<grid, HALO_THREADS, smem, st>>>(p);
-    else halo_conv_kernel<false><<<grid, HALO_THREADS, smem, st>>>(p);
+    kernels[ki]<<<grid, HALO_THREADS, smem, st>>>(p);
     prof_end(prof_kind, st);
     count_launch();
     *used = true;

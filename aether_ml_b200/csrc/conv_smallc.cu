@@ -78,9 +78,15 @@ __device__ __forceinline__ void stage_colT(const SmallcGeom& g, SmallcTables& t,
 template <int R>
 __global__ void __launch_bounds__(SC_THREADS) smallc_fwd_kernel(const SmallcGeom g, const float* __restrict__ x,
                                                                 const float* __restrict__ w, const float* __restrict__ b,
-                                                                float* __restrict__ y, long long ntiles) {
+                                                                float* __restrict__ y, float* __restrict__ stats,
+                                                                long long ntiles) {
     extern __shared__ float sm[];
     __shared__ SmallcTables tab;
+    __shared__ __align__(16) float red_s[SC_THREADS * 4];    // statistics, used once at the end of the kernel
+    __shared__ __align__(16) float red_q[SC_THREADS * 4];
+    __shared__ float red_n[SC_THREADS];
+    float4 st_s = make_float4(0.f, 0.f, 0.f, 0.f), st_q = st_s;   // sum / sum of squares of (y - bias), this thread's pixels
+    float st_n = 0.f;
     float* wsm = sm;                          // [K][Cout]
     float* colT = sm + g.K * g.Cout;          // [K][TP]
     for (int e = threadIdx.x; e < g.K * g.Cout; e += SC_THREADS) wsm[e] = w[e];
@@ -112,9 +118,42 @@ __global__ void __launch_bounds__(SC_THREADS) smallc_fwd_kernel(const SmallcGeom
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const long long p = p0 + (r * g.lanes + pl) * 4 + q;
-                if (p < g.P) __stcs(reinterpret_cast<float4*>(y + (size_t)p * g.Cout + cg * 4), acc[r][q]);
+                if (p < g.P) {
+                    __stcs(reinterpret_cast<float4*>(y + (size_t)p * g.Cout + cg * 4), acc[r][q]);
+                    if (stats) {
+                        const float dx = acc[r][q].x - bias.x, dy = acc[r][q].y - bias.y;
+                        const float dz = acc[r][q].z - bias.z, dw = acc[r][q].w - bias.w;
+                        st_s.x += dx; st_s.y += dy; st_s.z += dz; st_s.w += dw;
+                        st_q.x = fmaf(dx, dx, st_q.x); st_q.y = fmaf(dy, dy, st_q.y);
+                        st_q.z = fmaf(dz, dz, st_q.z); st_q.w = fmaf(dw, dw, st_q.w);
+                        st_n += 1.f;
+                    }
+                }
             }
         __syncthreads();                      // colT is rewritten by the next tile's gather
+    }
+    if (stats) {
+        // One (count, mean, M2) triple per channel and CTA: the pixel lanes are added in fixed order.  Sums are
+        // taken about the bias, the expected offset of the channel, to keep sum-of-squares cancellation small.
+        reinterpret_cast<float4*>(red_s)[threadIdx.x] = st_s;
+        reinterpret_cast<float4*>(red_q)[threadIdx.x] = st_q;
+        red_n[threadIdx.x] = st_n;
+        __syncthreads();
+        if (threadIdx.x < g.Cout) {
+            const int c = threadIdx.x, cgi = c >> 2, k = c & 3;
+            float n = 0.f, s = 0.f, q = 0.f;
+            for (int l = 0; l < g.lanes; ++l) {
+                const int t = (l << g.cg_shift) + cgi;
+                n += red_n[t];
+                s += red_s[t * 4 + k];
+                q += red_q[t * 4 + k];
+            }
+            const float m = n > 0.f ? s / n : 0.f;
+            float* out = stats + (size_t)blockIdx.x * 3 * g.Cout;
+            out[c] = n;
+            out[g.Cout + c] = m + (b ? b[c] : 0.f);
+            out[2 * g.Cout + c] = fmaxf(q - s * m, 0.f);
+        }
     }
 }
 
@@ -248,7 +287,7 @@ size_t smallc_conv_workspace_bytes(const AetherConvDesc& d) {
 
 template <typename Kern>
 static int smallc_smem(Kern kernel, size_t smem, size_t& configured, const char* what) {
-    if (smem > 40 * 1024 && smem > configured) {
+    if (smem > 32 * 1024 && smem > configured) {      // static + dynamic above 48 KB needs the opt-in
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(%s): %s", what, cudaGetErrorString(e));
         configured = smem;
@@ -257,26 +296,39 @@ static int smallc_smem(Kern kernel, size_t smem, size_t& configured, const char*
 }
 
 template <int R>
-static int launch_smallc_fwd(const SmallcGeom& g, const float* x, const float* w, const float* b, float* y, int nb,
-                             long long ntiles, size_t smem, cudaStream_t st) {
+static int launch_smallc_fwd(const SmallcGeom& g, const float* x, const float* w, const float* b, float* y, float* stats,
+                             int nb, long long ntiles, size_t smem, cudaStream_t st) {
     static size_t configured = 0;
     int rc = smallc_smem(smallc_fwd_kernel<R>, smem, configured, "smallc_fwd");
     if (rc) return rc;
-    smallc_fwd_kernel<R><<<nb, SC_THREADS, smem, st>>>(g, x, w, b, y, ntiles);
+    smallc_fwd_kernel<R><<<nb, SC_THREADS, smem, st>>>(g, x, w, b, y, stats, ntiles);
     count_launch();
     return check_launch("smallc_fwd_kernel");
 }
 
-int smallc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, cudaStream_t st) {
+static int smallc_fwd_blocks(const SmallcGeom& g) {
+    const long long ntiles = (g.P + g.TP - 1) / g.TP;
+    long long nb = 4LL * 148;
+    if (nb > ntiles) nb = ntiles;
+    return (int)(nb < 1 ? 1 : nb);
+}
+
+// Blocks of [3][Cout] (count, mean, M2) partial statistics the forward kernel writes when asked to: one per CTA.
+long long smallc_conv_stats_blocks(const AetherConvDesc& d) {
+    SmallcGeom g;
+    return smallc_geom(d, g) ? smallc_fwd_blocks(g) : 0;
+}
+
+int smallc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, float* stats,
+                    cudaStream_t st) {
     SmallcGeom g;
     if (!smallc_geom(d, g)) return set_error(AE_UNSUPPORTED, "smallc_conv_fwd: shape not supported");
     const long long ntiles = (g.P + g.TP - 1) / g.TP;
     const size_t smem = (size_t)(g.K * g.Cout + g.K * g.TP) * sizeof(float);
-    long long nb = 4LL * 148;
-    if (nb > ntiles) nb = ntiles;
-    if (g.R == 1) return launch_smallc_fwd<1>(g, x, w, b, y, (int)nb, ntiles, smem, st);
-    if (g.R == 2) return launch_smallc_fwd<2>(g, x, w, b, y, (int)nb, ntiles, smem, st);
-    return launch_smallc_fwd<4>(g, x, w, b, y, (int)nb, ntiles, smem, st);
+    const int nb = smallc_fwd_blocks(g);
+    if (g.R == 1) return launch_smallc_fwd<1>(g, x, w, b, y, stats, nb, ntiles, smem, st);
+    if (g.R == 2) return launch_smallc_fwd<2>(g, x, w, b, y, stats, nb, ntiles, smem, st);
+    return launch_smallc_fwd<4>(g, x, w, b, y, stats, nb, ntiles, smem, st);
 }
 
 template <int KPG>

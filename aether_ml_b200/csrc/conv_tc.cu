@@ -847,16 +847,18 @@ static int dispatch_igemm(IgemmParams& p, int nt, cudaStream_t st) {
 // Runs out[p, n] = sum_{tap,k} in[p (+/-) tap, k] * Wm[tap][n][k] (+ bias).
 static int run_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
                      int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, const PixelTiling& til,
-                     int n_padded, int fH, int fW, int sgn, int off_h, int off_w, const float* bias, cudaStream_t st) {
+                     int n_padded, int fH, int fW, int sgn, int off_h, int off_w, const float* bias, float* stats,
+                     cudaStream_t st) {
     {   // wide images with a filter that fits in shared memory: halo-reuse kernel
         bool used = false;
         const int padT = sgn > 0 ? -off_h : fH - 1 - off_h;
         const int padL = sgn > 0 ? -off_w : fW - 1 - off_w;
         int rc0 = run_halo_igemm(tf32, in, in_C, in_H, in_W, S, wmat, w_inner, rows_per_tap, taps, out, out_C, out_H, out_W,
-                                 n_padded, fH, fW, padT, padL, sgn > 0 ? 0 : 1, bias, sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX,
-                                 st, &used);
+                                 n_padded, fH, fW, padT, padL, sgn > 0 ? 0 : 1, bias, stats,
+                                 sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX, st, &used);
         if (rc0 || used) return rc0;
     }
+    if (stats) return set_error(AE_UNSUPPORTED, "conv forward: this shape's kernel does not emit Batch_Norm statistics");
     IgemmParams p;
     memset(&p, 0, sizeof(p));
     const int elt = tf32 ? 4 : 2;
@@ -901,7 +903,14 @@ static int launch_cast(const float* src, __nv_bfloat16* dst, long long rows, int
     return check_launch("cast_bf16_kernel");
 }
 
-int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, void* ws,
+long long tc_conv_stats_blocks(const AetherConvDesc& d) {
+    if (!tc_conv_eligible(d)) return 0;
+    const TcPlan pl = make_plan(d);
+    return halo_igemm_stats_blocks(pl.tf32, pl.tf32 ? d.Cin : pl.Cin_p, d.S, pl.taps, d.Cout, pl.Ho, pl.Wo, pl.Cout_p, d.fH,
+                                   d.fW);
+}
+
+int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, float* stats, void* ws,
                 size_t ws_bytes, cudaStream_t st) {
     const TcPlan pl = make_plan(d);
     if (ws_bytes < pl.total || !ws) return set_error(AE_BAD_ARG, "conv workspace too small: %zu < %zu", ws_bytes, pl.total);
@@ -914,7 +923,7 @@ int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const f
         count_launch();
         if ((rc = check_launch("filter_shadow_kernel"))) return rc;
         return run_igemm(true, x, d.Cin, d.H, d.W, d.S, wf, pl.Cin_p, pl.Cout_p, pl.taps, y, d.Cout, pl.Ho, pl.Wo,
-                         pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, st);
+                         pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, stats, st);
     }
     __nv_bfloat16* xsh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_xsh);
     __nv_bfloat16* wf = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_wf);
@@ -923,7 +932,7 @@ int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const f
     count_launch();
     if ((rc = check_launch("filter_shadow_kernel"))) return rc;
     return run_igemm(false, xsh, pl.Cin_p, d.H, d.W, d.S, wf, pl.Cin_p, pl.Cout_p, pl.taps, y, d.Cout, pl.Ho, pl.Wo,
-                     pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, st);
+                     pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, stats, st);
 }
 
 template <bool TF32, int NB>
@@ -983,7 +992,7 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
         if (pl.tf32) {
             // the caller's (taps, Cin, Cout) array already is the K-major matrix needed here
             rc = run_igemm(true, dy, d.Cout, pl.Ho, pl.Wo, d.S, w, d.Cout, d.Cin, pl.taps, dx, d.Cin, d.H, d.W,
-                           pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, st);
+                           pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, nullptr, st);
         } else {
             __nv_bfloat16* wd = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_wd);
             filter_shadow_kernel<__nv_bfloat16><<<fblocks, 256, 0, st>>>(w, wd, pl.taps, d.Cin, d.Cout, pl.Cin_p,
@@ -991,7 +1000,7 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
             count_launch();
             if ((rc = check_launch("filter_shadow_kernel"))) return rc;
             rc = run_igemm(false, dy_op, pl.Cout_p, pl.Ho, pl.Wo, d.S, wd, pl.Cout_p, pl.Cin_p, pl.taps, dx, d.Cin, d.H,
-                           d.W, pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, st);
+                           d.W, pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, nullptr, st);
         }
         if (rc) return rc;
     }

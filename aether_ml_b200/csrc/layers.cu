@@ -412,6 +412,29 @@ extern "C" int aether_bn_fwd_train(const float* x, const float* gamma, const flo
     return check_launch("aether_bn_fwd_train");
 }
 
+// Batch_Norm training forward when the producer of x (a convolution's epilogue) already wrote per-block
+// (count, mean, M2) partials of every channel: only the merge and the apply pass run, x is read once instead of twice.
+extern "C" int aether_bn_fwd_train_partials(const float* x, const float* partials, int64_t nblocks, const float* gamma,
+                                            const float* beta, float* running_mean, float* running_var, float* batch_mean,
+                                            float* batch_var, float* y, int64_t rows, int C, float eps, float momentum,
+                                            void* ws, size_t ws_bytes, void* stream) {
+    if (!x || !partials || !gamma || !beta || !running_mean || !running_var || !batch_mean || !batch_var || !y || !ws)
+        return set_error(AE_BAD_ARG, "aether_bn_fwd_train_partials: null pointer");
+    if (rows <= 0 || C <= 0 || nblocks <= 0 || nblocks > (1 << 30))
+        return set_error(AE_BAD_ARG, "aether_bn_fwd_train_partials: rows=%lld C=%d nblocks=%lld", (long long)rows, C, (long long)nblocks);
+    if (ws_bytes < 2 * (size_t)C * sizeof(float) || !aligned16(ws))
+        return set_error(AE_BAD_ARG, "aether_bn_fwd_train_partials: workspace too small or misaligned (needs 2*C floats)");
+    if ((C & 3) == 0 && (!aligned16(x) || !aligned16(y))) return set_error(AE_BAD_ARG, "aether_bn_fwd_train_partials: arrays must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* coeff = static_cast<float*>(ws);
+    bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(partials, (int)nblocks, C, gamma, beta, eps, momentum, running_mean,
+                                                            running_var, batch_mean, batch_var, coeff);
+    const long long n = rows * C;
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C);
+    count_launch(2);
+    return check_launch("aether_bn_fwd_train_partials");
+}
+
 // ---- Batch_Norm training forward for callers that cannot hand over a workspace ---------------------------
 // Scratch lives in a fixed device array that is part of the library image: every GPU that loads the library
 // carries these AETHER_BN_STATIC_SCRATCH_FLOATS * 4 bytes (about 1.8 MB) until the process exits.

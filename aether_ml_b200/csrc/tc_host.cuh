@@ -15,7 +15,12 @@ int make_map_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int el
 // Halo-reuse kernel (conv_halo.cu): launches and sets *used when the problem fits it, else leaves *used false.
 int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
                    int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, int n_padded, int fH, int fW,
-                   int padT, int padL, int flip, const float* bias, int prof_kind, cudaStream_t st, bool* used);
+                   int padT, int padL, int flip, const float* bias, float* stats, int prof_kind, cudaStream_t st,
+                   bool* used);
+// Partial-statistics blocks ([block][3][out_C]: count, mean, M2) the halo kernel writes when `stats` is given; 0 when
+// the halo kernel does not take the problem.
+long long halo_igemm_stats_blocks(bool tf32, int in_C, int S, int taps, int out_C, int out_H, int out_W, int n_padded,
+                                  int fH, int fW);
 
 // Halo-reuse dW kernel (conv_halo_dw.cu), bf16 shadows with 64-channel blocks.  `part` must have room for
 // max_splits split slices; the split count actually used is returned in *splits_out.

@@ -100,6 +100,9 @@ class Conv_Layer:
         self.filter_weights = to_device(w)
         self.biases = torch.zeros(num_filters, dtype=torch.float32, device=_device())
         self._ws = _Workspace()
+        self._stats_ws = _Workspace()
+        self.emit_bn_stats = False      # set when a Batch_Norm consumes this layer's output (Model.finalize does it)
+        self.bn_partials = None         # (buffer, blocks, data_ptr of the output they describe) after a training forward
         self._desc = None
         self._fwd_input_ptr = None
 
@@ -135,8 +138,19 @@ class Conv_Layer:
         L = lib()
         ws = self._ws.get(L.aether_conv2d_workspace_bytes(C.byref(d)))
         y = _empty((S, Ho, Wo, self.num_filters))
-        check(L.aether_conv2d_fwd(C.byref(d), _ptr(x), _ptr(self.filter_weights), _ptr(self.biases), _ptr(y),
-                                  _ptr(ws), ws.numel(), _stream()), "aether_conv2d_fwd")
+        # With emit_bn_stats the kernel's epilogue also writes the per-channel partial statistics that the
+        # Batch_Norm behind this layer would otherwise compute in a pass of its own over y (:467-470).
+        nblk = int(L.aether_conv2d_bnstats_blocks(C.byref(d))) if (training and self.emit_bn_stats) else 0
+        self.bn_partials = None
+        if nblk > 0:
+            stats = self._stats_ws.get(nblk * 3 * self.num_filters * 4)
+            check(L.aether_conv2d_fwd_bnstats(C.byref(d), _ptr(x), _ptr(self.filter_weights), _ptr(self.biases), _ptr(y),
+                                              _ptr(stats), stats.numel(), _ptr(ws), ws.numel(), _stream()),
+                  "aether_conv2d_fwd_bnstats")
+            self.bn_partials = (stats, nblk, y.data_ptr())
+        else:
+            check(L.aether_conv2d_fwd(C.byref(d), _ptr(x), _ptr(self.filter_weights), _ptr(self.biases), _ptr(y),
+                                      _ptr(ws), ws.numel(), _stream()), "aether_conv2d_fwd")
         self.inputs = x
         self.output = y
         self._desc = d
@@ -371,6 +385,7 @@ class Batch_Norm:
         self.bias_regularizer_l2 = 0
         self._ws = _Workspace()
         self._keep = None
+        self.stats_from = None          # a Conv_Layer whose forward leaves `bn_partials` for this layer's input
         if n_features is not None:
             self._create(n_features)
 
@@ -414,9 +429,17 @@ class Batch_Norm:
         if training:
             self._bm = _empty((Cc,))
             self._bv = _empty((Cc,))
-            check(L.aether_bn_fwd_train(_ptr(x), _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
-                                        _ptr(self._bm), _ptr(self._bv), _ptr(y), rows, Cc, float(self.epsilon),
-                                        float(self.momentum), _ptr(ws), ws.numel(), _stream()), "aether_bn_fwd_train")
+            part = getattr(self.stats_from, "bn_partials", None) if self.stats_from is not None else None
+            if part is not None and part[2] == x.data_ptr():
+                # the convolution that produced x already reduced it per channel: merge its partials, read x once
+                check(L.aether_bn_fwd_train_partials(_ptr(x), _ptr(part[0]), part[1], _ptr(self.gamma), _ptr(self.beta),
+                                                     _ptr(self._rm), _ptr(self._rv), _ptr(self._bm), _ptr(self._bv),
+                                                     _ptr(y), rows, Cc, float(self.epsilon), float(self.momentum),
+                                                     _ptr(ws), ws.numel(), _stream()), "aether_bn_fwd_train_partials")
+            else:
+                check(L.aether_bn_fwd_train(_ptr(x), _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
+                                            _ptr(self._bm), _ptr(self._bv), _ptr(y), rows, Cc, float(self.epsilon),
+                                            float(self.momentum), _ptr(ws), ws.numel(), _stream()), "aether_bn_fwd_train")
             self.batch_mean = self._bm.view(keep)
             self.batch_var = self._bv.view(keep)
             self.running_mean = self._rm.view(keep)       # the reference's stats pick up keep-dims here (:475-476)

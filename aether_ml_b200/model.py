@@ -16,8 +16,8 @@ import pickle
 import numpy as np
 import torch
 
-from .layers import (Activation_Softmax_Loss_CategoricalCrossEntropy, Loss_CategoricalCrossEntropy, SoftMax,
-                     to_device, _labels_i32)
+from .layers import (Activation_Softmax_Loss_CategoricalCrossEntropy, Batch_Norm, Conv_Layer,
+                     Loss_CategoricalCrossEntropy, SoftMax, to_device, _labels_i32)
 
 
 class Layer_Input:
@@ -109,6 +109,12 @@ class Model:
             layer.prev = chain[pos - 1]
             layer.next = chain[pos + 1]
         self.output_layer_activation = self.layers[-1]
+        # A Batch_Norm directly behind a Conv_Layer takes its batch statistics from the convolution's epilogue
+        # (when the kernel that serves the shape provides them) instead of reducing the activation again.
+        for a, b in zip(self.layers[:-1], self.layers[1:]):
+            if isinstance(a, Conv_Layer) and isinstance(b, Batch_Norm):
+                a.emit_bn_stats = True
+                b.stats_from = a
         self.trainable_layers = [l for l in self.layers if hasattr(l, "weights")]
         if self.loss is not None:
             self.loss.remember_trainable_layers(self.trainable_layers)

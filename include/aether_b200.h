@@ -82,6 +82,17 @@ size_t aether_conv2d_workspace_bytes(const AetherConvDesc* desc);
 int aether_conv2d_fwd(const AetherConvDesc* desc, const float* x, const float* w, const float* b, float* y, void* ws,
                       size_t ws_bytes, void* stream);
 
+/* Conv_Layer.forward with the Batch_Norm statistics of its output taken in the kernel's epilogue: the reference
+ * computes them in a separate pass over the layer output (Batch_Norm.forward, CNN_classes_cupy.py:467-470, mean and
+ * var over all axes but the last).  `stats` receives aether_conv2d_bnstats_blocks(desc) blocks of [3][Cout] floats:
+ * (count, mean, M2 = sum of squared deviations) of y over the rows each block covered; hand them to
+ * aether_bn_fwd_train_partials.  aether_conv2d_bnstats_blocks returns 0 when the forward kernel that serves the
+ * shape does not produce statistics; then aether_conv2d_fwd_bnstats fails with AETHER_E_UNSUPPORTED and the
+ * caller uses aether_conv2d_fwd + aether_bn_fwd_train. */
+int64_t aether_conv2d_bnstats_blocks(const AetherConvDesc* desc);
+int aether_conv2d_fwd_bnstats(const AetherConvDesc* desc, const float* x, const float* w, const float* b, float* y,
+                              float* stats, size_t stats_bytes, void* ws, size_t ws_bytes, void* stream);
+
 /* Conv_Layer.backward, CNN_classes_cupy.py:123-154: db = sum dy (:132), dw = windows^T dy (:134),
  * dx = scatter-add of dy w^T (:138-146) with the padding border removed (:149-153; returned
  * contiguous).  Any of dx, dw, db may be NULL to skip it.  x_shadow_valid != 0 tells the library that
@@ -96,6 +107,13 @@ size_t aether_bn_workspace_bytes(int64_t rows, int C);
 int aether_bn_fwd_train(const float* x, const float* gamma, const float* beta, float* running_mean, float* running_var,
                         float* batch_mean, float* batch_var, float* y, int64_t rows, int C, float eps, float momentum,
                         void* ws, size_t ws_bytes, void* stream);
+/* Training forward :467-476 from per-block partial statistics [nblocks][3][C] = (count, mean, M2) that the producer
+ * of x already wrote (aether_conv2d_fwd_bnstats): merges them (double precision), then normalises.  x is read once.
+ * ws: at least 2*C floats. */
+int aether_bn_fwd_train_partials(const float* x, const float* partials, int64_t nblocks, const float* gamma,
+                                 const float* beta, float* running_mean, float* running_var, float* batch_mean,
+                                 float* batch_var, float* y, int64_t rows, int C, float eps, float momentum, void* ws,
+                                 size_t ws_bytes, void* stream);
 /* Same result as aether_bn_fwd_train, for callers that have no way to provide the workspace.  (No counterpart
  * in the reference: its Batch_Norm lets CuPy allocate temporaries freely.)  Some hosts of this library must not
  * or cannot allocate device memory around a call -- a process whose whole device-memory budget was handed to

@@ -67,6 +67,45 @@ def test_batch_norm_shapes(env, shape):
     assert O.rel_l2(host(bn.dweights), dgo) <= 1e-4 and O.rel_l2(host(bn.dbiases), dbo) <= 1e-4
 
 
+# (S, H, W, Cin, Cout, mode, statistics expected from the conv epilogue)
+@pytest.mark.parametrize("case", [(8, 32, 32, 64, 128, "bf16", True), (37, 20, 24, 64, 64, "tf32", True),
+                                  (300, 32, 32, 3, 64, "bf16", True), (5, 28, 28, 1, 32, "bf16", True),
+                                  (16, 8, 8, 256, 256, "bf16", False)])
+def test_batch_norm_statistics_from_conv_epilogue(env, case):
+    """Conv_Layer -> Batch_Norm with the batch statistics taken in the convolution's epilogue: same result as
+    Batch_Norm's own reduction over the layer output (CNN_classes_cupy.py:467-476), bias far from zero included."""
+    torch, _lib, layers = env
+    S, H, W, Cin, Cout, mode, expect = case
+    rng = np.random.default_rng(5)
+    np.random.seed(5)
+    x = rng.standard_normal((S, H, W, Cin)).astype(np.float32)
+    conv = layers.Conv_Layer((H, W, Cin), Cout, (3, 3), (1, 1), "same", math_mode=mode)
+    conv.biases.copy_(torch.from_numpy((rng.standard_normal(Cout) * 4 + 3).astype(np.float32)))
+    gamma = (rng.standard_normal(Cout) + 1).astype(np.float32); beta = rng.standard_normal(Cout).astype(np.float32)
+    bn = layers.Batch_Norm(n_features=Cout)
+    bn.gamma.copy_(torch.from_numpy(gamma)); bn.beta.copy_(torch.from_numpy(beta))
+    conv.emit_bn_stats = True
+    bn.stats_from = conv
+    y = conv.forward(x, True)
+    assert (conv.bn_partials is not None) == expect
+    z = bn.forward(y, True)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    zo, _, mean, var, rm, rv = O.bn_forward_train(host(y), gamma, beta, np.zeros(Cout), np.ones(Cout))
+    assert O.rel_l2(host(bn.batch_mean), mean) <= 1e-5
+    assert O.rel_l2(host(bn.batch_var), var) <= 1e-4
+    assert O.rel_l2(host(bn.running_mean), rm) <= 1e-5 and O.rel_l2(host(bn.running_var), rv) <= 1e-4
+    assert O.rel_l2(host(z), zo) <= 5e-5
+    # a Batch_Norm fed something else than that convolution's output must ignore the partials
+    other = (rng.standard_normal(tuple(y.shape)) * 2 - 1).astype(np.float32)
+    z2 = bn.forward(other, True)
+    zo2 = O.bn_forward_train(other, gamma, beta, np.zeros(Cout), np.ones(Cout))[0]
+    assert O.rel_l2(host(z2), zo2) <= 2e-5
+    # inference keeps using the running statistics
+    conv.forward(x, False)
+    assert conv.bn_partials is None
+
+
 @pytest.mark.parametrize("name", ["pool_max_2x2", "pool_max_odd", "pool_max_overlap", "pool_avg_2x2"])
 def test_pooling_golden(env, golden, name):
     torch, _lib, layers = env

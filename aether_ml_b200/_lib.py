@@ -60,6 +60,9 @@ SIGNATURES = {
     "aether_dropout_fwd": (_I, [_P, _P, _P, _I64, _F, _U64, _U64, _P]),
     "aether_mul": (_I, [_P, _P, _P, _I64, _P]),
     "aether_adam_step": (_I, [_P, _P, _P, _P, _I64, _F, _F, _F, _F, _F, _F, _F, _P]),
+    "aether_adam_step_dev": (_I, [_P, _P, _P, _P, _I64, _F, _F, _F, _F, _F, _F, _P, _P]),
+    "aether_dropout_fwd_dev": (_I, [_P, _P, _P, _I64, _F, _U64, _U64, _P, _P]),
+    "aether_channel_mask_dev": (_I, [_P, _I, _F, _U64, _P, _P]),
     "aether_regularizer_grad": (_I, [_P, _P, _I64, _F, _F, _P]),
     "aether_regularizer_loss": (_I, [_P, _I64, _F, _F, _P, _P]),
     "aether_softmax_cce": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P]),

@@ -700,9 +700,12 @@ __device__ __forceinline__ uint4 philox4x32_10(uint2 key, uint4 ctr) {
 // mask[i] = (u < keep) / keep ; y = x * mask.  4 elements per thread.
 __global__ void __launch_bounds__(256) dropout_fwd_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                           float* __restrict__ mask, long long n, float keep,
-                                                          unsigned long long seed, unsigned long long offset) {
+                                                          unsigned long long seed, unsigned long long offset,
+                                                          const long long* __restrict__ calls_dev) {
     const long long stride = (long long)gridDim.x * blockDim.x;
     const float scale = 1.f / keep;
+    // a call counter kept in device memory (replayed CUDA graphs cannot change kernel arguments) selects the stream
+    if (calls_dev) offset += ((unsigned long long)*calls_dev) << 40;
     for (long long q = blockIdx.x * (long long)blockDim.x + threadIdx.x; q * 4 < n; q += stride) {
         const unsigned long long ctr = (unsigned long long)q + offset;
         const uint4 r = philox4x32_10(make_uint2((unsigned)seed, (unsigned)(seed >> 32)),
@@ -720,6 +723,17 @@ __global__ void __launch_bounds__(256) dropout_fwd_kernel(const float* __restric
         }
     }
 }
+// Channel mask of Layer_Dropout_Spatial drawn on the device: mask[c] = Bernoulli(keep) / keep, one Philox stream per call.
+__global__ void channel_mask_kernel(float* __restrict__ mask, int C, float keep, unsigned long long seed,
+                                    const long long* __restrict__ calls_dev) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const unsigned long long ctr = (unsigned long long)c + (((unsigned long long)*calls_dev) << 40);
+    const uint4 r = philox4x32_10(make_uint2((unsigned)seed, (unsigned)(seed >> 32)),
+                                  make_uint4((unsigned)ctr, (unsigned)(ctr >> 32), 0x5Du, 0u));
+    const float u = (float)(r.x >> 8) * (1.0f / 16777216.0f);
+    mask[c] = u < keep ? 1.f / keep : 0.f;
+}
 __global__ void __launch_bounds__(256) mul_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                                   float* __restrict__ y, long long n) {
     const long long stride = (long long)gridDim.x * blockDim.x;
@@ -734,6 +748,28 @@ __global__ void __launch_bounds__(256) adam_kernel(float* __restrict__ p, const 
                                                    float* __restrict__ m, float* __restrict__ v, long long n, float lr,
                                                    float b1, float b2, float eps, float inv_bc1, float inv_bc2,
                                                    float gscale) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float gi = g[i] * gscale;
+        const float mi = b1 * m[i] + (1.f - b1) * gi;
+        const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        p[i] -= lr * (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
+    }
+}
+
+// The same update with the step count read from device memory, so that a captured CUDA graph replays it with the
+// right learning-rate decay (:705-707) and bias corrections (:716-723) every time: `iterations` is the number of
+// updates already made, as Optimizer_Adam.iterations.
+__global__ void __launch_bounds__(256) adam_dev_kernel(float* __restrict__ p, const float* __restrict__ g,
+                                                       float* __restrict__ m, float* __restrict__ v, long long n, float lr0,
+                                                       float decay, float b1, float b2, float eps, float gscale,
+                                                       const long long* __restrict__ iterations) {
+    const double it = (double)*iterations;
+    const float lr = decay != 0.f ? (float)((double)lr0 * (1.0 / (1.0 + (double)decay * it))) : lr0;
+    const float inv_bc1 = (float)(1.0 / (1.0 - pow((double)b1, it + 1.0)));
+    const float inv_bc2 = (float)(1.0 / (1.0 - pow((double)b2, it + 1.0)));
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
         const float gi = g[i] * gscale;
@@ -908,9 +944,43 @@ extern "C" int aether_dropout_fwd(const float* x, float* y, float* mask, int64_t
                                   uint64_t offset, void* stream) {
     if (!x || !y || !mask || n <= 0 || !(keep_prob > 0.f) || keep_prob > 1.f)
         return set_error(AE_BAD_ARG, "aether_dropout_fwd: bad argument");
-    dropout_fwd_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, mask, n, keep_prob, seed, offset);
+    dropout_fwd_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, mask, n, keep_prob, seed, offset,
+                                                                                                  nullptr);
     count_launch();
     return check_launch("aether_dropout_fwd");
+}
+
+// Variants for captured CUDA graphs: whatever changes from step to step is read from device memory.
+extern "C" int aether_dropout_fwd_dev(const float* x, float* y, float* mask, int64_t n, float keep_prob, uint64_t seed,
+                                      uint64_t offset, const int64_t* calls_dev, void* stream) {
+    if (!x || !y || !mask || !calls_dev || n <= 0 || !(keep_prob > 0.f) || keep_prob > 1.f)
+        return set_error(AE_BAD_ARG, "aether_dropout_fwd_dev: bad argument");
+    dropout_fwd_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, y, mask, n, keep_prob, seed, offset, reinterpret_cast<const long long*>(calls_dev));
+    count_launch();
+    return check_launch("aether_dropout_fwd_dev");
+}
+
+extern "C" int aether_channel_mask_dev(float* mask, int C, float keep_prob, uint64_t seed, const int64_t* calls_dev,
+                                       void* stream) {
+    if (!mask || !calls_dev || C <= 0 || !(keep_prob > 0.f) || keep_prob > 1.f)
+        return set_error(AE_BAD_ARG, "aether_channel_mask_dev: bad argument");
+    channel_mask_kernel<<<ceil_div(C, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        mask, C, keep_prob, seed, reinterpret_cast<const long long*>(calls_dev));
+    count_launch();
+    return check_launch("aether_channel_mask_dev");
+}
+
+extern "C" int aether_adam_step_dev(float* p, const float* g, float* m, float* v, int64_t n, float lr0, float decay,
+                                    float beta1, float beta2, float eps, float grad_scale, const int64_t* iterations_dev,
+                                    void* stream) {
+    if (!p || !g || !m || !v || !iterations_dev || n <= 0) return set_error(AE_BAD_ARG, "aether_adam_step_dev: bad argument");
+    if (!(beta1 >= 0.f && beta1 < 1.f) || !(beta2 >= 0.f && beta2 < 1.f))
+        return set_error(AE_BAD_ARG, "aether_adam_step_dev: betas must be in [0, 1)");
+    adam_dev_kernel<<<blocks_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        p, g, m, v, n, lr0, decay, beta1, beta2, eps, grad_scale, reinterpret_cast<const long long*>(iterations_dev));
+    count_launch();
+    return check_launch("aether_adam_step_dev");
 }
 
 extern "C" int aether_mul(const float* a, const float* b, float* y, int64_t n, void* stream) {

@@ -294,10 +294,15 @@ class Layer_Dropout_Spatial:
     the reference's NumPy twin; ``channel_mask`` (1,1,1,C) may be overwritten before ``forward`` by
     setting ``fixed_mask``.  Output stays fp32 (the reference promotes to fp64 through its mask)."""
 
+    _next_seed = 0xC4A7
+
     def __init__(self, rate):
         self.rate = rate
         self.keep_prob = 1 - rate
         self.fixed_mask = None
+        self.seed = Layer_Dropout_Spatial._next_seed
+        Layer_Dropout_Spatial._next_seed += 1
+        self.step_dev = None            # int64 device counter: draw the mask on the device (CUDA-graph train step)
 
     def forward(self, inputs, training):
         x = to_device(inputs)
@@ -306,11 +311,16 @@ class Layer_Dropout_Spatial:
             self.output = x.clone()
             return self.output
         Cc = x.shape[-1]
-        if self.fixed_mask is not None:
-            mask = np.asarray(self.fixed_mask, dtype=np.float32).reshape(1, 1, 1, Cc)
+        if self.fixed_mask is None and self.step_dev is not None:
+            self.channel_mask = _empty((1, 1, 1, Cc))
+            check(lib().aether_channel_mask_dev(_ptr(self.channel_mask), Cc, float(self.keep_prob), self.seed,
+                                                _ptr(self.step_dev), _stream()), "aether_channel_mask_dev")
         else:
-            mask = (np.random.binomial(1, self.keep_prob, size=(1, 1, 1, Cc)) / self.keep_prob).astype(np.float32)
-        self.channel_mask = to_device(mask)
+            if self.fixed_mask is not None:
+                mask = np.asarray(self.fixed_mask, dtype=np.float32).reshape(1, 1, 1, Cc)
+            else:
+                mask = (np.random.binomial(1, self.keep_prob, size=(1, 1, 1, Cc)) / self.keep_prob).astype(np.float32)
+            self.channel_mask = to_device(mask)
         y = torch.empty_like(x)
         check(lib().aether_channel_scale(_ptr(x), _ptr(self.channel_mask), _ptr(y), x.numel(), Cc, _stream()),
               "aether_channel_scale")
@@ -340,6 +350,7 @@ class Layer_Dropout:
         self.seed = int(seed)
         self.rank_offset = int(rank_offset)
         self._calls = 0
+        self.step_dev = None
 
     def forward(self, inputs, training):
         x = to_device(inputs)
@@ -349,10 +360,15 @@ class Layer_Dropout:
             return self.output
         y = torch.empty_like(x)
         self.binary_mask = torch.empty_like(x)
-        offset = (self._calls << 40) + (self.rank_offset << 32)
-        self._calls += 1
-        check(lib().aether_dropout_fwd(_ptr(x), _ptr(y), _ptr(self.binary_mask), x.numel(), float(self.rate),
-                                       self.seed, offset, _stream()), "aether_dropout_fwd")
+        if self.step_dev is not None:   # the call counter lives on the device (CUDA-graph train step)
+            check(lib().aether_dropout_fwd_dev(_ptr(x), _ptr(y), _ptr(self.binary_mask), x.numel(), float(self.rate),
+                                               self.seed, self.rank_offset << 32, _ptr(self.step_dev), _stream()),
+                  "aether_dropout_fwd_dev")
+        else:
+            offset = (self._calls << 40) + (self.rank_offset << 32)
+            self._calls += 1
+            check(lib().aether_dropout_fwd(_ptr(x), _ptr(y), _ptr(self.binary_mask), x.numel(), float(self.rate),
+                                           self.seed, offset, _stream()), "aether_dropout_fwd")
         self.output = y
         return self.output
 
@@ -701,12 +717,19 @@ class Optimizer_Adam:
         self.beta_1 = beta_1
         self.beta_2 = beta_2
         self.grad_scale = 1.0
+        self.step_dev = None            # int64 device copy of `iterations` (CUDA-graph train step)
 
     def pre_update_parameters(self):
         if self.decay:
             self.current_learning_rate = self.learning_rate * (1. / (1. + self.decay * self.iterations))
 
     def _step(self, p, g, m, v):
+        if self.step_dev is not None:   # iterations, decay and bias corrections evaluated on the device
+            check(lib().aether_adam_step_dev(_ptr(p), _ptr(g), _ptr(m), _ptr(v), p.numel(), float(self.learning_rate),
+                                             float(self.decay), float(self.beta_1), float(self.beta_2),
+                                             float(self.epsilon), float(self.grad_scale), _ptr(self.step_dev),
+                                             _stream()), "aether_adam_step_dev")
+            return
         t = self.iterations + 1
         check(lib().aether_adam_step(_ptr(p), _ptr(g), _ptr(m), _ptr(v), p.numel(), float(self.current_learning_rate),
                                      float(self.beta_1), float(self.beta_2), float(self.epsilon),

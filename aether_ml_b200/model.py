@@ -192,6 +192,8 @@ class Model:
             for layer in self.trainable_layers:
                 opt.update_parameters(layer)
         opt.post_update_parameters()
+        if getattr(self, "_g_step", None) is not None:
+            self._g_step.add_(1)            # device copy of the step count (see enable_device_step)
 
     def train_step(self, X, y):
         """forward + loss gradient + backward + optimizer for one batch; returns the logits' softmax."""
@@ -199,6 +201,71 @@ class Model:
         self.backward(output, y)
         self._apply_optimizer()
         return output
+
+    # ------------------------------------------------------------------ CUDA-graph train step
+    def enable_device_step(self):
+        """Moves the per-step host state (Adam's iteration count, the dropout call counters) into one int64 device
+        counter that every train step increments; the channel masks of spatial dropout are then drawn on the device.
+        Required for a captured train step, usable on its own (same numbers eagerly and replayed)."""
+        if getattr(self, "_g_step", None) is None:
+            dev = self.trainable_layers[0].weights.device
+            self._g_step = torch.full((1,), int(self.optimizer.iterations), dtype=torch.int64, device=dev)
+            for obj in [self.optimizer] + [l for l in self.layers if hasattr(l, "step_dev")]:
+                obj.step_dev = self._g_step
+        return self._g_step
+
+    def _graph_body(self):
+        return self.train_step(self._g_X, self._g_y)
+
+    def _graph_state(self):
+        """Every tensor a train step changes besides activations: parameters, Adam moments, running statistics."""
+        ts = [self.flat_params, self.flat_m, self.flat_v, self._g_step]
+        for l in self.layers:
+            if isinstance(l, Batch_Norm) and l.gamma is not None:
+                ts += [l._rm, l._rv]
+        return ts
+
+    def capture_train_step(self, X, y, warmup=2):
+        """Records ``train_step`` for batches shaped like (X, y) into a CUDA graph; ``train_step_graph`` replays
+        it with one launch.  A step of the small reference networks is ~130 kernel launches of a few microseconds
+        each, so the eager step is bound by launch overhead, not by the GPU.  Needs ``finalize(flat=True)``.
+        Whatever the reference changes on the host per step (Adam's iteration count and decayed learning rate,
+        the dropout draws) is read from one int64 device counter that the graph itself increments.  The warm-up
+        steps (they size the workspaces) are undone, so capturing does not train."""
+        if self.flat_params is None:
+            raise RuntimeError("capture_train_step needs finalize(flat=True)")
+        self._g_X = to_device(X).clone()
+        self._g_y = _labels_i32(y).clone()
+        opt = self.optimizer
+        self.enable_device_step()
+        saved = [t.clone() for t in self._graph_state()]
+        saved_it = opt.iterations
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(max(int(warmup), 1)):
+                self._graph_body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        for t, s in zip(self._graph_state(), saved):
+            t.copy_(s)
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._g_out = self._graph_body()
+        opt.iterations = saved_it           # capture records work, it does not run it
+        return self._graph
+
+    def train_step_graph(self, X, y):
+        """One training step by replaying the captured graph on a new batch of the captured shape."""
+        if getattr(self, "_graph", None) is None:
+            raise RuntimeError("train_step_graph called before capture_train_step")
+        self._g_X.copy_(to_device(X), non_blocking=True)
+        self._g_y.copy_(_labels_i32(y), non_blocking=True)
+        self._graph.replay()
+        opt = self.optimizer
+        opt.pre_update_parameters()         # host mirror of what the graph just did on the device
+        opt.post_update_parameters()
+        return self._g_out
 
     def train(self, X, y, *, epochs=1, batch_size=None, print_every=1, validation_data=None):
         self.accuracy.init(y)

@@ -359,23 +359,31 @@ def run_train(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    l0 = _lib.launch_count()
     for _ in range(max(args.warmup, 3)):
         model.train_step(X, y)
     sync_all()
+    launches_per_step = (_lib.launch_count() - l0) // max(args.warmup, 3)
     if _lib.device_status() != 0:
         raise RuntimeError("a kernel abandoned a bounded wait: status %d" % _lib.device_status())
+    step = model.train_step
+    if args.graph:                                      # the whole step (all-reduce included) as one CUDA-graph launch
+        model.capture_train_step(X, y)
+        step = model.train_step_graph
+        for _ in range(3):
+            step(X, y)
+        sync_all()
     sampler = ClockSampler(local) if rank == 0 else None
-    launches0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
     t_begin = time.perf_counter()
     e0.record()
     for _ in range(args.steps):
-        model.train_step(X, y)
+        step(X, y)
     e1.record()
     sync_all()
     t_end = time.perf_counter()
-    launches = _lib.launch_count() - launches0
+    launches = launches_per_step * args.steps           # kernels of this library executed (replayed when --graph)
     ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -383,7 +391,7 @@ def run_train(args):
     clocks = sampler.stop(t_begin, t_end) if sampler else None
 
     def e2e_step():
-        out = model.train_step(X_host.to(dev, non_blocking=True), y_host.to(dev, non_blocking=True))
+        out = step(X_host.to(dev, non_blocking=True), y_host.to(dev, non_blocking=True))
         return out[:1].cpu()                             # read part of the step's result back every step
 
     e2e_step()
@@ -407,7 +415,8 @@ def run_train(args):
             "config": {"workload": "train step of the CIFAR-shaped 3-block CNN%s, global batch %d NHWC (32,32,3) ~ U[0,1), "
                                    "Adam lr 1e-3 decay 5e-5" % (" widened 4x (128/256/512, Dense 8192->1024->10)" if widen == 4 else "", global_batch),
                        "per_gpu_batch": hi - lo, "parallelism": "dp%d, one NCCL all-reduce of the flat gradient buffer per step" % world,
-                       "l2": "activations of a step (GBs) exceed the 126 MB L2", "params": int(model.flat_params.numel())},
+                       "l2": "activations of a step (GBs) exceed the 126 MB L2", "params": int(model.flat_params.numel()),
+                       "cuda_graph": bool(args.graph)},
             "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": "images/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": (X_host.numel() * 4 + y_host.numel() * 4) * world, "d2h_bytes_per_step": 40 * world},
             "gpu_launches": int(launches), "clocks": clocks}))
@@ -428,6 +437,7 @@ def main():
     ap.add_argument("--mode", default="bf16", choices=["bf16", "tf32"])
     ap.add_argument("--batch", type=int, default=SHAPE["S"], help="per-GPU batch (smaller only for profiler captures)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU sample (profiler captures)")
+    ap.add_argument("--graph", action="store_true", help="train workloads: replay the step from a captured CUDA graph")
     args = ap.parse_args()
     SHAPE["S"] = args.batch
     if args.impl == "reference":

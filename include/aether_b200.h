@@ -168,6 +168,20 @@ int aether_mul(const float* a, const float* b, float* y, int64_t n, void* stream
  *      data-parallel average). */
 int aether_adam_step(float* p, const float* g, float* m, float* v, int64_t n, float lr, float beta1, float beta2,
                      float eps, float bias_corr1, float bias_corr2, float grad_scale, void* stream);
+/* ---- Variants for a train step captured in a CUDA graph.  A replayed graph cannot change kernel arguments, so
+ *      whatever the reference changes on the host from step to step is read from device memory instead: one int64
+ *      counter that the caller increments once per step (a device-side add inside the graph).
+ *   aether_adam_step_dev: Optimizer_Adam.pre_update_parameters + update_parameters (:705-734) with
+ *      iterations = *iterations_dev: lr = lr0 / (1 + decay*iterations), bias_corr = 1 - beta^(iterations+1).
+ *   aether_dropout_fwd_dev: Layer_Dropout.forward (:364-382) on Philox stream offset + (*calls_dev << 40).
+ *   aether_channel_mask_dev: the (C,) mask of Layer_Dropout_Spatial.forward (:392-397), Bernoulli(keep_prob)/keep_prob
+ *      per channel, drawn on the device (the reference draws it with NumPy on the host); apply it with
+ *      aether_channel_scale. */
+int aether_adam_step_dev(float* p, const float* g, float* m, float* v, int64_t n, float lr0, float decay, float beta1,
+                         float beta2, float eps, float grad_scale, const int64_t* iterations_dev, void* stream);
+int aether_dropout_fwd_dev(const float* x, float* y, float* mask, int64_t n, float keep_prob, uint64_t seed,
+                           uint64_t offset, const int64_t* calls_dev, void* stream);
+int aether_channel_mask_dev(float* mask, int C, float keep_prob, uint64_t seed, const int64_t* calls_dev, void* stream);
 /* L1/L2 terms of Layer_Dense.backward :337-351: g += l1*sign(w) + 2*l2*w. */
 int aether_regularizer_grad(const float* w, float* g, int64_t n, float l1, float l2, void* stream);
 /* Loss.regularization_loss :593-609: out[0] += l1*sum|w| + l2*sum w^2. */

@@ -182,3 +182,48 @@ def test_train_loop_evaluate_predict_save_load(env, tmp_path, capsys):
     assert O.rel_l2(host(m2.predict(X, batch_size=16)), host(pred)) <= 1e-6
     conv = m2.layers[0]
     assert conv.weights is conv.filter_weights
+
+
+def test_train_step_cuda_graph_matches_eager(env):
+    """A train step captured in a CUDA graph (Model.capture_train_step) replays to the same parameters as the
+    eager steps: Adam's iteration count / decayed learning rate and the dropout draws come from a device counter,
+    so every replay is a NEW step, and capturing itself does not train."""
+    torch, _lib, Ly, M = env
+    rng = np.random.default_rng(9)
+    batches = [((rng.random((16, 32, 32, 3))).astype(np.float32), rng.integers(0, 10, 16)) for _ in range(4)]
+
+    def fresh():
+        m, _ = build(env, "cifar", "bf16", True)
+        for k, l in enumerate(m.layers):                   # identical dropout streams in both models
+            if hasattr(l, "seed"):
+                l.seed = 1000 + k
+        return m
+
+    eager = fresh()
+    eager.enable_device_step()
+    for X, y in batches:
+        eager.train_step(X, y)
+    masks_eager = [host(l.channel_mask) for l in eager.layers if isinstance(l, Ly.Layer_Dropout_Spatial)]
+
+    graph = fresh()
+    p0 = host(graph.flat_params).copy()
+    graph.capture_train_step(*batches[0])
+    assert np.array_equal(host(graph.flat_params), p0) and graph.optimizer.iterations == 0
+    outs = []
+    for X, y in batches:
+        outs.append(host(graph.train_step_graph(X, y)).copy())
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert graph.optimizer.iterations == len(batches) == int(graph._g_step.item())
+    assert O.rel_l2(host(graph.flat_params), host(eager.flat_params)) <= 1e-6
+    assert O.rel_l2(host(graph.flat_m), host(eager.flat_m)) <= 1e-6
+    assert not np.allclose(outs[0], outs[1])               # a replay sees the new batch and the new parameters
+    masks_graph = [host(l.channel_mask) for l in graph.layers if isinstance(l, Ly.Layer_Dropout_Spatial)]
+    for a, b in zip(masks_eager, masks_graph):
+        assert np.array_equal(a, b)
+    # the element dropout drew a different mask in every step (the device counter moved)
+    drop = [l for l in graph.layers if isinstance(l, Ly.Layer_Dropout)][0]
+    m_last = host(drop.binary_mask).copy()
+    graph.train_step_graph(*batches[0])
+    assert not np.array_equal(host(drop.binary_mask), m_last)
+    assert abs((m_last > 0).mean() - (1 - 0.075)) < 0.05

@@ -181,9 +181,9 @@ class Model:
             else:
                 layer.backward(layer.next.dinputs)
 
-    def _apply_optimizer(self):
+    def _apply_optimizer(self, run_hook=True):
         opt = self.optimizer
-        if self.grad_hook is not None and self.flat_params is not None:
+        if run_hook and self.grad_hook is not None and self.flat_params is not None:
             self.grad_hook(self.flat_grads)
         opt.pre_update_parameters()
         if self.flat_params is not None and hasattr(opt, "update_flat"):
@@ -227,7 +227,8 @@ class Model:
 
     def capture_train_step(self, X, y, warmup=2):
         """Records ``train_step`` for batches shaped like (X, y) into a CUDA graph; ``train_step_graph`` replays
-        it with one launch.  A step of the small reference networks is ~130 kernel launches of a few microseconds
+        it with one launch (two, around the gradient hook, when one is set).  A step of the small reference
+        networks is ~130 kernel launches of a few microseconds
         each, so the eager step is bound by launch overhead, not by the GPU.  Needs ``finalize(flat=True)``.
         Whatever the reference changes on the host per step (Adam's iteration count and decayed learning rate,
         the dropout draws) is read from one int64 device counter that the graph itself increments.  The warm-up
@@ -249,9 +250,20 @@ class Model:
         torch.cuda.synchronize()
         for t, s in zip(self._graph_state(), saved):
             t.copy_(s)
+        # With a gradient hook (the data-parallel all-reduce) the step is recorded as two graphs and the hook runs
+        # eagerly between them: collectives stay outside stream capture, where a rank that fails cannot leave
+        # its peers waiting inside a captured collective.
         self._graph = torch.cuda.CUDAGraph()
+        self._graph_opt = None
         with torch.cuda.graph(self._graph):
-            self._g_out = self._graph_body()
+            self._g_out = self.forward(self._g_X, training=True)
+            self.backward(self._g_out, self._g_y)
+            if self.grad_hook is None:
+                self._apply_optimizer()
+        if self.grad_hook is not None:
+            self._graph_opt = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph_opt):
+                self._apply_optimizer(run_hook=False)
         opt.iterations = saved_it           # capture records work, it does not run it
         return self._graph
 
@@ -262,6 +274,9 @@ class Model:
         self._g_X.copy_(to_device(X), non_blocking=True)
         self._g_y.copy_(_labels_i32(y), non_blocking=True)
         self._graph.replay()
+        if self._graph_opt is not None:
+            self.grad_hook(self.flat_grads)
+            self._graph_opt.replay()
         opt = self.optimizer
         opt.pre_update_parameters()         # host mirror of what the graph just did on the device
         opt.post_update_parameters()

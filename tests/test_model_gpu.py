@@ -184,7 +184,8 @@ def test_train_loop_evaluate_predict_save_load(env, tmp_path, capsys):
     assert conv.weights is conv.filter_weights
 
 
-def test_train_step_cuda_graph_matches_eager(env):
+@pytest.mark.parametrize("hook", [False, True])
+def test_train_step_cuda_graph_matches_eager(env, hook):
     """A train step captured in a CUDA graph (Model.capture_train_step) replays to the same parameters as the
     eager steps: Adam's iteration count / decayed learning rate and the dropout draws come from a device counter,
     so every replay is a NEW step, and capturing itself does not train."""
@@ -197,6 +198,8 @@ def test_train_step_cuda_graph_matches_eager(env):
         for k, l in enumerate(m.layers):                   # identical dropout streams in both models
             if hasattr(l, "seed"):
                 l.seed = 1000 + k
+        if hook:                                           # a gradient hook (the data-parallel all-reduce in real use)
+            m.grad_hook = lambda g: g.mul_(0.5)            # runs eagerly between the two captured graphs
         return m
 
     eager = fresh()

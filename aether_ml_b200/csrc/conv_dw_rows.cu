@@ -18,7 +18,6 @@
 // comes from L2 (DRAM traffic measured by ncu equals one pass over x and dy).  Each CTA keeps its
 // accumulators in TMEM for its whole life and writes one partial; the partials are added in fixed order by
 // dw_reduce_kernel (which is told the two split counts).
-#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"

@@ -17,6 +17,13 @@ static int blocks_for(long long items, int threads, int per_sm = 8) {
     return (int)b;
 }
 
+// Derivative of the (leaky) ReLU fused behind a Batch_Norm, judged from the ACTIVATED value: for alpha > 0 the sign of
+// the output is the sign of the pre-activation (the reference passes the gradient where that is 0,
+// CNN_classes_cupy.py:412-428); for alpha == 0 a zero output blocks the gradient.
+__device__ __forceinline__ float act_grad(float yact, float alpha) {
+    return alpha > 0.f ? (yact < 0.f ? alpha : 1.f) : (yact > 0.f ? 1.f : 0.f);
+}
+
 // ====================================================================================== batch norm
 // Per-channel reductions over a [rows][C] matrix.  Thread t of a block owns column (t % cols) and row
 // lane (t / cols); a block walks a contiguous slab of rows, so a warp reads consecutive addresses.
@@ -26,7 +33,8 @@ template <int MODE>
 __global__ void __launch_bounds__(256) bn_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                                                         const float* __restrict__ mean, const float* __restrict__ var,
                                                         float eps, long long rows, int C, float* __restrict__ part,
-                                                        long long rows_per_block) {
+                                                        long long rows_per_block, const float* __restrict__ yact,
+                                                        float alpha) {
     const long long r0 = blockIdx.x * rows_per_block;
     long long r1 = r0 + rows_per_block;
     if (r1 > rows) r1 = rows;
@@ -58,7 +66,8 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(const float* __restrict_
                 const float mu = mean[c];
                 const float inv = rsqrtf(var[c] + eps);
                 for (long long r = r0 + rl; r < r1; r += lanes) {
-                    const float g = dy[(size_t)r * C + c];
+                    float g = dy[(size_t)r * C + c];
+                    if (yact) g *= act_grad(yact[(size_t)r * C + c], alpha);   // gradient through the fused activation
                     a += g;
                     b = fmaf(g, (x[(size_t)r * C + c] - mu) * inv, b);
                 }
@@ -106,7 +115,8 @@ template <int MODE>
 __global__ void __launch_bounds__(256) bn_reduce_vec4_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                                                              const float* __restrict__ mean, const float* __restrict__ var,
                                                              float eps, long long rows, int C, float* __restrict__ part,
-                                                             long long rows_per_block) {
+                                                             long long rows_per_block, const float* __restrict__ yact,
+                                                             float alpha) {
     const long long r0 = blockIdx.x * rows_per_block;
     long long r1 = r0 + rows_per_block;
     if (r1 > rows) r1 = rows;
@@ -149,8 +159,13 @@ __global__ void __launch_bounds__(256) bn_reduce_vec4_kernel(const float* __rest
                 const float4* gr = reinterpret_cast<const float4*>(dy) + cv;
 #pragma unroll 4
                 for (long long r = r0 + rl; r < r1; r += lanes) {
-                    const float4 g = gr[(size_t)r * CV];
+                    float4 g = gr[(size_t)r * CV];
                     const float4 v = xr[(size_t)r * CV];
+                    if (yact) {                                                   // gradient through the fused activation
+                        const float4 ya = (reinterpret_cast<const float4*>(yact) + cv)[(size_t)r * CV];
+                        g.x *= act_grad(ya.x, alpha); g.y *= act_grad(ya.y, alpha);
+                        g.z *= act_grad(ya.z, alpha); g.w *= act_grad(ya.w, alpha);
+                    }
                     a.x += g.x; a.y += g.y; a.z += g.z; a.w += g.w;
                     b.x = fmaf(g.x, (v.x - mu.x) * inv.x, b.x); b.y = fmaf(g.y, (v.y - mu.y) * inv.y, b.y);
                     b.z = fmaf(g.z, (v.z - mu.z) * inv.z, b.z); b.w = fmaf(g.w, (v.w - mu.w) * inv.w, b.w);
@@ -199,12 +214,13 @@ __global__ void __launch_bounds__(256) bn_reduce_vec4_kernel(const float* __rest
 
 template <int MODE>
 static void launch_bn_reduce(int nb, cudaStream_t st, const float* x, const float* dy, const float* mean, const float* var,
-                             float eps, long long rows, int C, float* part) {
+                             float eps, long long rows, int C, float* part, const float* yact = nullptr, float alpha = 0.f) {
     const long long rpb = (rows + nb - 1) / nb;
     const bool vec = (C & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
-                     (MODE == 0 || (reinterpret_cast<uintptr_t>(dy) & 15u) == 0);
-    if (vec) bn_reduce_vec4_kernel<MODE><<<nb, 256, 0, st>>>(x, dy, mean, var, eps, rows, C, part, rpb);
-    else bn_reduce_kernel<MODE><<<nb, 256, 0, st>>>(x, dy, mean, var, eps, rows, C, part, rpb);
+                     (MODE == 0 || (reinterpret_cast<uintptr_t>(dy) & 15u) == 0) &&
+                     (yact == nullptr || (reinterpret_cast<uintptr_t>(yact) & 15u) == 0);
+    if (vec) bn_reduce_vec4_kernel<MODE><<<nb, 256, 0, st>>>(x, dy, mean, var, eps, rows, C, part, rpb, yact, alpha);
+    else bn_reduce_kernel<MODE><<<nb, 256, 0, st>>>(x, dy, mean, var, eps, rows, C, part, rpb, yact, alpha);
 }
 
 // Merges the per-block (n, mean, M2) triples in double precision, writes batch mean / biased variance,
@@ -269,11 +285,13 @@ __global__ void bn_eval_coeff_kernel(int C, const float* __restrict__ gamma, con
     scale_shift[C + c] = beta[c] - running_mean[c] * sc;
 }
 
-// y = x * scale[c] + shift[c]
+// y = x * scale[c] + shift[c], optionally followed by y = y > 0 ? y : act_alpha * y (act_alpha < 0: no activation)
 __global__ void __launch_bounds__(256) affine_channels_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                               const float* __restrict__ scale,
-                                                              const float* __restrict__ shift, long long n, int C) {
+                                                              const float* __restrict__ shift, long long n, int C,
+                                                              float act_alpha) {
     const long long stride = (long long)gridDim.x * blockDim.x;
+    const bool act = act_alpha >= 0.f;
     if ((C & 3) == 0) {
         const long long n4 = n >> 2;
         const int C4 = C >> 2;
@@ -295,12 +313,17 @@ __global__ void __launch_bounds__(256) affine_channels_kernel(const float* __res
             } else {
                 o = make_float4(v.x * s.x, v.y * s.y, v.z * s.z, v.w * s.w);
             }
+            if (act) {
+                o.x = o.x > 0.f ? o.x : act_alpha * o.x; o.y = o.y > 0.f ? o.y : act_alpha * o.y;
+                o.z = o.z > 0.f ? o.z : act_alpha * o.z; o.w = o.w > 0.f ? o.w : act_alpha * o.w;
+            }
             y4[i] = o;
         }
     } else {
         for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
             const int c = (int)(i % C);
-            y[i] = shift ? fmaf(x[i], scale[c], shift[c]) : x[i] * scale[c];
+            const float o = shift ? fmaf(x[i], scale[c], shift[c]) : x[i] * scale[c];
+            y[i] = (act && o <= 0.f) ? act_alpha * o : o;
         }
     }
 }
@@ -343,7 +366,8 @@ __global__ void bn_finalize_bwd_kernel(const float* __restrict__ part, int nbloc
 
 __global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                                                            float* __restrict__ dx, const float* __restrict__ coeff,
-                                                           long long n, int C) {
+                                                           long long n, int C, const float* __restrict__ yact,
+                                                           float alpha) {
     const long long stride = (long long)gridDim.x * blockDim.x;
     if ((C & 3) == 0) {
         const long long n4 = n >> 2;
@@ -356,7 +380,12 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const float* __restri
             cq += cstep;
             if (cq >= C4) cq -= C4;
             const float4 xv = reinterpret_cast<const float4*>(x)[i];
-            const float4 g = reinterpret_cast<const float4*>(dy)[i];
+            float4 g = reinterpret_cast<const float4*>(dy)[i];
+            if (yact) {                                                           // gradient through the fused activation
+                const float4 ya = reinterpret_cast<const float4*>(yact)[i];
+                g.x *= act_grad(ya.x, alpha); g.y *= act_grad(ya.y, alpha);
+                g.z *= act_grad(ya.z, alpha); g.w *= act_grad(ya.w, alpha);
+            }
             const float4 k1 = *reinterpret_cast<const float4*>(coeff + c);
             const float4 k2 = *reinterpret_cast<const float4*>(coeff + C + c);
             const float4 k3 = *reinterpret_cast<const float4*>(coeff + 2 * C + c);
@@ -370,7 +399,8 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const float* __restri
     } else {
         for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
             const int c = (int)(i % C);
-            dx[i] = fmaf(coeff[c], dy[i], fmaf(coeff[C + c], x[i], coeff[2 * C + c]));
+            const float g = yact ? dy[i] * act_grad(yact[i], alpha) : dy[i];
+            dx[i] = fmaf(coeff[c], g, fmaf(coeff[C + c], x[i], coeff[2 * C + c]));
         }
     }
 }
@@ -407,7 +437,7 @@ extern "C" int aether_bn_fwd_train(const float* x, const float* gamma, const flo
     bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
                                                             running_var, batch_mean, batch_var, coeff);
     const long long n = rows * C;
-    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C);
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C, -1.f);
     count_launch(3);
     return check_launch("aether_bn_fwd_train");
 }
@@ -430,7 +460,7 @@ extern "C" int aether_bn_fwd_train_partials(const float* x, const float* partial
     bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(partials, (int)nblocks, C, gamma, beta, eps, momentum, running_mean,
                                                             running_var, batch_mean, batch_var, coeff);
     const long long n = rows * C;
-    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C);
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C, -1.f);
     count_launch(2);
     return check_launch("aether_bn_fwd_train_partials");
 }
@@ -490,7 +520,7 @@ extern "C" int aether_bn_fwd_train_static(const float* x, const float* gamma, co
     bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
                                                             running_var, batch_mean, batch_var, coeff);
     const long long n = rows * C;
-    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C);
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C, -1.f);
     count_launch(3);
     return check_launch("aether_bn_fwd_train_static");
 }
@@ -506,7 +536,7 @@ extern "C" int aether_bn_fwd_eval(const float* x, const float* gamma, const floa
     float* coeff = static_cast<float*>(ws);
     bn_eval_coeff_kernel<<<ceil_div(C, 128), 128, 0, st>>>(C, gamma, beta, eps, running_mean, running_var, coeff);
     const long long n = rows * C;
-    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C);
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C, -1.f);
     count_launch(2);
     return check_launch("aether_bn_fwd_eval");
 }
@@ -528,9 +558,90 @@ extern "C" int aether_bn_bwd(const float* x, const float* dy, const float* gamma
     bn_finalize_bwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
                                                             dbeta, coeff);
     const long long n = rows * C;
-    bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C);
+    bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C, nullptr, 0.f);
     count_launch(3);
     return check_launch("aether_bn_bwd");
+}
+
+// ---- Batch_Norm with the (leaky) ReLU that follows it applied in the same passes ------------------------------
+// forward : y = act(bn(x)); the normalised, not yet activated tensor is never written.
+// backward: dy is the gradient w.r.t. y; the activation's derivative is taken from the sign of y while the
+//           statistics pass and the dx pass read it, so the ReLU's own backward pass disappears as well.
+static int bn_act_check(const char* who, int64_t rows, int C, float alpha, const void* a, const void* b, const void* c) {
+    if (rows <= 0 || C <= 0) return set_error(AE_BAD_ARG, "%s: rows=%lld C=%d", who, (long long)rows, C);
+    if (!(alpha >= 0.f && alpha < 1.f)) return set_error(AE_BAD_ARG, "%s: alpha must be in [0, 1)", who);
+    if ((C & 3) == 0 && (!aligned16(a) || !aligned16(b) || !aligned16(c)))
+        return set_error(AE_BAD_ARG, "%s: arrays must be 16-byte aligned", who);
+    return AE_OK;
+}
+
+extern "C" int aether_bn_act_fwd_train(const float* x, const float* partials, int64_t nblocks, const float* gamma,
+                                       const float* beta, float* running_mean, float* running_var, float* batch_mean,
+                                       float* batch_var, float* y, int64_t rows, int C, float eps, float momentum,
+                                       float alpha, void* ws, size_t ws_bytes, void* stream) {
+    if (!x || !gamma || !beta || !running_mean || !running_var || !batch_mean || !batch_var || !y || !ws)
+        return set_error(AE_BAD_ARG, "aether_bn_act_fwd_train: null pointer");
+    int rc = bn_act_check("aether_bn_act_fwd_train", rows, C, alpha, x, y, ws);
+    if (rc) return rc;
+    if (ws_bytes < aether_bn_workspace_bytes(rows, C)) return set_error(AE_BAD_ARG, "aether_bn_act_fwd_train: workspace too small");
+    if (partials && (nblocks <= 0 || nblocks > (1 << 30))) return set_error(AE_BAD_ARG, "aether_bn_act_fwd_train: nblocks");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int nb = bn_blocks(rows);
+    float* part = static_cast<float*>(ws);
+    float* coeff = part + (size_t)nb * 3 * C;
+    const float* src = partials;
+    if (!partials) {                       // no producer-side statistics: reduce x here
+        launch_bn_reduce<0>(nb, st, x, nullptr, nullptr, nullptr, eps, rows, C, part);
+        count_launch();
+        src = part;
+    } else {
+        nb = (int)nblocks;
+    }
+    bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(src, nb, C, gamma, beta, eps, momentum, running_mean, running_var,
+                                                            batch_mean, batch_var, coeff);
+    const long long n = rows * C;
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C, alpha);
+    count_launch(2);
+    return check_launch("aether_bn_act_fwd_train");
+}
+
+extern "C" int aether_bn_act_fwd_eval(const float* x, const float* gamma, const float* beta, const float* running_mean,
+                                      const float* running_var, float* y, int64_t rows, int C, float eps, float alpha,
+                                      void* ws, size_t ws_bytes, void* stream) {
+    if (!x || !gamma || !beta || !running_mean || !running_var || !y || !ws)
+        return set_error(AE_BAD_ARG, "aether_bn_act_fwd_eval: null pointer");
+    int rc = bn_act_check("aether_bn_act_fwd_eval", rows, C, alpha, x, y, ws);
+    if (rc) return rc;
+    if (ws_bytes < 2 * (size_t)C * sizeof(float)) return set_error(AE_BAD_ARG, "aether_bn_act_fwd_eval: workspace too small");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* coeff = static_cast<float*>(ws);
+    bn_eval_coeff_kernel<<<ceil_div(C, 128), 128, 0, st>>>(C, gamma, beta, eps, running_mean, running_var, coeff);
+    const long long n = rows * C;
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C, alpha);
+    count_launch(2);
+    return check_launch("aether_bn_act_fwd_eval");
+}
+
+extern "C" int aether_bn_act_bwd(const float* x, const float* y_act, const float* dy, const float* gamma,
+                                 const float* batch_mean, const float* batch_var, float* dx, float* dgamma, float* dbeta,
+                                 int64_t rows, int C, float eps, float alpha, void* ws, size_t ws_bytes, void* stream) {
+    if (!x || !y_act || !dy || !gamma || !batch_mean || !batch_var || !dx || !dgamma || !dbeta || !ws)
+        return set_error(AE_BAD_ARG, "aether_bn_act_bwd: null pointer");
+    int rc = bn_act_check("aether_bn_act_bwd", rows, C, alpha, x, dy, dx);
+    if (rc) return rc;
+    if ((C & 3) == 0 && !aligned16(y_act)) return set_error(AE_BAD_ARG, "aether_bn_act_bwd: arrays must be 16-byte aligned");
+    if (ws_bytes < aether_bn_workspace_bytes(rows, C)) return set_error(AE_BAD_ARG, "aether_bn_act_bwd: workspace too small");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int nb = bn_blocks(rows);
+    float* part = static_cast<float*>(ws);
+    float* coeff = part + (size_t)nb * 3 * C;
+    launch_bn_reduce<1>(nb, st, x, dy, batch_mean, batch_var, eps, rows, C, part, y_act, alpha);
+    bn_finalize_bwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
+                                                            dbeta, coeff);
+    const long long n = rows * C;
+    bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C, y_act, alpha);
+    count_launch(3);
+    return check_launch("aether_bn_act_bwd");
 }
 
 namespace aether {
@@ -935,7 +1046,7 @@ extern "C" int aether_channel_scale(const float* x, const float* scale, float* y
     if (!x || !scale || !y || n <= 0 || C <= 0 || n % C) return set_error(AE_BAD_ARG, "aether_channel_scale: bad argument");
     if ((C & 3) == 0 && (!aligned16(x) || !aligned16(y) || !aligned16(scale)))
         return set_error(AE_BAD_ARG, "aether_channel_scale: arrays must be 16-byte aligned");
-    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, scale, nullptr, n, C);
+    affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, scale, nullptr, n, C, -1.f);
     count_launch();
     return check_launch("aether_channel_scale");
 }

@@ -255,11 +255,17 @@ class Pooling:
 
 # ------------------------------------------------------------------------------------- activations
 class ReLU:
-    """Drop-in for ``ReLU`` (CNN_classes_cupy.py:406-415)."""
+    """Drop-in for ``ReLU`` (CNN_classes_cupy.py:406-415).  With ``fused_into_prev`` (set by
+    ``Model.finalize(fuse=True)`` when the layer follows a Batch_Norm) the activation is applied by that
+    Batch_Norm's kernels and this layer only hands tensors through."""
     _alpha = 0.0
+    fused_into_prev = False
 
     def forward(self, inputs, training):
         x = to_device(inputs)
+        if self.fused_into_prev:
+            self.inputs = self.output = x
+            return self.output
         y = torch.empty_like(x)
         check(lib().aether_leaky_relu_fwd(_ptr(x), _ptr(y), x.numel(), float(self._alpha), _stream()),
               "aether_leaky_relu_fwd")
@@ -269,6 +275,9 @@ class ReLU:
 
     def backward(self, dvalues):
         dy = to_device(dvalues)
+        if self.fused_into_prev:
+            self.dinputs = dy
+            return self.dinputs
         dx = torch.empty_like(dy)
         check(lib().aether_leaky_relu_bwd(_ptr(self.inputs), _ptr(dy), _ptr(dx), dy.numel(), float(self._alpha),
                                           _stream()), "aether_leaky_relu_bwd")
@@ -402,6 +411,7 @@ class Batch_Norm:
         self._ws = _Workspace()
         self._keep = None
         self.stats_from = None          # a Conv_Layer whose forward leaves `bn_partials` for this layer's input
+        self.fused_alpha = None         # slope of the (Leaky_)ReLU applied inside this layer's kernels (None: not fused)
         if n_features is not None:
             self._create(n_features)
 
@@ -446,7 +456,16 @@ class Batch_Norm:
             self._bm = _empty((Cc,))
             self._bv = _empty((Cc,))
             part = getattr(self.stats_from, "bn_partials", None) if self.stats_from is not None else None
-            if part is not None and part[2] == x.data_ptr():
+            if part is not None and part[2] != x.data_ptr():
+                part = None
+            if self.fused_alpha is not None:
+                # y = act(bn(x)) in the same passes; the ReLU / Leaky_ReLU behind this layer only hands y through
+                check(L.aether_bn_act_fwd_train(_ptr(x), _ptr(part[0]) if part else None, part[1] if part else 0,
+                                                _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
+                                                _ptr(self._bm), _ptr(self._bv), _ptr(y), rows, Cc, float(self.epsilon),
+                                                float(self.momentum), float(self.fused_alpha), _ptr(ws), ws.numel(),
+                                                _stream()), "aether_bn_act_fwd_train")
+            elif part is not None:
                 # the convolution that produced x already reduced it per channel: merge its partials, read x once
                 check(L.aether_bn_fwd_train_partials(_ptr(x), _ptr(part[0]), part[1], _ptr(self.gamma), _ptr(self.beta),
                                                      _ptr(self._rm), _ptr(self._rv), _ptr(self._bm), _ptr(self._bv),
@@ -460,6 +479,10 @@ class Batch_Norm:
             self.batch_var = self._bv.view(keep)
             self.running_mean = self._rm.view(keep)       # the reference's stats pick up keep-dims here (:475-476)
             self.running_var = self._rv.view(keep)
+        elif self.fused_alpha is not None:
+            check(L.aether_bn_act_fwd_eval(_ptr(x), _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
+                                           _ptr(y), rows, Cc, float(self.epsilon), float(self.fused_alpha), _ptr(ws),
+                                           ws.numel(), _stream()), "aether_bn_act_fwd_eval")
         else:
             check(L.aether_bn_fwd_eval(_ptr(x), _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
                                        _ptr(y), rows, Cc, float(self.epsilon), _ptr(ws), ws.numel(), _stream()),
@@ -481,9 +504,15 @@ class Batch_Norm:
         else:
             self.dweights = _empty((Cc,))
             self.dbiases = _empty((Cc,))
-        check(L.aether_bn_bwd(_ptr(x), _ptr(dy), _ptr(self.gamma), _ptr(self._bm), _ptr(self._bv), _ptr(dx),
-                              _ptr(self.dweights), _ptr(self.dbiases), rows, Cc, float(self.epsilon), _ptr(ws),
-                              ws.numel(), _stream()), "aether_bn_bwd")
+        if self.fused_alpha is not None:     # dvalues is the gradient w.r.t. the ACTIVATED output kept in self.output
+            check(L.aether_bn_act_bwd(_ptr(x), _ptr(self.output), _ptr(dy), _ptr(self.gamma), _ptr(self._bm),
+                                      _ptr(self._bv), _ptr(dx), _ptr(self.dweights), _ptr(self.dbiases), rows, Cc,
+                                      float(self.epsilon), float(self.fused_alpha), _ptr(ws), ws.numel(), _stream()),
+                  "aether_bn_act_bwd")
+        else:
+            check(L.aether_bn_bwd(_ptr(x), _ptr(dy), _ptr(self.gamma), _ptr(self._bm), _ptr(self._bv), _ptr(dx),
+                                  _ptr(self.dweights), _ptr(self.dbiases), rows, Cc, float(self.epsilon), _ptr(ws),
+                                  ws.numel(), _stream()), "aether_bn_bwd")
         self.dinputs = dx
         return self.dinputs
 

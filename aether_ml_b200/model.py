@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from .layers import (Activation_Softmax_Loss_CategoricalCrossEntropy, Batch_Norm, Conv_Layer,
-                     Loss_CategoricalCrossEntropy, SoftMax, to_device, _labels_i32)
+                     Loss_CategoricalCrossEntropy, ReLU, SoftMax, to_device, _labels_i32)
 
 
 class Layer_Input:
@@ -102,7 +102,7 @@ class Model:
             self.accuracy = accuracy
 
     # ------------------------------------------------------------------ wiring
-    def finalize(self, flat=False):
+    def finalize(self, flat=False, fuse=False):
         self.input_layer = Layer_Input()
         chain = [self.input_layer] + self.layers + [self.loss]
         for pos, layer in enumerate(self.layers, start=1):
@@ -115,6 +115,12 @@ class Model:
             if isinstance(a, Conv_Layer) and isinstance(b, Batch_Norm):
                 a.emit_bn_stats = True
                 b.stats_from = a
+            # fuse=True: a ReLU / Leaky_ReLU directly behind a Batch_Norm is applied by the Batch_Norm's own kernels
+            # (one read and one write of the activation less each way).  The Batch_Norm's `output` is then the
+            # ACTIVATED tensor and the activation layer hands its input through unchanged.
+            if fuse and isinstance(a, Batch_Norm) and isinstance(b, ReLU):
+                a.fused_alpha = float(b._alpha)
+                b.fused_into_prev = True
         self.trainable_layers = [l for l in self.layers if hasattr(l, "weights")]
         if self.loss is not None:
             self.loss.remember_trainable_layers(self.trainable_layers)

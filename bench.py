@@ -332,7 +332,7 @@ def run_gpu(args):
 
 
 # ----------------------------------------------------------------------------------- training workload
-def build_cnn(widen, math_mode):
+def build_cnn(widen, math_mode, fuse=False):
     """The CIFAR-shaped 3-block CNN of the reference's README example (CNN/architectures/CNN_cifar1.py:16-55):
     Conv 3->32->64->128 (3x3 same) each with Batch_Norm / ReLU / [spatial dropout] / 2x2 max pool, Dense
     2048->256 LeakyReLU dropout, Dense 256->10, softmax + CCE (label smoothing 0.01), Adam lr 1e-3 decay 5e-5.
@@ -357,7 +357,7 @@ def build_cnn(widen, math_mode):
     m.add(Ly.SoftMax())
     m.set(loss=Ly.Loss_CategoricalCrossEntropy(label_smoothing=0.01),
           optimizer=Ly.Optimizer_Adam(learning_rate=1e-3, decay=5e-5), accuracy=Accuracy_Categorical())
-    m.finalize(flat=True)
+    m.finalize(flat=True, fuse=fuse)
     return m
 
 
@@ -373,7 +373,7 @@ def run_train(args):
     global_batch = args.global_batch or (4096 if widen == 4 else 128)
     lo, hi = dp.shard_bounds(global_batch, rank, world)
     np.random.seed(7)                                   # same initial parameters on every rank
-    model = build_cnn(widen, args.mode)
+    model = build_cnn(widen, args.mode, args.fuse)
     dp.attach(model)
     g = torch.Generator(device="cpu").manual_seed(3)
     X_host = torch.rand((global_batch, 32, 32, 3), generator=g)[lo:hi].contiguous().pin_memory()
@@ -442,7 +442,7 @@ def run_train(args):
                                    "Adam lr 1e-3 decay 5e-5" % (" widened 4x (128/256/512, Dense 8192->1024->10)" if widen == 4 else "", global_batch),
                        "per_gpu_batch": hi - lo, "parallelism": "dp%d, one NCCL all-reduce of the flat gradient buffer per step" % world,
                        "l2": "activations of a step (GBs) exceed the 126 MB L2", "params": int(model.flat_params.numel()),
-                       "cuda_graph": bool(args.graph)},
+                       "cuda_graph": bool(args.graph), "fused_bn_relu": bool(args.fuse)},
             "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": "images/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": (X_host.numel() * 4 + y_host.numel() * 4) * world, "d2h_bytes_per_step": 40 * world},
             "gpu_launches": int(launches), "clocks": clocks}))
@@ -464,6 +464,8 @@ def main():
     ap.add_argument("--batch", type=int, default=SHAPE["S"], help="per-GPU batch (smaller only for profiler captures)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU sample (profiler captures)")
     ap.add_argument("--graph", action="store_true", help="train workloads: replay the step from a captured CUDA graph")
+    ap.add_argument("--fuse", action="store_true",
+                    help="train workloads: apply each ReLU inside the Batch_Norm kernels in front of it (finalize(fuse=True))")
     args = ap.parse_args()
     SHAPE["S"] = args.batch
     if args.impl == "reference":

@@ -139,6 +139,27 @@ int aether_bn_fwd_eval(const float* x, const float* gamma, const float* beta, co
 int aether_bn_bwd(const float* x, const float* dy, const float* gamma, const float* batch_mean, const float* batch_var,
                   float* dx, float* dgamma, float* dbeta, int64_t rows, int C, float eps, void* ws, size_t ws_bytes,
                   void* stream);
+/* Batch_Norm immediately followed by ReLU / Leaky_ReLU (:406-428), both applied in the same passes over the data:
+ * y = act(bn(x)) with act(v) = v > 0 ? v : alpha*v (alpha = 0 is ReLU, 0 <= alpha < 1); the normalised but not yet
+ * activated tensor is never written.  The reference runs them as two layers with one more read and write of the
+ * activation each way.
+ *   aether_bn_act_fwd_train: Batch_Norm.forward (training) + activation.  `partials` may be NULL (x is reduced here)
+ *     or [nblocks][3][C] partial statistics from aether_conv2d_fwd_bnstats.  ws: aether_bn_workspace_bytes(rows, C).
+ *   aether_bn_act_fwd_eval: the same with the running statistics (ws: 2*C floats).
+ *   aether_bn_act_bwd: dy is the gradient w.r.t. y = act(bn(x)); y_act is that y.  The activation's derivative is
+ *     taken from the sign of y_act: identical to Leaky_ReLU.backward for alpha > 0; for alpha = 0 an output that is
+ *     exactly 0 blocks the gradient whereas ReLU.backward (:412-414, dvalues[inputs < 0] = 0) would pass it when the
+ *     pre-activation is exactly 0. */
+int aether_bn_act_fwd_train(const float* x, const float* partials, int64_t nblocks, const float* gamma, const float* beta,
+                            float* running_mean, float* running_var, float* batch_mean, float* batch_var, float* y,
+                            int64_t rows, int C, float eps, float momentum, float alpha, void* ws, size_t ws_bytes,
+                            void* stream);
+int aether_bn_act_fwd_eval(const float* x, const float* gamma, const float* beta, const float* running_mean,
+                           const float* running_var, float* y, int64_t rows, int C, float eps, float alpha, void* ws,
+                           size_t ws_bytes, void* stream);
+int aether_bn_act_bwd(const float* x, const float* y_act, const float* dy, const float* gamma, const float* batch_mean,
+                      const float* batch_var, float* dx, float* dgamma, float* dbeta, int64_t rows, int C, float eps,
+                      float alpha, void* ws, size_t ws_bytes, void* stream);
 
 /* ---- Pooling, 'valid' padding (CNN_classes_cupy.py:204-312) ---------------------------------- */
 /* Forward :212-273.  argmax (uint8, same shape as y; max pooling only) receives i*fW+j of the first

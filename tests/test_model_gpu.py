@@ -25,7 +25,7 @@ def host(t):
     return t.detach().cpu().numpy().astype(np.float64)
 
 
-def build(env, topology, mode, flat):
+def build(env, topology, mode, flat, fuse=False):
     torch, _lib, Ly, M = env
     np.random.seed(42)
     m = M.Model()
@@ -55,7 +55,7 @@ def build(env, topology, mode, flat):
     m.add(Ly.SoftMax())
     m.set(loss=Ly.Loss_CategoricalCrossEntropy(label_smoothing=0.01),
           optimizer=Ly.Optimizer_Adam(learning_rate=1e-3, decay=5e-5), accuracy=M.Accuracy_Categorical())
-    m.finalize(flat=flat)
+    m.finalize(flat=flat, fuse=fuse)
     return m, shape
 
 
@@ -230,3 +230,37 @@ def test_train_step_cuda_graph_matches_eager(env, hook):
     graph.train_step_graph(*batches[0])
     assert not np.array_equal(host(drop.binary_mask), m_last)
     assert abs((m_last > 0).mean() - (1 - 0.075)) < 0.05
+
+
+@pytest.mark.parametrize("topology", ["fmnist", "cifar"])
+def test_fused_batch_norm_activation_matches_unfused(env, topology):
+    """finalize(fuse=True): the ReLU behind every Batch_Norm is applied inside the Batch_Norm kernels (forward,
+    backward, inference).  Same parameters after training steps and same predictions as the layer-by-layer model."""
+    torch, _lib, Ly, M = env
+    rng = np.random.default_rng(21)
+    plain, shape = build(env, topology, "bf16", True, fuse=False)
+    fused, _ = build(env, topology, "bf16", True, fuse=True)
+    for m in (plain, fused):
+        m.enable_device_step()                             # identical dropout draws in both models
+        for k, l in enumerate(m.layers):
+            if hasattr(l, "seed"):
+                l.seed = 500 + k
+    assert any(getattr(l, "fused_into_prev", False) for l in fused.layers)
+    assert not any(getattr(l, "fused_into_prev", False) for l in plain.layers)
+    assert np.array_equal(host(plain.flat_params), host(fused.flat_params))
+    for _ in range(3):
+        X = rng.random((24,) + shape).astype(np.float32)
+        y = rng.integers(0, 10, 24)
+        op = plain.train_step(X, y)
+        of = fused.train_step(X, y)
+        assert O.rel_l2(host(of), host(op)) <= 1e-5
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert O.rel_l2(host(fused.flat_params), host(plain.flat_params)) <= 1e-5
+    assert O.rel_l2(host(fused.flat_grads), host(plain.flat_grads)) <= 1e-4
+    Xe = rng.random((16,) + shape).astype(np.float32)
+    assert O.rel_l2(host(fused.predict(Xe, batch_size=8)), host(plain.predict(Xe, batch_size=8))) <= 1e-5
+    # the fused Batch_Norm exposes the ACTIVATED tensor and the ReLU hands it through
+    bn = [l for l in fused.layers if isinstance(l, Ly.Batch_Norm)][0]
+    act = bn.next
+    assert act.output is bn.output and float(bn.output.min()) >= 0.0

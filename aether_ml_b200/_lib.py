@@ -46,9 +46,9 @@ SIGNATURES = {
     "aether_conv2d_bnstats_blocks": (_I64, [_D]),
     "aether_conv2d_fwd_bnstats": (_I, [_D, _P, _P, _P, _P, _P, _SZ, _P, _SZ, _P]),
     "aether_conv2d_bwd": (_I, [_D, _P, _P, _P, _P, _P, _P, _P, _SZ, _I, _P]),
-    "aether_bn_act_fwd_train": (_I, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _F, _P, _SZ, _P]),
+    "aether_bn_act_fwd_train": (_I, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _F, _P, _P, _SZ, _P]),
     "aether_bn_act_fwd_eval": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _SZ, _P]),
-    "aether_bn_act_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _SZ, _P]),
+    "aether_bn_act_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _P, _SZ, _P]),
     "aether_bn_fwd_train_partials": (_I, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _SZ, _P]),
     "aether_bn_workspace_bytes": (_SZ, [_I64, _I]),
     "aether_bn_fwd_train": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _SZ, _P]),

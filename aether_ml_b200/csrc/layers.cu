@@ -333,7 +333,10 @@ __global__ void __launch_bounds__(256) affine_channels_kernel(const float* __res
 __global__ void bn_finalize_bwd_kernel(const float* __restrict__ part, int nblocks, int C, long long rows,
                                        const float* __restrict__ gamma, const float* __restrict__ mean,
                                        const float* __restrict__ var, float eps, float* __restrict__ dgamma,
-                                       float* __restrict__ dbeta, float* __restrict__ coeff) {
+                                       float* __restrict__ dbeta, float* __restrict__ coeff,
+                                       const float* __restrict__ pscale) {
+    // pscale (nullable): per-channel factor that multiplied the layer's output (a fused spatial-dropout mask).  The
+    // upstream gradient is that factor times what the kernels summed, so it scales both sums and the dy coefficient.
     __shared__ double red_a[8][32], red_b[8][32];
     const int cl = threadIdx.x & 31, ln = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + cl;
@@ -350,13 +353,16 @@ __global__ void bn_finalize_bwd_kernel(const float* __restrict__ part, int nbloc
     double sdy = 0.0, sdyx = 0.0;
 #pragma unroll
     for (int l = 0; l < 8; ++l) { sdy += red_a[l][cl]; sdyx += red_b[l][cl]; }
+    const double ms = pscale ? (double)pscale[c] : 1.0;
+    sdy *= ms;
+    sdyx *= ms;
     dgamma[c] = (float)sdyx;
     dbeta[c] = (float)sdy;
     // dx = gamma*inv/N * (N*dy - sum(dy) - xhat * sum(dy*xhat)),  xhat = (x - mean) * inv
     //    = k1*dy + k2*x + k3
     const double inv = 1.0 / sqrt((double)var[c] + (double)eps);
     const double g = gamma[c], N = (double)rows, mu = mean[c];
-    const double k1 = g * inv;
+    const double k1 = g * inv * ms;
     const double k2 = -g * inv * inv * sdyx / N;
     const double k3 = -g * inv * sdy / N - k2 * mu;
     coeff[c] = (float)k1;
@@ -556,7 +562,7 @@ extern "C" int aether_bn_bwd(const float* x, const float* dy, const float* gamma
     float* coeff = part + (size_t)nb * 3 * C;
     launch_bn_reduce<1>(nb, st, x, dy, batch_mean, batch_var, eps, rows, C, part);
     bn_finalize_bwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
-                                                            dbeta, coeff);
+                                                            dbeta, coeff, nullptr);
     const long long n = rows * C;
     bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C, nullptr, 0.f);
     count_launch(3);
@@ -567,6 +573,13 @@ extern "C" int aether_bn_bwd(const float* x, const float* dy, const float* gamma
 // forward : y = act(bn(x)); the normalised, not yet activated tensor is never written.
 // backward: dy is the gradient w.r.t. y; the activation's derivative is taken from the sign of y while the
 //           statistics pass and the dx pass read it, so the ReLU's own backward pass disappears as well.
+__global__ void coeff_scale_kernel(float* __restrict__ scale_shift, const float* __restrict__ m, int C) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    scale_shift[c] *= m[c];
+    scale_shift[C + c] *= m[c];
+}
+
 static int bn_act_check(const char* who, int64_t rows, int C, float alpha, const void* a, const void* b, const void* c) {
     if (rows <= 0 || C <= 0) return set_error(AE_BAD_ARG, "%s: rows=%lld C=%d", who, (long long)rows, C);
     if (!(alpha >= 0.f && alpha < 1.f)) return set_error(AE_BAD_ARG, "%s: alpha must be in [0, 1)", who);
@@ -578,7 +591,7 @@ static int bn_act_check(const char* who, int64_t rows, int C, float alpha, const
 extern "C" int aether_bn_act_fwd_train(const float* x, const float* partials, int64_t nblocks, const float* gamma,
                                        const float* beta, float* running_mean, float* running_var, float* batch_mean,
                                        float* batch_var, float* y, int64_t rows, int C, float eps, float momentum,
-                                       float alpha, void* ws, size_t ws_bytes, void* stream) {
+                                       float alpha, const float* channel_scale, void* ws, size_t ws_bytes, void* stream) {
     if (!x || !gamma || !beta || !running_mean || !running_var || !batch_mean || !batch_var || !y || !ws)
         return set_error(AE_BAD_ARG, "aether_bn_act_fwd_train: null pointer");
     int rc = bn_act_check("aether_bn_act_fwd_train", rows, C, alpha, x, y, ws);
@@ -599,6 +612,12 @@ extern "C" int aether_bn_act_fwd_train(const float* x, const float* partials, in
     }
     bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(src, nb, C, gamma, beta, eps, momentum, running_mean, running_var,
                                                             batch_mean, batch_var, coeff);
+    if (channel_scale) {
+        // act(v) * m = act(m * v) for m >= 0 (ReLU and Leaky_ReLU are positively homogeneous): a spatial-dropout
+        // mask behind the activation is folded into the affine coefficients, at no cost per element
+        coeff_scale_kernel<<<ceil_div(C, 128), 128, 0, st>>>(coeff, channel_scale, C);
+        count_launch();
+    }
     const long long n = rows * C;
     affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C, alpha);
     count_launch(2);
@@ -624,7 +643,8 @@ extern "C" int aether_bn_act_fwd_eval(const float* x, const float* gamma, const 
 
 extern "C" int aether_bn_act_bwd(const float* x, const float* y_act, const float* dy, const float* gamma,
                                  const float* batch_mean, const float* batch_var, float* dx, float* dgamma, float* dbeta,
-                                 int64_t rows, int C, float eps, float alpha, void* ws, size_t ws_bytes, void* stream) {
+                                 int64_t rows, int C, float eps, float alpha, const float* channel_scale, void* ws,
+                                 size_t ws_bytes, void* stream) {
     if (!x || !y_act || !dy || !gamma || !batch_mean || !batch_var || !dx || !dgamma || !dbeta || !ws)
         return set_error(AE_BAD_ARG, "aether_bn_act_bwd: null pointer");
     int rc = bn_act_check("aether_bn_act_bwd", rows, C, alpha, x, dy, dx);
@@ -637,7 +657,7 @@ extern "C" int aether_bn_act_bwd(const float* x, const float* y_act, const float
     float* coeff = part + (size_t)nb * 3 * C;
     launch_bn_reduce<1>(nb, st, x, dy, batch_mean, batch_var, eps, rows, C, part, y_act, alpha);
     bn_finalize_bwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
-                                                            dbeta, coeff);
+                                                            dbeta, coeff, channel_scale);
     const long long n = rows * C;
     bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C, y_act, alpha);
     count_launch(3);

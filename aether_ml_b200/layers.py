@@ -312,14 +312,10 @@ class Layer_Dropout_Spatial:
         self.seed = Layer_Dropout_Spatial._next_seed
         Layer_Dropout_Spatial._next_seed += 1
         self.step_dev = None            # int64 device counter: draw the mask on the device (CUDA-graph train step)
+        self.fused_into_prev = False    # the Batch_Norm in front applies the mask (Model.finalize(fuse=True))
 
-    def forward(self, inputs, training):
-        x = to_device(inputs)
-        self.inputs = x
-        if not training:
-            self.output = x.clone()
-            return self.output
-        Cc = x.shape[-1]
+    def draw_mask(self, Cc):
+        """Draws this step's channel mask (Bernoulli(keep)/keep per channel) into ``channel_mask``."""
         if self.fixed_mask is None and self.step_dev is not None:
             self.channel_mask = _empty((1, 1, 1, Cc))
             check(lib().aether_channel_mask_dev(_ptr(self.channel_mask), Cc, float(self.keep_prob), self.seed,
@@ -330,6 +326,19 @@ class Layer_Dropout_Spatial:
             else:
                 mask = (np.random.binomial(1, self.keep_prob, size=(1, 1, 1, Cc)) / self.keep_prob).astype(np.float32)
             self.channel_mask = to_device(mask)
+        return self.channel_mask
+
+    def forward(self, inputs, training):
+        x = to_device(inputs)
+        self.inputs = x
+        if self.fused_into_prev:        # already masked by the fused Batch_Norm (training) / identity (inference)
+            self.output = x
+            return self.output
+        if not training:
+            self.output = x.clone()
+            return self.output
+        Cc = x.shape[-1]
+        self.draw_mask(Cc)
         y = torch.empty_like(x)
         check(lib().aether_channel_scale(_ptr(x), _ptr(self.channel_mask), _ptr(y), x.numel(), Cc, _stream()),
               "aether_channel_scale")
@@ -338,6 +347,9 @@ class Layer_Dropout_Spatial:
 
     def backward(self, dvalues):
         dy = to_device(dvalues)
+        if self.fused_into_prev:
+            self.dinputs = dy
+            return self.dinputs
         dx = torch.empty_like(dy)
         check(lib().aether_channel_scale(_ptr(dy), _ptr(self.channel_mask), _ptr(dx), dy.numel(), dy.shape[-1],
                                          _stream()), "aether_channel_scale")
@@ -412,6 +424,7 @@ class Batch_Norm:
         self._keep = None
         self.stats_from = None          # a Conv_Layer whose forward leaves `bn_partials` for this layer's input
         self.fused_alpha = None         # slope of the (Leaky_)ReLU applied inside this layer's kernels (None: not fused)
+        self.fused_dropout = None       # a Layer_Dropout_Spatial behind that activation whose mask is applied here too
         if n_features is not None:
             self._create(n_features)
 
@@ -459,12 +472,14 @@ class Batch_Norm:
             if part is not None and part[2] != x.data_ptr():
                 part = None
             if self.fused_alpha is not None:
-                # y = act(bn(x)) in the same passes; the ReLU / Leaky_ReLU behind this layer only hands y through
+                # y = act(bn(x)) [* spatial-dropout mask] in the same passes; the layers behind only hand y through
+                mask = self.fused_dropout.draw_mask(Cc) if self.fused_dropout is not None else None
                 check(L.aether_bn_act_fwd_train(_ptr(x), _ptr(part[0]) if part else None, part[1] if part else 0,
                                                 _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
                                                 _ptr(self._bm), _ptr(self._bv), _ptr(y), rows, Cc, float(self.epsilon),
-                                                float(self.momentum), float(self.fused_alpha), _ptr(ws), ws.numel(),
-                                                _stream()), "aether_bn_act_fwd_train")
+                                                float(self.momentum), float(self.fused_alpha), _ptr(mask), _ptr(ws),
+                                                ws.numel(), _stream()), "aether_bn_act_fwd_train")
+                self._fused_mask = mask
             elif part is not None:
                 # the convolution that produced x already reduced it per channel: merge its partials, read x once
                 check(L.aether_bn_fwd_train_partials(_ptr(x), _ptr(part[0]), part[1], _ptr(self.gamma), _ptr(self.beta),
@@ -507,8 +522,8 @@ class Batch_Norm:
         if self.fused_alpha is not None:     # dvalues is the gradient w.r.t. the ACTIVATED output kept in self.output
             check(L.aether_bn_act_bwd(_ptr(x), _ptr(self.output), _ptr(dy), _ptr(self.gamma), _ptr(self._bm),
                                       _ptr(self._bv), _ptr(dx), _ptr(self.dweights), _ptr(self.dbiases), rows, Cc,
-                                      float(self.epsilon), float(self.fused_alpha), _ptr(ws), ws.numel(), _stream()),
-                  "aether_bn_act_bwd")
+                                      float(self.epsilon), float(self.fused_alpha), _ptr(getattr(self, "_fused_mask", None)),
+                                      _ptr(ws), ws.numel(), _stream()), "aether_bn_act_bwd")
         else:
             check(L.aether_bn_bwd(_ptr(x), _ptr(dy), _ptr(self.gamma), _ptr(self._bm), _ptr(self._bv), _ptr(dx),
                                   _ptr(self.dweights), _ptr(self.dbiases), rows, Cc, float(self.epsilon), _ptr(ws),

@@ -16,7 +16,7 @@ import pickle
 import numpy as np
 import torch
 
-from .layers import (Activation_Softmax_Loss_CategoricalCrossEntropy, Batch_Norm, Conv_Layer,
+from .layers import (Activation_Softmax_Loss_CategoricalCrossEntropy, Batch_Norm, Conv_Layer, Layer_Dropout_Spatial,
                      Loss_CategoricalCrossEntropy, ReLU, SoftMax, to_device, _labels_i32)
 
 
@@ -121,6 +121,12 @@ class Model:
             if fuse and isinstance(a, Batch_Norm) and isinstance(b, ReLU):
                 a.fused_alpha = float(b._alpha)
                 b.fused_into_prev = True
+                # ... and a Layer_Dropout_Spatial behind that activation: its per-channel mask is folded into the
+                # Batch_Norm's per-channel coefficients (act(v) * m = act(m * v) for m >= 0)
+                c = getattr(b, "next", None)
+                if isinstance(c, Layer_Dropout_Spatial):
+                    a.fused_dropout = c
+                    c.fused_into_prev = True
         self.trainable_layers = [l for l in self.layers if hasattr(l, "weights")]
         if self.loss is not None:
             self.loss.remember_trainable_layers(self.trainable_layers)

@@ -149,17 +149,20 @@ int aether_bn_bwd(const float* x, const float* dy, const float* gamma, const flo
  *   aether_bn_act_bwd: dy is the gradient w.r.t. y = act(bn(x)); y_act is that y.  The activation's derivative is
  *     taken from the sign of y_act: identical to Leaky_ReLU.backward for alpha > 0; for alpha = 0 an output that is
  *     exactly 0 blocks the gradient whereas ReLU.backward (:412-414, dvalues[inputs < 0] = 0) would pass it when the
- *     pre-activation is exactly 0. */
+ *     pre-activation is exactly 0.
+ *   channel_scale (C floats >= 0, or NULL): the mask / keep_prob of a Layer_Dropout_Spatial (:384-404) that follows
+ *     the activation; y = act(bn(x)) * channel_scale[c] and the backward treats dy as the gradient w.r.t. that y.
+ *     (Folded into the per-channel coefficients: act(v) * m = act(m * v) for m >= 0.) */
 int aether_bn_act_fwd_train(const float* x, const float* partials, int64_t nblocks, const float* gamma, const float* beta,
                             float* running_mean, float* running_var, float* batch_mean, float* batch_var, float* y,
-                            int64_t rows, int C, float eps, float momentum, float alpha, void* ws, size_t ws_bytes,
-                            void* stream);
+                            int64_t rows, int C, float eps, float momentum, float alpha, const float* channel_scale,
+                            void* ws, size_t ws_bytes, void* stream);
 int aether_bn_act_fwd_eval(const float* x, const float* gamma, const float* beta, const float* running_mean,
                            const float* running_var, float* y, int64_t rows, int C, float eps, float alpha, void* ws,
                            size_t ws_bytes, void* stream);
 int aether_bn_act_bwd(const float* x, const float* y_act, const float* dy, const float* gamma, const float* batch_mean,
                       const float* batch_var, float* dx, float* dgamma, float* dbeta, int64_t rows, int C, float eps,
-                      float alpha, void* ws, size_t ws_bytes, void* stream);
+                      float alpha, const float* channel_scale, void* ws, size_t ws_bytes, void* stream);
 
 /* ---- Pooling, 'valid' padding (CNN_classes_cupy.py:204-312) ---------------------------------- */
 /* Forward :212-273.  argmax (uint8, same shape as y; max pooling only) receives i*fW+j of the first

@@ -235,9 +235,13 @@ def test_train_step_cuda_graph_matches_eager(env, hook):
 @pytest.mark.parametrize("topology", ["fmnist", "cifar"])
 def test_fused_batch_norm_activation_matches_unfused(env, topology):
     """finalize(fuse=True): the ReLU behind every Batch_Norm is applied inside the Batch_Norm kernels (forward,
-    backward, inference).  Same parameters after training steps and same predictions as the layer-by-layer model."""
+    backward, inference), and in the CIFAR topology the spatial-dropout mask behind it is folded into the Batch_Norm
+    coefficients.  Same parameters after training steps and same predictions as the layer-by-layer model: to
+    rounding without the mask (identical arithmetic), to bf16 noise with it (the mask multiplies the coefficients
+    instead of the activations, and a last-bit difference can flip a bf16 rounding in the next convolution)."""
     torch, _lib, Ly, M = env
     rng = np.random.default_rng(21)
+    tol = 1e-5 if topology == "fmnist" else 5e-3
     plain, shape = build(env, topology, "bf16", True, fuse=False)
     fused, _ = build(env, topology, "bf16", True, fuse=True)
     for m in (plain, fused):
@@ -253,13 +257,15 @@ def test_fused_batch_norm_activation_matches_unfused(env, topology):
         y = rng.integers(0, 10, 24)
         op = plain.train_step(X, y)
         of = fused.train_step(X, y)
-        assert O.rel_l2(host(of), host(op)) <= 1e-5
+        assert O.rel_l2(host(of), host(op)) <= tol
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
-    assert O.rel_l2(host(fused.flat_params), host(plain.flat_params)) <= 1e-5
-    assert O.rel_l2(host(fused.flat_grads), host(plain.flat_grads)) <= 1e-4
+    assert O.rel_l2(host(fused.flat_params), host(plain.flat_params)) <= tol
+    assert O.rel_l2(host(fused.flat_grads), host(plain.flat_grads)) <= 10 * tol
     Xe = rng.random((16,) + shape).astype(np.float32)
-    assert O.rel_l2(host(fused.predict(Xe, batch_size=8)), host(plain.predict(Xe, batch_size=8))) <= 1e-5
+    assert O.rel_l2(host(fused.predict(Xe, batch_size=8)), host(plain.predict(Xe, batch_size=8))) <= tol
+    drops = [l for l in fused.layers if isinstance(l, Ly.Layer_Dropout_Spatial)]
+    assert all(d.fused_into_prev and d.output is d.inputs for d in drops)
     # the fused Batch_Norm exposes the ACTIVATED tensor and the ReLU hands it through
     bn = [l for l in fused.layers if isinstance(l, Ly.Batch_Norm)][0]
     act = bn.next

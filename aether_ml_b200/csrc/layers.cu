@@ -727,6 +727,39 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__
     }
 }
 
+// Backward for windows that tile the input exactly (stride == filter, H and W multiples of it; the 2x2/2 pooling of
+// every reference network): one thread per (window, 4 channels) reads dy and the argmax code once and writes the
+// fH*fW cells of its window -- no per-cell index decode, every byte moved exactly once.
+template <bool MAX>
+__global__ void __launch_bounds__(256) pool_bwd_tiled_kernel(const float* __restrict__ dy, const uint8_t* __restrict__ arg,
+                                                             float* __restrict__ dx, unsigned total, int W, int C4,
+                                                             int fH, int fW, int Ho, int Wo) {
+    const float inv = 1.f / (float)(fH * fW);
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const unsigned cv = idx % (unsigned)C4;
+        unsigned pix = idx / (unsigned)C4;
+        const unsigned wo = pix % (unsigned)Wo;
+        pix /= (unsigned)Wo;                                   // = s * Ho + ho
+        const float4 g = __ldcs(reinterpret_cast<const float4*>(dy) + idx);
+        uchar4 a = make_uchar4(0, 0, 0, 0);
+        if (MAX) a = reinterpret_cast<const uchar4*>(arg)[idx];
+        // first cell of the window: input row pix*fH (rows of all samples are stacked: H = Ho*fH), column wo*fW
+        float4* out = reinterpret_cast<float4*>(dx) + ((size_t)pix * fH * W + (size_t)wo * fW) * C4 + cv;
+        for (int i = 0; i < fH; ++i)
+            for (int j = 0; j < fW; ++j) {
+                float4 o;
+                if (MAX) {
+                    const unsigned char code = (unsigned char)(i * fW + j);
+                    o = make_float4(a.x == code ? g.x : 0.f, a.y == code ? g.y : 0.f, a.z == code ? g.z : 0.f,
+                                    a.w == code ? g.w : 0.f);
+                } else {
+                    o = make_float4(g.x * inv, g.y * inv, g.z * inv, g.w * inv);
+                }
+                out[((size_t)i * W + j) * C4] = o;
+            }
+    }
+}
+
 // Backward in gather form: each input cell sums the dy of every window that selected it (max) or
 // that covers it (average).  No atomics; cells outside every window get zero.
 template <bool MAX, int VEC, typename I>
@@ -1027,6 +1060,16 @@ extern "C" int aether_pool_bwd(const float* dy, const uint8_t* argmax, float* dx
     const long long total = 1LL * S * H * W * (vec ? C / 4 : C);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int nb = blocks_for(total, 256, 16);
+    const long long windows4 = 1LL * S * Ho * Wo * (C / 4);
+    if (vec && sH == fH && sW == fW && H == Ho * fH && W == Wo * fW && windows4 < (1LL << 32) - (1LL << 22)) {
+        const int nbt = blocks_for(windows4, 256, 16);
+        if (kind == AETHER_POOL_MAX)
+            pool_bwd_tiled_kernel<true><<<nbt, 256, 0, st>>>(dy, argmax, dx, (unsigned)windows4, W, C / 4, fH, fW, Ho, Wo);
+        else
+            pool_bwd_tiled_kernel<false><<<nbt, 256, 0, st>>>(dy, nullptr, dx, (unsigned)windows4, W, C / 4, fH, fW, Ho, Wo);
+        count_launch();
+        return check_launch("aether_pool_bwd");
+    }
 #define AETHER_POOL_BWD(MAXK, V, I, ARG) \
     pool_bwd_kernel<MAXK, V, I><<<nb, 256, 0, st>>>(dy, ARG, dx, S, H, W, C, fH, fW, sH, sW, Ho, Wo)
     const bool small = total < (1LL << 31);

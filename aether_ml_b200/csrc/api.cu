@@ -162,6 +162,7 @@ extern "C" int aether_conv2d_fwd(const AetherConvDesc* d, const float* x, const 
     if ((rc = pending_timeout("aether_conv2d_fwd"))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, nullptr, ws, ws_bytes, st);
+    if (first_tc_eligible(*d)) return first_tc_fwd(*d, x, w, b, y, nullptr, st);
     if (smallc_conv_eligible(*d) && (!b || aligned16(b))) return smallc_conv_fwd(*d, x, w, b, y, nullptr, st);
     return generic_conv_fwd(*d, x, w, b, y, st);
 }
@@ -169,6 +170,7 @@ extern "C" int aether_conv2d_fwd(const AetherConvDesc* d, const float* x, const 
 extern "C" int64_t aether_conv2d_bnstats_blocks(const AetherConvDesc* d) {
     if (validate_desc(d, "aether_conv2d_bnstats_blocks")) return 0;
     if (tc_conv_eligible(*d)) return tc_conv_stats_blocks(*d);
+    if (first_tc_eligible(*d)) return first_tc_stats_blocks(*d);
     if (smallc_conv_eligible(*d)) return smallc_conv_stats_blocks(*d);
     return 0;
 }
@@ -190,6 +192,7 @@ extern "C" int aether_conv2d_fwd_bnstats(const AetherConvDesc* d, const float* x
     if ((rc = pending_timeout("aether_conv2d_fwd_bnstats"))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, stats, ws, ws_bytes, st);
+    if (first_tc_eligible(*d)) return first_tc_fwd(*d, x, w, b, y, stats, st);
     return smallc_conv_fwd(*d, x, w, b, y, stats, st);
 }
 

@@ -52,6 +52,12 @@ long long smallc_conv_stats_blocks(const AetherConvDesc& d);
 int smallc_conv_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy, float* dw, float* db, void* ws,
                            size_t ws_bytes, cudaStream_t st);
 
+// ---- conv_first_tc.cu : first-layer forward on tensor cores (bf16 mode, thread-built im2col operand)
+bool first_tc_eligible(const AetherConvDesc& d);
+long long first_tc_stats_blocks(const AetherConvDesc& d);
+int first_tc_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, float* stats,
+                 cudaStream_t st);
+
 // ---- conv_tc.cu : tcgen05 implicit-GEMM convolution (stride 1)
 bool tc_conv_eligible(const AetherConvDesc& d);
 size_t tc_conv_workspace_bytes(const AetherConvDesc& d);

@@ -1,0 +1,401 @@
+// First-layer convolution (1..4 input channels, K = fH*fW*Cin <= 64) on the tensor cores, bf16 mode.
+//
+//   y[p][d] = b[d] + sum_k col[p][k] * w[k][d]            (Conv_Layer.forward, CNN_classes_cupy.py:70-120)
+//
+// With 3 input channels a pixel's 12 bytes cannot be the inner extent of a TMA box and K = 27 is less than one
+// 128-byte operand row, so the im2col rows are built by threads: four producer warps gather the K input values of
+// 128 output pixels (one pixel per thread), convert them to bf16 and write them as a K-major, 128-byte-swizzled
+// operand tile (16-byte chunk c of row r is stored at chunk c ^ (r % 8)); the filter is laid out the same way once
+// per CTA.  One warp issues K/16 (two for a 3x3 RGB filter) 128 x Cout x 16 MMAs per tile into one of up to four
+// TMEM accumulators; eight epilogue warps add the bias and write 64-byte row segments straight from registers, and
+// optionally accumulate the per-channel statistics the following Batch_Norm needs.  The layer is bound by the HBM
+// write of its output (the CUDA-core version of the same layer, conv_smallc.cu, is bound by its FMAs).
+#include <cuda_bf16.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "tc_host.cuh"
+
+namespace aether {
+
+struct FirstParams {
+    const float* x;
+    const float* w;      // (fH, fW, Cin, Cout) = [K][Cout]
+    const float* bias;   // nullable
+    float* y;
+    float* stats;        // nullable: [cta][4][3][Cout] (count, mean, M2) partials
+    int* status;
+    int H, W, Cin, Cout, NT, fH, fW, sH, sW, pH, pW, Ho, Wo, K, KP;
+    long long P;         // output pixels
+    int stages, ntiles;
+};
+
+static constexpr int FT_PROD_WARPS = 4;
+static constexpr int FT_EPI_WARPS = 8;
+static constexpr int FT_THREADS = 32 * (FT_PROD_WARPS + 1 + FT_EPI_WARPS);   // producers, MMA issuer, epilogue
+static constexpr int FT_STAGE_BYTES = 128 * 128;                             // 128 pixel rows of 128 bytes
+static constexpr int FT_TAIL = 2048;                                         // barriers, TMEM pointer, bias, k tables
+static constexpr int FT_STATS_BYTES = FT_EPI_WARPS * 2 * 128 * 4;
+
+__device__ __forceinline__ void ft_umma(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(hi), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <bool STATS>
+__global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_constant__ FirstParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const int NT = p.NT, S = p.stages;
+    const uint32_t sW = smem_base;                                  // filter: NT rows of 128 bytes
+    const uint32_t sA = sW + (uint32_t)NT * 128u;                   // NT is a multiple of 16 -> 1024-byte multiple? see host
+    const uint32_t sBar = sA + (uint32_t)S * FT_STAGE_BYTES;
+    auto full_bar = [&](int s) { return sBar + 8u * s; };
+    auto empty_bar = [&](int s) { return sBar + 8u * (S + s); };
+    auto tfull_bar = [&](int b) { return sBar + 8u * (2 * S + b); };
+    auto tempty_bar = [&](int b) { return sBar + 8u * (2 * S + 4 + b); };
+    const uint32_t sTmemPtr = sBar + 8u * (2 * S + 8);
+    volatile uint32_t* tmem_ptr_generic = reinterpret_cast<volatile uint32_t*>(gen_base + (sTmemPtr - smem_base));
+    float* bias_s = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + 256);         // NT <= 256 floats
+    int* koff_s = reinterpret_cast<int*>(gen_base + (sBar - smem_base) + 256 + 1024);      // K <= 64 entries each
+    int* ki_s = koff_s + 64;
+    int* kj_s = ki_s + 64;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t NB = (4 * NT <= 512) ? 4u : (3 * NT <= 512) ? 3u : 2u;
+    const uint32_t need_cols = NB * (uint32_t)NT;
+    const uint32_t tmem_cols = (need_cols <= 32) ? 32u : (need_cols <= 64) ? 64u : (need_cols <= 128) ? 128u : (need_cols <= 256) ? 256u : 512u;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full_bar(s), 32 * FT_PROD_WARPS);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 4; ++b) {
+            mbar_init(tfull_bar(b), 1);
+            mbar_init(tempty_bar(b), FT_EPI_WARPS);
+        }
+        mbar_fence_init();
+    }
+    for (int i = threadIdx.x; i < NT; i += blockDim.x) bias_s[i] = (p.bias != nullptr && i < p.Cout) ? p.bias[i] : 0.f;
+    for (int k = threadIdx.x; k < 64; k += blockDim.x) {
+        const int kk = k < p.K ? k : 0;
+        const int tap = kk / p.Cin, c = kk - tap * p.Cin;
+        const int i = tap / p.fW, j = tap - i * p.fW;
+        ki_s[k] = k < p.K ? i : (1 << 20);                         // entries past K fail the bounds test: zero
+        kj_s[k] = j;
+        koff_s[k] = (i * p.W + j) * p.Cin + c;
+    }
+    // filter operand: row n = output channel, element k at byte (k/8 ^ n%8)*16 + (k%8)*2 of the row
+    for (int it = threadIdx.x; it < NT * (p.KP >> 3); it += blockDim.x) {
+        const int n = it / (p.KP >> 3), ch = it - n * (p.KP >> 3);
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int k = ch * 8 + e;
+            v[e] = (n < p.Cout && k < p.K) ? p.w[(size_t)k * p.Cout + n] : 0.f;
+        }
+        const uint4 q = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        *reinterpret_cast<uint4*>(gen_base + (sW - smem_base) + n * 128 + ((ch ^ (n & 7)) << 4)) = q;
+    }
+    fence_proxy_async_smem();
+    if (warp == FT_PROD_WARPS) {
+        tmem_alloc(sTmemPtr, tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_generic;
+    const int grid = (int)gridDim.x;
+
+    if (warp < FT_PROD_WARPS) {
+        // ------------------------------------------------------------------ producers: one output pixel per thread
+        const int r = threadIdx.x;                                  // row of the operand tile
+        uint8_t* row_gen = gen_base + (sA - smem_base) + r * 128;
+        const int chunks = p.KP >> 3;
+        const long long HoWo = (long long)p.Ho * p.Wo;
+        int s = 0;
+        uint32_t ph = 0;
+        for (int t = blockIdx.x; t < p.ntiles; t += grid) {
+            const long long pix = (long long)t * 128 + r;
+            int h0 = -(1 << 20), w0 = 0;
+            long long base = 0;
+            if (pix < p.P) {
+                const long long n = pix / HoWo;
+                const int rem = (int)(pix - n * HoWo);
+                const int ho = rem / p.Wo, wo = rem - ho * p.Wo;
+                h0 = ho * p.sH - p.pH;
+                w0 = wo * p.sW - p.pW;
+                base = ((n * p.H + h0) * p.W + w0) * p.Cin;          // may point before the image: only used with valid taps
+            }
+            if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) break;
+            uint8_t* dst = row_gen + s * FT_STAGE_BYTES;
+            for (int ch = 0; ch < chunks; ++ch) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int k = ch * 8 + e;
+                    const int hi = h0 + ki_s[k], wi = w0 + kj_s[k];
+                    v[e] = (hi >= 0 && hi < p.H && wi >= 0 && wi < p.W) ? __ldg(p.x + base + koff_s[k]) : 0.f;
+                }
+                const uint4 q = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+                *reinterpret_cast<uint4*>(dst + ((ch ^ (r & 7)) << 4)) = q;
+            }
+            fence_proxy_async_smem();                               // generic-proxy writes -> visible to the tensor core
+            mbar_arrive(full_bar(s));
+            if (++s == S) { s = 0; ph ^= 1u; }
+        }
+    } else if (warp == FT_PROD_WARPS) {
+        // ------------------------------------------------------------------ MMA issuer
+        const bool leader = elect_one();
+        const uint32_t idesc = make_idesc(1u, 0u, 0u, 128u, (uint32_t)NT);
+        const uint64_t proto = make_smem_desc(0, 16, 1024);
+        const uint32_t hi = (uint32_t)(proto >> 32);
+        const uint32_t lo_proto = (uint32_t)proto;
+        const uint32_t w_lo = lo_proto + ((sW & 0x3FFFFu) >> 4);
+        const uint32_t a_lo0 = lo_proto + ((sA & 0x3FFFFu) >> 4);
+        const int ksteps = p.KP >> 4;
+        int s = 0;
+        uint32_t ph = 0, buf = 0, aph = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < p.ntiles && ok; t += grid) {
+            bool w_ok = mbar_wait_spin(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY);
+            w_ok = __all_sync(0xffffffffu, w_ok);
+            if (!w_ok) { ok = false; break; }
+            bool f_ok = mbar_wait_spin(full_bar(s), ph, p.status, DS_TIMEOUT_FULL);
+            f_ok = __all_sync(0xffffffffu, f_ok);
+            if (!f_ok) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + buf * NT;
+            const uint32_t a_lo = a_lo0 + (uint32_t)s * (FT_STAGE_BYTES >> 4);
+            if (leader) {
+                for (int ks = 0; ks < ksteps; ++ks) ft_umma(d_tmem, a_lo + 2u * ks, w_lo + 2u * ks, hi, idesc, ks ? 1u : 0u);
+                umma_commit(empty_bar(s));
+                umma_commit(tfull_bar(buf));
+            }
+            if (++s == S) { s = 0; ph ^= 1u; }
+            if (++buf == NB) { buf = 0; aph ^= 1u; }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (same scheme as conv_halo.cu)
+        const int ew = warp - FT_PROD_WARPS - 1;
+        const int q = warp & 3;                                      // TMEM lane quarter this warp may access
+        const int half = ew >> 2;
+        const int ncols = NT >> 1;
+        const int col_begin = half * ncols;
+        const int trow = lane >> 2, tcol4 = (lane & 3) * 4;
+        const bool lo2 = (lane & 2) == 0, odd = (lane & 1) != 0;
+        const bool all_cols = (p.Cout == NT);
+        float* stat_w = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + FT_TAIL) + ew * 256;
+        float st_rows = 0.f;
+        if (STATS) {
+            for (int i = lane; i < 256; i += 32) stat_w[i] = 0.f;
+            __syncwarp();
+        }
+        int row_in_tile[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) row_in_tile[j] = q * 32 + (j >> 1) * 16 + trow + (j & 1) * 8;
+        const float* bias4 = bias_s + col_begin + tcol4;
+        uint32_t buf = 0, aph = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < p.ntiles && ok; t += grid) {
+            float* rowp[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const long long pix = (long long)t * 128 + row_in_tile[j];
+                rowp[j] = pix < p.P ? p.y + (size_t)pix * p.Cout + col_begin + tcol4 : nullptr;
+            }
+            if (!mbar_wait(tfull_bar(buf), aph, p.status, DS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NT + col_begin;
+#pragma unroll 1
+            for (int cb = 0; cb < ncols; cb += 64) {
+                uint32_t v[2][4][8];
+                float4 st_s[4], st_q[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) st_s[u] = st_q[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (cb + u * 16 < ncols) {
+                        tmem_ld_16x256b_x2(taddr0 + cb + u * 16, v[0][u]);
+                        tmem_ld_16x256b_x2(taddr0 + (16u << 16) + cb + u * 16, v[1][u]);
+                    }
+                }
+                tmem_ld_wait();
+                if (cb + 64 >= ncols) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (cb + u * 16 < ncols) {
+                        const int cc = cb + u * 16;
+                        const float4 b4 = *reinterpret_cast<const float4*>(bias4 + cc);
+                        const bool cols_ok = all_cols || col_begin + tcol4 + cc < p.Cout;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            // quad exchange: 2+2 columns per lane -> 4 consecutive columns per lane (64-byte row segments)
+                            const uint32_t a0 = v[j >> 1][u][(j & 1) * 2 + 0], a1 = v[j >> 1][u][(j & 1) * 2 + 1];
+                            const uint32_t b0 = v[j >> 1][u][4 + (j & 1) * 2 + 0], b1 = v[j >> 1][u][4 + (j & 1) * 2 + 1];
+                            const uint32_t s0 = lo2 ? b0 : a0, s1 = lo2 ? b1 : a1;
+                            const uint32_t r0 = __shfl_xor_sync(0xffffffffu, s0, 2), r1 = __shfl_xor_sync(0xffffffffu, s1, 2);
+                            const uint32_t x0 = lo2 ? a0 : r0, x1 = lo2 ? a1 : r1;
+                            const uint32_t y0 = lo2 ? r0 : b0, y1 = lo2 ? r1 : b1;
+                            const uint32_t t0 = odd ? x0 : y0, t1 = odd ? x1 : y1;
+                            const uint32_t q0 = __shfl_xor_sync(0xffffffffu, t0, 1), q1 = __shfl_xor_sync(0xffffffffu, t1, 1);
+                            float4 a;
+                            a.x = __uint_as_float(odd ? q0 : x0);
+                            a.y = __uint_as_float(odd ? q1 : x1);
+                            a.z = __uint_as_float(odd ? y0 : q0);
+                            a.w = __uint_as_float(odd ? y1 : q1);
+                            const bool wr = cols_ok && rowp[j] != nullptr;
+                            if (wr)
+                                __stcs(reinterpret_cast<float4*>(rowp[j] + cc),
+                                       make_float4(a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w));
+                            if (STATS) {
+                                a.x = wr ? a.x : 0.f; a.y = wr ? a.y : 0.f; a.z = wr ? a.z : 0.f; a.w = wr ? a.w : 0.f;
+                                st_s[u].x += a.x; st_s[u].y += a.y; st_s[u].z += a.z; st_s[u].w += a.w;
+                                st_q[u].x = fmaf(a.x, a.x, st_q[u].x); st_q[u].y = fmaf(a.y, a.y, st_q[u].y);
+                                st_q[u].z = fmaf(a.z, a.z, st_q[u].z); st_q[u].w = fmaf(a.w, a.w, st_q[u].w);
+                            }
+                        }
+                    }
+                }
+                if (STATS) {
+                    if (cb == 0) {
+                        float nrows = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) nrows += (rowp[j] != nullptr) ? 1.f : 0.f;
+                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 4);
+                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 8);
+                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 16);
+                        st_rows += nrows;
+                    }
+#pragma unroll
+                    for (int m = 4; m <= 16; m <<= 1) {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            st_s[u].x += __shfl_xor_sync(0xffffffffu, st_s[u].x, m); st_s[u].y += __shfl_xor_sync(0xffffffffu, st_s[u].y, m);
+                            st_s[u].z += __shfl_xor_sync(0xffffffffu, st_s[u].z, m); st_s[u].w += __shfl_xor_sync(0xffffffffu, st_s[u].w, m);
+                            st_q[u].x += __shfl_xor_sync(0xffffffffu, st_q[u].x, m); st_q[u].y += __shfl_xor_sync(0xffffffffu, st_q[u].y, m);
+                            st_q[u].z += __shfl_xor_sync(0xffffffffu, st_q[u].z, m); st_q[u].w += __shfl_xor_sync(0xffffffffu, st_q[u].w, m);
+                        }
+                    }
+                    if (lane < 4) {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int cc = cb + u * 16;
+                            if (cc < ncols) {
+                                float4* ps = reinterpret_cast<float4*>(stat_w + cc + tcol4);
+                                float4* pq = reinterpret_cast<float4*>(stat_w + 128 + cc + tcol4);
+                                float4 s = *ps, qq = *pq;
+                                s.x += st_s[u].x; s.y += st_s[u].y; s.z += st_s[u].z; s.w += st_s[u].w;
+                                qq.x += st_q[u].x; qq.y += st_q[u].y; qq.z += st_q[u].z; qq.w += st_q[u].w;
+                                *ps = s;
+                                *pq = qq;
+                            }
+                        }
+                    }
+                }
+            }
+            if (++buf == NB) { buf = 0; aph ^= 1u; }
+        }
+        if (STATS && lane < 4) {
+            float* sp = p.stats + ((size_t)blockIdx.x * 4 + q) * 3 * (size_t)p.Cout;
+            const float inv_n = st_rows > 0.f ? 1.f / st_rows : 0.f;
+            for (int cc = 0; cc < ncols; cc += 16) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int col = col_begin + tcol4 + cc + k;
+                    if (col < p.Cout) {
+                        const float s = stat_w[cc + tcol4 + k], qq = stat_w[128 + cc + tcol4 + k];
+                        const float m = s * inv_n;
+                        sp[col] = st_rows;
+                        sp[p.Cout + col] = m + bias_s[col];
+                        sp[2 * p.Cout + col] = fmaxf(qq - s * m, 0.f);
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == FT_PROD_WARPS) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+// ---------------------------------------------------------------------------------- host
+static bool first_tc_shape(const AetherConvDesc& d, int& K, int& KP, int& NT, int& Ho, int& Wo) {
+    if (d.math_mode != AETHER_MATH_BF16) return false;
+    K = d.fH * d.fW * d.Cin;
+    if (d.Cin > 4 || K > 64) return false;
+    if (d.Cout % 4 || d.Cout < 16 || d.Cout > 256) return false;
+    KP = (K + 15) / 16 * 16;
+    NT = (d.Cout + 63) / 64 * 64;              // two column halves of 16-column groups; filter rows fill whole 8-row atoms
+    conv_out_hw(d, Ho, Wo);
+    if (Ho < 1 || Wo < 1) return false;
+    const long long P = 1LL * d.S * Ho * Wo;
+    return (P + 127) / 128 < 0x7fffffffLL && 1LL * d.S * d.H * d.W * d.Cin < (1LL << 40);
+}
+
+bool first_tc_eligible(const AetherConvDesc& d) {
+    int K, KP, NT, Ho, Wo;
+    return first_tc_shape(d, K, KP, NT, Ho, Wo);
+}
+
+static int first_tc_grid(long long ntiles) { return (int)(ntiles < num_sms() ? ntiles : num_sms()); }
+
+long long first_tc_stats_blocks(const AetherConvDesc& d) {
+    int K, KP, NT, Ho, Wo;
+    if (!first_tc_shape(d, K, KP, NT, Ho, Wo)) return 0;
+    const long long P = 1LL * d.S * Ho * Wo;
+    return 4LL * first_tc_grid((P + 127) / 128);
+}
+
+int first_tc_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, float* stats,
+                 cudaStream_t st) {
+    int K, KP, NT, Ho, Wo;
+    if (!first_tc_shape(d, K, KP, NT, Ho, Wo)) return set_error(AE_UNSUPPORTED, "first_tc_fwd: shape not supported");
+    FirstParams p;
+    memset(&p, 0, sizeof(p));
+    p.x = x; p.w = w; p.bias = b; p.y = y; p.stats = stats; p.status = device_status_word();
+    p.H = d.H; p.W = d.W; p.Cin = d.Cin; p.Cout = d.Cout; p.NT = NT; p.fH = d.fH; p.fW = d.fW; p.sH = d.sH; p.sW = d.sW;
+    p.pH = d.padH; p.pW = d.padW; p.Ho = Ho; p.Wo = Wo; p.K = K; p.KP = KP;
+    p.P = 1LL * d.S * Ho * Wo;
+    p.ntiles = (int)((p.P + 127) / 128);
+    p.stages = 4;
+    const int smem = 1024 + NT * 128 + p.stages * FT_STAGE_BYTES + FT_TAIL + FT_STATS_BYTES;
+    static bool configured[2] = {false, false};
+    const int ki = stats ? 1 : 0;
+    if (!configured[ki]) {
+        cudaError_t e = stats ? cudaFuncSetAttribute(first_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448)
+                              : cudaFuncSetAttribute(first_conv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+        if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(first_conv): %s", cudaGetErrorString(e));
+        configured[ki] = true;
+    }
+    const int grid = first_tc_grid(p.ntiles);
+    if (stats) first_conv_kernel<true><<<grid, FT_THREADS, smem, st>>>(p);
+    else first_conv_kernel<false><<<grid, FT_THREADS, smem, st>>>(p);
+    count_launch();
+    return check_launch("first_conv_kernel");
+}
+
+}  // namespace aether

@@ -207,6 +207,7 @@ extern "C" int aether_conv2d_bwd(const AetherConvDesc* d, const float* x, const 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (tc_conv_eligible(*d)) return tc_conv_bwd(*d, x, dy, w, dx, dw, db, ws, ws_bytes, x_shadow_valid, st);
     if (dx && (rc = generic_conv_bwd_data(*d, dy, w, dx, st))) return rc;
+    if (dw && first_tc_bwd_eligible(*d)) return first_tc_bwd_filter(*d, x, dy, dw, db, ws, ws_bytes, st);
     if ((dw || db) && smallc_conv_eligible(*d) && (!db || aligned16(db)))
         return smallc_conv_bwd_filter(*d, x, dy, dw, db, ws, ws_bytes, st);
     if (dw || db) return generic_conv_bwd_filter(*d, x, dy, dw, db, ws, ws_bytes, st);

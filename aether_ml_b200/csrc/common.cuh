@@ -57,6 +57,10 @@ bool first_tc_eligible(const AetherConvDesc& d);
 long long first_tc_stats_blocks(const AetherConvDesc& d);
 int first_tc_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, float* stats,
                  cudaStream_t st);
+bool first_tc_bwd_eligible(const AetherConvDesc& d);
+int first_tc_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy, float* dw, float* db, void* ws,
+                        size_t ws_bytes, cudaStream_t st);
+int smallc_reduce_partials(const float* part, int nb, int K, int Cout, float* dw, float* db, cudaStream_t st);
 
 // ---- conv_tc.cu : tcgen05 implicit-GEMM convolution (stride 1)
 bool tc_conv_eligible(const AetherConvDesc& d);

@@ -342,6 +342,235 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
     }
 }
 
+// ====================================================================================== filter / bias gradient
+//   dw[k][d] = sum_p col[p][k] * dy[p][d],  db[d] = sum_p dy[p][d]            (Conv_Layer.backward, :132-134)
+// as D[d][k] += dy^T[d][pixels] * col[pixels][k]: M = 128 output channels (two 64-channel chunks of an MN-major
+// operand), N = K padded to 16, reduction over the 128 pixels of a tile in eight K=16 steps.  The producers build
+// both operands: the col tile exactly as in the forward kernel (the same bytes serve as an MN-major B operand) and
+// the dy tile converted from fp32 to bf16; they also keep the fp32 column sums of dy for db.  The accumulators stay
+// in TMEM for the CTA's whole life; one partial per CTA, summed in fixed order by smallc_reduce_kernel.
+struct FirstDwParams {
+    const float* x;
+    const float* dy;
+    float* part;         // [cta][K + 1][Cout]
+    int* status;
+    int H, W, Cin, Cout, fH, fW, sH, sW, pH, pW, Ho, Wo, K, KP;
+    int dblocks;         // 128-channel blocks of dy
+    long long P;
+    int stages, ntiles, stage_bytes;
+};
+
+static constexpr int FD_THREADS = 32 * (FT_PROD_WARPS + 1 + 4);              // producers, MMA issuer, 4 epilogue warps
+
+__global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_constant__ FirstDwParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const int S = p.stages;
+    const uint32_t sBar = smem_base + (uint32_t)S * p.stage_bytes;           // stage: col tile, then 2*dblocks dy chunks
+    auto full_bar = [&](int s) { return sBar + 8u * s; };
+    auto empty_bar = [&](int s) { return sBar + 8u * (S + s); };
+    const uint32_t done_bar = sBar + 8u * (2 * S);
+    const uint32_t sTmemPtr = sBar + 8u * (2 * S + 1);
+    volatile uint32_t* tmem_ptr_generic = reinterpret_cast<volatile uint32_t*>(gen_base + (sTmemPtr - smem_base));
+    int* koff_s = reinterpret_cast<int*>(gen_base + (sBar - smem_base) + 256);
+    int* ki_s = koff_s + 64;
+    int* kj_s = ki_s + 64;
+    float* dbsum_s = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + 1024);      // [128 producer threads][8]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t tmem_cols = 128;                                          // dblocks (<= 2) x KP (<= 64) columns
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full_bar(s), 32 * FT_PROD_WARPS);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(done_bar, 1);
+        mbar_fence_init();
+    }
+    for (int k = threadIdx.x; k < 64; k += blockDim.x) {
+        const int kk = k < p.K ? k : 0;
+        const int tap = kk / p.Cin, c = kk - tap * p.Cin;
+        const int i = tap / p.fW, j = tap - i * p.fW;
+        ki_s[k] = k < p.K ? i : (1 << 20);
+        kj_s[k] = j;
+        koff_s[k] = (i * p.W + j) * p.Cin + c;
+    }
+    if (warp == FT_PROD_WARPS) {
+        tmem_alloc(sTmemPtr, tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_generic;
+    const int grid = (int)gridDim.x;
+    const bool any = (int)blockIdx.x < p.ntiles;
+
+    if (warp < FT_PROD_WARPS) {
+        // ------------------------------------------------------------------ producers
+        const int r = threadIdx.x;
+        const int chunks = p.KP >> 3;
+        const int C8 = p.Cout >> 3;                                  // 8-channel chunks of a dy row (power of two <= 32)
+        const int my_chunk = r & (C8 - 1);                           // fixed for this thread: 128 % C8 == 0
+        const int prow0 = r / C8, prow_step = 128 / C8;
+        const int dchunks = p.dblocks * 16;                          // 8-channel chunks the operand holds (zero padded)
+        const long long HoWo = (long long)p.Ho * p.Wo;
+        float bs[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) bs[e] = 0.f;
+        if (C8 < dchunks) {
+            // fewer than 128 channels: the chunks past Cout of the M = 128 operand are zero and stay zero (nobody
+            // writes them again); each thread's own fence before its first arrive publishes them
+            for (int i = r; i < S * p.stage_bytes / 16; i += 32 * FT_PROD_WARPS)
+                reinterpret_cast<uint4*>(gen_base)[i] = make_uint4(0, 0, 0, 0);
+        }
+        int s = 0;
+        uint32_t ph = 0;
+        for (int t = blockIdx.x; t < p.ntiles; t += grid) {
+            const long long pix0 = (long long)t * 128;
+            const long long pix = pix0 + r;
+            int h0 = -(1 << 20), w0 = 0;
+            long long base = 0;
+            if (pix < p.P) {
+                const long long n = pix / HoWo;
+                const int rem = (int)(pix - n * HoWo);
+                const int ho = rem / p.Wo, wo = rem - ho * p.Wo;
+                h0 = ho * p.sH - p.pH;
+                w0 = wo * p.sW - p.pW;
+                base = ((n * p.H + h0) * p.W + w0) * p.Cin;
+            }
+            if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) break;
+            uint8_t* stage = gen_base + (size_t)s * p.stage_bytes;
+            // col tile: row r = this thread's pixel (the forward kernel's operand, read here as MN-major B)
+            uint8_t* dst = stage + r * 128;
+            for (int ch = 0; ch < chunks; ++ch) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int k = ch * 8 + e;
+                    const int hi = h0 + ki_s[k], wi = w0 + kj_s[k];
+                    v[e] = (hi >= 0 && hi < p.H && wi >= 0 && wi < p.W) ? __ldg(p.x + base + koff_s[k]) : 0.f;
+                }
+                const uint4 q = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+                *reinterpret_cast<uint4*>(dst + ((ch ^ (r & 7)) << 4)) = q;
+            }
+            // dy tile: rows = pixels, 64-channel chunks of 128 bytes; chunk region c64 starts at 16 KB * (1 + c64)
+            uint8_t* reg = stage + FT_STAGE_BYTES * (1 + (my_chunk >> 3));
+            for (int pr0 = prow0; pr0 < 128; pr0 += 4 * prow_step) {
+                // four rows per round, all eight loads issued before the first use (the HBM latency needs them in flight)
+                float4 a[4], b[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int pr = pr0 + u * prow_step;
+                    const long long pp = pix0 + pr;
+                    a[u] = b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (pr < 128 && pp < p.P) {
+                        const float4* src = reinterpret_cast<const float4*>(p.dy + (size_t)pp * p.Cout + my_chunk * 8);
+                        a[u] = __ldcs(src);
+                        b[u] = __ldcs(src + 1);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int pr = pr0 + u * prow_step;
+                    if (pr < 128) {
+                        bs[0] += a[u].x; bs[1] += a[u].y; bs[2] += a[u].z; bs[3] += a[u].w;
+                        bs[4] += b[u].x; bs[5] += b[u].y; bs[6] += b[u].z; bs[7] += b[u].w;
+                        const uint4 q = make_uint4(pack_bf16(a[u].x, a[u].y), pack_bf16(a[u].z, a[u].w),
+                                                   pack_bf16(b[u].x, b[u].y), pack_bf16(b[u].z, b[u].w));
+                        *reinterpret_cast<uint4*>(reg + pr * 128 + (((my_chunk & 7) ^ (pr & 7)) << 4)) = q;
+                    }
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(full_bar(s));
+            if (++s == S) { s = 0; ph ^= 1u; }
+        }
+        // db: fp32 column sums of this thread's 8 channels; threads with the same chunk are added in fixed order
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dbsum_s[r * 8 + e] = bs[e];
+        named_bar_sync(1, 32 * FT_PROD_WARPS);
+        for (int c = r; c < p.Cout; c += 32 * FT_PROD_WARPS) {
+            const int ck = c >> 3, e = c & 7;
+            float tsum = 0.f;
+            for (int th = ck; th < 128; th += C8) tsum += dbsum_s[th * 8 + e];
+            p.part[(size_t)blockIdx.x * (p.K + 1) * p.Cout + (size_t)p.K * p.Cout + c] = tsum;
+        }
+    } else if (warp == FT_PROD_WARPS) {
+        // ------------------------------------------------------------------ MMA issuer
+        const bool leader = elect_one();
+        const uint32_t idesc = make_idesc(1u, 1u, 1u, 128u, (uint32_t)p.KP);      // A and B MN-major
+        const uint32_t hi = (uint32_t)(make_smem_desc(0, 0, 1024) >> 32);          // SBO = 8 reduction rows
+        const uint32_t a_lbo = ((uint32_t)FT_STAGE_BYTES >> 4) << 16;              // next 64-channel chunk of dy
+        int s = 0;
+        uint32_t ph = 0, acc = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < p.ntiles && ok; t += grid) {
+            bool f_ok = mbar_wait_spin(full_bar(s), ph, p.status, DS_TIMEOUT_FULL);
+            f_ok = __all_sync(0xffffffffu, f_ok);
+            if (!f_ok) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t st16 = ((smem_base + (uint32_t)s * p.stage_bytes) & 0x3FFFFu) >> 4;
+            if (leader) {
+                for (int db = 0; db < p.dblocks; ++db) {
+                    const uint32_t a0 = st16 + ((uint32_t)FT_STAGE_BYTES >> 4) * (1u + 2u * db);
+                    for (uint32_t ks = 0; ks < 8; ++ks)
+                        asm volatile(
+                            "{\n\t.reg .pred pp;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 pp, %5, 0;\n\t"
+                            "mov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, pp;\n\t}"
+                            ::"r"(tmem_base + (uint32_t)(db * 64)), "r"((a0 + ks * 128u) | a_lbo), "r"(st16 + ks * 128u),
+                              "r"(idesc), "r"(hi), "r"((ks | acc) ? 1u : 0u)
+                            : "memory");
+                }
+                umma_commit(empty_bar(s));
+            }
+            acc = 1u;
+            if (++s == S) { s = 0; ph ^= 1u; }
+            __syncwarp();
+        }
+        if (leader) umma_commit(done_bar);
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue: one partial per CTA
+        const int q = warp & 3;
+        bool ok = true;
+        if (any) ok = mbar_wait(done_bar, 0, p.status, DS_TIMEOUT_TMEM_FULL);
+        tc_fence_after();
+        if (ok) {
+            float* out = p.part + (size_t)blockIdx.x * (p.K + 1) * p.Cout;
+            for (int db = 0; db < p.dblocks; ++db) {
+                const int d = db * 128 + q * 32 + lane;
+                for (int cg = 0; cg < p.KP; cg += 32) {
+                    uint32_t v[32];
+                    if (any) {
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + db * 64 + cg, v);
+                        tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 32; ++k) v[k] = 0u;
+                    }
+                    if (d < p.Cout) {
+#pragma unroll
+                        for (int k = 0; k < 32; ++k)
+                            if (cg + k < p.K) out[(size_t)(cg + k) * p.Cout + d] = __uint_as_float(v[k]);
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == FT_PROD_WARPS) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
 // ---------------------------------------------------------------------------------- host
 static bool first_tc_shape(const AetherConvDesc& d, int& K, int& KP, int& NT, int& Ho, int& Wo) {
     if (d.math_mode != AETHER_MATH_BF16) return false;
@@ -396,6 +625,46 @@ int first_tc_fwd(const AetherConvDesc& d, const float* x, const float* w, const 
     else first_conv_kernel<false><<<grid, FT_THREADS, smem, st>>>(p);
     count_launch();
     return check_launch("first_conv_kernel");
+}
+
+// dW / dB on the tensor cores need, on top of the forward's conditions, a power-of-two filter count (the producers'
+// thread -> channel-chunk mapping) -- the same shapes conv_smallc.cu takes.
+bool first_tc_bwd_eligible(const AetherConvDesc& d) {
+    return first_tc_eligible(d) && smallc_conv_eligible(d) && d.Cout % 8 == 0;
+}
+
+int first_tc_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy, float* dw, float* db, void* ws,
+                        size_t ws_bytes, cudaStream_t st) {
+    int K, KP, NT, Ho, Wo;
+    if (!first_tc_bwd_eligible(d) || !first_tc_shape(d, K, KP, NT, Ho, Wo))
+        return set_error(AE_UNSUPPORTED, "first_tc_bwd_filter: shape not supported");
+    FirstDwParams p;
+    memset(&p, 0, sizeof(p));
+    p.x = x; p.dy = dy; p.part = static_cast<float*>(ws); p.status = device_status_word();
+    p.H = d.H; p.W = d.W; p.Cin = d.Cin; p.Cout = d.Cout; p.fH = d.fH; p.fW = d.fW; p.sH = d.sH; p.sW = d.sW;
+    p.pH = d.padH; p.pW = d.padW; p.Ho = Ho; p.Wo = Wo; p.K = K; p.KP = KP;
+    p.dblocks = (d.Cout + 127) / 128;
+    p.P = 1LL * d.S * Ho * Wo;
+    p.ntiles = (int)((p.P + 127) / 128);
+    p.stage_bytes = FT_STAGE_BYTES * (1 + 2 * p.dblocks);
+    const int tail = 6144;                                     // barriers, k tables, dB staging
+    p.stages = (232448 - 1024 - tail) / p.stage_bytes;
+    if (p.stages > 4) p.stages = 4;
+    const int grid = first_tc_grid(p.ntiles);
+    const size_t need = (size_t)grid * (K + 1) * d.Cout * sizeof(float);
+    if (!ws || ws_bytes < need) return set_error(AE_BAD_ARG, "conv workspace too small: %zu < %zu", ws_bytes, need);
+    const int smem = 1024 + p.stages * p.stage_bytes + tail;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(first_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+        if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(first_dw): %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    first_dw_kernel<<<grid, FD_THREADS, smem, st>>>(p);
+    count_launch();
+    int rc = check_launch("first_dw_kernel");
+    if (rc) return rc;
+    return smallc_reduce_partials(p.part, grid, K, d.Cout, dw, db, st);
 }
 
 }  // namespace aether

@@ -365,4 +365,11 @@ int smallc_conv_bwd_filter(const AetherConvDesc& d, const float* x, const float*
     return check_launch("smallc_reduce_kernel");
 }
 
+// Sums nb partials of [K + 1][Cout] floats (row K = dB) into dw / db in fixed order (also used by conv_first_tc.cu).
+int smallc_reduce_partials(const float* part, int nb, int K, int Cout, float* dw, float* db, cudaStream_t st) {
+    smallc_reduce_kernel<<<ceil_div((K + 1) * Cout, 32), 256, 0, st>>>(part, nb, K, Cout, dw, db);
+    count_launch();
+    return check_launch("smallc_reduce_kernel");
+}
+
 }  // namespace aether

@@ -31,7 +31,7 @@ struct FirstParams {
     int stages, ntiles;
 };
 
-static constexpr int FT_PROD_WARPS = 4;
+static constexpr int FT_PROD_WARPS = 8;       // two threads per pixel: a lone producer warp per scheduler cannot hide the gather latency
 static constexpr int FT_EPI_WARPS = 8;
 static constexpr int FT_THREADS = 32 * (FT_PROD_WARPS + 1 + FT_EPI_WARPS);   // producers, MMA issuer, epilogue
 static constexpr int FT_STAGE_BYTES = 128 * 128;                             // 128 pixel rows of 128 bytes
@@ -122,8 +122,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
     const int grid = (int)gridDim.x;
 
     if (warp < FT_PROD_WARPS) {
-        // ------------------------------------------------------------------ producers: one output pixel per thread
-        const int r = threadIdx.x;                                  // row of the operand tile
+        // ------------------------------------------------------------------ producers: one output pixel per thread pair
+        const int r = threadIdx.x & 127;                            // row of the operand tile
+        const int ch0 = threadIdx.x >> 7, ch_step = (32 * FT_PROD_WARPS) >> 7;   // this thread's 16-byte chunks of the row
         uint8_t* row_gen = gen_base + (sA - smem_base) + r * 128;
         const int chunks = p.KP >> 3;
         const long long HoWo = (long long)p.Ho * p.Wo;
@@ -143,7 +144,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
             }
             if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) break;
             uint8_t* dst = row_gen + s * FT_STAGE_BYTES;
-            for (int ch = 0; ch < chunks; ++ch) {
+            for (int ch = ch0; ch < chunks; ch += ch_step) {
                 float v[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
@@ -360,7 +361,13 @@ struct FirstDwParams {
     int stages, ntiles, stage_bytes;
 };
 
-static constexpr int FD_THREADS = 32 * (FT_PROD_WARPS + 1 + 4);              // producers, MMA issuer, 4 epilogue warps
+// Twelve producer warps: with one producer warp per scheduler every round of dy loads costs a full HBM round trip
+// and the kernel ran at a third of the HBM rate; 384 threads cover a 128-pixel tile of dy in one or two rounds.
+static constexpr int FD_PROD_WARPS = 12;
+static constexpr int FD_NP = 32 * FD_PROD_WARPS;
+static constexpr int FD_ROWS = 6;                                            // dy rows per thread and round
+static constexpr int FD_TAIL = 1024 + FD_NP * 8 * 4 + 1024;                  // barriers, k tables, dB staging
+static constexpr int FD_THREADS = 32 * (FD_PROD_WARPS + 1 + 4);              // producers, MMA issuer, 4 epilogue warps
 
 __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_constant__ FirstDwParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -376,7 +383,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
     int* koff_s = reinterpret_cast<int*>(gen_base + (sBar - smem_base) + 256);
     int* ki_s = koff_s + 64;
     int* kj_s = ki_s + 64;
-    float* dbsum_s = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + 1024);      // [128 producer threads][8]
+    float* dbsum_s = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + 1024);      // [producer threads][8]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -384,7 +391,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            mbar_init(full_bar(s), 32 * FT_PROD_WARPS);
+            mbar_init(full_bar(s), FD_NP);
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(done_bar, 1);
@@ -398,7 +405,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
         kj_s[k] = j;
         koff_s[k] = (i * p.W + j) * p.Cin + c;
     }
-    if (warp == FT_PROD_WARPS) {
+    if (warp == FD_PROD_WARPS) {
         tmem_alloc(sTmemPtr, tmem_cols);
         tmem_relinquish();
     }
@@ -409,13 +416,14 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
     const int grid = (int)gridDim.x;
     const bool any = (int)blockIdx.x < p.ntiles;
 
-    if (warp < FT_PROD_WARPS) {
+    if (warp < FD_PROD_WARPS) {
         // ------------------------------------------------------------------ producers
-        const int r = threadIdx.x;
+        const int r = threadIdx.x;                                   // 0 .. FD_NP-1
         const int chunks = p.KP >> 3;
+        const int col_items = 128 * chunks;                          // item -> pixel = item % 128, 16-byte chunk = item / 128
         const int C8 = p.Cout >> 3;                                  // 8-channel chunks of a dy row (power of two <= 32)
-        const int my_chunk = r & (C8 - 1);                           // fixed for this thread: 128 % C8 == 0
-        const int prow0 = r / C8, prow_step = 128 / C8;
+        const int my_chunk = r & (C8 - 1);                           // fixed for this thread: FD_NP % C8 == 0
+        const int prow0 = r / C8, prow_step = FD_NP / C8;
         const int dchunks = p.dblocks * 16;                          // 8-channel chunks the operand holds (zero padded)
         const long long HoWo = (long long)p.Ho * p.Wo;
         float bs[8];
@@ -424,46 +432,22 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
         if (C8 < dchunks) {
             // fewer than 128 channels: the chunks past Cout of the M = 128 operand are zero and stay zero (nobody
             // writes them again); each thread's own fence before its first arrive publishes them
-            for (int i = r; i < S * p.stage_bytes / 16; i += 32 * FT_PROD_WARPS)
+            for (int i = r; i < S * p.stage_bytes / 16; i += FD_NP)
                 reinterpret_cast<uint4*>(gen_base)[i] = make_uint4(0, 0, 0, 0);
         }
         int s = 0;
         uint32_t ph = 0;
         for (int t = blockIdx.x; t < p.ntiles; t += grid) {
             const long long pix0 = (long long)t * 128;
-            const long long pix = pix0 + r;
-            int h0 = -(1 << 20), w0 = 0;
-            long long base = 0;
-            if (pix < p.P) {
-                const long long n = pix / HoWo;
-                const int rem = (int)(pix - n * HoWo);
-                const int ho = rem / p.Wo, wo = rem - ho * p.Wo;
-                h0 = ho * p.sH - p.pH;
-                w0 = wo * p.sW - p.pW;
-                base = ((n * p.H + h0) * p.W + w0) * p.Cin;
-            }
             if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) break;
             uint8_t* stage = gen_base + (size_t)s * p.stage_bytes;
-            // col tile: row r = this thread's pixel (the forward kernel's operand, read here as MN-major B)
-            uint8_t* dst = stage + r * 128;
-            for (int ch = 0; ch < chunks; ++ch) {
-                float v[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const int k = ch * 8 + e;
-                    const int hi = h0 + ki_s[k], wi = w0 + kj_s[k];
-                    v[e] = (hi >= 0 && hi < p.H && wi >= 0 && wi < p.W) ? __ldg(p.x + base + koff_s[k]) : 0.f;
-                }
-                const uint4 q = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-                *reinterpret_cast<uint4*>(dst + ((ch ^ (r & 7)) << 4)) = q;
-            }
-            // dy tile: rows = pixels, 64-channel chunks of 128 bytes; chunk region c64 starts at 16 KB * (1 + c64)
+            // dy tile first (the long-latency loads): rows = pixels, 64-channel chunks of 128 bytes; chunk region c64
+            // starts at 16 KB * (1 + c64).  All loads of a round are issued before the first use.
             uint8_t* reg = stage + FT_STAGE_BYTES * (1 + (my_chunk >> 3));
-            for (int pr0 = prow0; pr0 < 128; pr0 += 4 * prow_step) {
-                // four rows per round, all eight loads issued before the first use (the HBM latency needs them in flight)
-                float4 a[4], b[4];
+            for (int pr0 = prow0; pr0 < 128; pr0 += FD_ROWS * prow_step) {
+                float4 a[FD_ROWS], b[FD_ROWS];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < FD_ROWS; ++u) {
                     const int pr = pr0 + u * prow_step;
                     const long long pp = pix0 + pr;
                     a[u] = b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -474,7 +458,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < FD_ROWS; ++u) {
                     const int pr = pr0 + u * prow_step;
                     if (pr < 128) {
                         bs[0] += a[u].x; bs[1] += a[u].y; bs[2] += a[u].z; bs[3] += a[u].w;
@@ -485,6 +469,30 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
                     }
                 }
             }
+            // col tile: row = pixel of the tile (the forward kernel's operand, read here as MN-major B)
+            for (int it = r; it < col_items; it += FD_NP) {
+                const int pr = it & 127, ch = it >> 7;
+                const long long pix = pix0 + pr;
+                int h0 = -(1 << 20), w0 = 0;
+                long long base = 0;
+                if (pix < p.P) {
+                    const long long n = pix / HoWo;
+                    const int rem = (int)(pix - n * HoWo);
+                    const int ho = rem / p.Wo, wo = rem - ho * p.Wo;
+                    h0 = ho * p.sH - p.pH;
+                    w0 = wo * p.sW - p.pW;
+                    base = ((n * p.H + h0) * p.W + w0) * p.Cin;
+                }
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int k = ch * 8 + e;
+                    const int hi = h0 + ki_s[k], wi = w0 + kj_s[k];
+                    v[e] = (hi >= 0 && hi < p.H && wi >= 0 && wi < p.W) ? __ldg(p.x + base + koff_s[k]) : 0.f;
+                }
+                const uint4 q = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+                *reinterpret_cast<uint4*>(stage + pr * 128 + ((ch ^ (pr & 7)) << 4)) = q;
+            }
             fence_proxy_async_smem();
             mbar_arrive(full_bar(s));
             if (++s == S) { s = 0; ph ^= 1u; }
@@ -492,14 +500,14 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
         // db: fp32 column sums of this thread's 8 channels; threads with the same chunk are added in fixed order
 #pragma unroll
         for (int e = 0; e < 8; ++e) dbsum_s[r * 8 + e] = bs[e];
-        named_bar_sync(1, 32 * FT_PROD_WARPS);
-        for (int c = r; c < p.Cout; c += 32 * FT_PROD_WARPS) {
+        named_bar_sync(1, FD_NP);
+        for (int c = r; c < p.Cout; c += FD_NP) {
             const int ck = c >> 3, e = c & 7;
             float tsum = 0.f;
-            for (int th = ck; th < 128; th += C8) tsum += dbsum_s[th * 8 + e];
+            for (int th = ck; th < FD_NP; th += C8) tsum += dbsum_s[th * 8 + e];
             p.part[(size_t)blockIdx.x * (p.K + 1) * p.Cout + (size_t)p.K * p.Cout + c] = tsum;
         }
-    } else if (warp == FT_PROD_WARPS) {
+    } else if (warp == FD_PROD_WARPS) {
         // ------------------------------------------------------------------ MMA issuer
         const bool leader = elect_one();
         const uint32_t idesc = make_idesc(1u, 1u, 1u, 128u, (uint32_t)p.KP);      // A and B MN-major
@@ -565,7 +573,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
 
     tc_fence_before();
     __syncthreads();
-    if (warp == FT_PROD_WARPS) {
+    if (warp == FD_PROD_WARPS) {
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);
     }
@@ -647,7 +655,7 @@ int first_tc_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy
     p.P = 1LL * d.S * Ho * Wo;
     p.ntiles = (int)((p.P + 127) / 128);
     p.stage_bytes = FT_STAGE_BYTES * (1 + 2 * p.dblocks);
-    const int tail = 6144;                                     // barriers, k tables, dB staging
+    const int tail = FD_TAIL;
     p.stages = (232448 - 1024 - tail) / p.stage_bytes;
     if (p.stages > 4) p.stages = 4;
     const int grid = first_tc_grid(p.ntiles);

@@ -98,7 +98,9 @@ __global__ void __launch_bounds__(256) gen_dw_partial_kernel(const float* __rest
     // Pixel coordinates are decoded once per chunk of GEN_DW_CHUNK pixels into shared memory
     // (sample row base s*H, top-left input row, top-left input column), not once per (entry, pixel).
     __shared__ int pix_s[GEN_DW_CHUNK], pix_h[GEN_DW_CHUNK], pix_w[GEN_DW_CHUNK];
-    for (int e0 = 0; e0 < entries + Cout; e0 += blockDim.x) {
+    // blockIdx.y walks the filter entries in groups of 256: every (pixel chunk, entry group) pair is a CTA of its own,
+    // so the dependent load chains of the inner loop are hidden by occupancy instead of running one after another.
+    for (int e0 = blockIdx.y * blockDim.x; e0 < entries + Cout; e0 += gridDim.y * blockDim.x) {
         const int e = e0 + threadIdx.x;
         const bool is_w = e < entries && x != nullptr;
         const bool is_b = e >= entries && e < entries + Cout;
@@ -207,7 +209,9 @@ int generic_conv_bwd_filter(const AetherConvDesc& d, const float* x, const float
     const long long ppb = (npix + nb - 1) / nb;
     const int entries = d.fH * d.fW * d.Cin * d.Cout;
     float* part = static_cast<float*>(ws);
-    gen_dw_partial_kernel<<<nb, 256, 0, st>>>(x, dy, part, d.S, d.H, d.W, d.Cin, d.Cout, d.fH, d.fW, d.sH, d.sW, d.padH,
+    int egroups = ceil_div(entries + d.Cout, 256);
+    if (egroups > 4096) egroups = 4096;
+    gen_dw_partial_kernel<<<dim3(nb, egroups), 256, 0, st>>>(x, dy, part, d.S, d.H, d.W, d.Cin, d.Cout, d.fH, d.fW, d.sH, d.sW, d.padH,
                                               d.padW, Ho, Wo, ppb);
     count_launch();
     int rc = check_launch("gen_dw_partial_kernel");

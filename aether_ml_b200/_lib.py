@@ -49,6 +49,9 @@ SIGNATURES = {
     "aether_bn_act_fwd_train": (_I, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _F, _P, _P, _SZ, _P]),
     "aether_bn_act_fwd_eval": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _SZ, _P]),
     "aether_bn_act_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _P, _SZ, _P]),
+    "aether_bn_act_pool_fwd": (_I, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _F, _P, _I,
+                                    _P, _SZ, _P]),
+    "aether_bn_act_pool_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P, _SZ, _P]),
     "aether_bn_fwd_train_partials": (_I, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _SZ, _P]),
     "aether_bn_workspace_bytes": (_SZ, [_I64, _I]),
     "aether_bn_fwd_train": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _SZ, _P]),

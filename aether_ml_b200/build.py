@@ -10,7 +10,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libaether_b200.so")
-SOURCES = ["api.cu", "conv_tc.cu", "conv_halo.cu", "conv_halo_dw.cu", "conv_dw_rows.cu", "conv_generic.cu", "conv_smallc.cu", "conv_first_tc.cu", "layers.cu"]
+SOURCES = ["api.cu", "conv_tc.cu", "conv_halo.cu", "conv_halo_dw.cu", "conv_dw_rows.cu", "conv_generic.cu", "conv_smallc.cu", "conv_first_tc.cu", "layers.cu",
+           "block_fused.cu"]
 # tcgen05 / TMA PTX only assembles for the arch-specific target, hence compute_100a + sm_100a.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]

@@ -72,6 +72,17 @@ long long tc_conv_stats_blocks(const AetherConvDesc& d);
 int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const float* w, float* dx, float* dw,
                 float* db, void* ws, size_t ws_bytes, int x_shadow_valid, cudaStream_t st);
 
+// ---- layers.cu : pieces of Batch_Norm shared with block_fused.cu
+int bn_partial_blocks(long long rows);
+float* bn_forward_coeffs(const float* x, const float* partials, long long nblocks, const float* gamma, const float* beta,
+                         float* running_mean, float* running_var, float* batch_mean, float* batch_var, long long rows,
+                         int C, float eps, float momentum, const float* channel_scale, float* ws, cudaStream_t st);
+float* bn_eval_coeffs(const float* gamma, const float* beta, const float* running_mean, const float* running_var, int C,
+                      float eps, float* ws, cudaStream_t st);
+void bn_backward_coeffs(const float* part, int nb, int C, long long rows, const float* gamma, const float* mean,
+                        const float* var, float eps, float* dgamma, float* dbeta, float* coeff, const float* pscale,
+                        cudaStream_t st);
+
 static inline void conv_out_hw(const AetherConvDesc& d, int& Ho, int& Wo) {
     Ho = (d.H + 2 * d.padH - d.fH) / d.sH + 1;
     Wo = (d.W + 2 * d.padW - d.fW) / d.sW + 1;

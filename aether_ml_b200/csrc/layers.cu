@@ -418,6 +418,58 @@ static int bn_blocks(long long rows) {
     return (int)nb;
 }
 
+__global__ void coeff_scale_kernel(float* __restrict__ scale_shift, const float* __restrict__ m, int C) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    scale_shift[c] *= m[c];
+    scale_shift[C + c] *= m[c];
+}
+
+// ---- pieces of Batch_Norm shared with block_fused.cu ----------------------------------------------------------
+int bn_partial_blocks(long long rows) { return bn_blocks(rows); }
+
+// Batch statistics (reduced here unless `partials` come from the producer of x), running-statistics update and the
+// per-channel affine coefficients scale/shift (times channel_scale when given) at ws + nb*3*C floats; returns them.
+float* bn_forward_coeffs(const float* x, const float* partials, long long nblocks, const float* gamma, const float* beta,
+                         float* running_mean, float* running_var, float* batch_mean, float* batch_var, long long rows,
+                         int C, float eps, float momentum, const float* channel_scale, float* ws, cudaStream_t st) {
+    int nb = bn_blocks(rows);
+    float* coeff = ws + (size_t)nb * 3 * C;
+    const float* src = partials;
+    if (!partials) {
+        launch_bn_reduce<0>(nb, st, x, nullptr, nullptr, nullptr, eps, rows, C, ws);
+        count_launch();
+        src = ws;
+    } else {
+        nb = (int)nblocks;
+    }
+    bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(src, nb, C, gamma, beta, eps, momentum, running_mean, running_var,
+                                                            batch_mean, batch_var, coeff);
+    count_launch();
+    if (channel_scale) {
+        coeff_scale_kernel<<<ceil_div(C, 128), 128, 0, st>>>(coeff, channel_scale, C);
+        count_launch();
+    }
+    return coeff;
+}
+
+// Inference coefficients from the running statistics into ws (2*C floats).
+float* bn_eval_coeffs(const float* gamma, const float* beta, const float* running_mean, const float* running_var, int C,
+                      float eps, float* ws, cudaStream_t st) {
+    bn_eval_coeff_kernel<<<ceil_div(C, 128), 128, 0, st>>>(C, gamma, beta, eps, running_mean, running_var, ws);
+    count_launch();
+    return ws;
+}
+
+// dgamma, dbeta and the dx coefficients (k1, k2, k3) from nb partial (sum g, sum g*xhat) pairs.
+void bn_backward_coeffs(const float* part, int nb, int C, long long rows, const float* gamma, const float* mean,
+                        const float* var, float eps, float* dgamma, float* dbeta, float* coeff, const float* pscale,
+                        cudaStream_t st) {
+    bn_finalize_bwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, rows, gamma, mean, var, eps, dgamma, dbeta, coeff,
+                                                            pscale);
+    count_launch();
+}
+
 }  // namespace aether
 
 using namespace aether;
@@ -573,13 +625,6 @@ extern "C" int aether_bn_bwd(const float* x, const float* dy, const float* gamma
 // forward : y = act(bn(x)); the normalised, not yet activated tensor is never written.
 // backward: dy is the gradient w.r.t. y; the activation's derivative is taken from the sign of y while the
 //           statistics pass and the dx pass read it, so the ReLU's own backward pass disappears as well.
-__global__ void coeff_scale_kernel(float* __restrict__ scale_shift, const float* __restrict__ m, int C) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    scale_shift[c] *= m[c];
-    scale_shift[C + c] *= m[c];
-}
-
 static int bn_act_check(const char* who, int64_t rows, int C, float alpha, const void* a, const void* b, const void* c) {
     if (rows <= 0 || C <= 0) return set_error(AE_BAD_ARG, "%s: rows=%lld C=%d", who, (long long)rows, C);
     if (!(alpha >= 0.f && alpha < 1.f)) return set_error(AE_BAD_ARG, "%s: alpha must be in [0, 1)", who);

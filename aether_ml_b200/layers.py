@@ -206,6 +206,7 @@ class Pooling:
         self.strides = strides
         self.padding = padding
         self.pooling_type = pooling_type
+        self.fused_bn = None            # a Batch_Norm that pools inside its own kernels (Model.finalize(fuse=True))
 
     def _kind(self):
         if self.pooling_type == "max":
@@ -216,6 +217,11 @@ class Pooling:
 
     def forward(self, inputs, training):
         x = to_device(inputs)
+        if self.fused_bn is not None and self.fused_bn.pooled_now:
+            # the fused Batch_Norm already produced the pooled tensor (and keeps the argmax codes)
+            self.inputs = self.output = x
+            self._argmax = self.fused_bn._pool_arg
+            return self.output
         if x.ndim != 4:
             raise ValueError(f"Expected a 4D tensor, got {x.ndim} instead.")
         if self.padding != "valid":
@@ -243,6 +249,9 @@ class Pooling:
 
     def backward(self, dvalues):
         dy = to_device(dvalues)
+        if self.fused_bn is not None and self.fused_bn.pooled_now:
+            self.dinputs = dy
+            return self.dinputs
         S, H, W, Cc = self.inputs.shape
         fH, fW = self.filter_size
         sH, sW = self.strides
@@ -425,6 +434,8 @@ class Batch_Norm:
         self.stats_from = None          # a Conv_Layer whose forward leaves `bn_partials` for this layer's input
         self.fused_alpha = None         # slope of the (Leaky_)ReLU applied inside this layer's kernels (None: not fused)
         self.fused_dropout = None       # a Layer_Dropout_Spatial behind that activation whose mask is applied here too
+        self.fused_pool = None          # a max Pooling behind those whose windows are reduced here too
+        self.pooled_now = False         # the last forward produced the pooled tensor
         if n_features is not None:
             self._create(n_features)
 
@@ -464,13 +475,43 @@ class Batch_Norm:
         keep = (1,) * (x.ndim - 1) + (Cc,)
         L = lib()
         ws = self._ws.get(L.aether_bn_workspace_bytes(rows, Cc))
-        y = torch.empty_like(x)
+        part = None
         if training:
             self._bm = _empty((Cc,))
             self._bv = _empty((Cc,))
             part = getattr(self.stats_from, "bn_partials", None) if self.stats_from is not None else None
             if part is not None and part[2] != x.data_ptr():
                 part = None
+        # Whole block tail in one pass: activation, dropout mask and a max pooling whose windows tile the input are
+        # applied while x is read once; the activated tensor is never written (block_fused.cu).
+        pool = self.fused_pool
+        self.pooled_now = False
+        if pool is not None and self.fused_alpha is not None and x.ndim == 4 and Cc % 4 == 0:
+            fH, fW = pool.filter_size
+            S, H, W = x.shape[0], x.shape[1], x.shape[2]
+            if H % fH == 0 and W % fW == 0:
+                mask = self.fused_dropout.draw_mask(Cc) if (training and self.fused_dropout is not None) else None
+                pooled = _empty((S, H // fH, W // fW, Cc))
+                self._pool_arg = _empty((S, H // fH, W // fW, Cc), torch.uint8)
+                check(L.aether_bn_act_pool_fwd(_ptr(x), _ptr(part[0]) if part else None, part[1] if part else 0,
+                                               _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
+                                               _ptr(self._bm) if training else None, _ptr(self._bv) if training else None,
+                                               _ptr(pooled), _ptr(self._pool_arg), S, H, W, Cc, fH, fW, float(self.epsilon),
+                                               float(self.momentum), float(self.fused_alpha), _ptr(mask),
+                                               1 if training else 0, _ptr(ws), ws.numel(), _stream()),
+                      "aether_bn_act_pool_fwd")
+                self._fused_mask = mask
+                self.pooled_now = True
+                if training:
+                    self.batch_mean = self._bm.view(keep)
+                    self.batch_var = self._bv.view(keep)
+                    self.running_mean = self._rm.view(keep)
+                    self.running_var = self._rv.view(keep)
+                self.inputs = x
+                self.output = pooled
+                return self.output
+        y = torch.empty_like(x)
+        if training:
             if self.fused_alpha is not None:
                 # y = act(bn(x)) [* spatial-dropout mask] in the same passes; the layers behind only hand y through
                 mask = self.fused_dropout.draw_mask(Cc) if self.fused_dropout is not None else None
@@ -519,7 +560,15 @@ class Batch_Norm:
         else:
             self.dweights = _empty((Cc,))
             self.dbiases = _empty((Cc,))
-        if self.fused_alpha is not None:     # dvalues is the gradient w.r.t. the ACTIVATED output kept in self.output
+        if self.pooled_now:                  # dvalues is the gradient w.r.t. the POOLED output of the fused block tail
+            S, H, W = x.shape[0], x.shape[1], x.shape[2]
+            fH, fW = self.fused_pool.filter_size
+            check(L.aether_bn_act_pool_bwd(_ptr(x), _ptr(dy), _ptr(self._pool_arg), _ptr(self.gamma), _ptr(self.beta),
+                                           _ptr(self._bm), _ptr(self._bv), _ptr(dx), _ptr(self.dweights),
+                                           _ptr(self.dbiases), S, H, W, Cc, fH, fW, float(self.epsilon),
+                                           float(self.fused_alpha), _ptr(getattr(self, "_fused_mask", None)), _ptr(ws),
+                                           ws.numel(), _stream()), "aether_bn_act_pool_bwd")
+        elif self.fused_alpha is not None:   # dvalues is the gradient w.r.t. the ACTIVATED output kept in self.output
             check(L.aether_bn_act_bwd(_ptr(x), _ptr(self.output), _ptr(dy), _ptr(self.gamma), _ptr(self._bm),
                                       _ptr(self._bv), _ptr(dx), _ptr(self.dweights), _ptr(self.dbiases), rows, Cc,
                                       float(self.epsilon), float(self.fused_alpha), _ptr(getattr(self, "_fused_mask", None)),

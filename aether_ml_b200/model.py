@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from .layers import (Activation_Softmax_Loss_CategoricalCrossEntropy, Batch_Norm, Conv_Layer, Layer_Dropout_Spatial,
-                     Loss_CategoricalCrossEntropy, ReLU, SoftMax, to_device, _labels_i32)
+                     Loss_CategoricalCrossEntropy, Pooling, ReLU, SoftMax, to_device, _labels_i32)
 
 
 class Layer_Input:
@@ -127,6 +127,14 @@ class Model:
                 if isinstance(c, Layer_Dropout_Spatial):
                     a.fused_dropout = c
                     c.fused_into_prev = True
+                    c = getattr(c, "next", None)
+                # ... and a max Pooling with stride == filter behind those: the Batch_Norm then reads the convolution
+                # output once and writes the pooled tensor; the activated tensor in between is never materialised
+                # (decided per call: the windows must tile the input)
+                if (isinstance(c, Pooling) and c.pooling_type == "max" and c.padding == "valid"
+                        and tuple(c.strides) == tuple(c.filter_size)):
+                    a.fused_pool = c
+                    c.fused_bn = a
         self.trainable_layers = [l for l in self.layers if hasattr(l, "weights")]
         if self.loss is not None:
             self.loss.remember_trainable_layers(self.trainable_layers)

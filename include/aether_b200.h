@@ -164,6 +164,26 @@ int aether_bn_act_bwd(const float* x, const float* y_act, const float* dy, const
                       const float* batch_var, float* dx, float* dgamma, float* dbeta, int64_t rows, int C, float eps,
                       float alpha, const float* channel_scale, void* ws, size_t ws_bytes, void* stream);
 
+/* The whole tail of a convolution block in one pass each way: Batch_Norm (:430-526), ReLU / Leaky_ReLU (:406-428),
+ * optional Layer_Dropout_Spatial (:384-404, channel_scale = mask / keep_prob or NULL) and a max Pooling (:204-312) with
+ * fH x fW windows of stride (fH, fW) that tile the input (H % fH == 0, W % fW == 0; C % 4 == 0).  The activated tensor
+ * between convolution and pooling is never written.
+ *   aether_bn_act_pool_fwd: x (S,H,W,C) -> pooled (S,H/fH,W/fW,C) and one argmax byte per pooled element (window-local
+ *     index i*fW+j of the first maximum, as aether_pool_fwd).  training != 0: batch statistics (from `partials` of
+ *     aether_conv2d_fwd_bnstats, or reduced here when NULL), running statistics updated, batch_mean/var written;
+ *     training == 0: running statistics, channel_scale ignored.  ws: aether_bn_workspace_bytes(S*H*W, C).
+ *   aether_bn_act_pool_bwd: dpooled is the gradient w.r.t. that pooled tensor; returns dx (S,H,W,C), dgamma, dbeta.
+ *     The activation's derivative is recomputed from x (pre-activation gamma*xhat + beta), so it equals
+ *     ReLU/Leaky_ReLU.backward exactly (the gradient passes where the pre-activation is 0). */
+int aether_bn_act_pool_fwd(const float* x, const float* partials, int64_t nblocks, const float* gamma, const float* beta,
+                           float* running_mean, float* running_var, float* batch_mean, float* batch_var, float* pooled,
+                           uint8_t* argmax, int S, int H, int W, int C, int fH, int fW, float eps, float momentum,
+                           float alpha, const float* channel_scale, int training, void* ws, size_t ws_bytes, void* stream);
+int aether_bn_act_pool_bwd(const float* x, const float* dpooled, const uint8_t* argmax, const float* gamma,
+                           const float* beta, const float* batch_mean, const float* batch_var, float* dx, float* dgamma,
+                           float* dbeta, int S, int H, int W, int C, int fH, int fW, float eps, float alpha,
+                           const float* channel_scale, void* ws, size_t ws_bytes, void* stream);
+
 /* ---- Pooling, 'valid' padding (CNN_classes_cupy.py:204-312) ---------------------------------- */
 /* Forward :212-273.  argmax (uint8, same shape as y; max pooling only) receives i*fW+j of the first
  * maximum of each window in row-major order (:259-265). */

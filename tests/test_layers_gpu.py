@@ -106,6 +106,60 @@ def test_batch_norm_statistics_from_conv_epilogue(env, case):
     assert conv.bn_partials is None
 
 
+@pytest.mark.parametrize("case", [(6, 8, 12, 32, 0.0, (2, 2), True), (3, 12, 6, 64, 0.01, (2, 2), False),
+                                  (2, 9, 6, 8, 0.2, (3, 3), True)])
+def test_fused_block_tail_matches_oracle_chain(env, case):
+    """Batch_Norm + (Leaky_)ReLU + spatial dropout + tiling max pooling in one pass each way (block_fused.cu) against
+    the oracle's layer-by-layer chain: pooled output, argmax, dX, dgamma, dbeta; inference path too."""
+    torch, _lib, layers = env
+    S, H, W, C, alpha, f, with_drop = case
+    rng = np.random.default_rng(13)
+    x = (rng.standard_normal((S, H, W, C)) * 2 + 0.5).astype(np.float32)
+    gamma = (rng.standard_normal(C) + 1).astype(np.float32); beta = rng.standard_normal(C).astype(np.float32)
+    mask = ((rng.random(C) < 0.7) / 0.7).astype(np.float32)            # some channels dropped, the rest scaled up
+    bn = layers.Batch_Norm(n_features=C)
+    bn.gamma.copy_(torch.from_numpy(gamma)); bn.beta.copy_(torch.from_numpy(beta))
+    act = layers.Leaky_ReLU(alpha) if alpha else layers.ReLU()
+    drop = layers.Layer_Dropout_Spatial(0.3)
+    drop.fixed_mask = mask
+    pool = layers.Pooling(f, f, "valid", "max")
+    bn.fused_alpha = float(alpha); act.fused_into_prev = True
+    if with_drop:
+        bn.fused_dropout = drop; drop.fused_into_prev = True
+    bn.fused_pool = pool; pool.fused_bn = bn
+    chain = [bn, act] + ([drop] if with_drop else []) + [pool]
+    out = x
+    for l in chain:
+        out = l.forward(out, True)
+    assert bn.pooled_now and tuple(out.shape) == (S, H // f[0], W // f[1], C)
+    # oracle: the same four layers one after the other
+    yb, _, mean, var, rm, rv = O.bn_forward_train(x, gamma, beta, np.zeros(C), np.ones(C))
+    ya = O.leaky_relu_forward(yb, alpha) if alpha else O.relu_forward(yb)
+    yd = ya * mask if with_drop else ya
+    yp, arg = O.pool_forward(yd, f, f)
+    assert O.rel_l2(host(out), yp) <= 1e-5
+    assert O.rel_l2(host(bn.running_mean), rm) <= 1e-5 and O.rel_l2(host(bn.running_var), rv) <= 1e-4
+    dyp = rng.standard_normal(yp.shape).astype(np.float32)
+    g = dyp
+    for l in reversed(chain):
+        g = l.backward(g)
+    torch.cuda.synchronize()
+    gd = O.pool_backward(dyp, yd.shape, arg, f, f)
+    if with_drop:
+        gd = gd * mask
+    ga = O.leaky_relu_backward(yb, gd, alpha) if alpha else O.relu_backward(yb, gd)
+    dxo, dgo, dbo = O.bn_backward(x, ga, gamma, mean, var)
+    assert O.rel_l2(host(g), dxo) <= 2e-4
+    assert O.rel_l2(host(bn.dweights), dgo) <= 1e-4 and O.rel_l2(host(bn.dbiases), dbo) <= 1e-4
+    # inference: running statistics, no mask
+    oe = x
+    for l in chain:
+        oe = l.forward(oe, False)
+    ye = O.bn_forward_eval(x, gamma, beta, host(bn.running_mean), host(bn.running_var))
+    ye = O.leaky_relu_forward(ye, alpha) if alpha else O.relu_forward(ye)
+    assert O.rel_l2(host(oe), O.pool_forward(ye, f, f)[0]) <= 1e-5
+
+
 @pytest.mark.parametrize("name", ["pool_max_2x2", "pool_max_odd", "pool_max_overlap", "pool_avg_2x2"])
 def test_pooling_golden(env, golden, name):
     torch, _lib, layers = env

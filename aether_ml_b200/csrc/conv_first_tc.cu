@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
     uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
     const int NT = p.NT, S = p.stages;
     const uint32_t sW = smem_base;                                  // filter: NT rows of 128 bytes
-    const uint32_t sA = sW + (uint32_t)NT * 128u;                   // NT is a multiple of 16 -> 1024-byte multiple? see host
+    const uint32_t sA = sW + (uint32_t)NT * 128u;                   // NT is a multiple of 64: stays 1024-byte aligned
     const uint32_t sBar = sA + (uint32_t)S * FT_STAGE_BYTES;
     auto full_bar = [&](int s) { return sBar + 8u * s; };
     auto empty_bar = [&](int s) { return sBar + 8u * (S + s); };

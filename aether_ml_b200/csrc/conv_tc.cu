@@ -106,10 +106,12 @@ int make_map_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int el
 struct IgemmParams {
     CUtensorMap tm_in;   // activations (C, W, H, N), box (128 B of channels, BW, BH, BN)
     CUtensorMap tm_w;    // filter matrix, K contiguous: (K, taps * rows_per_tap), box (128 B of K, NT)
-    CUtensorMap tm_out;  // fp32 output (C, W, H, N), box (32, BW, BH, BN)
+    float* out;          // fp32 output, NHWC (out_N, out_H, out_W, n_out), 16-byte aligned, n_out % 4 == 0
     const float* bias;   // nullable, n_out entries
+    float* stats;        // STATS only: [gridDim.x / n_tiles_n * 4][3][n_out] (count, mean, M2) partial blocks
     int* status;
     int n_out;
+    int out_W, out_H, out_N;   // output extent: accumulator rows outside it are by-products
     int BW, BH, BN, rows;
     int tiles_w, tiles_h, tiles_n, n_tiles_n;
     int rows_per_tap;
@@ -118,18 +120,23 @@ struct IgemmParams {
 };
 
 static constexpr int TILE_A_BYTES = 128 * 128;  // 128 pixel rows x 128 B
-static constexpr int STAGING_BYTES = 128 * 128; // 128 rows x 32 fp32
-static constexpr int IGEMM_THREADS = 192;       // warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 epilogue
+static constexpr int IGEMM_EPI_WARPS = 8;       // 4 TMEM lane quarters x 2 column halves
+static constexpr int IGEMM_EPI_UB = 4;          // 16-column TMEM loads in flight per batch
+static constexpr int IGEMM_THREADS = 64 + 32 * IGEMM_EPI_WARPS;   // warp 0 TMA producer, warp 1 MMA issuer, then epilogue
+static constexpr int IGEMM_TAIL = 1024;         // barriers, TMEM pointer
+static constexpr int IGEMM_STATS_BYTES = IGEMM_EPI_WARPS * 2 * 128 * 4;   // per-warp running column sums
 
 template <int NT>
 struct IgemmCfg {
     static constexpr int STAGES = (NT == 256) ? 4 : (NT == 128 ? 6 : 8);
     static constexpr int TILE_B_BYTES = NT * 128;
-    static constexpr int SMEM_BYTES =
-        1024 + STAGES * (TILE_A_BYTES + TILE_B_BYTES) + 2 * STAGING_BYTES + 256;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * (TILE_A_BYTES + TILE_B_BYTES) + IGEMM_TAIL + IGEMM_STATS_BYTES;
 };
 
-template <bool TF32, int NT>
+// STATS: the epilogue also accumulates per-channel (count, mean, M2) of the output about the bias, one block per
+// CTA group and 32-row quarter; the launch must use a grid that is a multiple of n_tiles_n so that every CTA keeps
+// one column tile for all its tiles.
+template <bool TF32, int NT, bool STATS>
 __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __grid_constant__ IgemmParams p) {
     using Cfg = IgemmCfg<NT>;
     constexpr int STAGES = Cfg::STAGES;
@@ -138,8 +145,7 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sA = smem_base;
     const uint32_t sB = sA + STAGES * TILE_A_BYTES;
-    const uint32_t sStage = sB + STAGES * Cfg::TILE_B_BYTES;
-    const uint32_t sBar = sStage + 2 * STAGING_BYTES;
+    const uint32_t sBar = sB + STAGES * Cfg::TILE_B_BYTES;
     // barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then the TMEM base address
     auto full_bar = [&](int s) { return sBar + 8u * s; };
     auto empty_bar = [&](int s) { return sBar + 8u * (STAGES + s); };
@@ -160,12 +166,11 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), 4);
+            mbar_init(tempty_bar(b), IGEMM_EPI_WARPS);
         }
         mbar_fence_init();
         tma_prefetch_desc(&p.tm_in);
         tma_prefetch_desc(&p.tm_w);
-        tma_prefetch_desc(&p.tm_out);
     }
     if (warp == 1) {
         tmem_alloc(sTmemPtr, 2 * NT);
@@ -241,12 +246,34 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (4 warps, 128 rows)
-        const int q = warp & 3;                  // TMEM lane quarter this warp may access
-        const int row = q * 32 + lane;
-        const bool leader = (threadIdx.x == 64);
-        uint8_t* stage_gen = gen_base + (sStage - smem_base);
-        uint32_t lt = 0, chunk_ctr = 0;
+        // ------------------------------------------------------------------ epilogue (8 warps)
+        // Warp (q, part): TMEM lanes [32q, 32q+32), columns [part*NT/2, (part+1)*NT/2).  Accumulators are read with
+        // the 16-lane x 256-bit shape and a butterfly exchange inside each quad leaves every lane with 4 consecutive
+        // columns of a row, so the registers go straight to global memory as 64-byte pieces per row.
+        const int ew = warp - 2;
+        const int q = warp & 3;
+        const int part = ew >> 2;
+        constexpr int ncols = NT / 2;              // columns this warp owns (multiple of 16)
+        const int col_begin = part * ncols;
+        const int trow = lane >> 2, tcol4 = (lane & 3) * 4;
+        const bool lo2 = (lane & 2) == 0, odd = (lane & 1) != 0;
+        // statistics: running per-column sums of this warp over all its tiles, [2][128] floats of its own
+        float* stat_w = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + IGEMM_TAIL) + ew * 256;
+        float st_rows = 0.f;                       // rows (pixels) summed so far, identical in every lane
+        if (STATS) {
+            for (int i = lane; i < 256; i += 32) stat_w[i] = 0.f;
+            __syncwarp();
+        }
+        // The four accumulator rows this thread holds are fixed pixels of the (BW, BH, BN) box.
+        int r_w[4], r_h[4], r_n[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = q * 32 + (j >> 1) * 16 + trow + (j & 1) * 8;
+            r_w[j] = r % p.BW;
+            r_h[j] = (r / p.BW) % p.BH;
+            r_n[j] = r < p.rows ? r / (p.BW * p.BH) : (1 << 29);      // rows past the box: never valid
+        }
+        uint32_t lt = 0;
         bool ok = true;
         for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
             const int nt = (int)(t % p.n_tiles_n);
@@ -256,50 +283,142 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
             const int th = (int)(mt % p.tiles_h);
             const int tn = (int)(mt / p.tiles_h);
             const int w0 = tw * p.BW, h0 = th * p.BH, n0 = tn * p.BN;
+            const int col0 = nt * NT + col_begin + tcol4;             // first of this thread's columns
+            float* rowp[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int w = w0 + r_w[j], h = h0 + r_h[j], n = n0 + r_n[j];
+                rowp[j] = (w < p.out_W && h < p.out_H && n < p.out_N)
+                              ? p.out + (((size_t)n * p.out_H + h) * p.out_W + w) * p.n_out + col0
+                              : nullptr;
+            }
             const uint32_t buf = lt & 1u;
             const uint32_t aph = (lt >> 1) & 1u;
             if (!mbar_wait(tfull_bar(buf), aph, p.status, DS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
             tc_fence_after();
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NT + col_begin;
 #pragma unroll 1
-            for (int ch = 0; ch < NT / 32; ++ch, ++chunk_ctr) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * NT + ch * 32, r);
+            for (int cb = 0; cb < ncols; cb += 16 * IGEMM_EPI_UB) {   // batches of IGEMM_EPI_UB x 16 columns
+                uint32_t v[2][IGEMM_EPI_UB][8];
+                float4 st_s[IGEMM_EPI_UB], st_q[IGEMM_EPI_UB];        // per-column sum / sum of squares of this tile's rows
+#pragma unroll
+                for (int u = 0; u < IGEMM_EPI_UB; ++u) st_s[u] = st_q[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < IGEMM_EPI_UB; ++u) {
+                    if (cb + u * 16 < ncols) {
+                        tmem_ld_16x256b_x2(taddr0 + cb + u * 16, v[0][u]);
+                        tmem_ld_16x256b_x2(taddr0 + (16u << 16) + cb + u * 16, v[1][u]);
+                    }
+                }
                 tmem_ld_wait();
-                if (ch == NT / 32 - 1) {          // accumulator fully read: hand the buffer back
+                if (cb + 16 * IGEMM_EPI_UB >= ncols) {           // accumulator fully read by this warp
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(buf));
                 }
-                const int c0 = nt * NT + ch * 32;
-                const uint32_t sb = chunk_ctr & 1u;
-                if (leader) tma_store_wait_read<1>();   // the store that last used this staging buffer is done
-                named_bar_sync(1, 128);
-                float4* dst_row = reinterpret_cast<float4*>(stage_gen + sb * STAGING_BYTES + row * 128);
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    float4 v;
-                    v.x = __uint_as_float(r[4 * u + 0]);
-                    v.y = __uint_as_float(r[4 * u + 1]);
-                    v.z = __uint_as_float(r[4 * u + 2]);
-                    v.w = __uint_as_float(r[4 * u + 3]);
-                    if (p.bias) {
-                        const int c = c0 + 4 * u;
-                        if (c + 0 < p.n_out) v.x += __ldg(p.bias + c + 0);
-                        if (c + 1 < p.n_out) v.y += __ldg(p.bias + c + 1);
-                        if (c + 2 < p.n_out) v.z += __ldg(p.bias + c + 2);
-                        if (c + 3 < p.n_out) v.w += __ldg(p.bias + c + 3);
+                for (int u = 0; u < IGEMM_EPI_UB; ++u) {
+                    if (cb + u * 16 < ncols) {
+                        const int cc = cb + u * 16;              // column relative to this thread's first column
+                        const bool cols_ok = col0 + cc < p.n_out;   // n_out % 4 == 0: all four columns or none
+                        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (p.bias != nullptr && cols_ok) {
+                            b4.x = __ldg(p.bias + col0 + cc + 0); b4.y = __ldg(p.bias + col0 + cc + 1);
+                            b4.z = __ldg(p.bias + col0 + cc + 2); b4.w = __ldg(p.bias + col0 + cc + 3);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t a0 = v[j >> 1][u][(j & 1) * 2 + 0], a1 = v[j >> 1][u][(j & 1) * 2 + 1];
+                            const uint32_t b0 = v[j >> 1][u][4 + (j & 1) * 2 + 0], b1 = v[j >> 1][u][4 + (j & 1) * 2 + 1];
+                            // step 1 (lane ^ 2): lanes 0,1 collect column group 0, lanes 2,3 collect group 1
+                            const uint32_t s0 = lo2 ? b0 : a0, s1 = lo2 ? b1 : a1;
+                            const uint32_t x2 = __shfl_xor_sync(0xffffffffu, s0, 2), x3 = __shfl_xor_sync(0xffffffffu, s1, 2);
+                            const uint32_t e0 = lo2 ? a0 : x2, e1 = lo2 ? a1 : x3;       // piece from the even source lane
+                            const uint32_t f0 = lo2 ? x2 : b0, f1 = lo2 ? x3 : b1;       // piece from the source lane + 2
+                            // step 2 (lane ^ 1): even lanes keep the lower pair of pieces, odd lanes the upper pair
+                            const uint32_t t0 = odd ? e0 : f0, t1 = odd ? e1 : f1;
+                            const uint32_t g0 = __shfl_xor_sync(0xffffffffu, t0, 1), g1 = __shfl_xor_sync(0xffffffffu, t1, 1);
+                            float4 a;                                                     // accumulator values (before the bias)
+                            a.x = __uint_as_float(odd ? g0 : e0);
+                            a.y = __uint_as_float(odd ? g1 : e1);
+                            a.z = __uint_as_float(odd ? f0 : g0);
+                            a.w = __uint_as_float(odd ? f1 : g1);
+                            const bool wr = cols_ok && rowp[j] != nullptr;
+                            if (wr)
+                                __stcs(reinterpret_cast<float4*>(rowp[j] + cc),
+                                       make_float4(a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w));
+                            if (STATS) {                                     // selects, not products: a by-product may be NaN
+                                a.x = wr ? a.x : 0.f; a.y = wr ? a.y : 0.f;
+                                a.z = wr ? a.z : 0.f; a.w = wr ? a.w : 0.f;
+                                st_s[u].x += a.x; st_s[u].y += a.y; st_s[u].z += a.z; st_s[u].w += a.w;
+                                st_q[u].x = fmaf(a.x, a.x, st_q[u].x); st_q[u].y = fmaf(a.y, a.y, st_q[u].y);
+                                st_q[u].z = fmaf(a.z, a.z, st_q[u].z); st_q[u].w = fmaf(a.w, a.w, st_q[u].w);
+                            }
+                        }
                     }
-                    dst_row[u ^ (row & 7)] = v;      // 128-byte swizzle: 16-byte unit index XOR (row mod 8)
                 }
-                fence_proxy_async_smem();
-                named_bar_sync(1, 128);
-                if (leader && c0 < p.n_out) {
-                    tma_store_4d(&p.tm_out, sStage + sb * STAGING_BYTES, c0, w0, h0, n0);
-                    tma_store_commit();
+                if (STATS) {
+                    // Lanes with equal lane%4 hold the same 4 columns of 8 different row groups: add them up
+                    // (xor 4, 8, 16); lanes 0..3 then add the tile's sums to this warp's running sums in shared
+                    // memory.  The sums are taken about the bias (the channel's expected offset).
+                    if (cb == 0) {
+                        float nrows = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) nrows += (rowp[j] != nullptr) ? 1.f : 0.f;
+                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 4);
+                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 8);
+                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 16);
+                        st_rows += nrows;
+                    }
+#pragma unroll
+                    for (int m = 4; m <= 16; m <<= 1) {
+#pragma unroll
+                        for (int u = 0; u < IGEMM_EPI_UB; ++u) {
+                            st_s[u].x += __shfl_xor_sync(0xffffffffu, st_s[u].x, m); st_s[u].y += __shfl_xor_sync(0xffffffffu, st_s[u].y, m);
+                            st_s[u].z += __shfl_xor_sync(0xffffffffu, st_s[u].z, m); st_s[u].w += __shfl_xor_sync(0xffffffffu, st_s[u].w, m);
+                            st_q[u].x += __shfl_xor_sync(0xffffffffu, st_q[u].x, m); st_q[u].y += __shfl_xor_sync(0xffffffffu, st_q[u].y, m);
+                            st_q[u].z += __shfl_xor_sync(0xffffffffu, st_q[u].z, m); st_q[u].w += __shfl_xor_sync(0xffffffffu, st_q[u].w, m);
+                        }
+                    }
+                    if (lane < 4) {
+#pragma unroll
+                        for (int u = 0; u < IGEMM_EPI_UB; ++u) {
+                            const int cc = cb + u * 16;
+                            if (cc < ncols) {
+                                float4* ps = reinterpret_cast<float4*>(stat_w + cc + tcol4);
+                                float4* pq = reinterpret_cast<float4*>(stat_w + 128 + cc + tcol4);
+                                float4 s = *ps, qq = *pq;
+                                s.x += st_s[u].x; s.y += st_s[u].y; s.z += st_s[u].z; s.w += st_s[u].w;
+                                qq.x += st_q[u].x; qq.y += st_q[u].y; qq.z += st_q[u].z; qq.w += st_q[u].w;
+                                *ps = s;
+                                *pq = qq;
+                            }
+                        }
+                    }
                 }
             }
         }
-        if (leader) tma_store_wait_all<0>();
+        if (STATS && lane < 4) {
+            // (count, mean, M2) of this warp's rows over all tiles of the CTA.  The grid is a multiple of
+            // n_tiles_n, so the CTA kept column tile blockIdx.x % n_tiles_n; the n_tiles_n CTAs of a group fill the
+            // disjoint column ranges of block (group * 4 + q) of [3][n_out].
+            const int ntc = blockIdx.x % p.n_tiles_n;
+            float* sp = p.stats + ((size_t)(blockIdx.x / p.n_tiles_n) * 4 + q) * 3 * (size_t)p.n_out;
+            const float inv_n = st_rows > 0.f ? 1.f / st_rows : 0.f;
+            for (int cc = 0; cc < ncols; cc += 16) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int col = ntc * NT + col_begin + tcol4 + cc + k;
+                    if (col < p.n_out) {
+                        const float s = stat_w[cc + tcol4 + k], qq = stat_w[128 + cc + tcol4 + k];
+                        const float m = s * inv_n;
+                        sp[col] = st_rows;
+                        sp[p.n_out + col] = m + (p.bias != nullptr ? __ldg(p.bias + col) : 0.f);
+                        sp[2 * p.n_out + col] = fmaxf(qq - s * m, 0.f);
+                    }
+                }
+            }
+        }
     }
 
     tc_fence_before();
@@ -808,23 +927,37 @@ static int set_smem(K kernel, int bytes) {
     return AE_OK;
 }
 
-template <bool TF32, int NT>
-static int launch_igemm(const IgemmParams& p, cudaStream_t st) {
+// CTAs of the per-tap kernel.  With statistics the grid is a multiple of the number of column tiles, so that a
+// CTA (tiles blockIdx.x + k * grid, column tile = tile % n_tiles_n) keeps one column tile throughout.
+static int igemm_grid(long long m_tiles, int n_tiles_n, bool stats) {
+    const long long total = m_tiles * n_tiles_n;
+    int grid = (int)(total < num_sms() ? total : num_sms());
+    if (stats && grid > n_tiles_n) grid -= grid % n_tiles_n;
+    return grid;
+}
+
+template <bool TF32, int NT, bool STATS>
+static int launch_igemm_k(const IgemmParams& p, cudaStream_t st) {
     using Cfg = IgemmCfg<NT>;
     static bool configured = false;
     if (!configured) {
-        int rc = set_smem(igemm_conv_kernel<TF32, NT>, Cfg::SMEM_BYTES);
+        int rc = set_smem(igemm_conv_kernel<TF32, NT, STATS>, Cfg::SMEM_BYTES);
         if (rc) return rc;
         configured = true;
     }
-    const long long total = 1LL * p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles_n;
-    int grid = (int)(total < num_sms() ? total : num_sms());
+    const int grid = igemm_grid(1LL * p.tiles_w * p.tiles_h * p.tiles_n, p.n_tiles_n, STATS);
+    if (STATS && grid % p.n_tiles_n) return set_error(AE_UNSUPPORTED, "conv forward statistics: %d column tiles on %d CTAs", p.n_tiles_n, grid);
     const int pk = p.sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX;
     prof_begin(pk, st);
-    igemm_conv_kernel<TF32, NT><<<grid, IGEMM_THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    igemm_conv_kernel<TF32, NT, STATS><<<grid, IGEMM_THREADS, Cfg::SMEM_BYTES, st>>>(p);
     prof_end(pk, st);
     count_launch();
     return check_launch("igemm_conv_kernel");
+}
+
+template <bool TF32, int NT>
+static int launch_igemm(const IgemmParams& p, cudaStream_t st) {
+    return p.stats ? launch_igemm_k<TF32, NT, true>(p, st) : launch_igemm_k<TF32, NT, false>(p, st);
 }
 
 static int pick_nt(int n_padded) {
@@ -858,7 +991,6 @@ static int run_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, in
                                  sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX, st, &used);
         if (rc0 || used) return rc0;
     }
-    if (stats) return set_error(AE_UNSUPPORTED, "conv forward: this shape's kernel does not emit Batch_Norm statistics");
     IgemmParams p;
     memset(&p, 0, sizeof(p));
     const int elt = tf32 ? 4 : 2;
@@ -868,12 +1000,14 @@ static int run_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, in
     int rc;
     if ((rc = make_map_nhwc(&p.tm_in, in, dt, elt, in_C, in_W, in_H, S, KC, til.BW, til.BH, til.BN))) return rc;
     if ((rc = make_map_2d(&p.tm_w, wmat, dt, elt, w_inner, 1LL * taps * rows_per_tap, KC, nt))) return rc;
-    if ((rc = make_map_nhwc(&p.tm_out, out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out_C, out_W, out_H, S, 32, til.BW,
-                            til.BH, til.BN)))
-        return rc;
+    if ((reinterpret_cast<uintptr_t>(out) & 15u) || (out_C & 3))
+        return set_error(AE_BAD_ARG, "conv output must be 16-byte aligned with a channel count that is a multiple of 4");
+    p.out = out;
     p.bias = bias;
+    p.stats = stats;
     p.status = device_status_word();
     p.n_out = out_C;
+    p.out_W = out_W; p.out_H = out_H; p.out_N = S;
     p.BW = til.BW; p.BH = til.BH; p.BN = til.BN; p.rows = til.rows;
     p.tiles_w = til.tiles_w; p.tiles_h = til.tiles_h; p.tiles_n = til.tiles_n;
     p.n_tiles_n = ceil_div(n_padded, nt);
@@ -906,8 +1040,14 @@ static int launch_cast(const float* src, __nv_bfloat16* dst, long long rows, int
 long long tc_conv_stats_blocks(const AetherConvDesc& d) {
     if (!tc_conv_eligible(d)) return 0;
     const TcPlan pl = make_plan(d);
-    return halo_igemm_stats_blocks(pl.tf32, pl.tf32 ? d.Cin : pl.Cin_p, d.S, pl.taps, d.Cout, pl.Ho, pl.Wo, pl.Cout_p, d.fH,
-                                   d.fW);
+    const long long hb = halo_igemm_stats_blocks(pl.tf32, pl.tf32 ? d.Cin : pl.Cin_p, d.S, pl.taps, d.Cout, pl.Ho, pl.Wo,
+                                                 pl.Cout_p, d.fH, d.fW);
+    if (hb > 0) return hb;
+    // per-tap kernel: one block per CTA group (the CTAs of one set of pixel tiles) and 32-row quarter
+    const int n_tiles_n = ceil_div(pl.Cout_p, pick_nt(pl.Cout_p));
+    const int grid = igemm_grid(pl.til_out.total(), n_tiles_n, true);
+    if (grid % n_tiles_n) return 0;
+    return 4LL * (grid / n_tiles_n);
 }
 
 int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, float* stats, void* ws,

@@ -70,7 +70,11 @@ def test_batch_norm_shapes(env, shape):
 # (S, H, W, Cin, Cout, mode, statistics expected from the conv epilogue)
 @pytest.mark.parametrize("case", [(8, 32, 32, 64, 128, "bf16", True), (37, 20, 24, 64, 64, "tf32", True),
                                   (300, 32, 32, 3, 64, "bf16", True), (5, 28, 28, 1, 32, "bf16", True),
-                                  (16, 8, 8, 256, 256, "bf16", False)])
+                                  # per-tap tensor-core kernel: one / two / three column tiles, ragged pixel tiles
+                                  (16, 8, 8, 256, 256, "bf16", True), (40, 8, 8, 128, 512, "bf16", True),
+                                  (50, 16, 16, 128, 256, "bf16", True), (7, 10, 10, 32, 96, "tf32", True),
+                                  (3, 5, 7, 32, 40, "bf16", True), (700, 6, 6, 16, 96, "bf16", True),
+                                  (4, 12, 12, 8, 16, "fp32", False)])
 def test_batch_norm_statistics_from_conv_epilogue(env, case):
     """Conv_Layer -> Batch_Norm with the batch statistics taken in the convolution's epilogue: same result as
     Batch_Norm's own reduction over the layer output (CNN_classes_cupy.py:467-476), bias far from zero included."""

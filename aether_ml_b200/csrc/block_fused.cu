@@ -18,10 +18,14 @@ __device__ __forceinline__ float lrelu(float v, float alpha) { return v > 0.f ? 
 // derivative of the activation at pre-activation v (the reference passes the gradient at v == 0, :412-428)
 __device__ __forceinline__ float lrelu_grad(float v, float alpha) { return v < 0.f ? alpha : 1.f; }
 
+// F > 0: square F x F windows known at compile time -- the window's loads are issued together (one load in flight
+// per thread does not cover the HBM latency); F == 0: any window, cells one after the other.
+template <int F>
 __global__ void __launch_bounds__(256) bn_act_pool_fwd_kernel(const float* __restrict__ x, const float* __restrict__ scale,
                                                               const float* __restrict__ shift, float alpha,
                                                               float* __restrict__ y, uint8_t* __restrict__ arg,
-                                                              unsigned total, int W, int C4, int fH, int fW, int Wo) {
+                                                              unsigned total, int W, int C4, int fH_, int fW_, int Wo) {
+    const int fH = F ? F : fH_, fW = F ? F : fW_;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
         const unsigned cv = idx % (unsigned)C4;
         unsigned pix = idx / (unsigned)C4;
@@ -32,9 +36,16 @@ __global__ void __launch_bounds__(256) bn_act_pool_fwd_kernel(const float* __res
         const float4* in = reinterpret_cast<const float4*>(x) + ((size_t)pix * fH * W + (size_t)wo * fW) * C4 + cv;
         float4 best = make_float4(0.f, 0.f, 0.f, 0.f);
         uchar4 code = make_uchar4(0, 0, 0, 0);
+        float4 pre[F ? F * F : 1];
+        if (F) {
+#pragma unroll
+            for (int k = 0; k < F * F; ++k) pre[k] = __ldcs(in + ((size_t)(k / (F ? F : 1)) * W + k % (F ? F : 1)) * C4);
+        }
+#pragma unroll
         for (int i = 0; i < fH; ++i)
+#pragma unroll
             for (int j = 0; j < fW; ++j) {
-                const float4 v = __ldcs(in + ((size_t)i * W + j) * C4);
+                const float4 v = F ? pre[F ? i * F + j : 0] : __ldcs(in + ((size_t)i * W + j) * C4);
                 float4 o;
                 o.x = lrelu(fmaf(v.x, s.x, t.x), alpha); o.y = lrelu(fmaf(v.y, s.y, t.y), alpha);
                 o.z = lrelu(fmaf(v.z, s.z, t.z), alpha); o.w = lrelu(fmaf(v.w, s.w, t.w), alpha);
@@ -120,11 +131,13 @@ __global__ void __launch_bounds__(256) bn_act_pool_bwd_reduce_kernel(
 }
 
 // dx = k1 * g + k2 * x + k3 for every cell of every window (g is non-zero only at the window's selected cell).
+template <int F>
 __global__ void __launch_bounds__(256) bn_act_pool_bwd_apply_kernel(
     const float* __restrict__ x, const float* __restrict__ dpool, const uint8_t* __restrict__ arg,
     const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mean,
     const float* __restrict__ var, float eps, float alpha, const float* __restrict__ coeff, float* __restrict__ dx,
-    unsigned total, int W, int C, int fH, int fW, int Wo) {
+    unsigned total, int W, int C, int fH_, int fW_, int Wo) {
+    const int fH = F ? F : fH_, fW = F ? F : fW_;
     const int C4 = C >> 2;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
         const unsigned cv = idx % (unsigned)C4;
@@ -143,10 +156,18 @@ __global__ void __launch_bounds__(256) bn_act_pool_bwd_apply_kernel(
         const float4 be = *reinterpret_cast<const float4*>(beta + c);
         const float4 inv = make_float4(rsqrtf(vr.x + eps), rsqrtf(vr.y + eps), rsqrtf(vr.z + eps), rsqrtf(vr.w + eps));
         const size_t first = ((size_t)pix * fH * W + (size_t)wo * fW) * C4 + cv;
+        float4 pre[F ? F * F : 1];
+        if (F) {
+#pragma unroll
+            for (int k = 0; k < F * F; ++k)
+                pre[k] = __ldcs(reinterpret_cast<const float4*>(x) + first + ((size_t)(k / (F ? F : 1)) * W + k % (F ? F : 1)) * C4);
+        }
+#pragma unroll
         for (int i = 0; i < fH; ++i)
+#pragma unroll
             for (int j = 0; j < fW; ++j) {
                 const size_t cell = first + ((size_t)i * W + j) * C4;
-                const float4 v = __ldcs(reinterpret_cast<const float4*>(x) + cell);
+                const float4 v = F ? pre[F ? i * F + j : 0] : __ldcs(reinterpret_cast<const float4*>(x) + cell);
                 const unsigned char k = (unsigned char)(i * fW + j);
                 float4 o;
                 o.x = fmaf(k2.x, v.x, k3.x); o.y = fmaf(k2.y, v.y, k3.y); o.z = fmaf(k2.z, v.z, k3.z); o.w = fmaf(k2.w, v.w, k3.w);
@@ -203,8 +224,13 @@ extern "C" int aether_bn_act_pool_fwd(const float* x, const float* partials, int
     float* coeff = training ? bn_forward_coeffs(x, partials, nblocks, gamma, beta, running_mean, running_var, batch_mean,
                                                 batch_var, rows, C, eps, momentum, channel_scale, static_cast<float*>(ws), st)
                             : bn_eval_coeffs(gamma, beta, running_mean, running_var, C, eps, static_cast<float*>(ws), st);
-    bn_act_pool_fwd_kernel<<<fused_blocks(windows4, 256, 16), 256, 0, st>>>(x, coeff, coeff + C, alpha, pooled, argmax,
-                                                                           (unsigned)windows4, W, C / 4, fH, fW, W / fW);
+    const int fb = fused_blocks(windows4, 256, 16);
+    if (fH == 2 && fW == 2)
+        bn_act_pool_fwd_kernel<2><<<fb, 256, 0, st>>>(x, coeff, coeff + C, alpha, pooled, argmax, (unsigned)windows4, W, C / 4,
+                                                     fH, fW, W / fW);
+    else
+        bn_act_pool_fwd_kernel<0><<<fb, 256, 0, st>>>(x, coeff, coeff + C, alpha, pooled, argmax, (unsigned)windows4, W, C / 4,
+                                                     fH, fW, W / fW);
     count_launch();
     return check_launch("aether_bn_act_pool_fwd");
 }
@@ -233,9 +259,13 @@ extern "C" int aether_bn_act_pool_bwd(const float* x, const float* dpooled, cons
                                                       (windows + nb - 1) / nb, W, C, fH, fW, W / fW, part);
     count_launch();
     bn_backward_coeffs(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma, dbeta, coeff, channel_scale, st);
-    bn_act_pool_bwd_apply_kernel<<<fused_blocks(windows4, 256, 16), 256, 0, st>>>(x, dpooled, argmax, gamma, beta, batch_mean,
-                                                                                 batch_var, eps, alpha, coeff, dx,
-                                                                                 (unsigned)windows4, W, C, fH, fW, W / fW);
+    const int fb = fused_blocks(windows4, 256, 16);
+    if (fH == 2 && fW == 2)
+        bn_act_pool_bwd_apply_kernel<2><<<fb, 256, 0, st>>>(x, dpooled, argmax, gamma, beta, batch_mean, batch_var, eps, alpha,
+                                                           coeff, dx, (unsigned)windows4, W, C, fH, fW, W / fW);
+    else
+        bn_act_pool_bwd_apply_kernel<0><<<fb, 256, 0, st>>>(x, dpooled, argmax, gamma, beta, batch_mean, batch_var, eps, alpha,
+                                                           coeff, dx, (unsigned)windows4, W, C, fH, fW, W / fW);
     count_launch();
     return check_launch("aether_bn_act_pool_bwd");
 }

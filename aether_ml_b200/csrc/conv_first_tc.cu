@@ -211,6 +211,41 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
 #pragma unroll
         for (int j = 0; j < 4; ++j) row_in_tile[j] = q * 32 + (j >> 1) * 16 + trow + (j & 1) * 8;
         const float* bias4 = bias_s + col_begin + tcol4;
+        // Statistics: per-thread sums of its (4 rows x 4 columns) cells per 16-column group.  With one column batch
+        // per tile (ncols <= 64) they run over all tiles of the CTA and the lanes are combined once at the end --
+        // the epilogue is this kernel's critical path, and a per-tile lane reduction doubles its length.
+        const bool persist = ncols <= 64;
+        float4 st_s[4], st_q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) st_s[u] = st_q[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        // adds the lanes with equal lane%4 (same 4 columns, 8 row groups) and accumulates into the warp's sums
+        auto flush_stats = [&](int cb) {
+#pragma unroll
+            for (int m = 4; m <= 16; m <<= 1) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    st_s[u].x += __shfl_xor_sync(0xffffffffu, st_s[u].x, m); st_s[u].y += __shfl_xor_sync(0xffffffffu, st_s[u].y, m);
+                    st_s[u].z += __shfl_xor_sync(0xffffffffu, st_s[u].z, m); st_s[u].w += __shfl_xor_sync(0xffffffffu, st_s[u].w, m);
+                    st_q[u].x += __shfl_xor_sync(0xffffffffu, st_q[u].x, m); st_q[u].y += __shfl_xor_sync(0xffffffffu, st_q[u].y, m);
+                    st_q[u].z += __shfl_xor_sync(0xffffffffu, st_q[u].z, m); st_q[u].w += __shfl_xor_sync(0xffffffffu, st_q[u].w, m);
+                }
+            }
+            if (lane < 4) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int cc = cb + u * 16;
+                    if (cc < ncols) {
+                        float4* ps = reinterpret_cast<float4*>(stat_w + cc + tcol4);
+                        float4* pq = reinterpret_cast<float4*>(stat_w + 128 + cc + tcol4);
+                        float4 s = *ps, qq = *pq;
+                        s.x += st_s[u].x; s.y += st_s[u].y; s.z += st_s[u].z; s.w += st_s[u].w;
+                        qq.x += st_q[u].x; qq.y += st_q[u].y; qq.z += st_q[u].z; qq.w += st_q[u].w;
+                        *ps = s;
+                        *pq = qq;
+                    }
+                }
+            }
+        };
         uint32_t buf = 0, aph = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < p.ntiles && ok; t += grid) {
@@ -224,61 +259,69 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
             tc_fence_after();
             const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NT + col_begin;
 #pragma unroll 1
-            for (int cb = 0; cb < ncols; cb += 64) {
-                uint32_t v[2][4][8];
-                float4 st_s[4], st_q[4];
+            for (int cb0 = 0; cb0 < ncols; cb0 += 64) {
+                if (STATS && !persist) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) st_s[u] = st_q[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int u = 0; u < 4; ++u) st_s[u] = st_q[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                // two half batches of 2 x 16 columns: 32 accumulator registers in flight beside the running sums
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (cb + u * 16 < ncols) {
-                        tmem_ld_16x256b_x2(taddr0 + cb + u * 16, v[0][u]);
-                        tmem_ld_16x256b_x2(taddr0 + (16u << 16) + cb + u * 16, v[1][u]);
+                for (int hb = 0; hb < 2; ++hb) {
+                    const int cb = cb0 + hb * 32;
+                    if (cb >= ncols) break;
+                    uint32_t v[2][2][8];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        if (cb + u * 16 < ncols) {
+                            tmem_ld_16x256b_x2(taddr0 + cb + u * 16, v[0][u]);
+                            tmem_ld_16x256b_x2(taddr0 + (16u << 16) + cb + u * 16, v[1][u]);
+                        }
                     }
-                }
-                tmem_ld_wait();
-                if (cb + 64 >= ncols) {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(buf));
-                }
+                    tmem_ld_wait();
+                    if (cb + 32 >= ncols) {                       // accumulator fully read by this warp
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty_bar(buf));
+                    }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (cb + u * 16 < ncols) {
-                        const int cc = cb + u * 16;
-                        const float4 b4 = *reinterpret_cast<const float4*>(bias4 + cc);
-                        const bool cols_ok = all_cols || col_begin + tcol4 + cc < p.Cout;
+                    for (int u = 0; u < 2; ++u) {
+                        if (cb + u * 16 < ncols) {
+                            const int cc = cb + u * 16;
+                            const int g = hb * 2 + u;             // 16-column group within the 64-column batch
+                            const float4 b4 = *reinterpret_cast<const float4*>(bias4 + cc);
+                            const bool cols_ok = all_cols || col_begin + tcol4 + cc < p.Cout;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            // quad exchange: 2+2 columns per lane -> 4 consecutive columns per lane (64-byte row segments)
-                            const uint32_t a0 = v[j >> 1][u][(j & 1) * 2 + 0], a1 = v[j >> 1][u][(j & 1) * 2 + 1];
-                            const uint32_t b0 = v[j >> 1][u][4 + (j & 1) * 2 + 0], b1 = v[j >> 1][u][4 + (j & 1) * 2 + 1];
-                            const uint32_t s0 = lo2 ? b0 : a0, s1 = lo2 ? b1 : a1;
-                            const uint32_t r0 = __shfl_xor_sync(0xffffffffu, s0, 2), r1 = __shfl_xor_sync(0xffffffffu, s1, 2);
-                            const uint32_t x0 = lo2 ? a0 : r0, x1 = lo2 ? a1 : r1;
-                            const uint32_t y0 = lo2 ? r0 : b0, y1 = lo2 ? r1 : b1;
-                            const uint32_t t0 = odd ? x0 : y0, t1 = odd ? x1 : y1;
-                            const uint32_t q0 = __shfl_xor_sync(0xffffffffu, t0, 1), q1 = __shfl_xor_sync(0xffffffffu, t1, 1);
-                            float4 a;
-                            a.x = __uint_as_float(odd ? q0 : x0);
-                            a.y = __uint_as_float(odd ? q1 : x1);
-                            a.z = __uint_as_float(odd ? y0 : q0);
-                            a.w = __uint_as_float(odd ? y1 : q1);
-                            const bool wr = cols_ok && rowp[j] != nullptr;
-                            if (wr)
-                                __stcs(reinterpret_cast<float4*>(rowp[j] + cc),
-                                       make_float4(a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w));
-                            if (STATS) {
-                                a.x = wr ? a.x : 0.f; a.y = wr ? a.y : 0.f; a.z = wr ? a.z : 0.f; a.w = wr ? a.w : 0.f;
-                                st_s[u].x += a.x; st_s[u].y += a.y; st_s[u].z += a.z; st_s[u].w += a.w;
-                                st_q[u].x = fmaf(a.x, a.x, st_q[u].x); st_q[u].y = fmaf(a.y, a.y, st_q[u].y);
-                                st_q[u].z = fmaf(a.z, a.z, st_q[u].z); st_q[u].w = fmaf(a.w, a.w, st_q[u].w);
+                            for (int j = 0; j < 4; ++j) {
+                                // quad exchange: 2+2 columns per lane -> 4 consecutive columns per lane (64-byte row segments)
+                                const uint32_t a0 = v[j >> 1][u][(j & 1) * 2 + 0], a1 = v[j >> 1][u][(j & 1) * 2 + 1];
+                                const uint32_t b0 = v[j >> 1][u][4 + (j & 1) * 2 + 0], b1 = v[j >> 1][u][4 + (j & 1) * 2 + 1];
+                                const uint32_t s0 = lo2 ? b0 : a0, s1 = lo2 ? b1 : a1;
+                                const uint32_t r0 = __shfl_xor_sync(0xffffffffu, s0, 2), r1 = __shfl_xor_sync(0xffffffffu, s1, 2);
+                                const uint32_t x0 = lo2 ? a0 : r0, x1 = lo2 ? a1 : r1;
+                                const uint32_t y0 = lo2 ? r0 : b0, y1 = lo2 ? r1 : b1;
+                                const uint32_t t0 = odd ? x0 : y0, t1 = odd ? x1 : y1;
+                                const uint32_t q0 = __shfl_xor_sync(0xffffffffu, t0, 1), q1 = __shfl_xor_sync(0xffffffffu, t1, 1);
+                                float4 a;
+                                a.x = __uint_as_float(odd ? q0 : x0);
+                                a.y = __uint_as_float(odd ? q1 : x1);
+                                a.z = __uint_as_float(odd ? y0 : q0);
+                                a.w = __uint_as_float(odd ? y1 : q1);
+                                const bool wr = cols_ok && rowp[j] != nullptr;
+                                if (wr)
+                                    __stcs(reinterpret_cast<float4*>(rowp[j] + cc),
+                                           make_float4(a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w));
+                                if (STATS) {
+                                    a.x = wr ? a.x : 0.f; a.y = wr ? a.y : 0.f; a.z = wr ? a.z : 0.f; a.w = wr ? a.w : 0.f;
+                                    st_s[g].x += a.x; st_s[g].y += a.y; st_s[g].z += a.z; st_s[g].w += a.w;
+                                    st_q[g].x = fmaf(a.x, a.x, st_q[g].x); st_q[g].y = fmaf(a.y, a.y, st_q[g].y);
+                                    st_q[g].z = fmaf(a.z, a.z, st_q[g].z); st_q[g].w = fmaf(a.w, a.w, st_q[g].w);
+                                }
                             }
                         }
                     }
                 }
                 if (STATS) {
-                    if (cb == 0) {
+                    if (cb0 == 0) {
                         float nrows = 0.f;
 #pragma unroll
                         for (int j = 0; j < 4; ++j) nrows += (rowp[j] != nullptr) ? 1.f : 0.f;
@@ -287,35 +330,12 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
                         nrows += __shfl_xor_sync(0xffffffffu, nrows, 16);
                         st_rows += nrows;
                     }
-#pragma unroll
-                    for (int m = 4; m <= 16; m <<= 1) {
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            st_s[u].x += __shfl_xor_sync(0xffffffffu, st_s[u].x, m); st_s[u].y += __shfl_xor_sync(0xffffffffu, st_s[u].y, m);
-                            st_s[u].z += __shfl_xor_sync(0xffffffffu, st_s[u].z, m); st_s[u].w += __shfl_xor_sync(0xffffffffu, st_s[u].w, m);
-                            st_q[u].x += __shfl_xor_sync(0xffffffffu, st_q[u].x, m); st_q[u].y += __shfl_xor_sync(0xffffffffu, st_q[u].y, m);
-                            st_q[u].z += __shfl_xor_sync(0xffffffffu, st_q[u].z, m); st_q[u].w += __shfl_xor_sync(0xffffffffu, st_q[u].w, m);
-                        }
-                    }
-                    if (lane < 4) {
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int cc = cb + u * 16;
-                            if (cc < ncols) {
-                                float4* ps = reinterpret_cast<float4*>(stat_w + cc + tcol4);
-                                float4* pq = reinterpret_cast<float4*>(stat_w + 128 + cc + tcol4);
-                                float4 s = *ps, qq = *pq;
-                                s.x += st_s[u].x; s.y += st_s[u].y; s.z += st_s[u].z; s.w += st_s[u].w;
-                                qq.x += st_q[u].x; qq.y += st_q[u].y; qq.z += st_q[u].z; qq.w += st_q[u].w;
-                                *ps = s;
-                                *pq = qq;
-                            }
-                        }
-                    }
+                    if (!persist) flush_stats(cb0);
                 }
             }
             if (++buf == NB) { buf = 0; aph ^= 1u; }
         }
+        if (STATS && persist) flush_stats(0);
         if (STATS && lane < 4) {
             float* sp = p.stats + ((size_t)blockIdx.x * 4 + q) * 3 * (size_t)p.Cout;
             const float inv_n = st_rows > 0.f ? 1.f / st_rows : 0.f;

@@ -70,6 +70,8 @@ def test_batch_norm_shapes(env, shape):
 # (S, H, W, Cin, Cout, mode, statistics expected from the conv epilogue)
 @pytest.mark.parametrize("case", [(8, 32, 32, 64, 128, "bf16", True), (37, 20, 24, 64, 64, "tf32", True),
                                   (300, 32, 32, 3, 64, "bf16", True), (5, 28, 28, 1, 32, "bf16", True),
+                                  (200, 32, 32, 3, 128, "bf16", True), (6, 20, 20, 3, 256, "bf16", True),
+                                  (3, 16, 16, 2, 192, "bf16", True),
                                   # per-tap tensor-core kernel: one / two / three column tiles, ragged pixel tiles
                                   (16, 8, 8, 256, 256, "bf16", True), (40, 8, 8, 128, 512, "bf16", True),
                                   (50, 16, 16, 128, 256, "bf16", True), (7, 10, 10, 32, 96, "tf32", True),

@@ -46,22 +46,27 @@ static constexpr int PROF_MAX = 2048;          // event pairs per kind; further 
 struct ProfSlot {
     cudaEvent_t beg[PROF_MAX], end[PROF_MAX];
     int used = 0;
+    int seen = 0;        // launches of this kind since profiling was enabled
+    bool open = false;   // the launch in progress is being timed
     bool created = false;
 };
 static ProfSlot g_prof[PK_COUNT];
 static bool g_prof_on = false;
+static int g_prof_stride = 1;   // every n-th launch of a kind is timed (event records cost stream time themselves)
 
 void prof_begin(int kind, cudaStream_t st) {
     if (!g_prof_on) return;
     ProfSlot& s = g_prof[kind];
-    if (s.used < PROF_MAX) cudaEventRecord(s.beg[s.used], st);
+    s.open = (s.seen++ % g_prof_stride) == 0 && s.used < PROF_MAX;
+    if (s.open) cudaEventRecord(s.beg[s.used], st);
 }
 void prof_end(int kind, cudaStream_t st) {
     if (!g_prof_on) return;
     ProfSlot& s = g_prof[kind];
-    if (s.used < PROF_MAX) {
+    if (s.open) {
         cudaEventRecord(s.end[s.used], st);
         ++s.used;
+        s.open = false;
     }
 }
 
@@ -111,7 +116,10 @@ extern "C" int aether_profile_enable(int on) {
                 s.created = true;
             }
             s.used = 0;
+            s.seen = 0;
+            s.open = false;
         }
+        g_prof_stride = on > 0 ? on : 1;
     }
     g_prof_on = on != 0;
     return AE_OK;
@@ -135,7 +143,7 @@ extern "C" int aether_profile_read(int kind, double* total_ms, int* launches) {
 }
 
 extern "C" void aether_profile_reset(void) {
-    for (int k = 0; k < PK_COUNT; ++k) g_prof[k].used = 0;
+    for (int k = 0; k < PK_COUNT; ++k) g_prof[k].used = g_prof[k].seen = 0;
 }
 
 extern "C" size_t aether_conv2d_workspace_bytes(const AetherConvDesc* d) {

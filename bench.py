@@ -205,7 +205,10 @@ def run_gpu(args):
 
     # ---- timed region: device-resident inputs
     sampler = ClockSampler(local) if rank == 0 else None
-    L.aether_profile_enable(1)
+    # Per-kernel CUDA events on every 5th launch of each kind (an odd stride, so the two alternating cast launches are
+    # both sampled): an event pair costs a few microseconds of stream time, ~6 % of this step when taken everywhere.
+    prof_stride = 5 if args.steps >= 10 else 1
+    L.aether_profile_enable(prof_stride)
     launches0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
@@ -318,7 +321,8 @@ def run_gpu(args):
                          "traffic": DRAM_TRAFFIC_S256.get(dom) if (S == 256 and args.mode == "bf16") else None,
                          "traffic_unit": "bytes per launch (dram read + write, ncu, full-size workload)",
                          "peak_source": "%s (%s bf16 figure of MEASURED_PEAKS.json)" % (pk["source"], "sustained" if ms_total > 1500 else "burst"),
-                         "launch_ms": dom_ms, "flops_per_launch": per_gemm},
+                         "launch_ms": dom_ms, "flops_per_launch": per_gemm,
+                         "timed_launches": kinds[dom][1], "timed_every": prof_stride},
             "kernels": {k: {"total_ms": v[0], "launches": v[1], "avg_ms": v[0] / max(v[1], 1),
                             "tflops": (per_gemm / (v[0] / max(v[1], 1) * 1e-3) / 1e12) if (v[1] and k != "operand_cast" and v[0] > 0) else None}
                         for k, v in kinds.items()},

@@ -61,9 +61,11 @@ uint64_t aether_launch_count(void);
 int aether_device_status(void);
 void aether_device_status_clear(void);
 
-/* Optional kernel timing for benchmarks (off by default).  aether_profile_enable(1) creates a fixed
+/* Optional kernel timing for benchmarks (off by default).  aether_profile_enable(n), n >= 1, creates a fixed
  * pool of CUDA events once and resets the counters; while enabled, events are recorded on the launch
- * stream around each convolution kernel.  aether_profile_read waits for the recorded events and
+ * stream around every n-th launch of each kind of convolution kernel (an event record takes a few
+ * microseconds of stream time itself, so timing every launch slows short steps measurably);
+ * aether_profile_enable(0) switches it off.  aether_profile_read waits for the recorded events and
  * returns the summed duration and the number of timed launches of one kind:
  * 0 = forward implicit GEMM, 1 = dX implicit GEMM, 2 = dW kernel, 3 = operand (bf16) cast kernels. */
 int aether_profile_enable(int on);

@@ -226,19 +226,24 @@ static void launch_bn_reduce(int nb, cudaStream_t st, const float* x, const floa
 // Merges the per-block (n, mean, M2) triples in double precision, writes batch mean / biased variance,
 // updates the running statistics (momentum * old + (1 - momentum) * batch) and the affine
 // coefficients scale = gamma / sqrt(var + eps), shift = beta - mean * scale used by the apply kernel.
-__global__ void bn_finalize_fwd_kernel(const float* __restrict__ part, int nblocks, int C,
+// Finalize kernels: FIN_CH channels x FIN_LANES lanes per CTA.  The merge is a chain of L2 round trips per lane, so
+// it is spread over many lanes (a few blocks each); a network with 32 channels still gets 4 CTAs.
+static constexpr int FIN_CH = 8, FIN_LANES = 64, FIN_THREADS = FIN_CH * FIN_LANES;
+
+__global__ void __launch_bounds__(FIN_THREADS) bn_finalize_fwd_kernel(const float* __restrict__ part, int nblocks, int C,
                                        const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
                                        float momentum, float* __restrict__ running_mean,
                                        float* __restrict__ running_var, float* __restrict__ batch_mean,
                                        float* __restrict__ batch_var, float* __restrict__ scale_shift) {
-    // 32 channels x 8 lanes per CTA (launch with 256 threads).  Two division-free passes over the per-block
-    // triples: total count and sum first, then M2 about the global mean; lanes are combined in fixed order.
-    __shared__ double red_a[8][32], red_b[8][32];
-    const int cl = threadIdx.x & 31, ln = threadIdx.x >> 5;
-    const int c = blockIdx.x * 32 + cl;
+    // Two division-free passes over the per-block triples: total count and sum first, then M2 about the global
+    // mean; lanes are combined in fixed order.
+    __shared__ double red_a[FIN_LANES][FIN_CH], red_b[FIN_LANES][FIN_CH];
+    const int cl = threadIdx.x % FIN_CH, ln = threadIdx.x / FIN_CH;
+    const int c = blockIdx.x * FIN_CH + cl;
     double n_sum = 0.0, s_sum = 0.0;
     if (c < C)
-        for (int b = ln; b < nblocks; b += 8) {
+#pragma unroll 4
+        for (int b = ln; b < nblocks; b += FIN_LANES) {
             const float* p = part + (size_t)b * 3 * C;
             const double nl = p[c];
             n_sum += nl;
@@ -248,13 +253,14 @@ __global__ void bn_finalize_fwd_kernel(const float* __restrict__ part, int nbloc
     red_b[ln][cl] = s_sum;
     __syncthreads();
     double N = 0.0, S1 = 0.0;
-#pragma unroll
-    for (int l = 0; l < 8; ++l) { N += red_a[l][cl]; S1 += red_b[l][cl]; }
+#pragma unroll 8
+    for (int l = 0; l < FIN_LANES; ++l) { N += red_a[l][cl]; S1 += red_b[l][cl]; }
     const double M = N > 0 ? S1 / N : 0.0;
     __syncthreads();
     double m2 = 0.0;
     if (c < C)
-        for (int b = ln; b < nblocks; b += 8) {
+#pragma unroll 4
+        for (int b = ln; b < nblocks; b += FIN_LANES) {
             const float* p = part + (size_t)b * 3 * C;
             const double d = (double)p[C + c] - M;
             m2 += (double)p[2 * C + c] + (double)p[c] * d * d;
@@ -263,8 +269,8 @@ __global__ void bn_finalize_fwd_kernel(const float* __restrict__ part, int nbloc
     __syncthreads();
     if (ln != 0 || c >= C) return;
     double M2 = 0.0;
-#pragma unroll
-    for (int l = 0; l < 8; ++l) M2 += red_a[l][cl];
+#pragma unroll 8
+    for (int l = 0; l < FIN_LANES; ++l) M2 += red_a[l][cl];
     const double var = N > 0 ? M2 / N : 0.0;
     batch_mean[c] = (float)M;
     batch_var[c] = (float)var;
@@ -330,19 +336,20 @@ __global__ void __launch_bounds__(256) affine_channels_kernel(const float* __res
 
 // dgamma = sum(dy * xhat), dbeta = sum(dy); coefficients for
 // dx = k1[c] * dy + k2[c] * x + k3[c]  with  k1 = gamma*inv, k2 = -gamma*inv^2*dgamma/N * ... (see below)
-__global__ void bn_finalize_bwd_kernel(const float* __restrict__ part, int nblocks, int C, long long rows,
+__global__ void __launch_bounds__(FIN_THREADS) bn_finalize_bwd_kernel(const float* __restrict__ part, int nblocks, int C, long long rows,
                                        const float* __restrict__ gamma, const float* __restrict__ mean,
                                        const float* __restrict__ var, float eps, float* __restrict__ dgamma,
                                        float* __restrict__ dbeta, float* __restrict__ coeff,
                                        const float* __restrict__ pscale) {
     // pscale (nullable): per-channel factor that multiplied the layer's output (a fused spatial-dropout mask).  The
     // upstream gradient is that factor times what the kernels summed, so it scales both sums and the dy coefficient.
-    __shared__ double red_a[8][32], red_b[8][32];
-    const int cl = threadIdx.x & 31, ln = threadIdx.x >> 5;
-    const int c = blockIdx.x * 32 + cl;
+    __shared__ double red_a[FIN_LANES][FIN_CH], red_b[FIN_LANES][FIN_CH];
+    const int cl = threadIdx.x % FIN_CH, ln = threadIdx.x / FIN_CH;
+    const int c = blockIdx.x * FIN_CH + cl;
     double pa = 0.0, pb = 0.0;
     if (c < C)
-        for (int b = ln; b < nblocks; b += 8) {
+#pragma unroll 4
+        for (int b = ln; b < nblocks; b += FIN_LANES) {
             pa += part[(size_t)b * 2 * C + c];
             pb += part[(size_t)b * 2 * C + C + c];
         }
@@ -351,8 +358,8 @@ __global__ void bn_finalize_bwd_kernel(const float* __restrict__ part, int nbloc
     __syncthreads();
     if (ln != 0 || c >= C) return;
     double sdy = 0.0, sdyx = 0.0;
-#pragma unroll
-    for (int l = 0; l < 8; ++l) { sdy += red_a[l][cl]; sdyx += red_b[l][cl]; }
+#pragma unroll 8
+    for (int l = 0; l < FIN_LANES; ++l) { sdy += red_a[l][cl]; sdyx += red_b[l][cl]; }
     const double ms = pscale ? (double)pscale[c] : 1.0;
     sdy *= ms;
     sdyx *= ms;
@@ -443,7 +450,7 @@ float* bn_forward_coeffs(const float* x, const float* partials, long long nblock
     } else {
         nb = (int)nblocks;
     }
-    bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(src, nb, C, gamma, beta, eps, momentum, running_mean, running_var,
+    bn_finalize_fwd_kernel<<<ceil_div(C, FIN_CH), FIN_THREADS, 0, st>>>(src, nb, C, gamma, beta, eps, momentum, running_mean, running_var,
                                                             batch_mean, batch_var, coeff);
     count_launch();
     if (channel_scale) {
@@ -465,7 +472,7 @@ float* bn_eval_coeffs(const float* gamma, const float* beta, const float* runnin
 void bn_backward_coeffs(const float* part, int nb, int C, long long rows, const float* gamma, const float* mean,
                         const float* var, float eps, float* dgamma, float* dbeta, float* coeff, const float* pscale,
                         cudaStream_t st) {
-    bn_finalize_bwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, rows, gamma, mean, var, eps, dgamma, dbeta, coeff,
+    bn_finalize_bwd_kernel<<<ceil_div(C, FIN_CH), FIN_THREADS, 0, st>>>(part, nb, C, rows, gamma, mean, var, eps, dgamma, dbeta, coeff,
                                                             pscale);
     count_launch();
 }
@@ -492,7 +499,7 @@ extern "C" int aether_bn_fwd_train(const float* x, const float* gamma, const flo
     float* part = static_cast<float*>(ws);
     float* coeff = part + (size_t)nb * 3 * C;
     launch_bn_reduce<0>(nb, st, x, nullptr, nullptr, nullptr, eps, rows, C, part);
-    bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
+    bn_finalize_fwd_kernel<<<ceil_div(C, FIN_CH), FIN_THREADS, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
                                                             running_var, batch_mean, batch_var, coeff);
     const long long n = rows * C;
     affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C, -1.f);
@@ -515,7 +522,7 @@ extern "C" int aether_bn_fwd_train_partials(const float* x, const float* partial
     if ((C & 3) == 0 && (!aligned16(x) || !aligned16(y))) return set_error(AE_BAD_ARG, "aether_bn_fwd_train_partials: arrays must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     float* coeff = static_cast<float*>(ws);
-    bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(partials, (int)nblocks, C, gamma, beta, eps, momentum, running_mean,
+    bn_finalize_fwd_kernel<<<ceil_div(C, FIN_CH), FIN_THREADS, 0, st>>>(partials, (int)nblocks, C, gamma, beta, eps, momentum, running_mean,
                                                             running_var, batch_mean, batch_var, coeff);
     const long long n = rows * C;
     affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C, -1.f);
@@ -575,7 +582,7 @@ extern "C" int aether_bn_fwd_train_static(const float* x, const float* gamma, co
     // partials, the finalize kernel stores all coefficients), so stale contents of a previous call never matter
     // and nothing has to be cleared.
     launch_bn_reduce<0>(nb, st, x, nullptr, nullptr, nullptr, eps, rows, C, part);
-    bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
+    bn_finalize_fwd_kernel<<<ceil_div(C, FIN_CH), FIN_THREADS, 0, st>>>(part, nb, C, gamma, beta, eps, momentum, running_mean,
                                                             running_var, batch_mean, batch_var, coeff);
     const long long n = rows * C;
     affine_channels_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, y, coeff, coeff + C, n, C, -1.f);
@@ -613,7 +620,7 @@ extern "C" int aether_bn_bwd(const float* x, const float* dy, const float* gamma
     float* part = static_cast<float*>(ws);
     float* coeff = part + (size_t)nb * 3 * C;
     launch_bn_reduce<1>(nb, st, x, dy, batch_mean, batch_var, eps, rows, C, part);
-    bn_finalize_bwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
+    bn_finalize_bwd_kernel<<<ceil_div(C, FIN_CH), FIN_THREADS, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
                                                             dbeta, coeff, nullptr);
     const long long n = rows * C;
     bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C, nullptr, 0.f);
@@ -655,7 +662,7 @@ extern "C" int aether_bn_act_fwd_train(const float* x, const float* partials, in
     } else {
         nb = (int)nblocks;
     }
-    bn_finalize_fwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(src, nb, C, gamma, beta, eps, momentum, running_mean, running_var,
+    bn_finalize_fwd_kernel<<<ceil_div(C, FIN_CH), FIN_THREADS, 0, st>>>(src, nb, C, gamma, beta, eps, momentum, running_mean, running_var,
                                                             batch_mean, batch_var, coeff);
     if (channel_scale) {
         // act(v) * m = act(m * v) for m >= 0 (ReLU and Leaky_ReLU are positively homogeneous): a spatial-dropout
@@ -701,7 +708,7 @@ extern "C" int aether_bn_act_bwd(const float* x, const float* y_act, const float
     float* part = static_cast<float*>(ws);
     float* coeff = part + (size_t)nb * 3 * C;
     launch_bn_reduce<1>(nb, st, x, dy, batch_mean, batch_var, eps, rows, C, part, y_act, alpha);
-    bn_finalize_bwd_kernel<<<ceil_div(C, 32), 256, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
+    bn_finalize_bwd_kernel<<<ceil_div(C, FIN_CH), FIN_THREADS, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
                                                             dbeta, coeff, channel_scale);
     const long long n = rows * C;
     bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C, y_act, alpha);

@@ -385,6 +385,7 @@ struct FirstDwParams {
 // and the kernel ran at a third of the HBM rate; 384 threads cover a 128-pixel tile of dy in one or two rounds.
 static constexpr int FD_PROD_WARPS = 12;
 static constexpr int FD_NP = 32 * FD_PROD_WARPS;
+static constexpr int FD_GRP = FD_NP / 2;                                     // two producer groups on alternate tiles
 static constexpr int FD_ROWS = 6;                                            // dy rows per thread and round
 static constexpr int FD_TAIL = 1024 + FD_NP * 8 * 4 + 1024;                  // barriers, k tables, dB staging
 static constexpr int FD_THREADS = 32 * (FD_PROD_WARPS + 1 + 4);              // producers, MMA issuer, 4 epilogue warps
@@ -411,7 +412,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            mbar_init(full_bar(s), FD_NP);
+            mbar_init(full_bar(s), FD_GRP);
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(done_bar, 1);
@@ -438,12 +439,15 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
 
     if (warp < FD_PROD_WARPS) {
         // ------------------------------------------------------------------ producers
+        // Two groups of six warps build alternate tiles: while one group converts and gathers, the other group's dy
+        // loads are in flight (one group in lock step left the HBM pipe idle for two thirds of every tile).
         const int r = threadIdx.x;                                   // 0 .. FD_NP-1
+        const int grp = r / FD_GRP, rg = r - grp * FD_GRP;
         const int chunks = p.KP >> 3;
         const int col_items = 128 * chunks;                          // item -> pixel = item % 128, 16-byte chunk = item / 128
         const int C8 = p.Cout >> 3;                                  // 8-channel chunks of a dy row (power of two <= 32)
-        const int my_chunk = r & (C8 - 1);                           // fixed for this thread: FD_NP % C8 == 0
-        const int prow0 = r / C8, prow_step = FD_NP / C8;
+        const int my_chunk = rg & (C8 - 1);                          // fixed for this thread: FD_GRP % C8 == 0
+        const int prow0 = rg / C8, prow_step = FD_GRP / C8;
         const int dchunks = p.dblocks * 16;                          // 8-channel chunks the operand holds (zero padded)
         const long long HoWo = (long long)p.Ho * p.Wo;
         float bs[8];
@@ -451,13 +455,16 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
         for (int e = 0; e < 8; ++e) bs[e] = 0.f;
         if (C8 < dchunks) {
             // fewer than 128 channels: the chunks past Cout of the M = 128 operand are zero and stay zero (nobody
-            // writes them again); each thread's own fence before its first arrive publishes them
+            // writes them again); published to the tensor core before any producer arrives on a stage
             for (int i = r; i < S * p.stage_bytes / 16; i += FD_NP)
                 reinterpret_cast<uint4*>(gen_base)[i] = make_uint4(0, 0, 0, 0);
+            fence_proxy_async_smem();
+            named_bar_sync(1, FD_NP);
         }
-        int s = 0;
-        uint32_t ph = 0;
-        for (int t = blockIdx.x; t < p.ntiles; t += grid) {
+        int k = grp;                                                 // index of the tile among this CTA's tiles
+        for (int t = blockIdx.x + grp * grid; t < p.ntiles; t += 2 * grid, k += 2) {
+            const int s = k % S;
+            const uint32_t ph = (uint32_t)(k / S) & 1u;
             const long long pix0 = (long long)t * 128;
             if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) break;
             uint8_t* stage = gen_base + (size_t)s * p.stage_bytes;
@@ -490,7 +497,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
                 }
             }
             // col tile: row = pixel of the tile (the forward kernel's operand, read here as MN-major B)
-            for (int it = r; it < col_items; it += FD_NP) {
+            for (int it = rg; it < col_items; it += FD_GRP) {
                 const int pr = it & 127, ch = it >> 7;
                 const long long pix = pix0 + pr;
                 int h0 = -(1 << 20), w0 = 0;
@@ -515,7 +522,6 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
             }
             fence_proxy_async_smem();
             mbar_arrive(full_bar(s));
-            if (++s == S) { s = 0; ph ^= 1u; }
         }
         // db: fp32 column sums of this thread's 8 channels; threads with the same chunk are added in fixed order
 #pragma unroll

@@ -379,13 +379,16 @@ struct FirstDwParams {
     int dblocks;         // 128-channel blocks of dy
     long long P;
     int stages, ntiles, stage_bytes;
+    int groups;          // producer groups (divides FD_NP; <= stages)
 };
 
 // Twelve producer warps: with one producer warp per scheduler every round of dy loads costs a full HBM round trip
 // and the kernel ran at a third of the HBM rate; 384 threads cover a 128-pixel tile of dy in one or two rounds.
 static constexpr int FD_PROD_WARPS = 12;
 static constexpr int FD_NP = 32 * FD_PROD_WARPS;
-static constexpr int FD_GRP = FD_NP / 2;                                     // two producer groups on alternate tiles
+// Producer groups, each building every groups-th tile.  At most as many groups as operand stages: a group that
+// could run two phases ahead of a stage's barrier would pass its parity wait early.
+static constexpr int FD_MAX_GROUPS = 3;
 static constexpr int FD_ROWS = 6;                                            // dy rows per thread and round
 static constexpr int FD_TAIL = 1024 + FD_NP * 8 * 4 + 1024;                  // barriers, k tables, dB staging
 static constexpr int FD_THREADS = 32 * (FD_PROD_WARPS + 1 + 4);              // producers, MMA issuer, 4 epilogue warps
@@ -412,7 +415,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            mbar_init(full_bar(s), FD_GRP);
+            mbar_init(full_bar(s), FD_NP / p.groups);
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(done_bar, 1);
@@ -439,9 +442,10 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
 
     if (warp < FD_PROD_WARPS) {
         // ------------------------------------------------------------------ producers
-        // Two groups of six warps build alternate tiles: while one group converts and gathers, the other group's dy
-        // loads are in flight (one group in lock step left the HBM pipe idle for two thirds of every tile).
+        // Groups of warps build alternate tiles: while one group converts and gathers, the other groups' dy loads are
+        // in flight (all twelve warps in lock step left the HBM pipe idle for two thirds of every tile).
         const int r = threadIdx.x;                                   // 0 .. FD_NP-1
+        const int FD_GRP = FD_NP / p.groups;
         const int grp = r / FD_GRP, rg = r - grp * FD_GRP;
         const int chunks = p.KP >> 3;
         const int col_items = 128 * chunks;                          // item -> pixel = item % 128, 16-byte chunk = item / 128
@@ -462,7 +466,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
             named_bar_sync(1, FD_NP);
         }
         int k = grp;                                                 // index of the tile among this CTA's tiles
-        for (int t = blockIdx.x + grp * grid; t < p.ntiles; t += 2 * grid, k += 2) {
+        for (int t = blockIdx.x + grp * grid; t < p.ntiles; t += p.groups * grid, k += p.groups) {
             const int s = k % S;
             const uint32_t ph = (uint32_t)(k / S) & 1u;
             const long long pix0 = (long long)t * 128;
@@ -684,6 +688,7 @@ int first_tc_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy
     const int tail = FD_TAIL;
     p.stages = (232448 - 1024 - tail) / p.stage_bytes;
     if (p.stages > 4) p.stages = 4;
+    p.groups = p.stages < FD_MAX_GROUPS ? p.stages : FD_MAX_GROUPS;      // 1, 2 or 3: all divide FD_NP, FD_NP / groups is a multiple of 32
     const int grid = first_tc_grid(p.ntiles);
     const size_t need = (size_t)grid * (K + 1) * d.Cout * sizeof(float);
     if (!ws || ws_bytes < need) return set_error(AE_BAD_ARG, "conv workspace too small: %zu < %zu", ws_bytes, need);

@@ -135,7 +135,9 @@ def test_filter_row_dw_shapes(env, shape):
                                    # first-layer kernels (1..4 input channels, power-of-two filter count 16..256)
                                    (5, 17, 13, 3, 128, 3, (1, 1), "same"), (3, 20, 20, 1, 64, 5, (2, 2), "valid"),
                                    (2, 9, 9, 3, 256, 3, (1, 2), "same"), (6, 14, 14, 2, 16, 3, (1, 1), "same"),
-                                   (70, 32, 32, 3, 128, 3, (1, 1), "same")])
+                                   (70, 32, 32, 3, 128, 3, (1, 1), "same"),
+                                   # several tiles per CTA with two operand stages (256 filters) / four (64)
+                                   (300, 16, 16, 3, 256, 3, (1, 1), "same"), (500, 16, 16, 4, 64, 3, (1, 1), "same")])
 def test_cuda_core_shapes(env, shape):
     S, H, W, Cin, Cout, f, st, pad = shape
     rng = np.random.default_rng(3)

@@ -722,10 +722,13 @@ namespace aether {
 // i*fW + j of the FIRST maximum in row-major window order (ties keep the earlier cell).
 // I is the flat-index type: unsigned int whenever the element count fits (32-bit divisions are several times
 // cheaper than 64-bit ones and the index decode is most of the kernel's instructions), else long long.
-template <bool MAX, typename I>
+// F > 0: F x F windows known at compile time (vec == 4 only): the window's loads are issued together -- one 16-byte
+// load in flight per thread does not cover the HBM latency.
+template <bool MAX, typename I, int F>
 __global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y,
-                                                       uint8_t* __restrict__ arg, int S, int H, int W, int C, int fH,
-                                                       int fW, int sH, int sW, int Ho, int Wo, int vec) {
+                                                       uint8_t* __restrict__ arg, int S, int H, int W, int C, int fH_,
+                                                       int fW_, int sH, int sW, int Ho, int Wo, int vec) {
+    const int fH = F ? F : fH_, fW = F ? F : fW_;
     const int Cv = C / vec;
     const I total = (I)(1LL * S * Ho * Wo * Cv);
     const float inv = 1.f / (float)(fH * fW);
@@ -740,10 +743,20 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const float* __restrict__
         if (vec == 4) {
             float4 best = make_float4(0.f, 0.f, 0.f, 0.f);
             uchar4 code = make_uchar4(0, 0, 0, 0);
+            float4 pre[F ? F * F : 1];
+            if (F) {
+#pragma unroll
+                for (int k = 0; k < F * F; ++k)
+                    pre[k] = *reinterpret_cast<const float4*>(
+                        x + (((size_t)s * H + ho * sH + k / (F ? F : 1)) * W + wo * sW + k % (F ? F : 1)) * C + cv * 4);
+            }
+#pragma unroll
             for (int i = 0; i < fH; ++i)
+#pragma unroll
                 for (int j = 0; j < fW; ++j) {
-                    const float4 v = *reinterpret_cast<const float4*>(
-                        x + (((size_t)s * H + ho * sH + i) * W + wo * sW + j) * C + cv * 4);
+                    const float4 v = F ? pre[F ? i * F + j : 0]
+                                       : *reinterpret_cast<const float4*>(
+                                             x + (((size_t)s * H + ho * sH + i) * W + wo * sW + j) * C + cv * 4);
                     const unsigned char k = (unsigned char)(i * fW + j);
                     if (MAX) {
                         if (k == 0) { best = v; }
@@ -1090,13 +1103,20 @@ extern "C" int aether_pool_fwd(const float* x, float* y, uint8_t* argmax, int S,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int nb = blocks_for(total, 256, 16);
     const bool small = total < (1LL << 31);
+    const bool two = vec == 4 && fH == 2 && fW == 2;
+#define AETHER_POOL_FWD(MAXK, I, ARG)                                                                                  \
+    do {                                                                                                               \
+        if (two) pool_fwd_kernel<MAXK, I, 2><<<nb, 256, 0, st>>>(x, y, ARG, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);  \
+        else pool_fwd_kernel<MAXK, I, 0><<<nb, 256, 0, st>>>(x, y, ARG, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);      \
+    } while (0)
     if (kind == AETHER_POOL_MAX) {
-        if (small) pool_fwd_kernel<true, unsigned><<<nb, 256, 0, st>>>(x, y, argmax, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
-        else pool_fwd_kernel<true, long long><<<nb, 256, 0, st>>>(x, y, argmax, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
+        if (small) AETHER_POOL_FWD(true, unsigned, argmax);
+        else AETHER_POOL_FWD(true, long long, argmax);
     } else {
-        if (small) pool_fwd_kernel<false, unsigned><<<nb, 256, 0, st>>>(x, y, nullptr, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
-        else pool_fwd_kernel<false, long long><<<nb, 256, 0, st>>>(x, y, nullptr, S, H, W, C, fH, fW, sH, sW, Ho, Wo, vec);
+        if (small) AETHER_POOL_FWD(false, unsigned, nullptr);
+        else AETHER_POOL_FWD(false, long long, nullptr);
     }
+#undef AETHER_POOL_FWD
     count_launch();
     return check_launch("aether_pool_fwd");
 }

@@ -82,6 +82,52 @@ __global__ void __launch_bounds__(256) gen_dx_kernel(const float* __restrict__ d
     }
 }
 
+// The same for layers with 1..4 input channels and a filter count that is a multiple of 4 (the first layer of a
+// network): one thread per input pixel keeps all CIN sums, so every dy vector is loaded once as float4 and the
+// filter reads are the same address for the whole warp.
+template <int CIN>
+__global__ void __launch_bounds__(256) gen_dx_fewc_kernel(const float* __restrict__ dy, const float* __restrict__ w,
+                                                          float* __restrict__ dx, int S, int H, int W, int Cout, int fH,
+                                                          int fW, int sH, int sW, int pH, int pW, int Ho, int Wo) {
+    const long long total = 1LL * S * H * W;
+    const int C4 = Cout >> 2;
+    for (long long pix = blockIdx.x * (long long)blockDim.x + threadIdx.x; pix < total;
+         pix += (long long)gridDim.x * blockDim.x) {
+        const int wi = (int)(pix % W);
+        const long long q = pix / W;
+        const int hi = (int)(q % H);
+        const int s = (int)(q / H);
+        float acc[CIN];
+#pragma unroll
+        for (int c = 0; c < CIN; ++c) acc[c] = 0.f;
+        for (int i = 0; i < fH; ++i) {
+            const int hn = hi + pH - i;
+            if (hn < 0 || hn % sH) continue;
+            const int ho = hn / sH;
+            if (ho >= Ho) continue;
+            for (int j = 0; j < fW; ++j) {
+                const int wn = wi + pW - j;
+                if (wn < 0 || wn % sW) continue;
+                const int wo = wn / sW;
+                if (wo >= Wo) continue;
+                const float4* dyp = reinterpret_cast<const float4*>(dy + (((size_t)s * Ho + ho) * Wo + wo) * Cout);
+                const float4* wq = reinterpret_cast<const float4*>(w + (size_t)(i * fW + j) * CIN * Cout);
+#pragma unroll 4
+                for (int d = 0; d < C4; ++d) {
+                    const float4 g = dyp[d];
+#pragma unroll
+                    for (int c = 0; c < CIN; ++c) {
+                        const float4 k = __ldg(wq + c * C4 + d);
+                        acc[c] = fmaf(g.x, k.x, fmaf(g.y, k.y, fmaf(g.z, k.z, fmaf(g.w, k.w, acc[c]))));
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < CIN; ++c) dx[pix * CIN + c] = acc[c];
+    }
+}
+
 // ---------------------------------------------------------------------------------- dW, dB
 // Block b owns a contiguous chunk of output pixels; thread t accumulates filter entries t, t+256, ...
 // over that chunk and writes them to part[b][entry].  A second kernel adds the chunks in fixed order.
@@ -177,6 +223,21 @@ int generic_conv_bwd_data(const AetherConvDesc& d, const float* dy, const float*
     int Ho, Wo;
     conv_out_hw(d, Ho, Wo);
     const long long total = 1LL * d.S * d.H * d.W * d.Cin;
+    if (d.Cin <= 4 && d.Cout % 4 == 0 && (reinterpret_cast<uintptr_t>(dy) & 15u) == 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0) {
+        const int nb = gen_blocks(1LL * d.S * d.H * d.W, 256);
+#define AETHER_DX_FEWC(CIN)                                                                                          \
+    gen_dx_fewc_kernel<CIN><<<nb, 256, 0, st>>>(dy, w, dx, d.S, d.H, d.W, d.Cout, d.fH, d.fW, d.sH, d.sW, d.padH, d.padW, \
+                                               Ho, Wo)
+        switch (d.Cin) {
+            case 1: AETHER_DX_FEWC(1); break;
+            case 2: AETHER_DX_FEWC(2); break;
+            case 3: AETHER_DX_FEWC(3); break;
+            default: AETHER_DX_FEWC(4); break;
+        }
+#undef AETHER_DX_FEWC
+        count_launch();
+        return check_launch("gen_dx_fewc_kernel");
+    }
     gen_dx_kernel<<<gen_blocks(total, 256), 256, 0, st>>>(dy, w, dx, d.S, d.H, d.W, d.Cin, d.Cout, d.fH, d.fW, d.sH,
                                                           d.sW, d.padH, d.padW, Ho, Wo);
     count_launch();

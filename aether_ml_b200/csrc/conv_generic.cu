@@ -23,6 +23,8 @@ __global__ void __launch_bounds__(256) gen_fwd_kernel(const float* __restrict__ 
         __syncthreads();
     }
     const float* wp = W_IN_SMEM ? wsm : w;
+    // rows of x are 16-byte aligned: four channels per load and four independent sums (a Dense layer is one long row)
+    const bool vec = (Cin & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     const long long total = 1LL * S * Ho * Wo * Cout;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -41,7 +43,22 @@ __global__ void __launch_bounds__(256) gen_fwd_kernel(const float* __restrict__ 
                 if (wi < 0 || wi >= W) continue;
                 const float* xp = x + (((size_t)s * H + hi) * W + wi) * Cin;
                 const float* wq = wp + ((size_t)(i * fW + j) * Cin) * Cout + d;
-                for (int c = 0; c < Cin; ++c) acc = fmaf(xp[c], wq[(size_t)c * Cout], acc);
+                if (vec) {
+                    const float4* xp4 = reinterpret_cast<const float4*>(xp);
+                    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 4
+                    for (int c4 = 0; c4 < (Cin >> 2); ++c4) {
+                        const float4 v = xp4[c4];
+                        const float* wr = wq + (size_t)(4 * c4) * Cout;
+                        a0 = fmaf(v.x, wr[0], a0);
+                        a1 = fmaf(v.y, wr[Cout], a1);
+                        a2 = fmaf(v.z, wr[2 * Cout], a2);
+                        a3 = fmaf(v.w, wr[3 * Cout], a3);
+                    }
+                    acc += (a0 + a1) + (a2 + a3);
+                } else {
+                    for (int c = 0; c < Cin; ++c) acc = fmaf(xp[c], wq[(size_t)c * Cout], acc);
+                }
             }
         }
         y[idx] = acc;

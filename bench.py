@@ -212,9 +212,9 @@ def run_gpu(args):
 
     # ---- timed region: device-resident inputs
     sampler = ClockSampler(local) if rank == 0 else None
-    # Per-kernel CUDA events on every 5th launch of each kind (an odd stride, so the two alternating cast launches are
-    # both sampled): an event pair costs a few microseconds of stream time, ~6 % of this step when taken everywhere.
-    prof_stride = 5 if args.steps >= 10 else 1
+    # Per-kernel CUDA events on every n-th launch of each kind, n >= 5 (an odd stride, so the two alternating cast
+    # launches are both sampled): an event pair costs a few microseconds of stream time, ~6 % of this step when taken everywhere.
+    prof_stride = max(5, (args.steps // 8) | 1) if args.steps >= 10 else 1      # about eight samples per kind, odd
     L.aether_profile_enable(prof_stride)
     launches0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -38,6 +38,7 @@ SIGNATURES = {
     "aether_launch_count": (_U64, []),
     "aether_device_status": (_I, []),
     "aether_device_status_clear": (None, []),
+    "aether_selftest_bounded_wait": (_I, [_I64, _P]),
     "aether_profile_enable": (_I, [_I]),
     "aether_profile_read": (_I, [_I, C.POINTER(C.c_double), C.POINTER(C.c_int)]),
     "aether_profile_reset": (None, []),

@@ -10,6 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libaether_b200.so")
+DIGEST_PATH = LIB_PATH + ".digest"
 SOURCES = ["api.cu", "conv_tc.cu", "conv_halo.cu", "conv_halo_dw.cu", "conv_dw_rows.cu", "conv_generic.cu", "conv_smallc.cu", "conv_first_tc.cu", "layers.cu",
            "block_fused.cu"]
 # tcgen05 / TMA PTX only assembles for the arch-specific target, hence compute_100a + sm_100a.
@@ -24,12 +25,26 @@ def _nvcc():
     return nvcc
 
 
+def _source_digest():
+    """sha256 over the CUDA sources, the public header and the compiler flags (what the .so is a function of)."""
+    import hashlib
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    deps = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC)) + [os.path.join(HERE, "..", "include", "aether_b200.h")]
+    for d in deps:
+        h.update(os.path.basename(d).encode())
+        with open(d, "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()
+
+
 def _stale():
-    if not os.path.exists(LIB_PATH):
+    """True when the library is missing or was built from other sources.  The check compares a digest of the
+    sources with the one recorded beside the .so at build time, so it does not depend on file times (a copied
+    tree keeps its built library)."""
+    if not os.path.exists(LIB_PATH) or not os.path.exists(DIGEST_PATH):
         return True
-    t = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "aether_b200.h")]
-    return any(os.path.getmtime(d) > t for d in deps)
+    with open(DIGEST_PATH) as fh:
+        return fh.read().strip() != _source_digest()
 
 
 def build_library(force=False, verbose=False):
@@ -53,6 +68,8 @@ def build_library(force=False, verbose=False):
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+    with open(DIGEST_PATH, "w") as fh:
+        fh.write(_source_digest() + "\n")
     return LIB_PATH
 
 

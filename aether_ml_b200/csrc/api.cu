@@ -5,7 +5,10 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace aether {
 
@@ -24,15 +27,28 @@ int set_error(int code, const char* fmt, ...) {
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 int* device_status_word() {
-    if (!g_status_host) {
+    static std::once_flag once;
+    std::call_once(once, [] {
         int* p = nullptr;
         if (cudaHostAlloc(reinterpret_cast<void**>(&p), sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) ==
             cudaSuccess) {
             *p = 0;
             g_status_host = p;
         }
-    }
+    });
     return g_status_host;   // may be null: kernels then skip reporting
+}
+
+// One thread waits on a barrier that nothing ever completes, with the same bounded wait the convolution kernels
+// use, gives up after `limit` cycles, records its code and returns: the give-up path of every kernel, run alone.
+__global__ void selftest_bounded_wait_kernel(int* status, long long limit) {
+    __shared__ __align__(8) unsigned long long bar;
+    if (threadIdx.x == 0) {
+        const uint32_t b = smem_u32(&bar);
+        mbar_init(b, 1);
+        mbar_fence_init();
+        mbar_wait(b, 0, status, DS_TIMEOUT_SELFTEST, limit);
+    }
 }
 
 int check_launch(const char* what) {
@@ -102,6 +118,16 @@ extern "C" uint64_t aether_launch_count(void) { return g_launches.load(std::memo
 extern "C" int aether_device_status(void) { return g_status_host ? *reinterpret_cast<volatile int*>(g_status_host) : 0; }
 extern "C" void aether_device_status_clear(void) {
     if (g_status_host) *reinterpret_cast<volatile int*>(g_status_host) = 0;
+}
+
+extern "C" int aether_selftest_bounded_wait(int64_t limit_cycles, void* stream) {
+    if (limit_cycles < 1 || limit_cycles > 2000000000LL)
+        return set_error(AE_BAD_ARG, "aether_selftest_bounded_wait: limit_cycles must be in [1, 2e9] (about a second at most)");
+    int* status = device_status_word();
+    if (!status) return set_error(AE_CUDA, "aether_selftest_bounded_wait: no status word (pinned allocation failed)");
+    selftest_bounded_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, (long long)limit_cycles);
+    count_launch();
+    return check_launch("selftest_bounded_wait_kernel");
 }
 
 extern "C" int aether_profile_enable(int on) {

@@ -6,6 +6,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/aether_b200.h"
 
 namespace aether {
@@ -31,6 +33,30 @@ int check_launch(const char* what);
 enum ProfKind : int { PK_IGEMM_FWD = 0, PK_IGEMM_DX = 1, PK_DW = 2, PK_SHADOW = 3, PK_COUNT = 4 };
 void prof_begin(int kind, cudaStream_t st);
 void prof_end(int kind, cudaStream_t st);
+
+// ---- per-device state.  Kernel attributes (the opt-in to more than 48 KB of dynamic shared memory) and the SM
+// count belong to a device, not to the process: a host that drives several GPUs from one process, or switches
+// device between calls, gets each of them configured on first use.  The flags are atomics, so any number of host
+// threads may call into the library (a doubled cudaFuncSetAttribute is harmless).
+static constexpr int AE_MAX_DEVICES = 64;
+static inline int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= AE_MAX_DEVICES) dev = 0;
+    return dev;
+}
+struct PerDeviceSmem {
+    std::atomic<int> bytes[AE_MAX_DEVICES];      // largest dynamic shared-memory size configured so far (0: none)
+};
+// Makes sure `kernel` may be launched with `bytes` of dynamic shared memory on the current device.
+template <typename K>
+static inline int ensure_dynamic_smem(K kernel, int bytes, PerDeviceSmem& once, const char* what) {
+    const int dev = current_device();
+    if (once.bytes[dev].load(std::memory_order_acquire) >= bytes) return AE_OK;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(%s, %d): %s", what, bytes, cudaGetErrorString(e));
+    once.bytes[dev].store(bytes, std::memory_order_release);
+    return AE_OK;
+}
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -286,12 +286,8 @@ int run_rows_dw(const void* x_sh, int Cin_p, int H, int W, int S, const void* dy
     p.splits_a = sa; p.splits_b = sb; p.rows_a = rows_a;
     *splits_a = sa; *splits_b = sb; *tap_split = rows_a * fW;
     const int smem = 1024 + p.stages * p.stage_bytes + 256;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(dw_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
-        if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(dw_rows, %d): %s", smem_max, cudaGetErrorString(e));
-        configured = true;
-    }
+    static PerDeviceSmem configured;
+    if ((rc = ensure_dynamic_smem(dw_rows_kernel, smem_max, configured, "dw_rows"))) return rc;
     prof_begin(PK_DW, st);
     dw_rows_kernel<<<units * (sa + sb), DWR_THREADS, smem, st>>>(p);
     prof_end(PK_DW, st);

@@ -650,14 +650,10 @@ int first_tc_fwd(const AetherConvDesc& d, const float* x, const float* w, const 
     p.ntiles = (int)((p.P + 127) / 128);
     p.stages = 4;
     const int smem = 1024 + NT * 128 + p.stages * FT_STAGE_BYTES + FT_TAIL + FT_STATS_BYTES;
-    static bool configured[2] = {false, false};
-    const int ki = stats ? 1 : 0;
-    if (!configured[ki]) {
-        cudaError_t e = stats ? cudaFuncSetAttribute(first_conv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448)
-                              : cudaFuncSetAttribute(first_conv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
-        if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(first_conv): %s", cudaGetErrorString(e));
-        configured[ki] = true;
-    }
+    static PerDeviceSmem configured[2];
+    if (int rc = stats ? ensure_dynamic_smem(first_conv_kernel<true>, 232448, configured[1], "first_conv")
+                       : ensure_dynamic_smem(first_conv_kernel<false>, 232448, configured[0], "first_conv"))
+        return rc;
     const int grid = first_tc_grid(p.ntiles);
     if (stats) first_conv_kernel<true><<<grid, FT_THREADS, smem, st>>>(p);
     else first_conv_kernel<false><<<grid, FT_THREADS, smem, st>>>(p);
@@ -693,12 +689,8 @@ int first_tc_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy
     const size_t need = (size_t)grid * (K + 1) * d.Cout * sizeof(float);
     if (!ws || ws_bytes < need) return set_error(AE_BAD_ARG, "conv workspace too small: %zu < %zu", ws_bytes, need);
     const int smem = 1024 + p.stages * p.stage_bytes + tail;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(first_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
-        if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(first_dw): %s", cudaGetErrorString(e));
-        configured = true;
-    }
+    static PerDeviceSmem configured;
+    if (int rc0 = ensure_dynamic_smem(first_dw_kernel, 232448, configured, "first_dw")) return rc0;
     first_dw_kernel<<<grid, FD_THREADS, smem, st>>>(p);
     count_launch();
     int rc = check_launch("first_dw_kernel");

@@ -249,12 +249,8 @@ int run_halo_dw(const void* x_sh, int Cin_p, int H, int W, int S, const void* dy
     if (splits > max_splits) splits = max_splits;
     *splits_out = (int)splits;
     const int smem = 1024 + p.stages * p.stage_bytes + 256;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(dw_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
-        if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(dw_halo, %d): %s", smem_max, cudaGetErrorString(e));
-        configured = true;
-    }
+    static PerDeviceSmem configured;
+    if (int rc0 = ensure_dynamic_smem(dw_halo_kernel, smem_max, configured, "dw_halo")) return rc0;
     prof_begin(PK_DW, st);
     dw_halo_kernel<<<dim3((unsigned)splits, gy), DWH_THREADS, smem, st>>>(p);
     prof_end(PK_DW, st);

@@ -286,19 +286,15 @@ size_t smallc_conv_workspace_bytes(const AetherConvDesc& d) {
 }
 
 template <typename Kern>
-static int smallc_smem(Kern kernel, size_t smem, size_t& configured, const char* what) {
-    if (smem > 32 * 1024 && smem > configured) {      // static + dynamic above 48 KB needs the opt-in
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(%s): %s", what, cudaGetErrorString(e));
-        configured = smem;
-    }
-    return AE_OK;
+static int smallc_smem(Kern kernel, size_t smem, PerDeviceSmem& configured, const char* what) {
+    if (smem <= 32 * 1024) return AE_OK;              // static + dynamic above 48 KB needs the opt-in
+    return ensure_dynamic_smem(kernel, (int)smem, configured, what);
 }
 
 template <int R>
 static int launch_smallc_fwd(const SmallcGeom& g, const float* x, const float* w, const float* b, float* y, float* stats,
                              int nb, long long ntiles, size_t smem, cudaStream_t st) {
-    static size_t configured = 0;
+    static PerDeviceSmem configured;
     int rc = smallc_smem(smallc_fwd_kernel<R>, smem, configured, "smallc_fwd");
     if (rc) return rc;
     smallc_fwd_kernel<R><<<nb, SC_THREADS, smem, st>>>(g, x, w, b, y, stats, ntiles);
@@ -334,7 +330,7 @@ int smallc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, con
 template <int KPG>
 static int launch_smallc_dw(const SmallcGeom& g, const float* x, const float* dy, float* part, int nb, long long ntiles,
                             size_t smem, cudaStream_t st) {
-    static size_t configured = 0;
+    static PerDeviceSmem configured;
     int rc = smallc_smem(smallc_dw_kernel<KPG>, smem, configured, "smallc_dw");
     if (rc) return rc;
     smallc_dw_kernel<KPG><<<nb, SC_THREADS, smem, st>>>(g, x, dy, part, ntiles);

@@ -838,18 +838,22 @@ struct TcPlan {
     // dW decomposition
     int dw_nb, dw_nt, dw_cblocks, dw_U, dw_MG, dw_gpc, dw_ngc, dw_ntn, dw_splits;
     int db_blocks;
+    bool cvt_fwd, cvt_dx;   // the forward / dX kernel converts its fp32 operand itself (no separate cast pass)
+    int cvt_dx_blocks;      // rows of per-CTA column sums the dX kernel then writes
     PixelTiling til_out;   // tiles over output pixels (forward, dW)
     PixelTiling til_in;    // tiles over input pixels (dX)
 };
 
 static int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
+// SM count of the calling thread's current device (looked up once per device).
 int num_sms() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
+    static std::atomic<int> cache[AE_MAX_DEVICES];
+    const int dev = current_device();
+    int n = cache[dev].load(std::memory_order_relaxed);
+    if (n <= 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cache[dev].store(n, std::memory_order_relaxed);
     }
     return n;
 }
@@ -887,6 +891,10 @@ static TcPlan make_plan(const AetherConvDesc& d) {
     const long long out_rows = 1LL * d.S * pl.Ho * pl.Wo;
     pl.db_blocks = (int)(out_rows < 4LL * num_sms() * 64 ? (out_rows + 63) / 64 : 4LL * num_sms());
     if (pl.db_blocks < 1) pl.db_blocks = 1;
+    // dX through the halo kernel's converter form: that kernel casts dy itself and leaves one row of column sums per CTA
+    pl.cvt_dx = !pl.tf32 && halo_igemm_converts(false, pl.Cout_p, d.S, pl.taps, d.Cin, d.H, d.W, pl.Cin_p, d.fH, d.fW);
+    pl.cvt_fwd = !pl.tf32 && halo_igemm_converts(false, pl.Cin_p, d.S, pl.taps, d.Cout, pl.Ho, pl.Wo, pl.Cout_p, d.fH, d.fW);
+    pl.cvt_dx_blocks = pl.cvt_dx ? halo_igemm_grid(d.S, d.H, d.W, d.fH, d.fW) : 0;
     // workspace
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 1024); return o; };
@@ -901,7 +909,7 @@ static TcPlan make_plan(const AetherConvDesc& d) {
         if (rs > part_splits) part_splits = rs;
     }
     pl.off_part = take((size_t)part_splits * pl.dw_U * UC * pl.Cout_p * 4);
-    pl.off_dbpart = take((size_t)pl.db_blocks * d.Cout * 4);
+    pl.off_dbpart = take((size_t)(pl.db_blocks > pl.cvt_dx_blocks ? pl.db_blocks : pl.cvt_dx_blocks) * d.Cout * 4);
     pl.total = off;
     return pl;
 }
@@ -920,13 +928,6 @@ bool tc_conv_eligible(const AetherConvDesc& d) {
 
 size_t tc_conv_workspace_bytes(const AetherConvDesc& d) { return make_plan(d).total; }
 
-template <typename K>
-static int set_smem(K kernel, int bytes) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e != cudaSuccess) return set_error(AE_CUDA, "cudaFuncSetAttribute(smem=%d): %s", bytes, cudaGetErrorString(e));
-    return AE_OK;
-}
-
 // CTAs of the per-tap kernel.  With statistics the grid is a multiple of the number of column tiles, so that a
 // CTA (tiles blockIdx.x + k * grid, column tile = tile % n_tiles_n) keeps one column tile throughout.
 static int igemm_grid(long long m_tiles, int n_tiles_n, bool stats) {
@@ -939,12 +940,8 @@ static int igemm_grid(long long m_tiles, int n_tiles_n, bool stats) {
 template <bool TF32, int NT, bool STATS>
 static int launch_igemm_k(const IgemmParams& p, cudaStream_t st) {
     using Cfg = IgemmCfg<NT>;
-    static bool configured = false;
-    if (!configured) {
-        int rc = set_smem(igemm_conv_kernel<TF32, NT, STATS>, Cfg::SMEM_BYTES);
-        if (rc) return rc;
-        configured = true;
-    }
+    static PerDeviceSmem configured;
+    if (int rc = ensure_dynamic_smem(igemm_conv_kernel<TF32, NT, STATS>, Cfg::SMEM_BYTES, configured, "igemm_conv")) return rc;
     const int grid = igemm_grid(1LL * p.tiles_w * p.tiles_h * p.tiles_n, p.n_tiles_n, STATS);
     if (STATS && grid % p.n_tiles_n) return set_error(AE_UNSUPPORTED, "conv forward statistics: %d column tiles on %d CTAs", p.n_tiles_n, grid);
     const int pk = p.sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX;
@@ -978,18 +975,21 @@ static int dispatch_igemm(IgemmParams& p, int nt, cudaStream_t st) {
 }
 
 // Runs out[p, n] = sum_{tap,k} in[p (+/-) tap, k] * Wm[tap][n][k] (+ bias).
+// cvt_src (nullable): `in` is a bf16 copy that does not exist yet; the halo kernel makes it from this fp32 array of
+// cvt_C channels while it runs (callers check halo_igemm_converts first), and fills cvt_colsum when given.
 static int run_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
                      int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, const PixelTiling& til,
                      int n_padded, int fH, int fW, int sgn, int off_h, int off_w, const float* bias, float* stats,
-                     cudaStream_t st) {
+                     cudaStream_t st, const float* cvt_src = nullptr, int cvt_C = 0, float* cvt_colsum = nullptr) {
     {   // wide images with a filter that fits in shared memory: halo-reuse kernel
         bool used = false;
         const int padT = sgn > 0 ? -off_h : fH - 1 - off_h;
         const int padL = sgn > 0 ? -off_w : fW - 1 - off_w;
         int rc0 = run_halo_igemm(tf32, in, in_C, in_H, in_W, S, wmat, w_inner, rows_per_tap, taps, out, out_C, out_H, out_W,
                                  n_padded, fH, fW, padT, padL, sgn > 0 ? 0 : 1, bias, stats,
-                                 sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX, st, &used);
+                                 sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX, st, &used, cvt_src, cvt_C, cvt_colsum);
         if (rc0 || used) return rc0;
+        if (cvt_src) return set_error(AE_UNSUPPORTED, "convolution: converter form requested for a shape the halo kernel does not take");
     }
     IgemmParams p;
     memset(&p, 0, sizeof(p));
@@ -1067,23 +1067,20 @@ int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const f
     }
     __nv_bfloat16* xsh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_xsh);
     __nv_bfloat16* wf = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_wf);
-    if ((rc = launch_cast(x, xsh, 1LL * d.S * d.H * d.W, d.Cin, pl.Cin_p, nullptr, 0, st))) return rc;
+    // The bf16 copy of x (kept for dW) is written by the forward kernel itself where it can, else by a cast pass.
+    if (!pl.cvt_fwd && (rc = launch_cast(x, xsh, 1LL * d.S * d.H * d.W, d.Cin, pl.Cin_p, nullptr, 0, st))) return rc;
     filter_shadow_kernel<__nv_bfloat16><<<fblocks, 256, 0, st>>>(w, wf, pl.taps, d.Cin, d.Cout, pl.Cout_p, pl.Cin_p, 1);
     count_launch();
     if ((rc = check_launch("filter_shadow_kernel"))) return rc;
     return run_igemm(false, xsh, pl.Cin_p, d.H, d.W, d.S, wf, pl.Cin_p, pl.Cout_p, pl.taps, y, d.Cout, pl.Ho, pl.Wo,
-                     pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, stats, st);
+                     pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, stats, st, pl.cvt_fwd ? x : nullptr, d.Cin);
 }
 
 template <bool TF32, int NB>
 static int launch_dw(const DwParams& p, int splits, int grid_y, cudaStream_t st) {
     using Cfg = DwCfg<TF32, NB>;
-    static bool configured = false;
-    if (!configured) {
-        int rc = set_smem(dw_conv_kernel<TF32, NB>, Cfg::SMEM_BYTES);
-        if (rc) return rc;
-        configured = true;
-    }
+    static PerDeviceSmem configured;
+    if (int rc = ensure_dynamic_smem(dw_conv_kernel<TF32, NB>, Cfg::SMEM_BYTES, configured, "dw_conv")) return rc;
     prof_begin(PK_DW, st);
     dw_conv_kernel<TF32, NB><<<dim3(splits, grid_y), DW_THREADS, Cfg::SMEM_BYTES, st>>>(p);
     prof_end(PK_DW, st);
@@ -1103,6 +1100,7 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
     const void* x_op = x;
     const void* dy_op = dy;
     const int fblocks = 2 * num_sms();
+    bool cvt_dx = false;
 
     // ---- shadows + dB
     if (pl.tf32) {
@@ -1115,13 +1113,15 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
     } else {
         __nv_bfloat16* dysh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_dysh);
         __nv_bfloat16* xsh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_xsh);
-        if ((rc = launch_cast(dy, dysh, out_rows, d.Cout, pl.Cout_p, dbpart, pl.db_blocks, st))) return rc;
+        // With dX on the halo kernel's converter form that kernel casts dy and sums its columns; otherwise a cast pass.
+        cvt_dx = pl.cvt_dx && dx != nullptr;
+        if (!cvt_dx && (rc = launch_cast(dy, dysh, out_rows, d.Cout, pl.Cout_p, dbpart, pl.db_blocks, st))) return rc;
         if (dw && !x_shadow_valid)
             if ((rc = launch_cast(x, xsh, in_rows, d.Cin, pl.Cin_p, nullptr, 0, st))) return rc;
         x_op = xsh;
         dy_op = dysh;
     }
-    if (db) {
+    if (db && !cvt_dx) {
         colsum_finish_kernel<<<ceil_div(d.Cout, 8), 256, 0, st>>>(dbpart, pl.db_blocks, d.Cout, db);
         count_launch();
         if ((rc = check_launch("colsum_finish_kernel"))) return rc;
@@ -1140,9 +1140,15 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
             count_launch();
             if ((rc = check_launch("filter_shadow_kernel"))) return rc;
             rc = run_igemm(false, dy_op, pl.Cout_p, pl.Ho, pl.Wo, d.S, wd, pl.Cout_p, pl.Cin_p, pl.taps, dx, d.Cin, d.H,
-                           d.W, pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, nullptr, st);
+                           d.W, pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, nullptr, st,
+                           cvt_dx ? dy : nullptr, d.Cout, (cvt_dx && db) ? dbpart : nullptr);
         }
         if (rc) return rc;
+        if (cvt_dx && db) {
+            colsum_finish_kernel<<<ceil_div(d.Cout, 8), 256, 0, st>>>(dbpart, pl.cvt_dx_blocks, d.Cout, db);
+            count_launch();
+            if ((rc = check_launch("colsum_finish_kernel"))) return rc;
+        }
     }
 
     // ---- dW: split over pixel tiles, fixed-order reduction of the partials

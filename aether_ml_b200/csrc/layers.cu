@@ -17,12 +17,10 @@ static int blocks_for(long long items, int threads, int per_sm = 8) {
     return (int)b;
 }
 
-// Derivative of the (leaky) ReLU fused behind a Batch_Norm, judged from the ACTIVATED value: for alpha > 0 the sign of
-// the output is the sign of the pre-activation (the reference passes the gradient where that is 0,
-// CNN_classes_cupy.py:412-428); for alpha == 0 a zero output blocks the gradient.
-__device__ __forceinline__ float act_grad(float yact, float alpha) {
-    return alpha > 0.f ? (yact < 0.f ? alpha : 1.f) : (yact > 0.f ? 1.f : 0.f);
-}
+// Derivative of the (leaky) ReLU fused behind a Batch_Norm at pre-activation v = gamma * xhat + beta, which the
+// backward kernels recompute from x: alpha where v < 0, else 1 -- the gradient passes at v == 0 exactly as in the
+// reference (CNN_classes_cupy.py:412-428).
+__device__ __forceinline__ float act_grad(float v, float alpha) { return v < 0.f ? alpha : 1.f; }
 
 // ====================================================================================== batch norm
 // Per-channel reductions over a [rows][C] matrix.  Thread t of a block owns column (t % cols) and row
@@ -33,8 +31,8 @@ template <int MODE>
 __global__ void __launch_bounds__(256) bn_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                                                         const float* __restrict__ mean, const float* __restrict__ var,
                                                         float eps, long long rows, int C, float* __restrict__ part,
-                                                        long long rows_per_block, const float* __restrict__ yact,
-                                                        float alpha) {
+                                                        long long rows_per_block, const float* __restrict__ act_gamma,
+                                                        const float* __restrict__ act_beta, float alpha) {
     const long long r0 = blockIdx.x * rows_per_block;
     long long r1 = r0 + rows_per_block;
     if (r1 > rows) r1 = rows;
@@ -65,11 +63,13 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(const float* __restrict_
             } else {
                 const float mu = mean[c];
                 const float inv = rsqrtf(var[c] + eps);
+                const float ag = act_gamma ? act_gamma[c] : 0.f, ab = act_gamma ? act_beta[c] : 0.f;
                 for (long long r = r0 + rl; r < r1; r += lanes) {
                     float g = dy[(size_t)r * C + c];
-                    if (yact) g *= act_grad(yact[(size_t)r * C + c], alpha);   // gradient through the fused activation
+                    const float xh = (x[(size_t)r * C + c] - mu) * inv;
+                    if (act_gamma) g *= act_grad(fmaf(ag, xh, ab), alpha);     // gradient through the fused activation
                     a += g;
-                    b = fmaf(g, (x[(size_t)r * C + c] - mu) * inv, b);
+                    b = fmaf(g, xh, b);
                 }
             }
         }
@@ -115,8 +115,8 @@ template <int MODE>
 __global__ void __launch_bounds__(256) bn_reduce_vec4_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                                                              const float* __restrict__ mean, const float* __restrict__ var,
                                                              float eps, long long rows, int C, float* __restrict__ part,
-                                                             long long rows_per_block, const float* __restrict__ yact,
-                                                             float alpha) {
+                                                             long long rows_per_block, const float* __restrict__ act_gamma,
+                                                             const float* __restrict__ act_beta, float alpha) {
     const long long r0 = blockIdx.x * rows_per_block;
     long long r1 = r0 + rows_per_block;
     if (r1 > rows) r1 = rows;
@@ -157,18 +157,22 @@ __global__ void __launch_bounds__(256) bn_reduce_vec4_kernel(const float* __rest
                 const float4 inv = make_float4(rsqrtf(var[c] + eps), rsqrtf(var[c + 1] + eps), rsqrtf(var[c + 2] + eps),
                                                rsqrtf(var[c + 3] + eps));
                 const float4* gr = reinterpret_cast<const float4*>(dy) + cv;
+                const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 ag = act_gamma ? *reinterpret_cast<const float4*>(act_gamma + c) : z4;
+                const float4 ab = act_gamma ? *reinterpret_cast<const float4*>(act_beta + c) : z4;
 #pragma unroll 4
                 for (long long r = r0 + rl; r < r1; r += lanes) {
                     float4 g = gr[(size_t)r * CV];
                     const float4 v = xr[(size_t)r * CV];
-                    if (yact) {                                                   // gradient through the fused activation
-                        const float4 ya = (reinterpret_cast<const float4*>(yact) + cv)[(size_t)r * CV];
-                        g.x *= act_grad(ya.x, alpha); g.y *= act_grad(ya.y, alpha);
-                        g.z *= act_grad(ya.z, alpha); g.w *= act_grad(ya.w, alpha);
+                    const float4 xh = make_float4((v.x - mu.x) * inv.x, (v.y - mu.y) * inv.y, (v.z - mu.z) * inv.z,
+                                                  (v.w - mu.w) * inv.w);
+                    if (act_gamma) {                                              // gradient through the fused activation
+                        g.x *= act_grad(fmaf(ag.x, xh.x, ab.x), alpha); g.y *= act_grad(fmaf(ag.y, xh.y, ab.y), alpha);
+                        g.z *= act_grad(fmaf(ag.z, xh.z, ab.z), alpha); g.w *= act_grad(fmaf(ag.w, xh.w, ab.w), alpha);
                     }
                     a.x += g.x; a.y += g.y; a.z += g.z; a.w += g.w;
-                    b.x = fmaf(g.x, (v.x - mu.x) * inv.x, b.x); b.y = fmaf(g.y, (v.y - mu.y) * inv.y, b.y);
-                    b.z = fmaf(g.z, (v.z - mu.z) * inv.z, b.z); b.w = fmaf(g.w, (v.w - mu.w) * inv.w, b.w);
+                    b.x = fmaf(g.x, xh.x, b.x); b.y = fmaf(g.y, xh.y, b.y);
+                    b.z = fmaf(g.z, xh.z, b.z); b.w = fmaf(g.w, xh.w, b.w);
                 }
             }
         }
@@ -214,13 +218,14 @@ __global__ void __launch_bounds__(256) bn_reduce_vec4_kernel(const float* __rest
 
 template <int MODE>
 static void launch_bn_reduce(int nb, cudaStream_t st, const float* x, const float* dy, const float* mean, const float* var,
-                             float eps, long long rows, int C, float* part, const float* yact = nullptr, float alpha = 0.f) {
+                             float eps, long long rows, int C, float* part, const float* act_gamma = nullptr,
+                             const float* act_beta = nullptr, float alpha = 0.f) {
     const long long rpb = (rows + nb - 1) / nb;
     const bool vec = (C & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
                      (MODE == 0 || (reinterpret_cast<uintptr_t>(dy) & 15u) == 0) &&
-                     (yact == nullptr || (reinterpret_cast<uintptr_t>(yact) & 15u) == 0);
-    if (vec) bn_reduce_vec4_kernel<MODE><<<nb, 256, 0, st>>>(x, dy, mean, var, eps, rows, C, part, rpb, yact, alpha);
-    else bn_reduce_kernel<MODE><<<nb, 256, 0, st>>>(x, dy, mean, var, eps, rows, C, part, rpb, yact, alpha);
+                     (act_gamma == nullptr || ((reinterpret_cast<uintptr_t>(act_gamma) | reinterpret_cast<uintptr_t>(act_beta)) & 15u) == 0);
+    if (vec) bn_reduce_vec4_kernel<MODE><<<nb, 256, 0, st>>>(x, dy, mean, var, eps, rows, C, part, rpb, act_gamma, act_beta, alpha);
+    else bn_reduce_kernel<MODE><<<nb, 256, 0, st>>>(x, dy, mean, var, eps, rows, C, part, rpb, act_gamma, act_beta, alpha);
 }
 
 // Merges the per-block (n, mean, M2) triples in double precision, writes batch mean / biased variance,
@@ -377,10 +382,15 @@ __global__ void __launch_bounds__(FIN_THREADS) bn_finalize_bwd_kernel(const floa
     coeff[2 * C + c] = (float)k3;
 }
 
+// act_gamma / act_beta (nullable): a fused activation's derivative is applied to dy first, taken at the pre-activation
+// v = gamma * ((x - mean) * rsqrt(var + eps)) + beta -- the same expression, operation for operation, as in the
+// reduction kernels above, so both passes judge every element alike.
 __global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                                                            float* __restrict__ dx, const float* __restrict__ coeff,
-                                                           long long n, int C, const float* __restrict__ yact,
-                                                           float alpha) {
+                                                           long long n, int C, const float* __restrict__ act_gamma,
+                                                           const float* __restrict__ act_beta,
+                                                           const float* __restrict__ mean, const float* __restrict__ var,
+                                                           float eps, float alpha) {
     const long long stride = (long long)gridDim.x * blockDim.x;
     if ((C & 3) == 0) {
         const long long n4 = n >> 2;
@@ -394,10 +404,15 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const float* __restri
             if (cq >= C4) cq -= C4;
             const float4 xv = reinterpret_cast<const float4*>(x)[i];
             float4 g = reinterpret_cast<const float4*>(dy)[i];
-            if (yact) {                                                           // gradient through the fused activation
-                const float4 ya = reinterpret_cast<const float4*>(yact)[i];
-                g.x *= act_grad(ya.x, alpha); g.y *= act_grad(ya.y, alpha);
-                g.z *= act_grad(ya.z, alpha); g.w *= act_grad(ya.w, alpha);
+            if (act_gamma) {                                                      // gradient through the fused activation
+                const float4 ag = *reinterpret_cast<const float4*>(act_gamma + c);
+                const float4 ab = *reinterpret_cast<const float4*>(act_beta + c);
+                const float4 mu = *reinterpret_cast<const float4*>(mean + c);
+                const float4 vr = *reinterpret_cast<const float4*>(var + c);
+                g.x *= act_grad(fmaf(ag.x, (xv.x - mu.x) * rsqrtf(vr.x + eps), ab.x), alpha);
+                g.y *= act_grad(fmaf(ag.y, (xv.y - mu.y) * rsqrtf(vr.y + eps), ab.y), alpha);
+                g.z *= act_grad(fmaf(ag.z, (xv.z - mu.z) * rsqrtf(vr.z + eps), ab.z), alpha);
+                g.w *= act_grad(fmaf(ag.w, (xv.w - mu.w) * rsqrtf(vr.w + eps), ab.w), alpha);
             }
             const float4 k1 = *reinterpret_cast<const float4*>(coeff + c);
             const float4 k2 = *reinterpret_cast<const float4*>(coeff + C + c);
@@ -412,7 +427,8 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const float* __restri
     } else {
         for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
             const int c = (int)(i % C);
-            const float g = yact ? dy[i] * act_grad(yact[i], alpha) : dy[i];
+            const float g = act_gamma ? dy[i] * act_grad(fmaf(act_gamma[c], (x[i] - mean[c]) * rsqrtf(var[c] + eps), act_beta[c]), alpha)
+                                      : dy[i];
             dx[i] = fmaf(coeff[c], g, fmaf(coeff[C + c], x[i], coeff[2 * C + c]));
         }
     }
@@ -540,21 +556,21 @@ static __device__ __align__(256) float g_bn_static_scratch[AETHER_BN_STATIC_SCRA
 
 // Host code cannot use the array's name as a pointer (on the host it is only a handle for the symbol): the
 // device address is looked up once per device and cached here.
-static float* g_bn_static_ptr[64] = {nullptr};
+static std::atomic<float*> g_bn_static_ptr[64];   // zero-initialised; two threads racing here look the same address up twice
 
 static int bn_static_scratch(float** out) {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return set_error(AE_CUDA, "aether_bn_fwd_train_static: cudaGetDevice: %s", cudaGetErrorString(e));
     if (dev < 0 || dev >= 64) return set_error(AE_UNSUPPORTED, "aether_bn_fwd_train_static: device ordinal %d out of range", dev);
-    if (g_bn_static_ptr[dev] == nullptr) {
-        float* ptr = nullptr;
+    float* ptr = g_bn_static_ptr[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_bn_static_scratch);   // address on the CURRENT device
         if (e != cudaSuccess || ptr == nullptr)
             return set_error(AE_CUDA, "aether_bn_fwd_train_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        g_bn_static_ptr[dev] = ptr;
+        g_bn_static_ptr[dev].store(ptr, std::memory_order_release);
     }
-    *out = g_bn_static_ptr[dev];
+    *out = ptr;
     return AE_OK;
 }
 
@@ -623,7 +639,7 @@ extern "C" int aether_bn_bwd(const float* x, const float* dy, const float* gamma
     bn_finalize_bwd_kernel<<<ceil_div(C, FIN_CH), FIN_THREADS, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
                                                             dbeta, coeff, nullptr);
     const long long n = rows * C;
-    bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C, nullptr, 0.f);
+    bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C, nullptr, nullptr, nullptr, nullptr, eps, 0.f);
     count_launch(3);
     return check_launch("aether_bn_bwd");
 }
@@ -693,25 +709,27 @@ extern "C" int aether_bn_act_fwd_eval(const float* x, const float* gamma, const 
     return check_launch("aether_bn_act_fwd_eval");
 }
 
-extern "C" int aether_bn_act_bwd(const float* x, const float* y_act, const float* dy, const float* gamma,
+extern "C" int aether_bn_act_bwd(const float* x, const float* beta, const float* dy, const float* gamma,
                                  const float* batch_mean, const float* batch_var, float* dx, float* dgamma, float* dbeta,
                                  int64_t rows, int C, float eps, float alpha, const float* channel_scale, void* ws,
                                  size_t ws_bytes, void* stream) {
-    if (!x || !y_act || !dy || !gamma || !batch_mean || !batch_var || !dx || !dgamma || !dbeta || !ws)
+    if (!x || !beta || !dy || !gamma || !batch_mean || !batch_var || !dx || !dgamma || !dbeta || !ws)
         return set_error(AE_BAD_ARG, "aether_bn_act_bwd: null pointer");
     int rc = bn_act_check("aether_bn_act_bwd", rows, C, alpha, x, dy, dx);
     if (rc) return rc;
-    if ((C & 3) == 0 && !aligned16(y_act)) return set_error(AE_BAD_ARG, "aether_bn_act_bwd: arrays must be 16-byte aligned");
     if (ws_bytes < aether_bn_workspace_bytes(rows, C)) return set_error(AE_BAD_ARG, "aether_bn_act_bwd: workspace too small");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int nb = bn_blocks(rows);
     float* part = static_cast<float*>(ws);
     float* coeff = part + (size_t)nb * 3 * C;
-    launch_bn_reduce<1>(nb, st, x, dy, batch_mean, batch_var, eps, rows, C, part, y_act, alpha);
+    launch_bn_reduce<1>(nb, st, x, dy, batch_mean, batch_var, eps, rows, C, part, gamma, beta, alpha);
     bn_finalize_bwd_kernel<<<ceil_div(C, FIN_CH), FIN_THREADS, 0, st>>>(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma,
                                                             dbeta, coeff, channel_scale);
     const long long n = rows * C;
-    bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C, y_act, alpha);
+    // the four per-channel vectors are read as float4 when C % 4 == 0
+    if ((C & 3) == 0 && (!aligned16(gamma) || !aligned16(beta) || !aligned16(batch_mean) || !aligned16(batch_var)))
+        return set_error(AE_BAD_ARG, "aether_bn_act_bwd: gamma, beta, batch_mean and batch_var must be 16-byte aligned");
+    bn_bwd_apply_kernel<<<blocks_for(n / 4 + 1, 256), 256, 0, st>>>(x, dy, dx, coeff, n, C, gamma, beta, batch_mean, batch_var, eps, alpha);
     count_launch(3);
     return check_launch("aether_bn_act_bwd");
 }

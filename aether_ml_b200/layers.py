@@ -568,8 +568,8 @@ class Batch_Norm:
                                            _ptr(self.dbiases), S, H, W, Cc, fH, fW, float(self.epsilon),
                                            float(self.fused_alpha), _ptr(getattr(self, "_fused_mask", None)), _ptr(ws),
                                            ws.numel(), _stream()), "aether_bn_act_pool_bwd")
-        elif self.fused_alpha is not None:   # dvalues is the gradient w.r.t. the ACTIVATED output kept in self.output
-            check(L.aether_bn_act_bwd(_ptr(x), _ptr(self.output), _ptr(dy), _ptr(self.gamma), _ptr(self._bm),
+        elif self.fused_alpha is not None:   # dvalues is the gradient w.r.t. the ACTIVATED output
+            check(L.aether_bn_act_bwd(_ptr(x), _ptr(self.beta), _ptr(dy), _ptr(self.gamma), _ptr(self._bm),
                                       _ptr(self._bv), _ptr(dx), _ptr(self.dweights), _ptr(self.dbiases), rows, Cc,
                                       float(self.epsilon), float(self.fused_alpha), _ptr(getattr(self, "_fused_mask", None)),
                                       _ptr(ws), ws.numel(), _stream()), "aether_bn_act_bwd")

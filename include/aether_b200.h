@@ -60,6 +60,12 @@ uint64_t aether_launch_count(void);
 /* Code recorded by a kernel that abandoned a bounded wait (0 = none).  Read after synchronising. */
 int aether_device_status(void);
 void aether_device_status_clear(void);
+/* Self-test of that give-up path (no counterpart in the reference, which has no device-side waits): launches one
+ * thread that waits, with the kernels' own bounded wait, on a barrier nothing completes; after `limit_cycles`
+ * SM clock cycles (1 .. 2e9) it records code 6 and the kernel ends by itself.  After the stream is synchronised
+ * aether_device_status() returns 6 and the convolution entry points return AETHER_E_DEVICE_TIMEOUT until
+ * aether_device_status_clear() is called. */
+int aether_selftest_bounded_wait(int64_t limit_cycles, void* stream);
 
 /* Optional kernel timing for benchmarks (off by default).  aether_profile_enable(n), n >= 1, creates a fixed
  * pool of CUDA events once and resets the counters; while enabled, events are recorded on the launch
@@ -148,10 +154,10 @@ int aether_bn_bwd(const float* x, const float* dy, const float* gamma, const flo
  *   aether_bn_act_fwd_train: Batch_Norm.forward (training) + activation.  `partials` may be NULL (x is reduced here)
  *     or [nblocks][3][C] partial statistics from aether_conv2d_fwd_bnstats.  ws: aether_bn_workspace_bytes(rows, C).
  *   aether_bn_act_fwd_eval: the same with the running statistics (ws: 2*C floats).
- *   aether_bn_act_bwd: dy is the gradient w.r.t. y = act(bn(x)); y_act is that y.  The activation's derivative is
- *     taken from the sign of y_act: identical to Leaky_ReLU.backward for alpha > 0; for alpha = 0 an output that is
- *     exactly 0 blocks the gradient whereas ReLU.backward (:412-414, dvalues[inputs < 0] = 0) would pass it when the
- *     pre-activation is exactly 0.
+ *   aether_bn_act_bwd: dy is the gradient w.r.t. y = act(bn(x)).  The activation's derivative is taken at the
+ *     pre-activation v = gamma*xhat + beta, recomputed from x while x is read for the Batch_Norm sums (y is not
+ *     read): alpha where v < 0, else 1 -- the gradient passes at v == 0 exactly as ReLU.backward (:412-414,
+ *     dvalues[inputs < 0] = 0) and Leaky_ReLU.backward (:424-428) do.
  *   channel_scale (C floats >= 0, or NULL): the mask / keep_prob of a Layer_Dropout_Spatial (:384-404) that follows
  *     the activation; y = act(bn(x)) * channel_scale[c] and the backward treats dy as the gradient w.r.t. that y.
  *     (Folded into the per-channel coefficients: act(v) * m = act(m * v) for m >= 0.) */
@@ -162,7 +168,7 @@ int aether_bn_act_fwd_train(const float* x, const float* partials, int64_t nbloc
 int aether_bn_act_fwd_eval(const float* x, const float* gamma, const float* beta, const float* running_mean,
                            const float* running_var, float* y, int64_t rows, int C, float eps, float alpha, void* ws,
                            size_t ws_bytes, void* stream);
-int aether_bn_act_bwd(const float* x, const float* y_act, const float* dy, const float* gamma, const float* batch_mean,
+int aether_bn_act_bwd(const float* x, const float* beta, const float* dy, const float* gamma, const float* batch_mean,
                       const float* batch_var, float* dx, float* dgamma, float* dbeta, int64_t rows, int C, float eps,
                       float alpha, const float* channel_scale, void* ws, size_t ws_bytes, void* stream);
 

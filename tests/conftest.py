@@ -20,3 +20,11 @@ def golden():
     def load(name):
         return np.load(os.path.join(GOLDEN, name + ".npz"), allow_pickle=False)
     return load
+
+
+@pytest.fixture(scope="session", autouse=True)
+def fresh_library():
+    """The tests must exercise the sources in the tree, not a library built from older ones: rebuild when the
+    recorded source digest differs (a no-op otherwise)."""
+    from aether_ml_b200.build import build_library
+    build_library()

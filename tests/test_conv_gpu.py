@@ -1,6 +1,8 @@
 """GPU parity tests of Conv_Layer (through the C ABI) against the NumPy oracle and the golden vectors
 made by the reference's own classes.  Tolerances are relative L2: 1e-2 for bf16, 1e-3 for tf32,
 1e-5 for the fp32 CUDA-core path."""
+import zlib
+
 import numpy as np
 import pytest
 
@@ -90,7 +92,7 @@ SHAPES = [
 @pytest.mark.parametrize("shape", SHAPES)
 def test_tensor_core_shapes(env, shape, mode):
     S, H, W, Cin, Cout, f, pad = shape
-    rng = np.random.default_rng(hash(shape) % 2**32)
+    rng = np.random.default_rng(zlib.crc32(repr(shape).encode()))       # the same inputs in every run
     x = rng.standard_normal((S, H, W, Cin)).astype(np.float32)
     w = (rng.standard_normal((f, f, Cin, Cout)) * np.sqrt(2.0 / (f * f * Cin))).astype(np.float32)
     b = (rng.standard_normal(Cout) * 0.1).astype(np.float32)

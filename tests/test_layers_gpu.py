@@ -166,6 +166,37 @@ def test_fused_block_tail_matches_oracle_chain(env, case):
     assert O.rel_l2(host(oe), O.pool_forward(ye, f, f)[0]) <= 1e-5
 
 
+@pytest.mark.parametrize("alpha", [0.0, 0.1])
+def test_fused_activation_gradient_at_zero_preactivation(env, alpha):
+    """Batch_Norm + (Leaky_)ReLU in the same passes, no pooling: where the pre-activation is exactly 0 the reference
+    lets the gradient through (ReLU.backward zeroes only inputs < 0, CNN_classes_cupy.py:412-414).  Channel 0 is
+    constant with beta = 0, so every one of its pre-activations is exactly 0; the other channels are ordinary."""
+    torch, _lib, layers = env
+    S, H, W, C = 4, 6, 5, 8
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((S, H, W, C)).astype(np.float32)
+    x[..., 0] = 1.5
+    gamma = (rng.random(C) + 0.5).astype(np.float32); beta = rng.standard_normal(C).astype(np.float32)
+    beta[0] = 0.0
+    bn = layers.Batch_Norm(n_features=C)
+    bn.gamma.copy_(torch.from_numpy(gamma)); bn.beta.copy_(torch.from_numpy(beta))
+    bn.fused_alpha = float(alpha)
+    y = bn.forward(x, True)
+    yb, _, mean, var, _, _ = O.bn_forward_train(x, gamma, beta, np.zeros(C), np.ones(C))
+    assert np.all(yb[..., 0] == 0.0)
+    ya = O.leaky_relu_forward(yb, alpha) if alpha else O.relu_forward(yb)
+    assert O.rel_l2(host(y), ya) <= 1e-5
+    dy = rng.standard_normal(x.shape).astype(np.float32)
+    dx = bn.backward(dy)
+    ga = O.leaky_relu_backward(yb, dy, alpha) if alpha else O.relu_backward(yb, dy)
+    assert np.array_equal(ga[..., 0], dy[..., 0])                       # the oracle passes the gradient at 0
+    dxo, dgo, dbo = O.bn_backward(x, ga, gamma, mean, var)
+    assert O.rel_l2(host(bn.dbiases), dbo) <= 1e-5                      # dbeta[0] = sum(dy[..., 0]): not blocked
+    assert abs(float(bn.dbiases[0]) - float(dy[..., 0].sum())) <= 1e-4 * np.abs(dy[..., 0]).sum()
+    assert O.rel_l2(host(bn.dweights)[1:], dgo[1:]) <= 1e-4
+    assert O.rel_l2(host(dx)[..., 1:], dxo[..., 1:]) <= 2e-4
+
+
 @pytest.mark.parametrize("name", ["pool_max_2x2", "pool_max_odd", "pool_max_overlap", "pool_avg_2x2"])
 def test_pooling_golden(env, golden, name):
     torch, _lib, layers = env

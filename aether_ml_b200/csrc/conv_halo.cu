@@ -23,20 +23,7 @@
 // memory (the store path handles about one cache line per cycle, so fewer, wider segments matter).
 // Everything that does not change from tile to tile (row -> pixel mapping, column offsets) is
 // computed once per thread.
-//
-// Converter form (bf16 operands, CVT = true): the caller's fp32 activations are turned into the bf16
-// operand copy by four extra warps of this kernel instead of by a separate pass.  Every CTA then owns a
-// CONTIGUOUS run of strips; its converter warps walk the input rows those strips need (its own rows plus
-// the halo rows at both ends of the run, which the neighbouring CTA converts as well -- both write the
-// same values), read them once with streaming loads, write the bf16 rows to the operand copy in global
-// memory and signal the TMA producer through a ring of shared-memory barriers; the producer's box load of
-// a strip then finds the rows in L2.  The tensor-core pipeline is untouched (hardware swizzle and zero
-// fill still come from TMA), the copy stays complete for the filter-gradient kernel that runs later, and
-// DRAM sees the fp32 tensor read once and the bf16 copy written once.  For dX the same warps also sum
-// the rows of dy per channel (the bias gradient), each row by the CTA whose run contains it.
 #include <string.h>
-
-#include <cuda_bf16.h>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -62,23 +49,14 @@ struct HaloParams {
     int region_stride;   // bytes between stages (multiple of 1024)
     int stages;
     int w_bytes;         // resident filter bytes = taps * kchunks * NT * 128
-    // converter form only
-    const float* cvt_src;        // fp32 input (N, in_H, in_W, in_C)
-    __nv_bfloat16* cvt_dst;      // bf16 operand copy [N*in_H*in_W][in_Cp] that tm_in describes
-    float* cvt_colsum;           // nullable: per-CTA column sums of the input rows, [gridDim.x][in_C]
-    int in_H, in_W, in_C, in_Cp;
 };
 
 static constexpr int HALO_EPI_WARPS = 8;                          // 4 lane quadrants x HALO_EPI_PARTS column parts
 static constexpr int HALO_EPI_PARTS = HALO_EPI_WARPS / 4;
 static constexpr int HALO_EPI_UB = 8 / HALO_EPI_PARTS;            // 16-column TMEM loads in flight per batch
 static constexpr int HALO_THREADS = 64 + 32 * HALO_EPI_WARPS;
-static constexpr int HALO_CVT_MAX_THREADS = 128; // converter warps of the CVT form: 2 or 4 (template parameter CW)
-static constexpr int HALO_CVT_DEPTH = 8;        // strips the converter may run ahead of the TMA producer
-static constexpr int HALO_CVT_UNROLL = 8;       // pixel groups a converter thread keeps in flight
 static constexpr int HALO_TAIL = 2048;          // barriers, TMEM pointer, bias
 static constexpr int HALO_STATS_BYTES = HALO_EPI_WARPS * 2 * 128 * 4;   // per-warp running column sums (statistics)
-static_assert(HALO_CVT_MAX_THREADS * 8 * 4 <= HALO_STATS_BYTES, "the converter's column-sum scratch shares the statistics area");
 
 // MMA with descriptors given as (low word, shared high word); K-major 128-byte-swizzle operands.
 template <bool TF32>
@@ -100,16 +78,8 @@ __device__ __forceinline__ void umma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32
 }
 
 // STATS: the epilogue also accumulates per-channel statistics of the output (p.stats must be set).
-// CW > 0: converter form (see the head of this file) with CW converter warps behind the epilogue warps.  The
-// register file is split over the SM's four schedulers, so up to 12 warps leave a thread 168 registers and 13 to 16
-// warps 128: CW = 2 keeps the epilogue's registers, CW = 4 doubles the loads the converter keeps in flight.
-template <bool TF32, bool STATS, int CW>
-__global__ void __launch_bounds__(HALO_THREADS + 32 * CW, 1)
-halo_conv_kernel(const __grid_constant__ HaloParams p) {
-    constexpr bool CVT = CW > 0;
-    constexpr int HALO_CVT_WARPS = CW > 0 ? CW : 1;
-    constexpr int HALO_CVT_THREADS = 32 * HALO_CVT_WARPS;
-    static_assert(!(CVT && TF32), "the TF32 form reads the caller's fp32 arrays directly");
+template <bool TF32, bool STATS>
+__global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid_constant__ HaloParams p) {
     constexpr int KC = TF32 ? 32 : 64;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -124,10 +94,8 @@ halo_conv_kernel(const __grid_constant__ HaloParams p) {
     auto tempty_bar = [&](int b) { return sBar + 8u * (2 * S + 4 + b); };
     const uint32_t wfull_bar = sBar + 8u * (2 * S + 8);
     const uint32_t sTmemPtr = sBar + 8u * (2 * S + 9);
-    auto cfull_bar = [&](int k) { return sBar + 8u * (2 * S + 10 + k); };                  // converter -> producer
-    auto cempty_bar = [&](int k) { return sBar + 8u * (2 * S + 10 + HALO_CVT_DEPTH + k); };   // producer -> converter
     volatile uint32_t* tmem_ptr_generic = reinterpret_cast<volatile uint32_t*>(gen_base + (sTmemPtr - smem_base));
-    float* bias_s = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + 512);     // NT floats
+    float* bias_s = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + 256);     // NT floats
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -147,12 +115,6 @@ halo_conv_kernel(const __grid_constant__ HaloParams p) {
             mbar_init(tempty_bar(b), HALO_EPI_WARPS);
         }
         mbar_init(wfull_bar, 1);
-        if (CVT) {
-            for (int k = 0; k < HALO_CVT_DEPTH; ++k) {
-                mbar_init(cfull_bar(k), 1);
-                mbar_init(cempty_bar(k), 1);
-            }
-        }
         mbar_fence_init();
         tma_prefetch_desc(&p.tm_in);
         tma_prefetch_desc(&p.tm_w);
@@ -172,18 +134,6 @@ halo_conv_kernel(const __grid_constant__ HaloParams p) {
     const int grid = (int)gridDim.x;
     const uint32_t region_tx = (uint32_t)p.region_rows * 128u;
     const uint32_t wtile_bytes = (uint32_t)NT * 128u;
-    // Strips of this CTA: every grid-th strip, or (converter form) a contiguous run so that the CTA's own
-    // converter warps produce the rows its box loads read.
-    int t_begin, t_step, t_count;
-    if (CVT) {
-        t_begin = (int)((long long)total_tiles * blockIdx.x / grid);
-        t_count = (int)((long long)total_tiles * (blockIdx.x + 1) / grid) - t_begin;
-        t_step = 1;
-    } else {
-        t_begin = blockIdx.x;
-        t_step = grid;
-        t_count = (total_tiles - (int)blockIdx.x + grid - 1) / grid;
-    }
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -196,24 +146,19 @@ halo_conv_kernel(const __grid_constant__ HaloParams p) {
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int k = 0, t = t_begin; k < t_count && ok; ++k, t += t_step) {
+            for (int t = blockIdx.x; t < total_tiles && ok; t += grid) {
                 const int n = t / p.tiles_h;
                 const int h0 = (t - n * p.tiles_h) * p.BH;
                 const int tp = t + 2 * grid;                       // tile after next: warm L2 with its window
                 const int np = tp / p.tiles_h;
                 const int hp = (tp - np * p.tiles_h) * p.BH;
-                const int cs = k % HALO_CVT_DEPTH;
-                if (CVT) {                                         // the strip's rows must be in the bf16 copy first
-                    if (!mbar_wait(cfull_bar(cs), (uint32_t)(k / HALO_CVT_DEPTH) & 1u, p.status, DS_TIMEOUT_CONVERT)) { ok = false; break; }
-                }
                 for (int kc = 0; kc < p.kchunks; ++kc) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) { ok = false; break; }
                     mbar_arrive_expect_tx(full_bar(s), region_tx);
                     tma_load_4d(sR + s * p.region_stride, &p.tm_in, full_bar(s), kc * KC, -p.padL, h0 - p.padT, n);
-                    if (!CVT && tp < total_tiles) tma_prefetch_l2_4d(&p.tm_in, kc * KC, -p.padL, hp - p.padT, np);
+                    if (tp < total_tiles) tma_prefetch_l2_4d(&p.tm_in, kc * KC, -p.padL, hp - p.padT, np);
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
-                if (CVT && ok) mbar_arrive(cempty_bar(cs));
             }
         }
     } else if (warp == 1) {
@@ -233,7 +178,7 @@ halo_conv_kernel(const __grid_constant__ HaloParams p) {
         bool ok = __all_sync(0xffffffffu, mbar_wait_spin(wfull_bar, 0, p.status, DS_TIMEOUT_FULL));
         int s = 0;
         uint32_t ph = 0, buf = 0, aph = 0;
-        for (int k = 0; k < t_count && ok; ++k) {
+        for (int t = blockIdx.x; t < total_tiles && ok; t += grid) {
             bool w_ok = mbar_wait_spin(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY);
             w_ok = __all_sync(0xffffffffu, w_ok);
             if (!w_ok) { ok = false; break; }
@@ -270,7 +215,7 @@ halo_conv_kernel(const __grid_constant__ HaloParams p) {
             if (++buf == NB) { buf = 0; aph ^= 1u; }
             __syncwarp();
         }
-    } else if (warp < 2 + HALO_EPI_WARPS) {
+    } else {
         // ------------------------------------------------------------------ epilogue
         // Warp (q, half): TMEM lanes [32q, 32q+32), columns [half*NT/2, (half+1)*NT/2).  Accumulators are read
         // with the 16-lane x 256-bit shape: thread t receives, per 8-column group, columns 2*(t%4)+{0,1} of rows
@@ -307,7 +252,7 @@ halo_conv_kernel(const __grid_constant__ HaloParams p) {
         const size_t image_floats = (size_t)p.Hout * p.Wout * p.n_out;
         uint32_t buf = 0, aph = 0;
         bool ok = true;
-        for (int k = 0, t = t_begin; k < t_count && ok; ++k, t += t_step) {
+        for (int t = blockIdx.x; t < total_tiles && ok; t += grid) {
             const int n = t / p.tiles_h;
             const int th = t - n * p.tiles_h;
             const int rows_left = p.Hout - th * p.BH;
@@ -440,136 +385,6 @@ halo_conv_kernel(const __grid_constant__ HaloParams p) {
         }
     }
 
-    if constexpr (CVT) {
-        if (warp >= 2 + HALO_EPI_WARPS) {
-            // -------------------------------------------------------------- converter
-            // Converter warp cw takes strips cw, cw + CW, ... of the CTA's run, so CW strips are being converted at
-            // any time.  Lane -> (8-channel group g, pixel lane pl): the groups per pixel divide 32, so a lane keeps
-            // its channels for the whole kernel and holds their running sums in registers.  The fp32 rows of the
-            // warp's strip after next are requested into L2 first (one bulk prefetch, no registers, no shared
-            // memory), so the loads below pay an L2 round trip instead of a DRAM one.
-            const int cw = warp - (2 + HALO_EPI_WARPS);
-            const int G = p.in_Cp >> 3;
-            const int g = lane % G, pl = lane / G, planes = 32 / G;
-            const int c0 = g * 8;
-            const bool vec = c0 + 8 <= p.in_C;
-            const bool sums = p.cvt_colsum != nullptr;
-            float acc[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-            const int t_end = t_begin + t_count;
-            // input rows [lo, hi) that strip k of the run adds to the copy (what its window covers beyond the
-            // previous strip's window when that strip is in the same image and in this run)
-            auto new_rows = [&](int k, int& n, int& lo, int& hi) {
-                const int t = t_begin + k;
-                n = t / p.tiles_h;
-                const int th = t - n * p.tiles_h;
-                lo = th * p.BH - p.padT;
-                hi = lo + p.BH + p.fH - 1;
-                if (k > 0 && th > 0 && lo < hi - p.BH) lo = hi - p.BH;      // the previous strip's window ended at hi - BH
-                if (lo < 0) lo = 0;
-                if (hi > p.in_H) hi = p.in_H;
-            };
-            auto prefetch = [&](int k) {
-                if (k >= t_count || lane != 0) return;
-                int n, lo, hi;
-                new_rows(k, n, lo, hi);
-                if (hi <= lo) return;
-                const char* base = reinterpret_cast<const char*>(p.cvt_src + (((size_t)n * p.in_H + lo) * p.in_W) * p.in_C);
-                const size_t bytes = (size_t)(hi - lo) * p.in_W * p.in_C * sizeof(float);     // a multiple of 16
-                for (size_t o = 0; o < bytes; o += 32768) bulk_prefetch_l2(base + o, (uint32_t)(bytes - o < 32768 ? bytes - o : 32768));
-            };
-            prefetch(cw);
-            prefetch(cw + CW);
-            bool ok = true;
-            for (int k = cw; k < t_count && ok; k += CW) {
-                prefetch(k + 2 * CW);
-                int n, lo, hi;
-                new_rows(k, n, lo, hi);
-                const int cs = k % HALO_CVT_DEPTH;
-                if (!mbar_wait(cempty_bar(cs), ((uint32_t)(k / HALO_CVT_DEPTH) & 1u) ^ 1u, p.status, DS_TIMEOUT_CONVERT)) { ok = false; break; }
-                if (hi > lo) {
-                    // Rows [lo, hi) are one contiguous run of (hi-lo)*in_W pixels.  A row adds to the column sums
-                    // when the strip that owns it (row / BH, the last strip of the image for rows beyond) belongs
-                    // to this CTA's run: rows [own_lo, own_hi).
-                    int own_lo = hi, own_hi = hi;
-                    if (sums) {
-                        for (int r = hi - 1; r >= lo; --r) {
-                            int o = r / p.BH;
-                            if (o > p.tiles_h - 1) o = p.tiles_h - 1;
-                            o += n * p.tiles_h;
-                            if (o >= t_end) own_hi = r;
-                            if (o >= t_begin) own_lo = r;
-                        }
-                        if (own_lo > own_hi) own_lo = own_hi;
-                    }
-                    const int npix = (hi - lo) * p.in_W;
-                    const int sum_lo = (own_lo - lo) * p.in_W, sum_hi = (own_hi - lo) * p.in_W;
-                    const size_t pix0 = ((size_t)n * p.in_H + lo) * p.in_W;
-                    const float* src = p.cvt_src + pix0 * p.in_C + c0;
-                    __nv_bfloat16* dst = p.cvt_dst + pix0 * p.in_Cp + c0;
-                    for (int base = pl; base < npix; base += planes * HALO_CVT_UNROLL) {
-                        float4 va[HALO_CVT_UNROLL], vb[HALO_CVT_UNROLL];
-#pragma unroll
-                        for (int u = 0; u < HALO_CVT_UNROLL; ++u) {
-                            const int px = base + u * planes;
-                            va[u] = vb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (px < npix) {
-                                const float* sp = src + (size_t)px * p.in_C;
-                                if (vec) {
-                                    va[u] = __ldcs(reinterpret_cast<const float4*>(sp));
-                                    vb[u] = __ldcs(reinterpret_cast<const float4*>(sp + 4));
-                                } else {                                           // ragged last group: channels beyond in_C are zero
-                                    float tmp[8];
-#pragma unroll
-                                    for (int e = 0; e < 8; ++e) tmp[e] = (c0 + e < p.in_C) ? sp[e] : 0.f;
-                                    va[u] = make_float4(tmp[0], tmp[1], tmp[2], tmp[3]);
-                                    vb[u] = make_float4(tmp[4], tmp[5], tmp[6], tmp[7]);
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < HALO_CVT_UNROLL; ++u) {
-                            const int px = base + u * planes;
-                            if (px < npix) {
-                                __nv_bfloat162 o[4];
-                                o[0] = __floats2bfloat162_rn(va[u].x, va[u].y);
-                                o[1] = __floats2bfloat162_rn(va[u].z, va[u].w);
-                                o[2] = __floats2bfloat162_rn(vb[u].x, vb[u].y);
-                                o[3] = __floats2bfloat162_rn(vb[u].z, vb[u].w);
-                                *reinterpret_cast<uint4*>(dst + (size_t)px * p.in_Cp) = *reinterpret_cast<uint4*>(o);
-                                if (sums && px >= sum_lo && px < sum_hi) {
-                                    acc[0] += va[u].x; acc[1] += va[u].y; acc[2] += va[u].z; acc[3] += va[u].w;
-                                    acc[4] += vb[u].x; acc[5] += vb[u].y; acc[6] += vb[u].z; acc[7] += vb[u].w;
-                                }
-                            }
-                        }
-                    }
-                }
-                // The rows were written through the generic proxy and are read by TMA (async proxy): every writer
-                // fences, then the warp reports the strip.
-                fence_proxy_async_all();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(cfull_bar(cs));
-            }
-            if (sums) {
-                // Lanes with the same channel group add up in a fixed order (warp 0, pixel lane 0 first): one row of
-                // per-CTA sums, reduced over the CTAs by the caller's finish kernel.
-                float* red = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + HALO_TAIL);   // [CW*32][8]
-                const int ct = cw * 32 + lane;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) red[ct * 8 + e] = acc[e];
-                named_bar_sync(1, HALO_CVT_THREADS);
-                for (int c = ct; c < p.in_C; c += HALO_CVT_THREADS) {
-                    const int gg = c >> 3, e = c & 7;
-                    float sum = 0.f;
-                    for (int q = 0; q < CW * planes; ++q) sum += red[(q * G + gg) * 8 + e];
-                    p.cvt_colsum[(size_t)blockIdx.x * p.in_C + c] = sum;
-                }
-            }
-        }
-    }
-
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -625,36 +440,10 @@ long long halo_igemm_stats_blocks(bool tf32, int in_C, int S, int taps, int out_
     return 4LL * (total < num_sms() ? total : num_sms());       // one block per CTA and 32-row quarter
 }
 
-// Converter warps for an operand of in_Cp (padded) channels: none unless a pixel's 8-channel groups divide a warp
-// (64, 128 or 256 channels); 4 from 128 channels per pixel on, else 2.
-static int halo_cvt_warps(int in_Cp) {
-    const int G = in_Cp / 8;
-    if (G < 1 || 32 % G) return 0;     // a warp's lanes must split into whole pixels
-    return G >= 16 ? 4 : 2;
-}
-
-// True when the halo kernel takes the problem in its converter form: bf16 operands whose 8-channel groups per
-// pixel divide the converter's thread count (a thread then keeps its channels for the whole kernel).
-bool halo_igemm_converts(bool tf32, int in_Cp, int S, int taps, int out_C, int out_H, int out_W, int n_padded, int fH,
-                         int fW) {
-    if (tf32 || in_Cp % 64 || halo_cvt_warps(in_Cp) == 0) return false;
-    HaloGeom g;
-    return halo_geometry(false, in_Cp, S, taps, out_C, out_H, out_W, n_padded, fH, fW, g);
-}
-
-// CTAs the halo kernel runs for the problem (= rows of per-CTA column sums the converter form writes).
-int halo_igemm_grid(int S, int out_H, int out_W, int fH, int fW) {
-    const int Wp = out_W + fW - 1;
-    int BH = (128 - out_W) / Wp + 1;
-    if (BH > out_H) BH = out_H;
-    const long long total = 1LL * ceil_div(out_H, BH) * S;
-    return (int)(total < num_sms() ? total : num_sms());
-}
-
 int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
                    int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, int n_padded, int fH, int fW,
                    int padT, int padL, int flip, const float* bias, float* stats, int prof_kind, cudaStream_t st,
-                   bool* used, const float* cvt_src, int cvt_C, float* cvt_colsum) {
+                   bool* used) {
     *used = false;
     const int elt = tf32 ? 4 : 2;
     const int KC = 128 / elt;
@@ -682,30 +471,18 @@ int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int 
     p.kchunks = kchunks; p.rows_per_tap = rows_per_tap;
     p.region_rows = region_rows; p.region_stride = region_stride; p.stages = stages; p.w_bytes = w_bytes;
     const int smem = fixed + stages * region_stride;
-    const bool cvt = cvt_src != nullptr;
-    if (cvt) {
-        if (!halo_igemm_converts(tf32, in_C, S, taps, out_C, out_H, out_W, n_padded, fH, fW) || (cvt_colsum && stats))
-            return set_error(AE_UNSUPPORTED, "halo convolution: converter form not available for this problem");
-        p.cvt_src = cvt_src;
-        p.cvt_dst = static_cast<__nv_bfloat16*>(const_cast<void*>(in));
-        p.cvt_colsum = cvt_colsum;
-        p.in_H = in_H; p.in_W = in_W; p.in_C = cvt_C; p.in_Cp = in_C;
-    }
 
-    // operand type x (with / without the statistics epilogue); bf16 also in the converter form with 2 or 4 converter warps
+    // four instantiations: operand type x (with / without the statistics epilogue)
     using KernelFn = void (*)(const HaloParams);
-    static const KernelFn kernels[8] = {halo_conv_kernel<false, false, 0>, halo_conv_kernel<true, false, 0>,
-                                        halo_conv_kernel<false, true, 0>,  halo_conv_kernel<true, true, 0>,
-                                        halo_conv_kernel<false, false, 2>, halo_conv_kernel<false, true, 2>,
-                                        halo_conv_kernel<false, false, 4>, halo_conv_kernel<false, true, 4>};
-    static PerDeviceSmem configured[8];
-    const int cw = cvt ? halo_cvt_warps(in_C) : 0;
-    const int ki = cvt ? (cw == 4 ? 6 : 4) + (stats ? 1 : 0) : (tf32 ? 1 : 0) + (stats ? 2 : 0);
+    static const KernelFn kernels[4] = {halo_conv_kernel<false, false>, halo_conv_kernel<true, false>,
+                                        halo_conv_kernel<false, true>, halo_conv_kernel<true, true>};
+    static PerDeviceSmem configured[4];
+    const int ki = (tf32 ? 1 : 0) + (stats ? 2 : 0);
     if ((rc = ensure_dynamic_smem(kernels[ki], smem_max, configured[ki], "halo_conv"))) return rc;
     const long long total = 1LL * tiles_h * S;
     const int grid = (int)(total < num_sms() ? total : num_sms());
     prof_begin(prof_kind, st);
-    kernels[ki]<<<grid, HALO_THREADS + 32 * cw, smem, st>>>(p);
+    kernels[ki]<<<grid, HALO_THREADS, smem, st>>>(p);
     prof_end(prof_kind, st);
     count_launch();
     *used = true;

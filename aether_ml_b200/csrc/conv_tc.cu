@@ -838,8 +838,6 @@ struct TcPlan {
     // dW decomposition
     int dw_nb, dw_nt, dw_cblocks, dw_U, dw_MG, dw_gpc, dw_ngc, dw_ntn, dw_splits;
     int db_blocks;
-    bool cvt_fwd, cvt_dx;   // the forward / dX kernel converts its fp32 operand itself (no separate cast pass)
-    int cvt_dx_blocks;      // rows of per-CTA column sums the dX kernel then writes
     PixelTiling til_out;   // tiles over output pixels (forward, dW)
     PixelTiling til_in;    // tiles over input pixels (dX)
 };
@@ -891,10 +889,7 @@ static TcPlan make_plan(const AetherConvDesc& d) {
     const long long out_rows = 1LL * d.S * pl.Ho * pl.Wo;
     pl.db_blocks = (int)(out_rows < 4LL * num_sms() * 64 ? (out_rows + 63) / 64 : 4LL * num_sms());
     if (pl.db_blocks < 1) pl.db_blocks = 1;
-    // dX through the halo kernel's converter form: that kernel casts dy itself and leaves one row of column sums per CTA
-    pl.cvt_dx = !pl.tf32 && halo_igemm_converts(false, pl.Cout_p, d.S, pl.taps, d.Cin, d.H, d.W, pl.Cin_p, d.fH, d.fW);
-    pl.cvt_fwd = !pl.tf32 && halo_igemm_converts(false, pl.Cin_p, d.S, pl.taps, d.Cout, pl.Ho, pl.Wo, pl.Cout_p, d.fH, d.fW);
-    pl.cvt_dx_blocks = pl.cvt_dx ? halo_igemm_grid(d.S, d.H, d.W, d.fH, d.fW) : 0;
+
     // workspace
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 1024); return o; };
@@ -909,7 +904,7 @@ static TcPlan make_plan(const AetherConvDesc& d) {
         if (rs > part_splits) part_splits = rs;
     }
     pl.off_part = take((size_t)part_splits * pl.dw_U * UC * pl.Cout_p * 4);
-    pl.off_dbpart = take((size_t)(pl.db_blocks > pl.cvt_dx_blocks ? pl.db_blocks : pl.cvt_dx_blocks) * d.Cout * 4);
+    pl.off_dbpart = take((size_t)pl.db_blocks * d.Cout * 4);
     pl.total = off;
     return pl;
 }
@@ -975,21 +970,18 @@ static int dispatch_igemm(IgemmParams& p, int nt, cudaStream_t st) {
 }
 
 // Runs out[p, n] = sum_{tap,k} in[p (+/-) tap, k] * Wm[tap][n][k] (+ bias).
-// cvt_src (nullable): `in` is a bf16 copy that does not exist yet; the halo kernel makes it from this fp32 array of
-// cvt_C channels while it runs (callers check halo_igemm_converts first), and fills cvt_colsum when given.
 static int run_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
                      int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, const PixelTiling& til,
                      int n_padded, int fH, int fW, int sgn, int off_h, int off_w, const float* bias, float* stats,
-                     cudaStream_t st, const float* cvt_src = nullptr, int cvt_C = 0, float* cvt_colsum = nullptr) {
+                     cudaStream_t st) {
     {   // wide images with a filter that fits in shared memory: halo-reuse kernel
         bool used = false;
         const int padT = sgn > 0 ? -off_h : fH - 1 - off_h;
         const int padL = sgn > 0 ? -off_w : fW - 1 - off_w;
         int rc0 = run_halo_igemm(tf32, in, in_C, in_H, in_W, S, wmat, w_inner, rows_per_tap, taps, out, out_C, out_H, out_W,
                                  n_padded, fH, fW, padT, padL, sgn > 0 ? 0 : 1, bias, stats,
-                                 sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX, st, &used, cvt_src, cvt_C, cvt_colsum);
+                                 sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX, st, &used);
         if (rc0 || used) return rc0;
-        if (cvt_src) return set_error(AE_UNSUPPORTED, "convolution: converter form requested for a shape the halo kernel does not take");
     }
     IgemmParams p;
     memset(&p, 0, sizeof(p));
@@ -1067,13 +1059,12 @@ int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const f
     }
     __nv_bfloat16* xsh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_xsh);
     __nv_bfloat16* wf = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_wf);
-    // The bf16 copy of x (kept for dW) is written by the forward kernel itself where it can, else by a cast pass.
-    if (!pl.cvt_fwd && (rc = launch_cast(x, xsh, 1LL * d.S * d.H * d.W, d.Cin, pl.Cin_p, nullptr, 0, st))) return rc;
+    if ((rc = launch_cast(x, xsh, 1LL * d.S * d.H * d.W, d.Cin, pl.Cin_p, nullptr, 0, st))) return rc;
     filter_shadow_kernel<__nv_bfloat16><<<fblocks, 256, 0, st>>>(w, wf, pl.taps, d.Cin, d.Cout, pl.Cout_p, pl.Cin_p, 1);
     count_launch();
     if ((rc = check_launch("filter_shadow_kernel"))) return rc;
     return run_igemm(false, xsh, pl.Cin_p, d.H, d.W, d.S, wf, pl.Cin_p, pl.Cout_p, pl.taps, y, d.Cout, pl.Ho, pl.Wo,
-                     pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, stats, st, pl.cvt_fwd ? x : nullptr, d.Cin);
+                     pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, stats, st);
 }
 
 template <bool TF32, int NB>
@@ -1100,7 +1091,6 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
     const void* x_op = x;
     const void* dy_op = dy;
     const int fblocks = 2 * num_sms();
-    bool cvt_dx = false;
 
     // ---- shadows + dB
     if (pl.tf32) {
@@ -1113,15 +1103,13 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
     } else {
         __nv_bfloat16* dysh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_dysh);
         __nv_bfloat16* xsh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_xsh);
-        // With dX on the halo kernel's converter form that kernel casts dy and sums its columns; otherwise a cast pass.
-        cvt_dx = pl.cvt_dx && dx != nullptr;
-        if (!cvt_dx && (rc = launch_cast(dy, dysh, out_rows, d.Cout, pl.Cout_p, dbpart, pl.db_blocks, st))) return rc;
+        if ((rc = launch_cast(dy, dysh, out_rows, d.Cout, pl.Cout_p, dbpart, pl.db_blocks, st))) return rc;
         if (dw && !x_shadow_valid)
             if ((rc = launch_cast(x, xsh, in_rows, d.Cin, pl.Cin_p, nullptr, 0, st))) return rc;
         x_op = xsh;
         dy_op = dysh;
     }
-    if (db && !cvt_dx) {
+    if (db) {
         colsum_finish_kernel<<<ceil_div(d.Cout, 8), 256, 0, st>>>(dbpart, pl.db_blocks, d.Cout, db);
         count_launch();
         if ((rc = check_launch("colsum_finish_kernel"))) return rc;
@@ -1140,15 +1128,9 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
             count_launch();
             if ((rc = check_launch("filter_shadow_kernel"))) return rc;
             rc = run_igemm(false, dy_op, pl.Cout_p, pl.Ho, pl.Wo, d.S, wd, pl.Cout_p, pl.Cin_p, pl.taps, dx, d.Cin, d.H,
-                           d.W, pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, nullptr, st,
-                           cvt_dx ? dy : nullptr, d.Cout, (cvt_dx && db) ? dbpart : nullptr);
+                           d.W, pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, nullptr, st);
         }
         if (rc) return rc;
-        if (cvt_dx && db) {
-            colsum_finish_kernel<<<ceil_div(d.Cout, 8), 256, 0, st>>>(dbpart, pl.cvt_dx_blocks, d.Cout, db);
-            count_launch();
-            if ((rc = check_launch("colsum_finish_kernel"))) return rc;
-        }
     }
 
     // ---- dW: split over pixel tiles, fixed-order reduction of the partials

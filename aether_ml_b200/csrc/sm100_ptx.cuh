@@ -18,8 +18,7 @@ enum DeviceStatus : int {
     DS_TIMEOUT_EMPTY = 2,     // producer gave up waiting for a free stage
     DS_TIMEOUT_TMEM_FULL = 3, // epilogue gave up waiting for an accumulator
     DS_TIMEOUT_TMEM_EMPTY = 4,// MMA issuer gave up waiting for a drained accumulator
-    DS_TIMEOUT_CONVERT = 5,   // operand-converter hand-off (converter warps <-> TMA producer) gave up
-    DS_TIMEOUT_SELFTEST = 6   // the self-test kernel's wait ran out (as it is meant to)
+    DS_TIMEOUT_SELFTEST = 5   // the self-test kernel's wait ran out (as it is meant to)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -93,11 +92,6 @@ __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, in
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-// Orders this thread's earlier generic-proxy writes (shared or global memory) before later async-proxy
-// accesses (TMA) that other threads issue after synchronising with it.
-__device__ __forceinline__ void fence_proxy_async_all() {
-    asm volatile("fence.proxy.async;" ::: "memory");
-}
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
@@ -124,10 +118,6 @@ __device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* m, int c0,
     asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
                  ::"l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
-}
-// Requests `bytes` (multiple of 16) from a 16-byte-aligned global address into L2; nothing waits for it.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* gptr, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(gptr)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"

@@ -13,16 +13,10 @@ int make_map_nhwc(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int 
 int make_map_2d(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elt, int inner, long long rows, int box_k,
                 int box_rows);
 // Halo-reuse kernel (conv_halo.cu): launches and sets *used when the problem fits it, else leaves *used false.
-// Converter form: `cvt_src` (fp32, cvt_C channels per pixel) is turned into the bf16 operand copy `in` (in_C =
-// padded channels) by the kernel itself; `cvt_colsum` (nullable, no `stats` then) receives one row of per-channel
-// sums of cvt_src per CTA, halo_igemm_grid(...) rows of cvt_C floats.  Only when halo_igemm_converts(...) is true.
 int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
                    int rows_per_tap, int taps, float* out, int out_C, int out_H, int out_W, int n_padded, int fH, int fW,
                    int padT, int padL, int flip, const float* bias, float* stats, int prof_kind, cudaStream_t st,
-                   bool* used, const float* cvt_src = nullptr, int cvt_C = 0, float* cvt_colsum = nullptr);
-bool halo_igemm_converts(bool tf32, int in_Cp, int S, int taps, int out_C, int out_H, int out_W, int n_padded, int fH,
-                         int fW);
-int halo_igemm_grid(int S, int out_H, int out_W, int fH, int fW);
+                   bool* used);
 // Partial-statistics blocks ([block][3][out_C]: count, mean, M2) the halo kernel writes when `stats` is given; 0 when
 // the halo kernel does not take the problem.
 long long halo_igemm_stats_blocks(bool tf32, int in_C, int S, int taps, int out_C, int out_H, int out_W, int n_padded,

@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from .layers import (Activation_Softmax_Loss_CategoricalCrossEntropy, Batch_Norm, Conv_Layer, Layer_Dropout_Spatial,
-                     Loss_CategoricalCrossEntropy, Pooling, ReLU, SoftMax, to_device, _labels_i32)
+                     Loss_CategoricalCrossEntropy, Pooling, ReLU, SoftMax, to_device, _labels_i32, _softmax_cce)
 
 
 class Layer_Input:
@@ -89,6 +89,11 @@ class Model:
         self.accuracy = None
         self.flat_params = None
         self.grad_hook = None      # callable(flat_grads) run between backward and the optimizer (all-reduce)
+        self._graph = self._graph_opt = None
+        self._graph_metrics = False
+        self._m_last = self._m_sum = None
+        self.bucket_reducer = None # dp.BucketReducer: all-reduces the flat gradients bucket by bucket during backward
+        self._bucket_of_layer = {}
 
     def add(self, layer):
         self.layers.append(layer)
@@ -163,6 +168,9 @@ class Model:
         self.flat_grads = torch.zeros(total, dtype=torch.float32, device=dev)
         self.flat_m = torch.zeros(total, dtype=torch.float32, device=dev)
         self.flat_v = torch.zeros(total, dtype=torch.float32, device=dev)
+        # element range of each trainable layer (its weights, biases and padding), in forward order: contiguous
+        bounds = offs[0::2] + [total]
+        self.flat_layer_ranges = [(bounds[i], bounds[i + 1]) for i in range(len(self.trainable_layers))]
         k = 0
         for l in self.trainable_layers:
             views = []
@@ -178,6 +186,15 @@ class Model:
                 setattr(l, mom + "_momentums", self.flat_m[o:o + n].view(old.shape))
                 setattr(l, mom + "_cache", self.flat_v[o:o + n].view(old.shape))
             l._grad_views = tuple(views)
+
+    def set_bucket_reducer(self, reducer):
+        """Installs a gradient reducer (see dp.BucketReducer): bucket i is started as soon as the backward pass has
+        written the gradients of its last layer, and waited for right before that bucket's optimizer update."""
+        self.bucket_reducer = reducer
+        self._bucket_of_layer = {}
+        if reducer is not None:
+            for i, (_, _, trigger) in enumerate(reducer.buckets):
+                self._bucket_of_layer[id(self.trainable_layers[trigger])] = i
 
     # ------------------------------------------------------------------ passes
     def forward(self, X, training):
@@ -200,13 +217,23 @@ class Model:
                 layer.backward(layer.next.dinputs, need_dinputs=False)   # nobody consumes d(loss)/d(images)
             else:
                 layer.backward(layer.next.dinputs)
+            b = self._bucket_of_layer.get(id(layer))
+            if b is not None:                   # this layer's gradients complete a bucket: start reducing it
+                self.bucket_reducer.start(b)
 
     def _apply_optimizer(self, run_hook=True):
         opt = self.optimizer
         if run_hook and self.grad_hook is not None and self.flat_params is not None:
             self.grad_hook(self.flat_grads)
         opt.pre_update_parameters()
-        if self.flat_params is not None and hasattr(opt, "update_flat"):
+        if self.bucket_reducer is not None and self.flat_params is not None and hasattr(opt, "update_flat"):
+            # one update per bucket, each behind its own all-reduce only (the first bucket's update overlaps the
+            # second bucket's all-reduce)
+            for i, (lo, hi, _) in enumerate(self.bucket_reducer.buckets):
+                if run_hook:
+                    self.bucket_reducer.wait(i)
+                opt.update_flat(self.flat_params[lo:hi], self.flat_grads[lo:hi], self.flat_m[lo:hi], self.flat_v[lo:hi])
+        elif self.flat_params is not None and hasattr(opt, "update_flat"):
             opt.update_flat(self.flat_params, self.flat_grads, self.flat_m, self.flat_v)
         else:
             for layer in self.trainable_layers:
@@ -235,30 +262,71 @@ class Model:
         return self._g_step
 
     def _graph_body(self):
-        return self.train_step(self._g_X, self._g_y)
+        out = self.train_step(self._g_X, self._g_y)
+        if self._graph_metrics:
+            self._step_metrics(out, self._g_y)
+        return out
+
+    def _step_metrics(self, output, labels):
+        """This step's data loss, accuracy and regularisation loss, kept on the device: `_m_last` holds the three
+        values of the latest step, `_m_sum` the running sums of the per-sample losses and of the hits that the
+        reference accumulates on the host (CNN_model_cupy.py:104-111, CNN_classes_cupy.py:577-589)."""
+        smooth = self.loss.label_smoothing
+        _, rows_loss, _, hits = _softmax_cce(output, labels, False, True, False, True, smooth, 0.0, input_is_prob=True)
+        self._m_last[0:1].copy_(rows_loss.mean().reshape(1))
+        self._m_last[1:2].copy_(hits.float().mean().reshape(1))
+        reg = self.loss.regularization_loss()
+        if isinstance(reg, torch.Tensor):
+            self._m_last[2:3].copy_(reg.reshape(1))
+        else:
+            self._m_last[2:3].fill_(float(reg))
+        self._m_sum[0] += rows_loss.sum()
+        self._m_sum[1] += hits.sum()
 
     def _graph_state(self):
         """Every tensor a train step changes besides activations: parameters, Adam moments, running statistics."""
-        ts = [self.flat_params, self.flat_m, self.flat_v, self._g_step]
+        ts = [self.flat_params, self.flat_m, self.flat_v, self._g_step, self._m_last, self._m_sum]
         for l in self.layers:
             if isinstance(l, Batch_Norm) and l.gamma is not None:
                 ts += [l._rm, l._rv]
         return ts
 
-    def capture_train_step(self, X, y, warmup=2):
+    def _all_ranks_agree(self, ok):
+        """True when `ok` holds on every rank (one small eager all-reduce; single process: `ok` itself)."""
+        import torch.distributed as dist
+        if not (dist.is_initialized() and dist.get_world_size() > 1):
+            return ok
+        flag = torch.tensor([1.0 if ok else 0.0], device=self.flat_params.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return bool(flag.item() > 0.5)
+
+    def capture_train_step(self, X, y, warmup=2, collectives_in_graph=True, metrics=False):
         """Records ``train_step`` for batches shaped like (X, y) into a CUDA graph; ``train_step_graph`` replays
-        it with one launch (two, around the gradient hook, when one is set).  A step of the small reference
-        networks is ~130 kernel launches of a few microseconds
+        it with one launch.  A step of the small reference networks is ~130 kernel launches of a few microseconds
         each, so the eager step is bound by launch overhead, not by the GPU.  Needs ``finalize(flat=True)``.
         Whatever the reference changes on the host per step (Adam's iteration count and decayed learning rate,
         the dropout draws) is read from one int64 device counter that the graph itself increments.  The warm-up
-        steps (they size the workspaces) are undone, so capturing does not train."""
+        steps (they size the workspaces) are undone, so capturing does not train.
+
+        Data parallelism: the bucketed all-reduces (dp.BucketReducer) are recorded inside the same graph, forked
+        onto NCCL's stream where the backward pass starts them and joined before each bucket's update.  The
+        capture runs in thread-local error mode: the process group's watchdog thread polls CUDA events of earlier
+        collectives, which a global-mode capture treats as an illegal call and aborts with -- on that rank only.
+        A rank whose capture failed must not leave its peers inside a recorded collective, so after the attempt
+        every rank reports over one eager all-reduce and, unless all succeeded, all fall back to two graphs with
+        the collectives launched eagerly between them.  ``collectives_in_graph=False`` asks for that form.
+        ``metrics=True`` also records the step's loss / accuracy bookkeeping (``Model.train`` uses it)."""
         if self.flat_params is None:
             raise RuntimeError("capture_train_step needs finalize(flat=True)")
         self._g_X = to_device(X).clone()
         self._g_y = _labels_i32(y).clone()
         opt = self.optimizer
+        dev = self.flat_params.device
         self.enable_device_step()
+        self._graph_metrics = bool(metrics)
+        if getattr(self, "_m_last", None) is None:
+            self._m_last = torch.zeros(3, dtype=torch.float32, device=dev)
+            self._m_sum = torch.zeros(2, dtype=torch.float64, device=dev)
         saved = [t.clone() for t in self._graph_state()]
         saved_it = opt.iterations
         side = torch.cuda.Stream()
@@ -268,22 +336,51 @@ class Model:
                 self._graph_body()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        for t, s in zip(self._graph_state(), saved):
-            t.copy_(s)
-        # With a gradient hook (the data-parallel all-reduce) the step is recorded as two graphs and the hook runs
-        # eagerly between them: collectives stay outside stream capture, where a rank that fails cannot leave
-        # its peers waiting inside a captured collective.
-        self._graph = torch.cuda.CUDAGraph()
-        self._graph_opt = None
-        with torch.cuda.graph(self._graph):
-            self._g_out = self.forward(self._g_X, training=True)
-            self.backward(self._g_out, self._g_y)
-            if self.grad_hook is None:
-                self._apply_optimizer()
-        if self.grad_hook is not None:
-            self._graph_opt = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self._graph_opt):
-                self._apply_optimizer(run_hook=False)
+        for t, sv in zip(self._graph_state(), saved):
+            t.copy_(sv)
+        reducer = self.bucket_reducer if (self.bucket_reducer is not None and self.bucket_reducer.active) else None
+        eager_between = self.grad_hook is not None or (reducer is not None and not collectives_in_graph)
+        self._graph = self._graph_opt = None
+        self.capture_note = "one graph"
+        if reducer is not None and not eager_between:
+            graph, ok, err = torch.cuda.CUDAGraph(), True, ""
+            outer = torch.cuda.current_stream()
+            try:
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    self._g_out = self._graph_body()
+            except Exception as e:                  # noqa: BLE001 -- any failure means "do not replay this graph"
+                ok, err = False, repr(e)
+                reducer.works = [None] * len(reducer.buckets)
+                torch.cuda.set_stream(outer)        # a failed capture may leave its side stream current
+            if self._all_ranks_agree(ok):
+                self._graph = graph
+                self.capture_note = "one graph with %d all-reduce bucket(s) inside" % len(reducer.buckets)
+            else:
+                eager_between = True
+                self.capture_note = "two graphs, collectives eager (in-graph capture failed on a rank%s)" % (": " + err if err else "")
+        if self._graph is None:
+            # With collectives outside: graph 1 = forward + backward (no bucket is started inside it), then the
+            # reduction runs eagerly, then graph 2 = the optimizer.
+            self._graph = torch.cuda.CUDAGraph()
+            held, self._bucket_of_layer = self._bucket_of_layer, {}
+            try:
+                with torch.cuda.graph(self._graph, capture_error_mode="thread_local"):
+                    self._g_out = self.forward(self._g_X, training=True)
+                    self.backward(self._g_out, self._g_y)
+                    if not eager_between:
+                        self._apply_optimizer()
+                        if self._graph_metrics:
+                            self._step_metrics(self._g_out, self._g_y)
+            finally:
+                self._bucket_of_layer = held
+            if eager_between:
+                self._graph_opt = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self._graph_opt, capture_error_mode="thread_local"):
+                    self._apply_optimizer(run_hook=False)
+                    if self._graph_metrics:
+                        self._step_metrics(self._g_out, self._g_y)
+                if self.capture_note == "one graph":
+                    self.capture_note = "two graphs, collectives eager"
         opt.iterations = saved_it           # capture records work, it does not run it
         return self._graph
 
@@ -295,35 +392,78 @@ class Model:
         self._g_y.copy_(_labels_i32(y), non_blocking=True)
         self._graph.replay()
         if self._graph_opt is not None:
-            self.grad_hook(self.flat_grads)
+            if self.grad_hook is not None:
+                self.grad_hook(self.flat_grads)
+            elif self.bucket_reducer is not None:
+                self.bucket_reducer.reduce_all()
             self._graph_opt.replay()
         opt = self.optimizer
         opt.pre_update_parameters()         # host mirror of what the graph just did on the device
         opt.post_update_parameters()
         return self._g_out
 
-    def train(self, X, y, *, epochs=1, batch_size=None, print_every=1, validation_data=None):
+    def _graph_train_possible(self, X, y, chunks):
+        """The captured step serves ``train`` when every batch has the same shape and the step is the combined
+        softmax + cross-entropy one on flat parameters."""
+        if self.flat_params is None or self.softmax_classifier_output is None or not torch.cuda.is_available():
+            return False
+        if not isinstance(self.accuracy, Accuracy_Categorical) or len(chunks) == 0:
+            return False
+        sizes = {len(range(*sl.indices(len(X)))) for sl in chunks}
+        return len(sizes) == 1
+
+    def train(self, X, y, *, epochs=1, batch_size=None, print_every=1, validation_data=None, use_graph=None):
+        """The reference's training loop (CNN_model_cupy.py:67-151), same printed lines.  When every batch has the
+        same shape and the model was finalized with ``flat=True`` the step is captured once and replayed
+        (``use_graph=None`` decides by itself, True / False force it): loss and accuracy are then computed and
+        accumulated on the device inside the replayed step and read back only for the lines that are printed,
+        so the loop never waits for the GPU in between."""
         self.accuracy.init(y)
         chunks = _batches(len(X), batch_size)
+        graph = self._graph_train_possible(X, y, chunks) if use_graph is None else bool(use_graph)
+        if graph and not self._graph_train_possible(X, y, chunks):
+            raise RuntimeError("use_graph=True needs finalize(flat=True), softmax + categorical cross-entropy, "
+                               "Accuracy_Categorical and batches of one size")
         print("Training")
+        if graph:
+            first = chunks[0]
+            shape = tuple(to_device(X[first]).shape)
+            if getattr(self, "_graph", None) is None or not self._graph_metrics or tuple(self._g_X.shape) != shape:
+                self.capture_train_step(X[first], y[first], metrics=True)
+            per_batch = shape[0]
         for epoch in range(1, epochs + 1):
             print(f' epoch: {epoch}')
             self.loss.new_pass()
             self.accuracy.new_pass()
+            if graph:
+                self._m_sum.zero_()
             for step, sl in enumerate(chunks):
                 batch_X, batch_y = X[sl], y[sl]
-                output = self.forward(batch_X, training=True)
-                data_loss, regularization_loss = self.loss.calculate(output, batch_y, include_regularization=True,
-                                                                     training=True)
-                loss = data_loss + regularization_loss
-                predictions = self.output_layer_activation.predictions(output)
-                accuracy = self.accuracy.calculate(predictions, batch_y)
-                self.backward(output, batch_y)
-                self._apply_optimizer()
+                if graph:
+                    self.train_step_graph(batch_X, batch_y)
+                    data_loss, accuracy, regularization_loss = self._m_last[0], self._m_last[1], self._m_last[2]
+                    loss = None
+                else:
+                    output = self.forward(batch_X, training=True)
+                    data_loss, regularization_loss = self.loss.calculate(output, batch_y, include_regularization=True,
+                                                                         training=True)
+                    loss = data_loss + regularization_loss
+                    predictions = self.output_layer_activation.predictions(output)
+                    accuracy = self.accuracy.calculate(predictions, batch_y)
+                    self.backward(output, batch_y)
+                    self._apply_optimizer()
                 if not step % print_every or step == len(chunks) - 1:
+                    if graph:                   # one read-back of the three device scalars, only for printed steps
+                        data_loss, accuracy, regularization_loss = (float(v) for v in self._m_last.tolist())
+                        loss = data_loss + regularization_loss
                     print(f'epoch: {epoch}, acc: {float(accuracy):.3f}, loss: {float(loss):.3f} ('
                           f'data_loss: {float(data_loss):.3f}, reg_loss: {float(regularization_loss):.3f}, '
                           f'lr:: {self.optimizer.current_learning_rate}')
+            if graph:                           # hand the device-side sums to the reference's accumulators
+                self.loss.accumulated_sum = self._m_sum[0].float()
+                self.loss.accumulated_count = per_batch * len(chunks)
+                self.accuracy.accumulated_sum = self._m_sum[1].float()
+                self.accuracy.accumulated_count = per_batch * len(chunks)
         epoch_data_loss, epoch_regularization_loss = self.loss.calculate_accumulated(include_regularization=True)
         epoch_loss = epoch_data_loss + epoch_regularization_loss
         epoch_accuracy = self.accuracy.calculate_accumulated()
@@ -357,15 +497,72 @@ class Model:
         for parameter_set, layer in zip(parameters, self.trainable_layers):
             layer.set_parameters(*parameter_set)
 
-    def save_parameters(self, path):
+    def save_parameters(self, path, include_optimizer=False):
         """Same on-disk format as the reference (a pickled list of per-layer tuples,
-        CNN_model_cupy.py:277-282), with NumPy arrays so the file loads without a GPU."""
+        CNN_model_cupy.py:277-282), with NumPy arrays so the file loads without a GPU.
+        ``include_optimizer=True`` (not in the reference, whose checkpoints drop Adam's state) writes a dict
+        {"parameters": that list, "optimizer": iteration count + per-layer moment arrays} instead, so training
+        resumes with the same moments and decayed learning rate."""
         host = [tuple(np.asarray(a.detach().cpu()) for a in params) for params in self.get_parameters()]
+        payload = host
+        if include_optimizer:
+            state = []
+            for l in self.trainable_layers:
+                if hasattr(l, "weight_cache"):
+                    state.append(tuple(np.asarray(getattr(l, n).detach().cpu()) for n in
+                                       ("weight_momentums", "weight_cache", "bias_momentums", "bias_cache")))
+                else:
+                    state.append(None)
+            payload = {"parameters": host,
+                       "optimizer": {"iterations": int(self.optimizer.iterations), "layers": state}}
         with open(path, 'wb') as f:
-            pickle.dump(host, f)
+            pickle.dump(payload, f)
 
     def load_parameters(self, path):
+        """Reads a checkpoint written by ``save_parameters`` here or by the reference (CNN_model_cupy.py:284-289).
+        The reference's CuPy model pickles ``cupy`` arrays; they are rebuilt as NumPy arrays (the pickle stores
+        them as host arrays wrapped in a ``cupy._core.core.array`` call), so such files load without CuPy.  Only
+        array reconstruction is allowed while unpickling; anything else in the file is refused."""
         with open(path, 'rb') as f:
-            self.set_parameters(pickle.load(f))
+            payload = _CheckpointUnpickler(f).load()
+        if isinstance(payload, dict):
+            self.set_parameters(payload["parameters"])
+            opt_state = payload.get("optimizer")
+            if opt_state is not None and self.optimizer is not None:
+                self.optimizer.iterations = int(opt_state["iterations"])
+                self.optimizer.pre_update_parameters()
+                step_dev = getattr(self, "_g_step", None)
+                if step_dev is not None:
+                    step_dev.fill_(self.optimizer.iterations)
+                for l, st in zip(self.trainable_layers, opt_state["layers"]):
+                    if st is None:
+                        continue
+                    for name, arr in zip(("weight_momentums", "weight_cache", "bias_momentums", "bias_cache"), st):
+                        cur = getattr(l, name, None)
+                        t = to_device(arr)
+                        if cur is not None:
+                            cur.copy_(t.reshape(cur.shape))     # in place: flat-buffer views stay views
+                        else:
+                            setattr(l, name, t.clone())
+        else:
+            self.set_parameters(payload)
 
     load_paramters = load_parameters      # spelling used by the reference's NumPy model and two of its scripts
+
+
+class _CheckpointUnpickler(pickle.Unpickler):
+    """Unpickler for parameter checkpoints: NumPy's array reconstruction helpers, and ``cupy`` array
+    constructors mapped to ``numpy.asarray``; every other global is refused."""
+
+    _NUMPY = {("numpy._core.multiarray", "_reconstruct"), ("numpy.core.multiarray", "_reconstruct"),
+              ("numpy._core.multiarray", "scalar"), ("numpy.core.multiarray", "scalar"),
+              ("numpy", "ndarray"), ("numpy", "dtype")}
+
+    def find_class(self, module, name):
+        if module.split(".")[0] == "cupy" and name in ("array", "asarray", "ndarray"):
+            if name == "ndarray":
+                raise pickle.UnpicklingError("cupy.ndarray subclass state is not a parameter checkpoint")
+            return np.asarray
+        if (module, name) in self._NUMPY:
+            return super().find_class(module, name)
+        raise pickle.UnpicklingError("checkpoint refers to %s.%s, which is not an array constructor" % (module, name))

@@ -62,8 +62,8 @@ int aether_device_status(void);
 void aether_device_status_clear(void);
 /* Self-test of that give-up path (no counterpart in the reference, which has no device-side waits): launches one
  * thread that waits, with the kernels' own bounded wait, on a barrier nothing completes; after `limit_cycles`
- * SM clock cycles (1 .. 2e9) it records code 6 and the kernel ends by itself.  After the stream is synchronised
- * aether_device_status() returns 6 and the convolution entry points return AETHER_E_DEVICE_TIMEOUT until
+ * SM clock cycles (1 .. 2e9) it records code 5 and the kernel ends by itself.  After the stream is synchronised
+ * aether_device_status() returns 5 and the convolution entry points return AETHER_E_DEVICE_TIMEOUT until
  * aether_device_status_clear() is called. */
 int aether_selftest_bounded_wait(int64_t limit_cycles, void* stream);
 

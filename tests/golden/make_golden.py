@@ -150,6 +150,98 @@ def main(ref_root):
         image=np.array([[1, 2, 3, 0], [0, 1, 2, 3], [3, 0, 1, 2], [2, 3, 0, 1]], dtype=np.float32),
         kernel=np.array([[1, 0, -1], [1, 0, -1], [1, 0, -1]], dtype=np.float32),
         expected=np.array([[-3, -4, 0, 5], [-3, -2, -2, 6], [-4, 2, -2, 3], [-3, 4, 0, 1]], dtype=np.float32))
+    # ------------------------------------------------------------------ parameter checkpoint in the CuPy model's format
+    # A small network in the layout of the reference's shipped checkpoints (CNN/saved_models/model2..5: conv, BN,
+    # conv, BN, ..., dense, dense; float32 conv/BN arrays with keep-dims running statistics, float64 dense arrays),
+    # built and evaluated with the reference's NumPy Model.  The file is written the way the CuPy model writes it
+    # (CNN_model_cupy.py:277-282): every array pickles as a call of ``cupy._core.core.array`` on its host copy,
+    # which is what ``cupy.ndarray.__reduce__`` emits.  CuPy itself is not needed: a stand-in module of that name
+    # provides the constructor while the file is being written.
+    import pickle
+    import types
+    from CNN.models import CNN_model as RM
+    np.random.seed(11)
+    net = RM.Model()
+    net.add(R.Conv_Layer((8, 8, 1), num_filters=4, filter_size=(3, 3), strides=(1, 1), padding="same"))
+    net.add(R.Batch_Norm())
+    net.add(R.ReLU())
+    net.add(R.Pooling((2, 2), (2, 2), "valid", "max"))
+    net.add(R.Conv_Layer((4, 4, 4), num_filters=8, filter_size=(3, 3), strides=(1, 1), padding="same"))
+    net.add(R.Batch_Norm())
+    net.add(R.ReLU())
+    net.add(R.Pooling((2, 2), (2, 2), "valid", "max"))
+    net.add(R.Flatten())
+    net.add(R.Layer_Dense(2 * 2 * 8, 12))
+    net.add(R.ReLU())
+    net.add(R.Layer_Dense(12, 5))
+    net.add(R.SoftMax())
+    net.set(loss=R.Loss_CategoricalCrossEntropy(), optimizer=R.Optimizer_Adam(learning_rate=1e-2),
+            accuracy=RM.Accuracy_Categorical())
+    for layer in net.layers:                             # the CuPy twin's alias (CNN_classes_cupy.py:68): conv layers train
+        if isinstance(layer, R.Conv_Layer):
+            layer.weights = layer.filter_weights
+    net.finalize()
+    xs = rng.random((6, 8, 8, 1)).astype(np.float32)
+    ys = rng.integers(0, 5, size=6)
+    for _ in range(3):                                   # a few steps so that no parameter is at its initial value
+        out = net.forward(xs.astype(np.float64), training=True)
+        net.backward(out, ys)
+        net.optimizer.pre_update_parameters()
+        for layer in net.trainable_layers:
+            net.optimizer.update_parameters(layer)
+        net.optimizer.post_update_parameters()
+    probs = net.forward(xs.astype(np.float64), training=False)
+    # per-layer tuples as the CuPy twin's get_parameters returns them (the NumPy Batch_Norm has no such method):
+    # conv (filter_weights, biases) CNN_classes_cupy.py:156-158, Batch_Norm (gamma, beta, running_mean, running_var)
+    # :510-516 with (C,) parameters and keep-dims statistics as in the shipped checkpoints, dense (weights, biases)
+    params = []
+    for layer in (l for l in net.layers if isinstance(l, (R.Conv_Layer, R.Batch_Norm, R.Layer_Dense))):
+        if isinstance(layer, R.Batch_Norm):
+            Cn = np.asarray(layer.gamma).size
+            params.append((np.asarray(layer.gamma).reshape(-1), np.asarray(layer.beta).reshape(-1),
+                           np.asarray(layer.running_mean).reshape(1, 1, 1, Cn),
+                           np.asarray(layer.running_var).reshape(1, 1, 1, Cn)))
+        elif isinstance(layer, R.Conv_Layer):
+            params.append((np.asarray(layer.filter_weights), np.asarray(layer.biases)))
+        else:
+            params.append((np.asarray(layer.weights), np.asarray(layer.biases)))
+
+    stub_names = ("cupy", "cupy._core", "cupy._core.core")
+    saved_modules = {n: sys.modules.get(n) for n in stub_names}
+    mods = {n: types.ModuleType(n) for n in stub_names}
+
+    def array(host):
+        return np.asarray(host)
+    array.__module__ = "cupy._core.core"
+    array.__qualname__ = "array"
+    mods["cupy._core.core"].array = array
+    mods["cupy._core"].core = mods["cupy._core.core"]
+    mods["cupy"]._core = mods["cupy._core"]
+
+    class DeviceArray:                                   # pickles like cupy.ndarray: array(host copy)
+        def __init__(self, host):
+            self.host = host
+
+        def __reduce__(self):
+            return array, (self.host,)
+
+    def as_saved(a, k):
+        a = np.asarray(a)
+        # conv and BN arrays are float32 in the CuPy model (CNN_classes_cupy.py:44,66,443-448), dense ones float64
+        return DeviceArray(a.astype(np.float32) if k < 4 else a.astype(np.float64))
+
+    sys.modules.update(mods)
+    try:
+        with open(os.path.join(out_dir, "checkpoint_cupy_format.pkl"), "wb") as fh:
+            pickle.dump([tuple(as_saved(a, k) for a in layer_params) for k, layer_params in enumerate(params)], fh)
+    finally:
+        for n, m in saved_modules.items():
+            if m is None:
+                sys.modules.pop(n, None)
+            else:
+                sys.modules[n] = m
+    np.savez_compressed(os.path.join(out_dir, "checkpoint_cupy_format.npz"), x=xs, probs=probs.astype(np.float64),
+                        **{"p%d_%d" % (k, j): np.asarray(a) for k, lp in enumerate(params) for j, a in enumerate(lp)})
     print("golden fixtures written to", out_dir)
 
 

@@ -49,6 +49,27 @@ def _worker(rank, world, port, out):
     dp.allreduce_sum_(flat)
     avg = flat.numpy() / world
     full = _oracle_grads(X, labels, w, wd)
+    # the same gradients reduced in buckets: bucket order = backward order (tail of the buffer first), each bucket
+    # reduced once, the result equal to the single all-reduce
+    n_conv = w.size + w.shape[3]
+    ranges = [(0, n_conv), (n_conv, n_conv + wd.size)]   # conv layer, dense layer (forward order)
+    buckets = dp.plan_buckets(ranges, 2)
+    assert buckets == [(n_conv, n_conv + wd.size, 1), (0, n_conv, 0)]
+    assert dp.plan_buckets(ranges, 1) == [(0, n_conv + wd.size, 0)]
+    assert dp.plan_buckets(ranges, 5) == buckets                      # never more buckets than layers
+    flat_b = torch.from_numpy(_oracle_grads(xs, ys, w, wd))
+    red = dp.BucketReducer(flat_b, buckets)
+    assert red.active
+    red.start(0)                                         # the dense head is complete first ...
+    head_before_wait = flat_b[:n_conv].clone()           # ... while the conv part is still this rank's own gradient
+    red.wait(0)
+    assert torch.equal(flat_b[:n_conv], head_before_wait)
+    assert torch.allclose(flat_b[n_conv:], flat[n_conv:], rtol=0, atol=0)
+    red.start(1)
+    red.wait(1)
+    assert torch.equal(flat_b, flat)
+    flat_c = torch.from_numpy(_oracle_grads(xs, ys, w, wd))
+    assert torch.equal(dp.BucketReducer(flat_c, buckets).reduce_all(), flat)
     params = torch.full((5,), float(rank))
     dp.broadcast_(params)
     if rank == 0:

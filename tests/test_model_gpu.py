@@ -275,3 +275,131 @@ def test_fused_batch_norm_activation_matches_unfused(env, topology):
     # ... and the pooling behind it is done by the same kernels: the Batch_Norm's output is the pooled tensor
     pool = [l for l in fused.layers if isinstance(l, Ly.Pooling)][0]
     assert bn.pooled_now and pool.output is bn.output and tuple(bn.output.shape[1:3]) == (shape[0] // 2, shape[1] // 2)
+
+
+def _parse_lines(text):
+    """(acc, loss, data_loss, reg_loss) of every 'epoch: ...' / ' training, ...' line Model.train printed."""
+    import re
+    rows = []
+    for line in text.splitlines():
+        m = re.search(r"acc: ([\d.]+), loss: ([\d.]+) \(data_loss: ([\d.]+), reg_loss: ([\d.]+)", line)
+        if m:
+            rows.append(tuple(float(v) for v in m.groups()))
+    return rows
+
+
+def test_train_loop_on_captured_step_prints_the_eager_numbers(env, capsys):
+    """Model.train on the captured step (loss / accuracy accumulated on the device, read back only for printed
+    lines) prints the same lines as the eager loop of the reference and ends with the same parameters."""
+    torch, _lib, Ly, M = env
+    rng = np.random.default_rng(31)
+    y = rng.integers(0, 10, 96)
+    X = rng.random((96, 32, 32, 3)).astype(np.float32)
+
+    def run(use_graph):
+        m, _ = build(env, "cifar", "bf16", True)
+        m.enable_device_step()                             # the same dropout draws in both loops
+        for k, l in enumerate(m.layers):
+            if hasattr(l, "seed"):
+                l.seed = 900 + k
+        capsys.readouterr()
+        m.train(X, y, epochs=2, batch_size=32, print_every=2, use_graph=use_graph)
+        torch.cuda.synchronize()
+        return m, capsys.readouterr().out
+
+    eager, text_e = run(False)
+    graph, text_g = run(True)
+    assert graph._graph is not None and eager._graph is None
+    rows_e, rows_g = _parse_lines(text_e), _parse_lines(text_g)
+    assert len(rows_e) == len(rows_g) == 2 * 2 + 1          # steps 0 and 2 of each epoch + the closing line
+    assert [l.split(",")[0] for l in text_e.splitlines()] == [l.split(",")[0] for l in text_g.splitlines()]
+    for a, b in zip(rows_e, rows_g):
+        assert np.allclose(a, b, atol=2e-3), (a, b)
+    assert O.rel_l2(host(graph.flat_params), host(eager.flat_params)) <= 1e-5
+    assert graph.optimizer.iterations == eager.optimizer.iterations == 6
+    # ragged last batch: the loop falls back to the eager step by itself
+    m3, _ = build(env, "cifar", "bf16", True)
+    m3.train(X[:80], y[:80], epochs=1, batch_size=32, print_every=10)
+    assert m3._graph is None
+
+
+def test_gradient_buckets_follow_the_backward_order(env):
+    """dp.plan_buckets on a real model: two buckets, the dense head first (it is complete first in the backward
+    pass and holds most of the elements), the convolution blocks second; a single-process reducer changes nothing."""
+    torch, _lib, Ly, M = env
+    from aether_ml_b200 import dp
+    m, shape = build(env, "cifar", "bf16", True)
+    ranges = m.flat_layer_ranges
+    assert ranges[0][0] == 0 and ranges[-1][1] == m.flat_params.numel()
+    assert all(a[1] == b[0] for a, b in zip(ranges[:-1], ranges[1:]))
+    buckets = dp.plan_buckets(ranges, 2)
+    assert len(buckets) == 2
+    (lo1, hi1, t1), (lo2, hi2, t2) = buckets
+    assert hi1 == m.flat_params.numel() and lo1 == hi2 and lo2 == 0 and t2 == 0
+    assert isinstance(m.trainable_layers[t1], Ly.Layer_Dense) and hi1 - lo1 > hi2 - lo2
+    assert dp.plan_buckets(ranges, 1) == [(0, m.flat_params.numel(), 0)]
+    ref, _ = build(env, "cifar", "bf16", True)
+    dp.attach(m, buckets=2)
+    assert m.bucket_reducer is not None and not m.bucket_reducer.active
+    rng = np.random.default_rng(2)
+    for mm in (m, ref):
+        mm.enable_device_step()
+        for k, l in enumerate(mm.layers):
+            if hasattr(l, "seed"):
+                l.seed = 40 + k
+    for _ in range(2):
+        X = rng.random((8,) + shape).astype(np.float32); y = rng.integers(0, 10, 8)
+        m.train_step(X, y); ref.train_step(X, y)
+    assert O.rel_l2(host(m.flat_params), host(ref.flat_params)) <= 1e-6      # per-bucket Adam == one Adam launch
+
+
+def test_reference_checkpoint_file_loads_and_predicts(env, golden):
+    """A parameter file in the reference CuPy model's format (pickled cupy arrays, float64 dense layers, keep-dims
+    running statistics) loads through Model.load_parameters without CuPy and reproduces the probabilities the
+    reference's NumPy model computed with those parameters."""
+    torch, _lib, Ly, M = env
+    g = golden("checkpoint_cupy_format")
+    np.random.seed(1)
+    m = M.Model()
+    m.add(Ly.Conv_Layer((8, 8, 1), 4, (3, 3), (1, 1), "same"))
+    m.add(Ly.Batch_Norm())
+    m.add(Ly.ReLU())
+    m.add(Ly.Pooling((2, 2), (2, 2), "valid", "max"))
+    m.add(Ly.Conv_Layer((4, 4, 4), 8, (3, 3), (1, 1), "same"))
+    m.add(Ly.Batch_Norm())
+    m.add(Ly.ReLU())
+    m.add(Ly.Pooling((2, 2), (2, 2), "valid", "max"))
+    m.add(Ly.Flatten())
+    m.add(Ly.Layer_Dense(2 * 2 * 8, 12))
+    m.add(Ly.ReLU())
+    m.add(Ly.Layer_Dense(12, 5))
+    m.add(Ly.SoftMax())
+    m.set(loss=Ly.Loss_CategoricalCrossEntropy(), optimizer=Ly.Optimizer_Adam(), accuracy=M.Accuracy_Categorical())
+    m.finalize()
+    m.load_parameters(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "checkpoint_cupy_format.pkl"))
+    assert m.layers[9].weights.dtype == torch.float32       # float64 dense arrays are cast on load
+    probs = m.predict(g["x"])
+    assert O.rel_l2(host(probs), g["probs"]) <= 1e-5
+    conv = m.layers[0]
+    assert conv.weights is conv.filter_weights
+
+
+def test_checkpoint_with_optimizer_state_resumes_training(env, tmp_path):
+    torch, _lib, Ly, M = env
+    rng = np.random.default_rng(17)
+    a, shape = build(env, "fmnist", "bf16", True)
+    batches = [(rng.random((8,) + shape).astype(np.float32), rng.integers(0, 10, 8)) for _ in range(3)]
+    for X, y in batches[:2]:
+        a.train_step(X, y)
+    path = os.path.join(tmp_path, "ckpt")
+    a.save_parameters(path, include_optimizer=True)
+    b, _ = build(env, "fmnist", "bf16", True)
+    b.load_parameters(path)
+    assert b.optimizer.iterations == 2
+    assert O.rel_l2(host(b.flat_m), host(a.flat_m)) <= 1e-7 and O.rel_l2(host(b.flat_v), host(a.flat_v)) <= 1e-7
+    cache2 = host(a.layers[0].weight_cache).copy()
+    a.train_step(*batches[2]); b.train_step(*batches[2])
+    assert O.rel_l2(host(b.flat_params), host(a.flat_params)) <= 1e-6
+    c, _ = build(env, "fmnist", "bf16", False)              # per-layer state (no flat buffers) resumes as well
+    c.load_parameters(path)
+    assert c.optimizer.iterations == 2 and O.rel_l2(host(c.layers[0].weight_cache), cache2) <= 1e-7

@@ -140,3 +140,30 @@ def test_dense_loss_adam(golden):
         b, mb, vb = O.adam_step(b, db, mb, vb, lr, it)
         assert O.rel_l2(w, g["w_hist"][it]) < 1e-7 and O.rel_l2(b, g["b_hist"][it]) < 1e-7
     assert O.rel_l2(mw, g["m_w"]) < 1e-7 and O.rel_l2(vw, g["v_w"]) < 1e-7
+
+
+def test_reference_checkpoint_format_loads_without_cupy(golden):
+    """A parameter file in the reference CuPy model's on-disk format (pickled cupy arrays, CNN_model_cupy.py:277-282;
+    the fixture was written by make_golden.py from the reference's NumPy model) unpickles to NumPy arrays through
+    the restricted checkpoint unpickler; anything that is not an array constructor is refused."""
+    import io
+    import os
+    import pickle
+
+    from aether_ml_b200.model import _CheckpointUnpickler
+    g = golden("checkpoint_cupy_format")
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "checkpoint_cupy_format.pkl")
+    raw = open(path, "rb").read()
+    assert b"cupy._core.core" in raw                       # the file really names cupy's constructor
+    params = _CheckpointUnpickler(io.BytesIO(raw)).load()
+    assert isinstance(params, list) and len(params) == 6
+    assert [len(p) for p in params] == [2, 4, 2, 4, 2, 2]
+    for k, layer_params in enumerate(params):
+        for j, a in enumerate(layer_params):
+            assert isinstance(a, np.ndarray)
+            assert a.dtype == (np.float32 if k < 4 else np.float64)
+            assert np.array_equal(a, g["p%d_%d" % (k, j)].astype(a.dtype))
+    assert params[1][2].shape == (1, 1, 1, 4)              # keep-dims running statistics, as in the shipped files
+    evil = pickle.dumps(os.system)                         # a global that is not an array constructor
+    with pytest.raises(pickle.UnpicklingError):
+        _CheckpointUnpickler(io.BytesIO(evil)).load()

@@ -144,3 +144,16 @@ def attach(model, buckets=2):
     model.grad_hook = None
     model.set_bucket_reducer(BucketReducer(model.flat_grads, plan_buckets(model.flat_layer_ranges, buckets)))
     return world
+
+
+def shutdown(*models):
+    """Ends data-parallel work: releases the models' captured graphs first (a graph that recorded collectives pins
+    the NCCL communicator, and ``destroy_process_group`` then never returns), then destroys the process group."""
+    import gc
+    for m in models:
+        m.release_graphs()
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    if dist.is_initialized():
+        dist.destroy_process_group()

@@ -384,6 +384,16 @@ class Model:
         opt.iterations = saved_it           # capture records work, it does not run it
         return self._graph
 
+    def release_graphs(self):
+        """Drops the captured graphs (and the batch buffers they read).  A graph that recorded collectives keeps the
+        NCCL communicator busy for as long as it exists: destroying the process group while such a graph is alive
+        waits for ever, so data-parallel programs call this (or ``dp.shutdown``) before tearing the group down."""
+        self._graph = self._graph_opt = None
+        self._g_out = None
+        self._graph_metrics = False
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+
     def train_step_graph(self, X, y):
         """One training step by replaying the captured graph on a new batch of the captured shape."""
         if getattr(self, "_graph", None) is None:

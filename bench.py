@@ -666,6 +666,7 @@ def train_block(args, world, rank, local, widen=4, global_batch=4096, fuse=True,
     res = {"train": train}
     if dp_check is not None:
         res["dp_check"] = dp_check
+    model.release_graphs()      # before the process group goes: a graph with recorded collectives pins the communicator
     del model, X, y
     torch.cuda.empty_cache()
     return res

@@ -41,6 +41,10 @@ def build(buckets):
     return m
 
 
+def note(rank, what):
+    print("[dp_gpu_worker rank %d] %s" % (rank, what), file=sys.stderr, flush=True)
+
+
 def rel(a, b):
     return float((a.double() - b.double()).norm() / b.double().norm())
 
@@ -56,9 +60,11 @@ def main():
         batches.append(dp.shard_batch(X, y, rank, world))
 
     bucketed, single = build(2), build(1)
+    single.enable_device_step()                          # Adam's step count on the device in both, as under capture
     assert len(bucketed.bucket_reducer.buckets) == 2 and len(single.bucket_reducer.buckets) == 1
     assert bucketed.bucket_reducer.active
 
+    note(rank, "models built")
     # 1. reduced buffer == all-gathered sum
     held, bucketed._bucket_of_layer = bucketed._bucket_of_layer, {}
     out = bucketed.forward(batches[0][0], training=True)
@@ -72,8 +78,10 @@ def main():
     assert rel(bucketed.flat_grads, want) <= 1e-6
     assert rel(own, want) > 0.05                         # one rank's gradient is not the sum
 
+    note(rank, "reduced buffer checked")
     # 2. one captured graph with the collectives inside == eager steps with one all-reduce
     bucketed.capture_train_step(*batches[0])
+    note(rank, "captured: " + bucketed.capture_note)
     assert "all-reduce bucket" in bucketed.capture_note, bucketed.capture_note
     for X, y in batches:
         bucketed.train_step_graph(X, y)
@@ -81,25 +89,30 @@ def main():
     torch.cuda.synchronize()
     assert rel(bucketed.flat_params, single.flat_params) <= 1e-6, rel(bucketed.flat_params, single.flat_params)
 
+    note(rank, "graph steps == eager steps")
     # 3. identical parameters on all ranks
     mine = bucketed.flat_params.clone()
     theirs = [torch.empty_like(mine) for _ in range(world)]
     dist.all_gather(theirs, mine)
     assert all(torch.equal(t, mine) for t in theirs)
 
+    note(rank, "parameters identical on all ranks")
     # 4. the fallback form (collectives launched eagerly between two graphs) gives the same parameters
     fallback = build(2)
     fallback.capture_train_step(*batches[0], collectives_in_graph=False)
+    note(rank, "captured: " + fallback.capture_note)
     assert fallback.capture_note.startswith("two graphs")
     for X, y in batches:
         fallback.train_step_graph(X, y)
     torch.cuda.synchronize()
     assert rel(fallback.flat_params, single.flat_params) <= 1e-6
 
+    note(rank, "fallback steps == eager steps")
     dist.barrier()
     if rank == 0:
-        print("DP_GPU_OK %d" % world)
-    dist.destroy_process_group()
+        print("DP_GPU_OK %d" % world, flush=True)
+    dp.shutdown(bucketed, single, fallback)              # graphs first, then the process group
+    note(rank, "process group destroyed")
 
 
 if __name__ == "__main__":

@@ -21,6 +21,6 @@ def test_two_gpu_train_step_bucketed_allreduce_in_graph():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", AETHER_DP_TIMEOUT_S="60")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
            "--master-port", "29533", os.path.join(ROOT, "tests", "dp_gpu_worker.py")]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=420)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert "DP_GPU_OK 2" in r.stdout

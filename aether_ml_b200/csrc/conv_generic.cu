@@ -65,6 +65,46 @@ __global__ void __launch_bounds__(256) gen_fwd_kernel(const float* __restrict__ 
     }
 }
 
+// Pointwise layers with very few outputs per pixel (a classifier head: Dense 1024 -> 10 is a 1x1 convolution with
+// Cout = 10): with one thread per output element a batch of 512 rows is 5120 threads walking 1024 channels each.
+// Here a warp takes a row: the lanes split the channels (float4 loads of x, the row is read once), keep Cout partial
+// sums each and combine them with shuffles in a fixed order.
+template <int MAXD>
+__global__ void __launch_bounds__(256) gen_fwd_pointwise_few_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                    const float* __restrict__ b, float* __restrict__ y,
+                                                                    long long rows, int Cin, int Cout) {
+    const int lane = threadIdx.x & 31;
+    const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const int C4 = Cin >> 2;
+    for (long long row = warp0; row < rows; row += nwarps) {
+        float acc[MAXD];
+#pragma unroll
+        for (int d = 0; d < MAXD; ++d) acc[d] = 0.f;
+        const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * Cin);
+        for (int c4 = lane; c4 < C4; c4 += 32) {
+            const float4 v = xr[c4];
+            const float* wr = w + (size_t)(4 * c4) * Cout;
+#pragma unroll
+            for (int d = 0; d < MAXD; ++d) {
+                if (d < Cout)
+                    acc[d] = fmaf(v.x, wr[d], fmaf(v.y, wr[Cout + d], fmaf(v.z, wr[2 * Cout + d], fmaf(v.w, wr[3 * Cout + d], acc[d]))));
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < MAXD; ++d) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], o);
+        }
+        if (lane < Cout) {
+            float r = 0.f;
+#pragma unroll
+            for (int d = 0; d < MAXD; ++d) r = (d == lane) ? acc[d] : r;
+            y[(size_t)row * Cout + lane] = r + (b ? b[lane] : 0.f);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------- dX (gather form)
 // dx[s,h,w,c] = sum over taps (i,j) and d of dy[s,ho,wo,d] * w[i,j,c,d] with ho*sH + i - pH == h.
 __global__ void __launch_bounds__(256) gen_dx_kernel(const float* __restrict__ dy, const float* __restrict__ w,
@@ -225,6 +265,13 @@ int generic_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, co
     conv_out_hw(d, Ho, Wo);
     const long long total = 1LL * d.S * Ho * Wo * d.Cout;
     const int wcount = d.fH * d.fW * d.Cin * d.Cout;
+    if (d.fH == 1 && d.fW == 1 && d.sH == 1 && d.sW == 1 && d.padH == 0 && d.padW == 0 && d.Cout <= 16 && d.Cin >= 128 &&
+        (d.Cin & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+        const long long rows = 1LL * d.S * d.H * d.W;
+        gen_fwd_pointwise_few_kernel<16><<<gen_blocks(rows * 32, 256), 256, 0, st>>>(x, w, b, y, rows, d.Cin, d.Cout);
+        count_launch();
+        return check_launch("gen_fwd_pointwise_few_kernel");
+    }
     if (wcount <= GEN_MAX_W_SMEM) {
         gen_fwd_kernel<true><<<gen_blocks(total, 256), 256, wcount * sizeof(float), st>>>(
             x, w, b, y, d.S, d.H, d.W, d.Cin, d.Cout, d.fH, d.fW, d.sH, d.sW, d.padH, d.padW, Ho, Wo);

@@ -803,27 +803,44 @@ __global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restr
     }
 }
 
-// Filter shadows.  w is (taps, Cin, Cout) fp32.
-//   transpose=1: out[tap][n < Np][k < Kp] = w[tap][k][n]   (forward B operand: K = Cin contiguous)
-//   transpose=0: out[tap][n < Np][k < Kp] = w[tap][n][k]   (dX B operand: rows = Cin, K = Cout contiguous)
+// Filter shadows.  w is (taps, Cin, Cout) fp32; the operand copies are zero padded to Cin_p / Cout_p channels.
+// They are made through 32 x 32 tiles in shared memory, so that both the reads (consecutive n of w's innermost Cout axis)
+// and the writes (consecutive k of the operand's innermost axis) are coalesced; a Dense layer's 8192 x 1024 weight
+// matrix goes through here every step.  Writes, from one read of w:
+//   fwd (nullable): [tap][Np_f = Cout_p][Kp_f = Cin_p]  = w transposed (forward B operand)
+//   dx  (nullable): [tap][Np_d = Cin_p][Kp_d = Cout_p]  = w as it is, padded (dX B operand)
+// grid (ceil(Cout_p/32), ceil(Cin_p/32), taps), block (32, 8).
 template <typename OutT>
-__global__ void filter_shadow_kernel(const float* __restrict__ w, OutT* __restrict__ out, int taps, int Cin, int Cout,
-                                     int Np, int Kp, int transpose) {
-    const long long total = 1LL * taps * Np * Kp;
-    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-         idx += (long long)gridDim.x * blockDim.x) {
-        const int k = (int)(idx % Kp);
-        const long long tn = idx / Kp;
-        const int n = (int)(tn % Np);
-        const int tap = (int)(tn / Np);
-        float v = 0.f;
-        if (transpose) {
-            if (k < Cin && n < Cout) v = w[((size_t)tap * Cin + k) * Cout + n];
-        } else {
-            if (n < Cin && k < Cout) v = w[((size_t)tap * Cin + n) * Cout + k];
-        }
-        out[idx] = static_cast<OutT>(v);
+__global__ void __launch_bounds__(256) filter_shadow_tiled_kernel(const float* __restrict__ w, OutT* __restrict__ fwd,
+                                                                  OutT* __restrict__ dx, int Cin, int Cout, int Cin_p,
+                                                                  int Cout_p) {
+    __shared__ float tile[32][33];
+    const int tap = blockIdx.z;
+    const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;       // n: output channel, k: input channel
+    const float* wt = w + (size_t)tap * Cin * Cout;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int k = k0 + threadIdx.y + 8 * r, n = n0 + threadIdx.x;
+        const float v = (k < Cin && n < Cout) ? wt[(size_t)k * Cout + n] : 0.f;
+        tile[threadIdx.y + 8 * r][threadIdx.x] = v;
+        if (dx != nullptr && k < Cin_p && n < Cout_p) dx[((size_t)tap * Cin_p + k) * Cout_p + n] = static_cast<OutT>(v);
     }
+    if (fwd == nullptr) return;
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int n = n0 + threadIdx.y + 8 * r, k = k0 + threadIdx.x;
+        if (n < Cout_p && k < Cin_p) fwd[((size_t)tap * Cout_p + n) * Cin_p + k] = static_cast<OutT>(tile[threadIdx.x][threadIdx.y + 8 * r]);
+    }
+}
+
+template <typename OutT>
+static int launch_filter_shadows(const float* w, OutT* fwd, OutT* dx, int taps, int Cin, int Cout, int Cin_p, int Cout_p,
+                                 cudaStream_t st) {
+    const dim3 grid((unsigned)ceil_div(Cout_p, 32), (unsigned)ceil_div(Cin_p, 32), (unsigned)taps);
+    filter_shadow_tiled_kernel<OutT><<<grid, dim3(32, 8), 0, st>>>(w, fwd, dx, Cin, Cout, Cin_p, Cout_p);
+    count_launch();
+    return check_launch("filter_shadow_tiled_kernel");
 }
 
 // ====================================================================================== host side
@@ -1048,21 +1065,19 @@ int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const f
     if (ws_bytes < pl.total || !ws) return set_error(AE_BAD_ARG, "conv workspace too small: %zu < %zu", ws_bytes, pl.total);
     uint8_t* wsb = static_cast<uint8_t*>(ws);
     int rc;
-    const int fblocks = 2 * num_sms();
     if (pl.tf32) {
         float* wf = reinterpret_cast<float*>(wsb + pl.off_wf);
-        filter_shadow_kernel<float><<<fblocks, 256, 0, st>>>(w, wf, pl.taps, d.Cin, d.Cout, pl.Cout_p, pl.Cin_p, 1);
-        count_launch();
-        if ((rc = check_launch("filter_shadow_kernel"))) return rc;
+        if ((rc = launch_filter_shadows<float>(w, wf, nullptr, pl.taps, d.Cin, d.Cout, pl.Cin_p, pl.Cout_p, st))) return rc;
         return run_igemm(true, x, d.Cin, d.H, d.W, d.S, wf, pl.Cin_p, pl.Cout_p, pl.taps, y, d.Cout, pl.Ho, pl.Wo,
                          pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, stats, st);
     }
     __nv_bfloat16* xsh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_xsh);
     __nv_bfloat16* wf = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_wf);
     if ((rc = launch_cast(x, xsh, 1LL * d.S * d.H * d.W, d.Cin, pl.Cin_p, nullptr, 0, st))) return rc;
-    filter_shadow_kernel<__nv_bfloat16><<<fblocks, 256, 0, st>>>(w, wf, pl.taps, d.Cin, d.Cout, pl.Cout_p, pl.Cin_p, 1);
-    count_launch();
-    if ((rc = check_launch("filter_shadow_kernel"))) return rc;
+    // both filter operands (forward: transposed, dX: as stored) from one read of w; a backward call that is told
+    // the weights have not changed since (x_shadow_valid bit 1) reuses the second one
+    __nv_bfloat16* wd = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_wd);
+    if ((rc = launch_filter_shadows<__nv_bfloat16>(w, wf, wd, pl.taps, d.Cin, d.Cout, pl.Cin_p, pl.Cout_p, st))) return rc;
     return run_igemm(false, xsh, pl.Cin_p, d.H, d.W, d.S, wf, pl.Cin_p, pl.Cout_p, pl.taps, y, d.Cout, pl.Ho, pl.Wo,
                      pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, stats, st);
 }
@@ -1090,7 +1105,8 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
     float* dbpart = reinterpret_cast<float*>(wsb + pl.off_dbpart);
     const void* x_op = x;
     const void* dy_op = dy;
-    const int fblocks = 2 * num_sms();
+    const bool w_shadow_valid = (x_shadow_valid & 2) != 0;
+    x_shadow_valid &= 1;
 
     // ---- shadows + dB
     if (pl.tf32) {
@@ -1123,10 +1139,9 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
                            pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, nullptr, st);
         } else {
             __nv_bfloat16* wd = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_wd);
-            filter_shadow_kernel<__nv_bfloat16><<<fblocks, 256, 0, st>>>(w, wd, pl.taps, d.Cin, d.Cout, pl.Cin_p,
-                                                                          pl.Cout_p, 0);
-            count_launch();
-            if ((rc = check_launch("filter_shadow_kernel"))) return rc;
+            if (!w_shadow_valid &&
+                (rc = launch_filter_shadows<__nv_bfloat16>(w, nullptr, wd, pl.taps, d.Cin, d.Cout, pl.Cin_p, pl.Cout_p, st)))
+                return rc;
             rc = run_igemm(false, dy_op, pl.Cout_p, pl.Ho, pl.Wo, d.S, wd, pl.Cout_p, pl.Cin_p, pl.taps, dx, d.Cin, d.H,
                            d.W, pl.til_in, pl.Cin_p, d.fH, d.fW, -1, d.padH, d.padW, nullptr, nullptr, st);
         }
@@ -1172,7 +1187,10 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
             return rc;
         if ((rc = make_map_nhwc(&p.tm_dy, dy_op, dt, pl.elt, dyC, pl.Wo, pl.Ho, d.S, pl.KC, til.BW, til.BH, til.BN, swz)))
             return rc;
-        p.part = reinterpret_cast<float*>(wsb + pl.off_part);
+        // One split and no padded channels: the partial buffer's layout [tap*Cin + c][Cout] IS the layout of dW, so
+        // the kernel writes the gradient itself and no reduction pass follows (a Dense layer's 8192 x 1024 matrix).
+        const bool direct = pl.dw_splits == 1 && pl.Cin_p == d.Cin && pl.Cout_p == d.Cout;
+        p.part = direct ? dw : reinterpret_cast<float*>(wsb + pl.off_part);
         p.status = device_status_word();
         p.BW = til.BW; p.BH = til.BH; p.BN = til.BN; p.rows = til.rows;
         p.tiles_w = til.tiles_w; p.tiles_h = til.tiles_h; p.tiles_n = til.tiles_n;
@@ -1183,10 +1201,12 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
         if (pl.tf32) rc = (pl.dw_nb == 2) ? launch_dw<true, 2>(p, pl.dw_splits, gy, st) : launch_dw<true, 1>(p, pl.dw_splits, gy, st);
         else rc = (pl.dw_nb == 2) ? launch_dw<false, 2>(p, pl.dw_splits, gy, st) : launch_dw<false, 1>(p, pl.dw_splits, gy, st);
         if (rc) return rc;
-        dw_reduce_kernel<<<dw_reduce_grid(pl.taps, d.Cin, d.Cout), 256, 0, st>>>(p.part, dw, pl.dw_splits, pl.dw_U, pl.KC, pl.Cout_p,
-                                                        pl.dw_cblocks, pl.taps, d.Cin, d.Cout, pl.taps, pl.dw_splits);
-        count_launch();
-        if ((rc = check_launch("dw_reduce_kernel"))) return rc;
+        if (!direct) {
+            dw_reduce_kernel<<<dw_reduce_grid(pl.taps, d.Cin, d.Cout), 256, 0, st>>>(p.part, dw, pl.dw_splits, pl.dw_U, pl.KC, pl.Cout_p,
+                                                            pl.dw_cblocks, pl.taps, d.Cin, d.Cout, pl.taps, pl.dw_splits);
+            count_launch();
+            if ((rc = check_launch("dw_reduce_kernel"))) return rc;
+        }
     }
     return AE_OK;
 }

@@ -67,6 +67,33 @@ class _Workspace:
         return self.buf
 
 
+class _OperandCopies:
+    """Remembers which arrays the forward pass left bf16 operand copies of in a layer's workspace, so that the
+    backward pass reuses a copy only while it still describes the array: same workspace buffer, same array, and
+    no in-place change since (torch's per-tensor version counter).  Anything else -- a regrown workspace, an input
+    modified between the passes, weights replaced -- makes the backward pass rebuild the copy."""
+
+    def __init__(self):
+        self.ws_ptr = None
+        self.x = None
+        self.w = None
+
+    @staticmethod
+    def _tag(t):
+        return (t.data_ptr(), t._version, tuple(t.shape))
+
+    def record(self, ws, x, w):
+        self.ws_ptr = ws.data_ptr()
+        self.x = self._tag(x)
+        self.w = self._tag(w)
+
+    def flags(self, ws, x, w):
+        """Bit 0: the copy of x is valid; bit 1: the copies of the weights are (aether_conv2d_bwd's x_shadow_valid)."""
+        if self.ws_ptr is None or ws.data_ptr() != self.ws_ptr:
+            return 0
+        return (1 if self._tag(x) == self.x else 0) | (2 if self._tag(w) == self.w else 0)
+
+
 # ------------------------------------------------------------------------------------- Conv_Layer
 class Conv_Layer:
     """Drop-in for ``Conv_Layer`` (CNN_classes_cupy.py:37-161).
@@ -104,7 +131,7 @@ class Conv_Layer:
         self.emit_bn_stats = False      # set when a Batch_Norm consumes this layer's output (Model.finalize does it)
         self.bn_partials = None         # (buffer, blocks, data_ptr of the output they describe) after a training forward
         self._desc = None
-        self._fwd_input_ptr = None
+        self._copies = _OperandCopies()
 
     # `weights` is the same array object as `filter_weights` (:68); in-place optimizer updates on
     # either name are visible through both.
@@ -154,7 +181,7 @@ class Conv_Layer:
         self.inputs = x
         self.output = y
         self._desc = d
-        self._fwd_input_ptr = x.data_ptr()
+        self._copies.record(ws, x, self.filter_weights)
         return self.output
 
     def backward(self, dvalues, need_dinputs=True):
@@ -175,7 +202,7 @@ class Conv_Layer:
             self.dweights = _empty(tuple(self.filter_weights.shape))
             self.dbiases = _empty((d.Cout,))
         dx = _empty((d.S, d.H, d.W, d.Cin)) if need_dinputs else None
-        shadow_ok = 1 if self._fwd_input_ptr == x.data_ptr() else 0
+        shadow_ok = self._copies.flags(ws, x, self.filter_weights)
         check(L.aether_conv2d_bwd(C.byref(d), _ptr(x), _ptr(dy), _ptr(self.filter_weights), _ptr(dx),
                                   _ptr(self.dweights), _ptr(self.dbiases), _ptr(ws), ws.numel(), shadow_ok,
                                   _stream()), "aether_conv2d_bwd")
@@ -625,6 +652,7 @@ class Layer_Dense:
         self.bias_regularizer_l2 = bias_regularizer_l2
         self.math_mode = math_mode or DEFAULT_MATH_MODE
         self._ws = _Workspace()
+        self._copies = _OperandCopies()
 
     def _desc(self, S):
         n_in, n_out = self.weights.shape
@@ -642,6 +670,7 @@ class Layer_Dense:
                                   ws.numel(), _stream()), "aether_conv2d_fwd")
         self.inputs = x
         self.output = y
+        self._copies.record(ws, x, self.weights)
         return self.output
 
     def backward(self, dvalues):
@@ -657,7 +686,8 @@ class Layer_Dense:
             self.dbiases = torch.empty_like(self.biases)
         dx = torch.empty_like(x)
         check(L.aether_conv2d_bwd(C.byref(d), _ptr(x), _ptr(dy), _ptr(self.weights), _ptr(dx), _ptr(self.dweights),
-                                  _ptr(self.dbiases), _ptr(ws), ws.numel(), 1, _stream()), "aether_conv2d_bwd")
+                                  _ptr(self.dbiases), _ptr(ws), ws.numel(), self._copies.flags(ws, x, self.weights),
+                                  _stream()), "aether_conv2d_bwd")
         if self.weight_regularizer_l1 > 0 or self.weight_regularizer_l2 > 0:
             check(L.aether_regularizer_grad(_ptr(self.weights), _ptr(self.dweights), self.weights.numel(),
                                             float(self.weight_regularizer_l1), float(self.weight_regularizer_l2),

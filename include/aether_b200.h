@@ -103,8 +103,10 @@ int aether_conv2d_fwd_bnstats(const AetherConvDesc* desc, const float* x, const 
 
 /* Conv_Layer.backward, CNN_classes_cupy.py:123-154: db = sum dy (:132), dw = windows^T dy (:134),
  * dx = scatter-add of dy w^T (:138-146) with the padding border removed (:149-153; returned
- * contiguous).  Any of dx, dw, db may be NULL to skip it.  x_shadow_valid != 0 tells the library that
- * `ws` still holds the operand copy of the same x made by aether_conv2d_fwd (saves one pass). */
+ * contiguous).  Any of dx, dw, db may be NULL to skip it.  x_shadow_valid is a bit mask about the operand copies
+ * that the last aether_conv2d_fwd / aether_conv2d_fwd_bnstats call with this `ws` left in it: bit 0 = the copy of x
+ * is still the copy of this x (saves one pass over x), bit 1 = w has not changed since, so the copy of the filter
+ * that dX multiplies by is reused (saves one pass over w).  0 is always safe: everything is rebuilt. */
 int aether_conv2d_bwd(const AetherConvDesc* desc, const float* x, const float* dy, const float* w, float* dx, float* dw,
                       float* db, void* ws, size_t ws_bytes, int x_shadow_valid, void* stream);
 

@@ -254,3 +254,33 @@ def test_edge_cases_and_errors(env):
     x = np.ones((1, 1, 1, 64), np.float32)
     y = one.forward(x, True).cpu().numpy()
     assert O.rel_l2(y, O.conv_forward(x, one.filter_weights.cpu().numpy(), np.zeros(64))) <= 1e-2
+
+
+def test_operand_copies_are_rebuilt_when_their_source_changes(env):
+    """The backward pass reuses the bf16 copies of x and of the filter that the forward pass left in the workspace
+    only while they still describe the arrays: after an in-place change of the weights (dX must use the NEW
+    weights, as the reference's backward reads filter_weights when it runs, CNN_classes_cupy.py:138) or of the
+    stored input (dW must use the new values) the copies are rebuilt; untouched arrays take the short path."""
+    torch, _lib, layers = env
+    rng = np.random.default_rng(8)
+    S, H, W, Cin, Cout = 3, 12, 12, 64, 64
+    x = rng.standard_normal((S, H, W, Cin)).astype(np.float32)
+    dy = rng.standard_normal((S, H, W, Cout)).astype(np.float32)
+    np.random.seed(3)
+    layer = layers.Conv_Layer((H, W, Cin), Cout, (3, 3), (1, 1), "same", math_mode="bf16")
+    xt = torch.from_numpy(x).cuda()
+    layer.forward(xt, True)
+    n0 = _lib.launch_count()
+    layer.backward(dy)
+    short = _lib.launch_count() - n0                          # nothing changed: both copies reused
+    layer.forward(xt, True)
+    layer.filter_weights.mul_(-0.5)                           # in-place change between the passes
+    xt.add_(1.0)
+    n0 = _lib.launch_count()
+    dx = layer.backward(dy)
+    assert _lib.launch_count() - n0 == short + 2              # one more cast pass (x) and one more filter pass
+    torch.cuda.synchronize()
+    w_new = layer.filter_weights.cpu().numpy()
+    dxo, dwo, dbo = O.conv_backward_blas(x + 1.0, w_new, dy, dtype=np.float64)
+    assert O.rel_l2(dx.cpu().numpy(), dxo) <= TOL["bf16"]
+    assert O.rel_l2(layer.dweights.cpu().numpy(), dwo) <= TOL["bf16"]

@@ -323,6 +323,28 @@ def test_dense_tensor_core(env, mode, tol):
     assert O.rel_l2(host(dense.dbiases), dbo) <= 1e-5 and dense.dbiases.shape == (1, 256)
 
 
+@pytest.mark.parametrize("shape", [(512, 1024, 10), (37, 132, 7), (5, 256, 12), (64, 8192, 3)])
+def test_dense_classifier_head(env, shape):
+    """Dense layers with very few outputs (the 10-class head of the reference's networks) run a warp-per-row forward
+    on the CUDA cores in every math mode: fp32 results against the oracle."""
+    torch, _lib, layers = env
+    rows, n_in, n_out = shape
+    rng = np.random.default_rng(rows)
+    x = rng.standard_normal((rows, n_in)).astype(np.float32)
+    dy = rng.standard_normal((rows, n_out)).astype(np.float32)
+    np.random.seed(1)
+    dense = layers.Layer_Dense(n_in, n_out, math_mode="bf16")
+    dense.weights.copy_(torch.from_numpy(rng.standard_normal((n_in, n_out)).astype(np.float32) * 0.1))
+    dense.biases.copy_(torch.from_numpy(rng.standard_normal((1, n_out)).astype(np.float32)))
+    w, b = host(dense.weights), host(dense.biases)
+    y = dense.forward(x, True)
+    dx = dense.backward(dy)
+    assert O.rel_l2(host(y), O.dense_forward(x, w, b)) <= 1e-5
+    dxo, dwo, dbo = O.dense_backward(x, w, b, dy)
+    assert O.rel_l2(host(dx), dxo) <= 1e-5 and O.rel_l2(host(dense.dweights), dwo) <= 1e-5
+    assert O.rel_l2(host(dense.dbiases), dbo) <= 1e-5
+
+
 def test_regularization_loss(env):
     torch, _lib, layers = env
     np.random.seed(1)

@@ -15,6 +15,7 @@
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "stats_epilogue.cuh"
 #include "tc_host.cuh"
 
 namespace aether {
@@ -36,7 +37,7 @@ static constexpr int FT_EPI_WARPS = 8;
 static constexpr int FT_THREADS = 32 * (FT_PROD_WARPS + 1 + FT_EPI_WARPS);   // producers, MMA issuer, epilogue
 static constexpr int FT_STAGE_BYTES = 128 * 128;                             // 128 pixel rows of 128 bytes
 static constexpr int FT_TAIL = 2048;                                         // barriers, TMEM pointer, bias, k tables
-static constexpr int FT_STATS_BYTES = FT_EPI_WARPS * 2 * 128 * 4;
+static constexpr int FT_STATS_BYTES = FT_EPI_WARPS * STATS_WARP_FLOATS * 4;
 
 __device__ __forceinline__ void ft_umma(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
                                         uint32_t accumulate) {
@@ -201,10 +202,10 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
         const int trow = lane >> 2, tcol4 = (lane & 3) * 4;
         const bool lo2 = (lane & 2) == 0, odd = (lane & 1) != 0;
         const bool all_cols = (p.Cout == NT);
-        float* stat_w = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + FT_TAIL) + ew * 256;
+        float* stat_w = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + FT_TAIL) + ew * STATS_WARP_FLOATS;
         float st_rows = 0.f;
         if (STATS) {
-            for (int i = lane; i < 256; i += 32) stat_w[i] = 0.f;
+            for (int i = lane; i < STATS_WARP_FLOATS; i += 32) stat_w[i] = 0.f;
             __syncwarp();
         }
         int row_in_tile[4];
@@ -219,7 +220,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
 #pragma unroll
         for (int u = 0; u < 4; ++u) st_s[u] = st_q[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         // adds the lanes with equal lane%4 (same 4 columns, 8 row groups) and accumulates into the warp's sums
-        auto flush_stats = [&](int cb) {
+        // (about the columns' pivots, see stats_epilogue.cuh; `first`: the sums are the warp's first tile, taken
+        // without pivots, which are set from them)
+        auto flush_stats = [&](int cb, bool first, float rows) {
 #pragma unroll
             for (int m = 4; m <= 16; m <<= 1) {
 #pragma unroll
@@ -234,17 +237,10 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int cc = cb + u * 16;
-                    if (cc < ncols) {
-                        float4* ps = reinterpret_cast<float4*>(stat_w + cc + tcol4);
-                        float4* pq = reinterpret_cast<float4*>(stat_w + 128 + cc + tcol4);
-                        float4 s = *ps, qq = *pq;
-                        s.x += st_s[u].x; s.y += st_s[u].y; s.z += st_s[u].z; s.w += st_s[u].w;
-                        qq.x += st_q[u].x; qq.y += st_q[u].y; qq.z += st_q[u].z; qq.w += st_q[u].w;
-                        *ps = s;
-                        *pq = qq;
-                    }
+                    if (cc < ncols) stats_fold(stat_w, cc + tcol4, st_s[u], st_q[u], first, rows);
                 }
             }
+            if (first) __syncwarp();               // the pivots must be visible to the whole warp before its next tile
         };
         uint32_t buf = 0, aph = 0;
         bool ok = true;
@@ -255,6 +251,15 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
                 const long long pix = (long long)t * 128 + row_in_tile[j];
                 rowp[j] = pix < p.P ? p.y + (size_t)pix * p.Cout + col_begin + tcol4 : nullptr;
             }
+            float tile_rows = 0.f;                 // valid rows of this tile in this warp's quarter
+            if (STATS) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) tile_rows += (rowp[j] != nullptr) ? 1.f : 0.f;
+                tile_rows += __shfl_xor_sync(0xffffffffu, tile_rows, 4);
+                tile_rows += __shfl_xor_sync(0xffffffffu, tile_rows, 8);
+                tile_rows += __shfl_xor_sync(0xffffffffu, tile_rows, 16);
+            }
+            const bool first_stats = STATS && st_rows == 0.f && tile_rows > 0.f;      // the tile that sets the pivots
             if (!mbar_wait(tfull_bar(buf), aph, p.status, DS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NT + col_begin;
@@ -290,6 +295,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
                             const int g = hb * 2 + u;             // 16-column group within the 64-column batch
                             const float4 b4 = *reinterpret_cast<const float4*>(bias4 + cc);
                             const bool cols_ok = all_cols || col_begin + tcol4 + cc < p.Cout;
+                            float4 pv = make_float4(0.f, 0.f, 0.f, 0.f);  // pivot of this lane's four columns
+                            if (STATS) pv = *reinterpret_cast<const float4*>(stat_w + 256 + cc + tcol4);
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 // quad exchange: 2+2 columns per lane -> 4 consecutive columns per lane (64-byte row segments)
@@ -311,7 +318,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
                                     __stcs(reinterpret_cast<float4*>(rowp[j] + cc),
                                            make_float4(a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w));
                                 if (STATS) {
-                                    a.x = wr ? a.x : 0.f; a.y = wr ? a.y : 0.f; a.z = wr ? a.z : 0.f; a.w = wr ? a.w : 0.f;
+                                    a.x = wr ? a.x - pv.x : 0.f; a.y = wr ? a.y - pv.y : 0.f;
+                                    a.z = wr ? a.z - pv.z : 0.f; a.w = wr ? a.w - pv.w : 0.f;
                                     st_s[g].x += a.x; st_s[g].y += a.y; st_s[g].z += a.z; st_s[g].w += a.w;
                                     st_q[g].x = fmaf(a.x, a.x, st_q[g].x); st_q[g].y = fmaf(a.y, a.y, st_q[g].y);
                                     st_q[g].z = fmaf(a.z, a.z, st_q[g].z); st_q[g].w = fmaf(a.w, a.w, st_q[g].w);
@@ -321,34 +329,33 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
                     }
                 }
                 if (STATS) {
-                    if (cb0 == 0) {
-                        float nrows = 0.f;
+                    // the first tile is always folded at once (it sets the pivots); with running per-thread sums the
+                    // other tiles are folded together after the last one
+                    if (!persist || first_stats) {
+                        flush_stats(cb0, first_stats, tile_rows);
+                        if (persist) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) nrows += (rowp[j] != nullptr) ? 1.f : 0.f;
-                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 4);
-                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 8);
-                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 16);
-                        st_rows += nrows;
+                            for (int u = 0; u < 4; ++u) st_s[u] = st_q[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
                     }
-                    if (!persist) flush_stats(cb0);
                 }
             }
+            st_rows += tile_rows;
             if (++buf == NB) { buf = 0; aph ^= 1u; }
         }
-        if (STATS && persist) flush_stats(0);
+        if (STATS && persist) flush_stats(0, false, 0.f);
         if (STATS && lane < 4) {
             float* sp = p.stats + ((size_t)blockIdx.x * 4 + q) * 3 * (size_t)p.Cout;
-            const float inv_n = st_rows > 0.f ? 1.f / st_rows : 0.f;
             for (int cc = 0; cc < ncols; cc += 16) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int col = col_begin + tcol4 + cc + k;
                     if (col < p.Cout) {
-                        const float s = stat_w[cc + tcol4 + k], qq = stat_w[128 + cc + tcol4 + k];
-                        const float m = s * inv_n;
+                        float m, m2;
+                        stats_result(stat_w, cc + tcol4 + k, st_rows, m, m2);
                         sp[col] = st_rows;
                         sp[p.Cout + col] = m + bias_s[col];
-                        sp[2 * p.Cout + col] = fmaxf(qq - s * m, 0.f);
+                        sp[2 * p.Cout + col] = m2;
                     }
                 }
             }

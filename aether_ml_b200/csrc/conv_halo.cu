@@ -27,6 +27,7 @@
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "stats_epilogue.cuh"
 #include "tc_host.cuh"
 
 namespace aether {
@@ -56,7 +57,7 @@ static constexpr int HALO_EPI_PARTS = HALO_EPI_WARPS / 4;
 static constexpr int HALO_EPI_UB = 8 / HALO_EPI_PARTS;            // 16-column TMEM loads in flight per batch
 static constexpr int HALO_THREADS = 64 + 32 * HALO_EPI_WARPS;
 static constexpr int HALO_TAIL = 2048;          // barriers, TMEM pointer, bias
-static constexpr int HALO_STATS_BYTES = HALO_EPI_WARPS * 2 * 128 * 4;   // per-warp running column sums (statistics)
+static constexpr int HALO_STATS_BYTES = HALO_EPI_WARPS * STATS_WARP_FLOATS * 4;   // per-warp running column sums and pivots
 
 // MMA with descriptors given as (low word, shared high word); K-major 128-byte-swizzle operands.
 template <bool TF32>
@@ -230,11 +231,11 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
         const bool lo2 = (lane & 2) == 0, odd = (lane & 1) != 0;
         const bool all_cols = (p.n_out == NT);     // no padded output channels: no per-column bound checks
         constexpr bool do_stats = STATS;
-        // running per-column sums of this warp over all its tiles: [2][128] floats of warp-private shared memory
-        float* stat_w = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + HALO_TAIL) + ew * 256;
+        // running per-column sums of this warp over all its tiles (stats_epilogue.cuh): warp-private shared memory
+        float* stat_w = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + HALO_TAIL) + ew * STATS_WARP_FLOATS;
         float st_rows = 0.f;                       // rows (pixels) summed so far, identical in every lane
         if (do_stats) {
-            for (int i = lane; i < 256; i += 32) stat_w[i] = 0.f;
+            for (int i = lane; i < STATS_WARP_FLOATS; i += 32) stat_w[i] = 0.f;
             __syncwarp();
         }
         // The four accumulator rows this thread holds map to fixed pixels of every strip: precompute their
@@ -260,6 +261,15 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
             float* rowp[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) rowp[j] = (row_hl[j] < rows_left) ? tile_base + row_off[j] : nullptr;
+            float tile_rows = 0.f;                 // valid rows of this tile in this warp's quarter
+            if (do_stats) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) tile_rows += (rowp[j] != nullptr) ? 1.f : 0.f;
+                tile_rows += __shfl_xor_sync(0xffffffffu, tile_rows, 4);
+                tile_rows += __shfl_xor_sync(0xffffffffu, tile_rows, 8);
+                tile_rows += __shfl_xor_sync(0xffffffffu, tile_rows, 16);
+            }
+            const bool first_stats = do_stats && st_rows == 0.f && tile_rows > 0.f;   // the tile that sets the pivots
             if (!mbar_wait(tfull_bar(buf), aph, p.status, DS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NT + col_begin;
@@ -292,6 +302,8 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                         const int cc = cb + u * 16;              // column relative to this thread's first column
                         const float4 b4 = *reinterpret_cast<const float4*>(bias4 + cc);
                         const bool cols_ok = all_cols || col_begin + tcol4 + cc < p.n_out;
+                        float4 pv = make_float4(0.f, 0.f, 0.f, 0.f);      // pivot of this lane's four columns
+                        if (do_stats) pv = *reinterpret_cast<const float4*>(stat_w + 256 + cc + tcol4);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const uint32_t a0 = v[j >> 1][u][(j & 1) * 2 + 0], a1 = v[j >> 1][u][(j & 1) * 2 + 1];
@@ -314,8 +326,8 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                                 __stcs(reinterpret_cast<float4*>(rowp[j] + cc),
                                        make_float4(a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w));
                             if (do_stats) {                                  // branch-free: by-product rows count as zero
-                                a.x = wr ? a.x : 0.f; a.y = wr ? a.y : 0.f;  // selects, not products: a by-product may be NaN
-                                a.z = wr ? a.z : 0.f; a.w = wr ? a.w : 0.f;
+                                a.x = wr ? a.x - pv.x : 0.f; a.y = wr ? a.y - pv.y : 0.f;  // selects, not products: a by-product may be NaN
+                                a.z = wr ? a.z - pv.z : 0.f; a.w = wr ? a.w - pv.w : 0.f;
                                 st_s[u].x += a.x; st_s[u].y += a.y; st_s[u].z += a.z; st_s[u].w += a.w;
                                 st_q[u].x = fmaf(a.x, a.x, st_q[u].x); st_q[u].y = fmaf(a.y, a.y, st_q[u].y);
                                 st_q[u].z = fmaf(a.z, a.z, st_q[u].z); st_q[u].w = fmaf(a.w, a.w, st_q[u].w);
@@ -326,16 +338,7 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                 if (do_stats) {
                     // Lanes with equal lane%4 hold the same 4 columns of 8 different row groups: add them up
                     // (xor 4, 8, 16); lanes 0..3 then add the tile's sums to this warp's running sums in
-                    // shared memory.  The sums are taken about the bias (the channel's expected offset).
-                    if (cb == 0) {
-                        float nrows = 0.f;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) nrows += (rowp[j] != nullptr) ? 1.f : 0.f;
-                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 4);
-                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 8);
-                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 16);
-                        st_rows += nrows;
-                    }
+                    // shared memory (about the column's pivot, see stats_epilogue.cuh).
 #pragma unroll
                     for (int m = 4; m <= 16; m <<= 1) {
 #pragma unroll
@@ -350,35 +353,28 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
 #pragma unroll
                         for (int u = 0; u < HALO_EPI_UB; ++u) {
                             const int cc = cb + u * 16;
-                            if (cc < ncols) {
-                                float4* ps = reinterpret_cast<float4*>(stat_w + cc + tcol4);
-                                float4* pq = reinterpret_cast<float4*>(stat_w + 128 + cc + tcol4);
-                                float4 s = *ps, qq = *pq;
-                                s.x += st_s[u].x; s.y += st_s[u].y; s.z += st_s[u].z; s.w += st_s[u].w;
-                                qq.x += st_q[u].x; qq.y += st_q[u].y; qq.z += st_q[u].z; qq.w += st_q[u].w;
-                                *ps = s;
-                                *pq = qq;
-                            }
+                            if (cc < ncols) stats_fold(stat_w, cc + tcol4, st_s[u], st_q[u], first_stats, tile_rows);
                         }
                     }
+                    if (first_stats) __syncwarp();     // the pivots must be visible to the whole warp before its next tile
                 }
             }
+            st_rows += tile_rows;
             if (++buf == NB) { buf = 0; aph ^= 1u; }
         }
         if (do_stats && lane < 4) {
             // (count, mean, M2) of this warp's rows over all tiles of the CTA: block blockIdx.x*4 + q of [3][n_out]
             float* sp = p.stats + ((size_t)blockIdx.x * 4 + q) * 3 * (size_t)p.n_out;
-            const float inv_n = st_rows > 0.f ? 1.f / st_rows : 0.f;
             for (int cc = 0; cc < ncols; cc += 16) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int col = col_begin + tcol4 + cc + k;
                     if (col < p.n_out) {
-                        const float s = stat_w[cc + tcol4 + k], qq = stat_w[128 + cc + tcol4 + k];
-                        const float m = s * inv_n;
+                        float m, m2;
+                        stats_result(stat_w, cc + tcol4 + k, st_rows, m, m2);
                         sp[col] = st_rows;
                         sp[p.n_out + col] = m + bias_s[col];
-                        sp[2 * p.n_out + col] = fmaxf(qq - s * m, 0.f);
+                        sp[2 * p.n_out + col] = m2;
                     }
                 }
             }

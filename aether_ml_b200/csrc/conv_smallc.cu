@@ -85,7 +85,9 @@ __global__ void __launch_bounds__(SC_THREADS) smallc_fwd_kernel(const SmallcGeom
     __shared__ __align__(16) float red_s[SC_THREADS * 4];    // statistics, used once at the end of the kernel
     __shared__ __align__(16) float red_q[SC_THREADS * 4];
     __shared__ float red_n[SC_THREADS];
-    float4 st_s = make_float4(0.f, 0.f, 0.f, 0.f), st_q = st_s;   // sum / sum of squares of (y - bias), this thread's pixels
+    // Statistics of this thread's pixels: count, sum and sum of squares of (y - pivot).  The pivot is the thread's
+    // first output value, so the sums stay small whatever the channel's mean is (no cancellation when |mean| >> std).
+    float4 st_s = make_float4(0.f, 0.f, 0.f, 0.f), st_q = st_s, st_p = st_s;
     float st_n = 0.f;
     float* wsm = sm;                          // [K][Cout]
     float* colT = sm + g.K * g.Cout;          // [K][TP]
@@ -121,8 +123,9 @@ __global__ void __launch_bounds__(SC_THREADS) smallc_fwd_kernel(const SmallcGeom
                 if (p < g.P) {
                     __stcs(reinterpret_cast<float4*>(y + (size_t)p * g.Cout + cg * 4), acc[r][q]);
                     if (stats) {
-                        const float dx = acc[r][q].x - bias.x, dy = acc[r][q].y - bias.y;
-                        const float dz = acc[r][q].z - bias.z, dw = acc[r][q].w - bias.w;
+                        if (st_n == 0.f) st_p = acc[r][q];
+                        const float dx = acc[r][q].x - st_p.x, dy = acc[r][q].y - st_p.y;
+                        const float dz = acc[r][q].z - st_p.z, dw = acc[r][q].w - st_p.w;
                         st_s.x += dx; st_s.y += dy; st_s.z += dz; st_s.w += dw;
                         st_q.x = fmaf(dx, dx, st_q.x); st_q.y = fmaf(dy, dy, st_q.y);
                         st_q.z = fmaf(dz, dz, st_q.z); st_q.w = fmaf(dw, dw, st_q.w);
@@ -133,26 +136,34 @@ __global__ void __launch_bounds__(SC_THREADS) smallc_fwd_kernel(const SmallcGeom
         __syncthreads();                      // colT is rewritten by the next tile's gather
     }
     if (stats) {
-        // One (count, mean, M2) triple per channel and CTA: the pixel lanes are added in fixed order.  Sums are
-        // taken about the bias, the expected offset of the channel, to keep sum-of-squares cancellation small.
-        reinterpret_cast<float4*>(red_s)[threadIdx.x] = st_s;
-        reinterpret_cast<float4*>(red_q)[threadIdx.x] = st_q;
+        // One (count, mean, M2) triple per channel and CTA: every thread turns its pivoted sums into (n, mean, M2),
+        // and the pixel lanes are merged in fixed order with Chan's formula.
+        const float inv = st_n > 0.f ? 1.f / st_n : 0.f;
+        float4 mean, m2;
+        mean.x = st_p.x + st_s.x * inv; m2.x = st_q.x - st_s.x * st_s.x * inv;
+        mean.y = st_p.y + st_s.y * inv; m2.y = st_q.y - st_s.y * st_s.y * inv;
+        mean.z = st_p.z + st_s.z * inv; m2.z = st_q.z - st_s.z * st_s.z * inv;
+        mean.w = st_p.w + st_s.w * inv; m2.w = st_q.w - st_s.w * st_s.w * inv;
+        reinterpret_cast<float4*>(red_s)[threadIdx.x] = mean;
+        reinterpret_cast<float4*>(red_q)[threadIdx.x] = m2;
         red_n[threadIdx.x] = st_n;
         __syncthreads();
         if (threadIdx.x < g.Cout) {
             const int c = threadIdx.x, cgi = c >> 2, k = c & 3;
-            float n = 0.f, s = 0.f, q = 0.f;
+            float N = 0.f, M = 0.f, M2 = 0.f;
             for (int l = 0; l < g.lanes; ++l) {
                 const int t = (l << g.cg_shift) + cgi;
-                n += red_n[t];
-                s += red_s[t * 4 + k];
-                q += red_q[t * 4 + k];
+                const float nl = red_n[t];
+                if (nl == 0.f) continue;
+                const float tot = N + nl, delta = red_s[t * 4 + k] - M;
+                M2 += red_q[t * 4 + k] + delta * delta * N * nl / tot;
+                M += delta * nl / tot;
+                N = tot;
             }
-            const float m = n > 0.f ? s / n : 0.f;
             float* out = stats + (size_t)blockIdx.x * 3 * g.Cout;
-            out[c] = n;
-            out[g.Cout + c] = m + (b ? b[c] : 0.f);
-            out[2 * g.Cout + c] = fmaxf(q - s * m, 0.f);
+            out[c] = N;
+            out[g.Cout + c] = M;
+            out[2 * g.Cout + c] = fmaxf(M2, 0.f);
         }
     }
 }

@@ -19,6 +19,7 @@
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "stats_epilogue.cuh"
 #include "tc_host.cuh"
 
 namespace aether {
@@ -124,7 +125,7 @@ static constexpr int IGEMM_EPI_WARPS = 8;       // 4 TMEM lane quarters x 2 colu
 static constexpr int IGEMM_EPI_UB = 4;          // 16-column TMEM loads in flight per batch
 static constexpr int IGEMM_THREADS = 64 + 32 * IGEMM_EPI_WARPS;   // warp 0 TMA producer, warp 1 MMA issuer, then epilogue
 static constexpr int IGEMM_TAIL = 1024;         // barriers, TMEM pointer
-static constexpr int IGEMM_STATS_BYTES = IGEMM_EPI_WARPS * 2 * 128 * 4;   // per-warp running column sums
+static constexpr int IGEMM_STATS_BYTES = IGEMM_EPI_WARPS * STATS_WARP_FLOATS * 4;   // per-warp running column sums and pivots
 
 template <int NT>
 struct IgemmCfg {
@@ -257,11 +258,11 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
         const int col_begin = part * ncols;
         const int trow = lane >> 2, tcol4 = (lane & 3) * 4;
         const bool lo2 = (lane & 2) == 0, odd = (lane & 1) != 0;
-        // statistics: running per-column sums of this warp over all its tiles, [2][128] floats of its own
-        float* stat_w = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + IGEMM_TAIL) + ew * 256;
+        // statistics: running per-column sums of this warp over all its tiles (stats_epilogue.cuh), memory of its own
+        float* stat_w = reinterpret_cast<float*>(gen_base + (sBar - smem_base) + IGEMM_TAIL) + ew * STATS_WARP_FLOATS;
         float st_rows = 0.f;                       // rows (pixels) summed so far, identical in every lane
         if (STATS) {
-            for (int i = lane; i < 256; i += 32) stat_w[i] = 0.f;
+            for (int i = lane; i < STATS_WARP_FLOATS; i += 32) stat_w[i] = 0.f;
             __syncwarp();
         }
         // The four accumulator rows this thread holds are fixed pixels of the (BW, BH, BN) box.
@@ -292,6 +293,15 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
                               ? p.out + (((size_t)n * p.out_H + h) * p.out_W + w) * p.n_out + col0
                               : nullptr;
             }
+            float tile_rows = 0.f;                 // valid rows of this tile in this warp's quarter
+            if (STATS) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) tile_rows += (rowp[j] != nullptr) ? 1.f : 0.f;
+                tile_rows += __shfl_xor_sync(0xffffffffu, tile_rows, 4);
+                tile_rows += __shfl_xor_sync(0xffffffffu, tile_rows, 8);
+                tile_rows += __shfl_xor_sync(0xffffffffu, tile_rows, 16);
+            }
+            const bool first_stats = STATS && st_rows == 0.f && tile_rows > 0.f;      // the tile that sets the pivots
             const uint32_t buf = lt & 1u;
             const uint32_t aph = (lt >> 1) & 1u;
             if (!mbar_wait(tfull_bar(buf), aph, p.status, DS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
@@ -326,6 +336,8 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
                             b4.x = __ldg(p.bias + col0 + cc + 0); b4.y = __ldg(p.bias + col0 + cc + 1);
                             b4.z = __ldg(p.bias + col0 + cc + 2); b4.w = __ldg(p.bias + col0 + cc + 3);
                         }
+                        float4 pv = make_float4(0.f, 0.f, 0.f, 0.f);      // pivot of this lane's four columns
+                        if (STATS) pv = *reinterpret_cast<const float4*>(stat_w + 256 + cc + tcol4);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const uint32_t a0 = v[j >> 1][u][(j & 1) * 2 + 0], a1 = v[j >> 1][u][(j & 1) * 2 + 1];
@@ -348,8 +360,8 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
                                 __stcs(reinterpret_cast<float4*>(rowp[j] + cc),
                                        make_float4(a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w));
                             if (STATS) {                                     // selects, not products: a by-product may be NaN
-                                a.x = wr ? a.x : 0.f; a.y = wr ? a.y : 0.f;
-                                a.z = wr ? a.z : 0.f; a.w = wr ? a.w : 0.f;
+                                a.x = wr ? a.x - pv.x : 0.f; a.y = wr ? a.y - pv.y : 0.f;
+                                a.z = wr ? a.z - pv.z : 0.f; a.w = wr ? a.w - pv.w : 0.f;
                                 st_s[u].x += a.x; st_s[u].y += a.y; st_s[u].z += a.z; st_s[u].w += a.w;
                                 st_q[u].x = fmaf(a.x, a.x, st_q[u].x); st_q[u].y = fmaf(a.y, a.y, st_q[u].y);
                                 st_q[u].z = fmaf(a.z, a.z, st_q[u].z); st_q[u].w = fmaf(a.w, a.w, st_q[u].w);
@@ -360,16 +372,7 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
                 if (STATS) {
                     // Lanes with equal lane%4 hold the same 4 columns of 8 different row groups: add them up
                     // (xor 4, 8, 16); lanes 0..3 then add the tile's sums to this warp's running sums in shared
-                    // memory.  The sums are taken about the bias (the channel's expected offset).
-                    if (cb == 0) {
-                        float nrows = 0.f;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) nrows += (rowp[j] != nullptr) ? 1.f : 0.f;
-                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 4);
-                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 8);
-                        nrows += __shfl_xor_sync(0xffffffffu, nrows, 16);
-                        st_rows += nrows;
-                    }
+                    // memory (about the column's pivot, see stats_epilogue.cuh).
 #pragma unroll
                     for (int m = 4; m <= 16; m <<= 1) {
 #pragma unroll
@@ -384,19 +387,13 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
 #pragma unroll
                         for (int u = 0; u < IGEMM_EPI_UB; ++u) {
                             const int cc = cb + u * 16;
-                            if (cc < ncols) {
-                                float4* ps = reinterpret_cast<float4*>(stat_w + cc + tcol4);
-                                float4* pq = reinterpret_cast<float4*>(stat_w + 128 + cc + tcol4);
-                                float4 s = *ps, qq = *pq;
-                                s.x += st_s[u].x; s.y += st_s[u].y; s.z += st_s[u].z; s.w += st_s[u].w;
-                                qq.x += st_q[u].x; qq.y += st_q[u].y; qq.z += st_q[u].z; qq.w += st_q[u].w;
-                                *ps = s;
-                                *pq = qq;
-                            }
+                            if (cc < ncols) stats_fold(stat_w, cc + tcol4, st_s[u], st_q[u], first_stats, tile_rows);
                         }
                     }
+                    if (first_stats) __syncwarp();     // the pivots must be visible to the whole warp before its next tile
                 }
             }
+            st_rows += tile_rows;
         }
         if (STATS && lane < 4) {
             // (count, mean, M2) of this warp's rows over all tiles of the CTA.  The grid is a multiple of
@@ -404,17 +401,16 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
             // disjoint column ranges of block (group * 4 + q) of [3][n_out].
             const int ntc = blockIdx.x % p.n_tiles_n;
             float* sp = p.stats + ((size_t)(blockIdx.x / p.n_tiles_n) * 4 + q) * 3 * (size_t)p.n_out;
-            const float inv_n = st_rows > 0.f ? 1.f / st_rows : 0.f;
             for (int cc = 0; cc < ncols; cc += 16) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int col = ntc * NT + col_begin + tcol4 + cc + k;
                     if (col < p.n_out) {
-                        const float s = stat_w[cc + tcol4 + k], qq = stat_w[128 + cc + tcol4 + k];
-                        const float m = s * inv_n;
+                        float m, m2;
+                        stats_result(stat_w, cc + tcol4 + k, st_rows, m, m2);
                         sp[col] = st_rows;
                         sp[p.n_out + col] = m + (p.bias != nullptr ? __ldg(p.bias + col) : 0.f);
-                        sp[2 * p.n_out + col] = fmaxf(qq - s * m, 0.f);
+                        sp[2 * p.n_out + col] = m2;
                     }
                 }
             }

@@ -112,6 +112,41 @@ def test_batch_norm_statistics_from_conv_epilogue(env, case):
     assert conv.bn_partials is None
 
 
+# inputs whose convolution outputs have |mean| >> std per channel: a large offset, raw 0..255 pixels, |N(0,1)|
+@pytest.mark.parametrize("kind", ["offset50", "pixels", "abs"])
+@pytest.mark.parametrize("case", [(8, 32, 32, 64, 128, "bf16"),        # halo kernel
+                                  (50, 16, 16, 128, 256, "bf16"),      # per-tap kernel
+                                  (37, 20, 24, 64, 64, "tf32"),        # halo kernel, TF32
+                                  (200, 32, 32, 3, 128, "bf16"),       # first layer on the tensor cores
+                                  (64, 28, 28, 1, 32, "fp32")])        # first layer on the CUDA cores
+def test_conv_epilogue_statistics_with_nonzero_mean_outputs(env, case, kind):
+    """The epilogue statistics sum about a per-column pivot (the mean of the first tile), so a channel whose mean is
+    far from zero compared with its spread keeps its variance: same 1e-4 tolerance as for centred data, against the
+    oracle's Batch_Norm statistics of the very tensor the convolution wrote."""
+    torch, _lib, layers = env
+    S, H, W, Cin, Cout, mode = case
+    rng = np.random.default_rng(9)
+    np.random.seed(9)
+    base = rng.standard_normal((S, H, W, Cin))
+    x = {"offset50": base + 50.0, "pixels": np.floor(rng.random((S, H, W, Cin)) * 256.0), "abs": np.abs(base)}[kind]
+    x = x.astype(np.float32)
+    conv = layers.Conv_Layer((H, W, Cin), Cout, (3, 3), (1, 1), "same", math_mode=mode)
+    # all-positive filters push every channel's mean far from zero (a zero-mean filter would cancel the offset)
+    conv.filter_weights.copy_(conv.filter_weights.abs())
+    bn = layers.Batch_Norm(n_features=Cout)
+    conv.emit_bn_stats = True
+    bn.stats_from = conv
+    y = conv.forward(x, True)
+    assert conv.bn_partials is not None
+    bn.forward(y, True)
+    torch.cuda.synchronize()
+    yh = host(y).astype(np.float64).reshape(-1, Cout)
+    mean, var = yh.mean(axis=0), yh.var(axis=0)
+    assert np.median(np.abs(mean) / np.sqrt(var)) > 3.0          # the case is what it claims to be
+    assert O.rel_l2(host(bn.batch_mean), mean) <= 1e-5
+    assert O.rel_l2(host(bn.batch_var), var) <= 1e-4
+
+
 @pytest.mark.parametrize("case", [(6, 8, 12, 32, 0.0, (2, 2), True), (3, 12, 6, 64, 0.01, (2, 2), False),
                                   (2, 9, 6, 8, 0.2, (3, 3), True)])
 def test_fused_block_tail_matches_oracle_chain(env, case):

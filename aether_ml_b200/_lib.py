@@ -19,6 +19,14 @@ class AetherConvDesc(C.Structure):
                 ("S", "H", "W", "Cin", "Cout", "fH", "fW", "sH", "sW", "padH", "padW", "math_mode")]
 
 
+class AetherOperandLayout(C.Structure):
+    _fields_ = [("x_copy_offset", C.c_size_t), ("x_copy_ld", C.c_int32), ("dy_copy_offset", C.c_size_t),
+                ("dy_copy_ld", C.c_int32), ("dy_colsum_offset", C.c_size_t), ("dy_colsum_rows_max", C.c_int32)]
+
+
+CONV_X_COPY_READY, CONV_W_COPY_READY, CONV_DY_COPY_READY = 1, 2, 4
+
+
 class AetherError(RuntimeError):
     pass
 
@@ -47,6 +55,13 @@ SIGNATURES = {
     "aether_conv2d_bnstats_blocks": (_I64, [_D]),
     "aether_conv2d_fwd_bnstats": (_I, [_D, _P, _P, _P, _P, _P, _SZ, _P, _SZ, _P]),
     "aether_conv2d_bwd": (_I, [_D, _P, _P, _P, _P, _P, _P, _P, _SZ, _I, _P]),
+    "aether_conv2d_operand_layout": (_I, [_D, C.POINTER(AetherOperandLayout)]),
+    "aether_conv2d_fwd_ex": (_I, [_D, _P, _P, _P, _P, _P, _SZ, _P, _SZ, _I, _P]),
+    "aether_conv2d_bwd_ex": (_I, [_D, _P, _P, _P, _P, _P, _P, _P, _SZ, _I, _I, _P]),
+    "aether_bn_act_pool_fwd_copy": (_I, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _F, _P,
+                                         _I, _P, _I, _P, _SZ, _P]),
+    "aether_bn_act_pool_bwd_copy": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P, _I,
+                                         _P, _I, C.POINTER(C.c_int), _P, _SZ, _P]),
     "aether_bn_act_fwd_train": (_I, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _F, _P, _P, _SZ, _P]),
     "aether_bn_act_fwd_eval": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _SZ, _P]),
     "aether_bn_act_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _P, _SZ, _P]),

@@ -112,7 +112,10 @@ static int pending_timeout(const char* fn) {
 
 using namespace aether;
 
-extern "C" int aether_version(void) { return 100; }
+int aether_conv2d_fwd_bnstats_flags(const AetherConvDesc* d, const float* x, const float* w, const float* b, float* y,
+                                    float* stats, size_t stats_bytes, void* ws, size_t ws_bytes, int flags, void* stream);
+
+extern "C" int aether_version(void) { return 101; }
 extern "C" const char* aether_last_error(void) { return g_err; }
 extern "C" uint64_t aether_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 extern "C" int aether_device_status(void) { return g_status_host ? *reinterpret_cast<volatile int*>(g_status_host) : 0; }
@@ -186,6 +189,31 @@ extern "C" size_t aether_conv2d_workspace_bytes(const AetherConvDesc* d) {
     return g;
 }
 
+extern "C" int aether_conv2d_operand_layout(const AetherConvDesc* d, AetherOperandLayout* out) {
+    if (!out) return 0;
+    memset(out, 0, sizeof(*out));
+    if (validate_desc(d, "aether_conv2d_operand_layout")) return 0;
+    return tc_conv_operand_layout(*d, out) ? 1 : 0;
+}
+
+extern "C" int aether_conv2d_fwd_ex(const AetherConvDesc* d, const float* x, const float* w, const float* b, float* y,
+                                    float* stats, size_t stats_bytes, void* ws, size_t ws_bytes, int flags, void* stream) {
+    int rc = validate_desc(d, "aether_conv2d_fwd_ex");
+    if (rc) return rc;
+    if (flags & ~AETHER_CONV_X_COPY_READY) return set_error(AE_BAD_ARG, "aether_conv2d_fwd_ex: unknown flag bits 0x%x", flags);
+    if ((flags & AETHER_CONV_X_COPY_READY) && !(tc_conv_eligible(*d) && d->math_mode == AETHER_MATH_BF16))
+        return set_error(AE_UNSUPPORTED, "aether_conv2d_fwd_ex: this shape / math mode reads no operand copy of x "
+                                         "(aether_conv2d_operand_layout returned 0)");
+    if (stats) return aether_conv2d_fwd_bnstats_flags(d, x, w, b, y, stats, stats_bytes, ws, ws_bytes, flags, stream);
+    if (!x || !w || !y) return set_error(AE_BAD_ARG, "aether_conv2d_fwd_ex: null pointer");
+    if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (ws && !aligned16(ws)))
+        return set_error(AE_BAD_ARG, "aether_conv2d_fwd_ex: arrays must be 16-byte aligned");
+    if ((rc = pending_timeout("aether_conv2d_fwd_ex"))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, nullptr, ws, ws_bytes, flags, st);
+    return aether_conv2d_fwd(d, x, w, b, y, ws, ws_bytes, stream);
+}
+
 extern "C" int aether_conv2d_fwd(const AetherConvDesc* d, const float* x, const float* w, const float* b, float* y,
                                  void* ws, size_t ws_bytes, void* stream) {
     int rc = validate_desc(d, "aether_conv2d_fwd");
@@ -195,7 +223,7 @@ extern "C" int aether_conv2d_fwd(const AetherConvDesc* d, const float* x, const 
         return set_error(AE_BAD_ARG, "aether_conv2d_fwd: arrays must be 16-byte aligned");
     if ((rc = pending_timeout("aether_conv2d_fwd"))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, nullptr, ws, ws_bytes, st);
+    if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, nullptr, ws, ws_bytes, 0, st);
     if (first_tc_eligible(*d)) return first_tc_fwd(*d, x, w, b, y, nullptr, st);
     if (smallc_conv_eligible(*d) && (!b || aligned16(b))) return smallc_conv_fwd(*d, x, w, b, y, nullptr, st);
     return generic_conv_fwd(*d, x, w, b, y, st);
@@ -211,6 +239,11 @@ extern "C" int64_t aether_conv2d_bnstats_blocks(const AetherConvDesc* d) {
 
 extern "C" int aether_conv2d_fwd_bnstats(const AetherConvDesc* d, const float* x, const float* w, const float* b, float* y,
                                          float* stats, size_t stats_bytes, void* ws, size_t ws_bytes, void* stream) {
+    return aether_conv2d_fwd_bnstats_flags(d, x, w, b, y, stats, stats_bytes, ws, ws_bytes, 0, stream);
+}
+
+int aether_conv2d_fwd_bnstats_flags(const AetherConvDesc* d, const float* x, const float* w, const float* b, float* y,
+                                    float* stats, size_t stats_bytes, void* ws, size_t ws_bytes, int flags, void* stream) {
     int rc = validate_desc(d, "aether_conv2d_fwd_bnstats");
     if (rc) return rc;
     if (!x || !w || !y || !stats) return set_error(AE_BAD_ARG, "aether_conv2d_fwd_bnstats: null pointer");
@@ -225,13 +258,21 @@ extern "C" int aether_conv2d_fwd_bnstats(const AetherConvDesc* d, const float* x
                          (size_t)blocks * 3 * d->Cout * sizeof(float));
     if ((rc = pending_timeout("aether_conv2d_fwd_bnstats"))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, stats, ws, ws_bytes, st);
+    if (tc_conv_eligible(*d)) return tc_conv_fwd(*d, x, w, b, y, stats, ws, ws_bytes, flags, st);
     if (first_tc_eligible(*d)) return first_tc_fwd(*d, x, w, b, y, stats, st);
     return smallc_conv_fwd(*d, x, w, b, y, stats, st);
 }
 
 extern "C" int aether_conv2d_bwd(const AetherConvDesc* d, const float* x, const float* dy, const float* w, float* dx,
                                  float* dw, float* db, void* ws, size_t ws_bytes, int x_shadow_valid, void* stream) {
+    if (x_shadow_valid & AETHER_CONV_DY_COPY_READY)
+        return set_error(AE_BAD_ARG, "aether_conv2d_bwd: AETHER_CONV_DY_COPY_READY needs aether_conv2d_bwd_ex (row count)");
+    return aether_conv2d_bwd_ex(d, x, dy, w, dx, dw, db, ws, ws_bytes, x_shadow_valid, 0, stream);
+}
+
+extern "C" int aether_conv2d_bwd_ex(const AetherConvDesc* d, const float* x, const float* dy, const float* w, float* dx,
+                                    float* dw, float* db, void* ws, size_t ws_bytes, int x_shadow_valid,
+                                    int dy_colsum_rows, void* stream) {
     int rc = validate_desc(d, "aether_conv2d_bwd");
     if (rc) return rc;
     if (!dy || !w || ((dw != nullptr) && !x)) return set_error(AE_BAD_ARG, "aether_conv2d_bwd: null pointer");
@@ -239,7 +280,10 @@ extern "C" int aether_conv2d_bwd(const AetherConvDesc* d, const float* x, const 
         return set_error(AE_BAD_ARG, "aether_conv2d_bwd: arrays must be 16-byte aligned");
     if ((rc = pending_timeout("aether_conv2d_bwd"))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (tc_conv_eligible(*d)) return tc_conv_bwd(*d, x, dy, w, dx, dw, db, ws, ws_bytes, x_shadow_valid, st);
+    if ((x_shadow_valid & AETHER_CONV_DY_COPY_READY) && !(tc_conv_eligible(*d) && d->math_mode == AETHER_MATH_BF16))
+        return set_error(AE_UNSUPPORTED, "aether_conv2d_bwd_ex: this shape / math mode reads no operand copy of dy "
+                                         "(aether_conv2d_operand_layout returned 0)");
+    if (tc_conv_eligible(*d)) return tc_conv_bwd(*d, x, dy, w, dx, dw, db, ws, ws_bytes, x_shadow_valid, dy_colsum_rows, st);
     if (dx && (rc = generic_conv_bwd_data(*d, dy, w, dx, st))) return rc;
     if (dw && first_tc_bwd_eligible(*d)) return first_tc_bwd_filter(*d, x, dy, dw, db, ws, ws_bytes, st);
     if ((dw || db) && smallc_conv_eligible(*d) && (!db || aligned16(db)))

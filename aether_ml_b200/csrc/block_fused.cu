@@ -10,9 +10,23 @@
 //
 // Every thread owns one window and four channels.  Statistics, running averages, coefficient algebra and the
 // fixed-order reductions are the Batch_Norm kernels of layers.cu.
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace aether {
+
+// Operand copy hand-off.  The tensor these passes write (the pooled activation going forward, dx going back) is the
+// next convolution's x, respectively the previous convolution's dy, whose tensor-core kernels read a bf16 copy with
+// the channels padded to `ld`.  When the consumer's workspace is known the copy is written here, from the values
+// already in registers, instead of by a cast pass that reads the fp32 tensor again: 4 channels = 8 bytes per thread,
+// and the threads of the first channel groups also zero the padding [C, ld) of their pixel.
+__device__ __forceinline__ void store_operand_copy(__nv_bfloat16* copy, int ld, size_t pixel, int cv, int C4, float4 v) {
+    __nv_bfloat162 o[2] = {__floats2bfloat162_rn(v.x, v.y), __floats2bfloat162_rn(v.z, v.w)};
+    __nv_bfloat16* row = copy + pixel * (size_t)ld;
+    *reinterpret_cast<uint2*>(row + cv * 4) = *reinterpret_cast<uint2*>(o);
+    for (int pg = C4 + cv; pg * 4 < ld; pg += C4) *reinterpret_cast<uint2*>(row + pg * 4) = make_uint2(0u, 0u);
+}
 
 __device__ __forceinline__ float lrelu(float v, float alpha) { return v > 0.f ? v : alpha * v; }
 // derivative of the activation at pre-activation v (the reference passes the gradient at v == 0, :412-428)
@@ -24,11 +38,13 @@ template <int F>
 __global__ void __launch_bounds__(256) bn_act_pool_fwd_kernel(const float* __restrict__ x, const float* __restrict__ scale,
                                                               const float* __restrict__ shift, float alpha,
                                                               float* __restrict__ y, uint8_t* __restrict__ arg,
-                                                              unsigned total, int W, int C4, int fH_, int fW_, int Wo) {
+                                                              unsigned total, int W, int C4, int fH_, int fW_, int Wo,
+                                                              __nv_bfloat16* __restrict__ copy, int copy_ld) {
     const int fH = F ? F : fH_, fW = F ? F : fW_;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
         const unsigned cv = idx % (unsigned)C4;
         unsigned pix = idx / (unsigned)C4;
+        const unsigned opix = pix;                             // output pixel of this window
         const unsigned wo = pix % (unsigned)Wo;
         pix /= (unsigned)Wo;                                   // = s * Ho + ho; input rows of all samples are stacked
         const float4 s = *reinterpret_cast<const float4*>(scale + cv * 4);
@@ -61,6 +77,7 @@ __global__ void __launch_bounds__(256) bn_act_pool_fwd_kernel(const float* __res
             }
         reinterpret_cast<float4*>(y)[idx] = best;
         reinterpret_cast<uchar4*>(arg)[idx] = code;
+        if (copy != nullptr) store_operand_copy(copy, copy_ld, opix, (int)cv, C4, best);
     }
 }
 
@@ -136,9 +153,13 @@ __global__ void __launch_bounds__(256) bn_act_pool_bwd_apply_kernel(
     const float* __restrict__ x, const float* __restrict__ dpool, const uint8_t* __restrict__ arg,
     const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mean,
     const float* __restrict__ var, float eps, float alpha, const float* __restrict__ coeff, float* __restrict__ dx,
-    unsigned total, int W, int C, int fH_, int fW_, int Wo) {
+    unsigned total, int W, int C, int fH_, int fW_, int Wo, __nv_bfloat16* __restrict__ copy, int copy_ld,
+    float* __restrict__ colsum_part) {
     const int fH = F ? F : fH_, fW = F ? F : fW_;
     const int C4 = C >> 2;
+    // column sums of dx (the bias gradient of the convolution in front): only with grids whose stride keeps a thread on
+    // one channel group (gridDim.x * 256 a multiple of C4; the host checks), so four running sums per thread suffice
+    float4 csum = make_float4(0.f, 0.f, 0.f, 0.f);
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
         const unsigned cv = idx % (unsigned)C4;
         unsigned pix = idx / (unsigned)C4;
@@ -176,7 +197,22 @@ __global__ void __launch_bounds__(256) bn_act_pool_bwd_apply_kernel(
                 if (cd.z == k) o.z = fmaf(k1.z, g.z * lrelu_grad(fmaf(ga.z, (v.z - mu.z) * inv.z, be.z), alpha), o.z);
                 if (cd.w == k) o.w = fmaf(k1.w, g.w * lrelu_grad(fmaf(ga.w, (v.w - mu.w) * inv.w, be.w), alpha), o.w);
                 reinterpret_cast<float4*>(dx)[cell] = o;
+                if (copy != nullptr) {
+                    store_operand_copy(copy, copy_ld, (size_t)pix * fH * W + (size_t)wo * fW + (size_t)i * W + j, (int)cv, C4, o);
+                    csum.x += o.x; csum.y += o.y; csum.z += o.z; csum.w += o.w;
+                }
             }
+    }
+    if (colsum_part != nullptr) {
+        // threads t, t + C4, ... of the block hold the same four channels: added in that order, one row per block
+        __shared__ float4 red[256];
+        red[threadIdx.x] = csum;
+        __syncthreads();
+        if ((int)threadIdx.x < C4) {
+            float4 t = red[threadIdx.x];
+            for (int l = threadIdx.x + C4; l < 256; l += C4) { const float4 v = red[l]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+            *reinterpret_cast<float4*>(colsum_part + (size_t)blockIdx.x * C + threadIdx.x * 4) = t;
+        }
     }
 }
 
@@ -209,9 +245,22 @@ extern "C" int aether_bn_act_pool_fwd(const float* x, const float* partials, int
                                       float* batch_var, float* pooled, uint8_t* argmax, int S, int H, int W, int C, int fH,
                                       int fW, float eps, float momentum, float alpha, const float* channel_scale,
                                       int training, void* ws, size_t ws_bytes, void* stream) {
+    return aether_bn_act_pool_fwd_copy(x, partials, nblocks, gamma, beta, running_mean, running_var, batch_mean, batch_var,
+                                       pooled, argmax, S, H, W, C, fH, fW, eps, momentum, alpha, channel_scale, training,
+                                       nullptr, 0, ws, ws_bytes, stream);
+}
+
+extern "C" int aether_bn_act_pool_fwd_copy(const float* x, const float* partials, int64_t nblocks, const float* gamma,
+                                           const float* beta, float* running_mean, float* running_var, float* batch_mean,
+                                           float* batch_var, float* pooled, uint8_t* argmax, int S, int H, int W, int C,
+                                           int fH, int fW, float eps, float momentum, float alpha,
+                                           const float* channel_scale, int training, void* operand_copy, int copy_ld,
+                                           void* ws, size_t ws_bytes, void* stream) {
     if (!x || !gamma || !beta || !running_mean || !running_var || !pooled || !argmax || !ws ||
         (training && (!batch_mean || !batch_var)))
         return set_error(AE_BAD_ARG, "aether_bn_act_pool_fwd: null pointer");
+    if (operand_copy && (copy_ld < C || copy_ld % 4 || (reinterpret_cast<uintptr_t>(operand_copy) & 7)))
+        return set_error(AE_BAD_ARG, "aether_bn_act_pool_fwd_copy: operand copy needs ld >= C, ld %% 4 == 0, 8-byte alignment");
     long long windows4 = 0;
     int rc = block_check("aether_bn_act_pool_fwd", S, H, W, C, fH, fW, alpha, &windows4);
     if (rc) return rc;
@@ -225,12 +274,13 @@ extern "C" int aether_bn_act_pool_fwd(const float* x, const float* partials, int
                                                 batch_var, rows, C, eps, momentum, channel_scale, static_cast<float*>(ws), st)
                             : bn_eval_coeffs(gamma, beta, running_mean, running_var, C, eps, static_cast<float*>(ws), st);
     const int fb = fused_blocks(windows4, 256, 16);
+    __nv_bfloat16* copy = static_cast<__nv_bfloat16*>(operand_copy);
     if (fH == 2 && fW == 2)
         bn_act_pool_fwd_kernel<2><<<fb, 256, 0, st>>>(x, coeff, coeff + C, alpha, pooled, argmax, (unsigned)windows4, W, C / 4,
-                                                     fH, fW, W / fW);
+                                                     fH, fW, W / fW, copy, copy_ld);
     else
         bn_act_pool_fwd_kernel<0><<<fb, 256, 0, st>>>(x, coeff, coeff + C, alpha, pooled, argmax, (unsigned)windows4, W, C / 4,
-                                                     fH, fW, W / fW);
+                                                     fH, fW, W / fW, copy, copy_ld);
     count_launch();
     return check_launch("aether_bn_act_pool_fwd");
 }
@@ -239,8 +289,26 @@ extern "C" int aether_bn_act_pool_bwd(const float* x, const float* dpooled, cons
                                       const float* beta, const float* batch_mean, const float* batch_var, float* dx,
                                       float* dgamma, float* dbeta, int S, int H, int W, int C, int fH, int fW, float eps,
                                       float alpha, const float* channel_scale, void* ws, size_t ws_bytes, void* stream) {
+    return aether_bn_act_pool_bwd_copy(x, dpooled, argmax, gamma, beta, batch_mean, batch_var, dx, dgamma, dbeta, S, H, W, C, fH,
+                                       fW, eps, alpha, channel_scale, nullptr, 0, nullptr, 0, nullptr, ws, ws_bytes, stream);
+}
+
+extern "C" int aether_bn_act_pool_bwd_copy(const float* x, const float* dpooled, const uint8_t* argmax, const float* gamma,
+                                           const float* beta, const float* batch_mean, const float* batch_var, float* dx,
+                                           float* dgamma, float* dbeta, int S, int H, int W, int C, int fH, int fW, float eps,
+                                           float alpha, const float* channel_scale, void* operand_copy, int copy_ld,
+                                           float* colsum_part, int colsum_rows_max, int* colsum_rows, void* ws,
+                                           size_t ws_bytes, void* stream) {
     if (!x || !dpooled || !argmax || !gamma || !beta || !batch_mean || !batch_var || !dx || !dgamma || !dbeta || !ws)
         return set_error(AE_BAD_ARG, "aether_bn_act_pool_bwd: null pointer");
+    if (operand_copy) {
+        if (copy_ld < C || copy_ld % 4 || (reinterpret_cast<uintptr_t>(operand_copy) & 7) || !colsum_part || !colsum_rows ||
+            colsum_rows_max < 1 || !aligned16(colsum_part))
+            return set_error(AE_BAD_ARG, "aether_bn_act_pool_bwd_copy: operand copy needs ld >= C, ld %% 4 == 0, 8-byte alignment "
+                                         "and a column-sum buffer");
+        if (256 % (C / 4 > 0 ? C / 4 : 1) || C / 4 > 256)
+            return set_error(AE_UNSUPPORTED, "aether_bn_act_pool_bwd_copy: the column sums need C / 4 to divide 256 (C = %d)", C);
+    }
     long long windows4 = 0;
     int rc = block_check("aether_bn_act_pool_bwd", S, H, W, C, fH, fW, alpha, &windows4);
     if (rc) return rc;
@@ -259,13 +327,20 @@ extern "C" int aether_bn_act_pool_bwd(const float* x, const float* dpooled, cons
                                                       (windows + nb - 1) / nb, W, C, fH, fW, W / fW, part);
     count_launch();
     bn_backward_coeffs(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma, dbeta, coeff, channel_scale, st);
-    const int fb = fused_blocks(windows4, 256, 16);
+    int fb = fused_blocks(windows4, 256, 16);
+    __nv_bfloat16* copy = static_cast<__nv_bfloat16*>(operand_copy);
+    if (copy) {                                  // one row of column sums per CTA: no more CTAs than rows offered
+        if (fb > colsum_rows_max) fb = colsum_rows_max;
+        *colsum_rows = fb;
+    }
     if (fH == 2 && fW == 2)
         bn_act_pool_bwd_apply_kernel<2><<<fb, 256, 0, st>>>(x, dpooled, argmax, gamma, beta, batch_mean, batch_var, eps, alpha,
-                                                           coeff, dx, (unsigned)windows4, W, C, fH, fW, W / fW);
+                                                           coeff, dx, (unsigned)windows4, W, C, fH, fW, W / fW, copy, copy_ld,
+                                                           copy ? colsum_part : nullptr);
     else
         bn_act_pool_bwd_apply_kernel<0><<<fb, 256, 0, st>>>(x, dpooled, argmax, gamma, beta, batch_mean, batch_var, eps, alpha,
-                                                           coeff, dx, (unsigned)windows4, W, C, fH, fW, W / fW);
+                                                           coeff, dx, (unsigned)windows4, W, C, fH, fW, W / fW, copy, copy_ld,
+                                                           copy ? colsum_part : nullptr);
     count_launch();
     return check_launch("aether_bn_act_pool_bwd");
 }

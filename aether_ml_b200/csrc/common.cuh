@@ -93,10 +93,11 @@ bool tc_conv_eligible(const AetherConvDesc& d);
 size_t tc_conv_workspace_bytes(const AetherConvDesc& d);
 // `stats` (nullable): per-block (count, mean, M2) of every output channel, tc_conv_stats_blocks(d) blocks of [3][Cout]
 int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, float* stats, void* ws,
-                size_t ws_bytes, cudaStream_t st);
+                size_t ws_bytes, int flags, cudaStream_t st);
+bool tc_conv_operand_layout(const AetherConvDesc& d, AetherOperandLayout* out);
 long long tc_conv_stats_blocks(const AetherConvDesc& d);
 int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const float* w, float* dx, float* dw,
-                float* db, void* ws, size_t ws_bytes, int x_shadow_valid, cudaStream_t st);
+                float* db, void* ws, size_t ws_bytes, int x_shadow_valid, int dy_colsum_rows, cudaStream_t st);
 
 // ---- layers.cu : pieces of Batch_Norm shared with block_fused.cu
 int bn_partial_blocks(long long rows);

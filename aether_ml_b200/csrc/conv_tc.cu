@@ -850,7 +850,7 @@ struct TcPlan {
     size_t off_xsh, off_dysh, off_wf, off_wd, off_part, off_dbpart, total;
     // dW decomposition
     int dw_nb, dw_nt, dw_cblocks, dw_U, dw_MG, dw_gpc, dw_ngc, dw_ntn, dw_splits;
-    int db_blocks;
+    int db_blocks, db_rows_max;
     PixelTiling til_out;   // tiles over output pixels (forward, dW)
     PixelTiling til_in;    // tiles over input pixels (dX)
 };
@@ -917,7 +917,10 @@ static TcPlan make_plan(const AetherConvDesc& d) {
         if (rs > part_splits) part_splits = rs;
     }
     pl.off_part = take((size_t)part_splits * pl.dw_U * UC * pl.Cout_p * 4);
-    pl.off_dbpart = take((size_t)pl.db_blocks * d.Cout * 4);
+    // rows of per-block column sums of dy: the cast pass writes db_blocks of them; a producer of dy that hands its own
+    // in (aether_conv2d_operand_layout) may use up to db_rows_max
+    pl.db_rows_max = pl.db_blocks > 8 * num_sms() ? pl.db_blocks : 8 * num_sms();
+    pl.off_dbpart = take((size_t)pl.db_rows_max * d.Cout * 4);
     pl.total = off;
     return pl;
 }
@@ -935,6 +938,18 @@ bool tc_conv_eligible(const AetherConvDesc& d) {
 }
 
 size_t tc_conv_workspace_bytes(const AetherConvDesc& d) { return make_plan(d).total; }
+
+bool tc_conv_operand_layout(const AetherConvDesc& d, AetherOperandLayout* out) {
+    if (!tc_conv_eligible(d) || d.math_mode != AETHER_MATH_BF16) return false;
+    const TcPlan pl = make_plan(d);
+    out->x_copy_offset = pl.off_xsh;
+    out->x_copy_ld = pl.Cin_p;
+    out->dy_copy_offset = pl.off_dysh;
+    out->dy_copy_ld = pl.Cout_p;
+    out->dy_colsum_offset = pl.off_dbpart;
+    out->dy_colsum_rows_max = pl.db_rows_max;
+    return true;
+}
 
 // CTAs of the per-tap kernel.  With statistics the grid is a multiple of the number of column tiles, so that a
 // CTA (tiles blockIdx.x + k * grid, column tile = tile % n_tiles_n) keeps one column tile throughout.
@@ -1056,7 +1071,7 @@ long long tc_conv_stats_blocks(const AetherConvDesc& d) {
 }
 
 int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const float* b, float* y, float* stats, void* ws,
-                size_t ws_bytes, cudaStream_t st) {
+                size_t ws_bytes, int flags, cudaStream_t st) {
     const TcPlan pl = make_plan(d);
     if (ws_bytes < pl.total || !ws) return set_error(AE_BAD_ARG, "conv workspace too small: %zu < %zu", ws_bytes, pl.total);
     uint8_t* wsb = static_cast<uint8_t*>(ws);
@@ -1069,7 +1084,10 @@ int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const f
     }
     __nv_bfloat16* xsh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_xsh);
     __nv_bfloat16* wf = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_wf);
-    if ((rc = launch_cast(x, xsh, 1LL * d.S * d.H * d.W, d.Cin, pl.Cin_p, nullptr, 0, st))) return rc;
+    // the bf16 copy of x: handed in by the kernel that produced x, else made here
+    if (!(flags & AETHER_CONV_X_COPY_READY) &&
+        (rc = launch_cast(x, xsh, 1LL * d.S * d.H * d.W, d.Cin, pl.Cin_p, nullptr, 0, st)))
+        return rc;
     // both filter operands (forward: transposed, dX: as stored) from one read of w; a backward call that is told
     // the weights have not changed since (x_shadow_valid bit 1) reuses the second one
     __nv_bfloat16* wd = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_wd);
@@ -1091,7 +1109,7 @@ static int launch_dw(const DwParams& p, int splits, int grid_y, cudaStream_t st)
 }
 
 int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const float* w, float* dx, float* dw,
-                float* db, void* ws, size_t ws_bytes, int x_shadow_valid, cudaStream_t st) {
+                float* db, void* ws, size_t ws_bytes, int x_shadow_valid, int dy_colsum_rows, cudaStream_t st) {
     const TcPlan pl = make_plan(d);
     if (ws_bytes < pl.total || !ws) return set_error(AE_BAD_ARG, "conv workspace too small: %zu < %zu", ws_bytes, pl.total);
     uint8_t* wsb = static_cast<uint8_t*>(ws);
@@ -1101,8 +1119,15 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
     float* dbpart = reinterpret_cast<float*>(wsb + pl.off_dbpart);
     const void* x_op = x;
     const void* dy_op = dy;
-    const bool w_shadow_valid = (x_shadow_valid & 2) != 0;
-    x_shadow_valid &= 1;
+    const bool w_shadow_valid = (x_shadow_valid & AETHER_CONV_W_COPY_READY) != 0;
+    const bool dy_ready = (x_shadow_valid & AETHER_CONV_DY_COPY_READY) != 0 && !pl.tf32;
+    x_shadow_valid &= AETHER_CONV_X_COPY_READY;
+    int db_rows = pl.db_blocks;
+    if (dy_ready) {
+        if (dy_colsum_rows < 1 || dy_colsum_rows > pl.db_rows_max)
+            return set_error(AE_BAD_ARG, "aether_conv2d_bwd_ex: dy_colsum_rows %d outside [1, %d]", dy_colsum_rows, pl.db_rows_max);
+        db_rows = dy_colsum_rows;
+    }
 
     // ---- shadows + dB
     if (pl.tf32) {
@@ -1115,14 +1140,15 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
     } else {
         __nv_bfloat16* dysh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_dysh);
         __nv_bfloat16* xsh = reinterpret_cast<__nv_bfloat16*>(wsb + pl.off_xsh);
-        if ((rc = launch_cast(dy, dysh, out_rows, d.Cout, pl.Cout_p, dbpart, pl.db_blocks, st))) return rc;
+        // the bf16 copy of dy and the column sums for dB: handed in by the kernel that produced dy, else made here
+        if (!dy_ready && (rc = launch_cast(dy, dysh, out_rows, d.Cout, pl.Cout_p, dbpart, pl.db_blocks, st))) return rc;
         if (dw && !x_shadow_valid)
             if ((rc = launch_cast(x, xsh, in_rows, d.Cin, pl.Cin_p, nullptr, 0, st))) return rc;
         x_op = xsh;
         dy_op = dysh;
     }
     if (db) {
-        colsum_finish_kernel<<<ceil_div(d.Cout, 8), 256, 0, st>>>(dbpart, pl.db_blocks, d.Cout, db);
+        colsum_finish_kernel<<<ceil_div(d.Cout, 8), 256, 0, st>>>(dbpart, db_rows, d.Cout, db);
         count_launch();
         if ((rc = check_launch("colsum_finish_kernel"))) return rc;
     }

@@ -94,6 +94,36 @@ class _OperandCopies:
         return (1 if self._tag(x) == self.x else 0) | (2 if self._tag(w) == self.w else 0)
 
 
+def _array_tag(t):
+    """Identity of a device array's contents as far as the host can tell: address, element count, version counter
+    (a reshaped view of the same memory has the same tag)."""
+    return (t.data_ptr(), t.numel(), t._version)
+
+
+class _HandedIn:
+    """Operand copies that a neighbouring layer's kernel wrote into this layer's workspace (see
+    aether_conv2d_operand_layout): which array each describes, so the layer skips its own cast pass only for
+    exactly that array in exactly that workspace buffer."""
+
+    def __init__(self):
+        self.x = None        # (workspace address, tag of x)
+        self.dy = None       # (workspace address, tag of dy, rows of column sums)
+
+    def x_ready(self, ws, x):
+        return self.x is not None and self.x == (ws.data_ptr(), _array_tag(x))
+
+    def dy_rows(self, ws, dy):
+        if self.dy is not None and self.dy[:2] == (ws.data_ptr(), _array_tag(dy)):
+            return self.dy[2]
+        return 0
+
+
+def _operand_layout(d):
+    """AetherOperandLayout of a convolution descriptor, or None when the shape reads no bf16 operand copies."""
+    lay = _lib.AetherOperandLayout()
+    return lay if lib().aether_conv2d_operand_layout(C.byref(d), C.byref(lay)) else None
+
+
 # ------------------------------------------------------------------------------------- Conv_Layer
 class Conv_Layer:
     """Drop-in for ``Conv_Layer`` (CNN_classes_cupy.py:37-161).
@@ -132,6 +162,7 @@ class Conv_Layer:
         self.bn_partials = None         # (buffer, blocks, data_ptr of the output they describe) after a training forward
         self._desc = None
         self._copies = _OperandCopies()
+        self._handed = _HandedIn()
 
     # `weights` is the same array object as `filter_weights` (:68); in-place optimizer updates on
     # either name are visible through both.
@@ -152,6 +183,35 @@ class Conv_Layer:
         d = AetherConvDesc(S, H, W, Cin, self.num_filters, fH, fW, sH, sW, P, P, _lib.MATH_MODES[self.math_mode])
         return d, Ho, Wo
 
+    # -- operand-copy hand-off: the kernel that produces this layer's x (going forward) or dy (going back) may write
+    # the bf16 copy the tensor-core kernels read straight into this layer's workspace
+    def x_copy_target(self, shape):
+        """(address, row length) where the bf16 copy of an input of `shape` goes, or None."""
+        if len(shape) != 4 or shape[3] != self.filter_weights.shape[2]:
+            return None
+        d, Ho, Wo = self._make_desc(*shape)
+        lay = _operand_layout(d) if (Ho >= 1 and Wo >= 1) else None
+        if lay is None:
+            return None
+        ws = self._ws.get(lib().aether_conv2d_workspace_bytes(C.byref(d)))
+        return ws.data_ptr() + lay.x_copy_offset, lay.x_copy_ld
+
+    def x_copy_written(self, x):
+        self._handed.x = (self._ws.buf.data_ptr(), _array_tag(x))
+
+    def dy_copy_target(self):
+        """(address, row length, column-sum address, rows available) for the bf16 copy of the coming dvalues, or None."""
+        if self._desc is None:
+            return None
+        lay = _operand_layout(self._desc)
+        if lay is None:
+            return None
+        ws = self._ws.get(lib().aether_conv2d_workspace_bytes(C.byref(self._desc)))
+        return ws.data_ptr() + lay.dy_copy_offset, lay.dy_copy_ld, ws.data_ptr() + lay.dy_colsum_offset, lay.dy_colsum_rows_max
+
+    def dy_copy_written(self, dy, rows):
+        self._handed.dy = (self._ws.buf.data_ptr(), _array_tag(dy), int(rows))
+
     def forward(self, inputs, training):
         x = to_device(inputs)
         if x.ndim != 4:
@@ -165,19 +225,21 @@ class Conv_Layer:
         L = lib()
         ws = self._ws.get(L.aether_conv2d_workspace_bytes(C.byref(d)))
         y = _empty((S, Ho, Wo, self.num_filters))
+        flags = _lib.CONV_X_COPY_READY if self._handed.x_ready(ws, x) else 0
+        self._handed.x = None
         # With emit_bn_stats the kernel's epilogue also writes the per-channel partial statistics that the
         # Batch_Norm behind this layer would otherwise compute in a pass of its own over y (:467-470).
         nblk = int(L.aether_conv2d_bnstats_blocks(C.byref(d))) if (training and self.emit_bn_stats) else 0
         self.bn_partials = None
         if nblk > 0:
             stats = self._stats_ws.get(nblk * 3 * self.num_filters * 4)
-            check(L.aether_conv2d_fwd_bnstats(C.byref(d), _ptr(x), _ptr(self.filter_weights), _ptr(self.biases), _ptr(y),
-                                              _ptr(stats), stats.numel(), _ptr(ws), ws.numel(), _stream()),
-                  "aether_conv2d_fwd_bnstats")
+            check(L.aether_conv2d_fwd_ex(C.byref(d), _ptr(x), _ptr(self.filter_weights), _ptr(self.biases), _ptr(y),
+                                         _ptr(stats), stats.numel(), _ptr(ws), ws.numel(), flags, _stream()),
+                  "aether_conv2d_fwd_ex")
             self.bn_partials = (stats, nblk, y.data_ptr())
         else:
-            check(L.aether_conv2d_fwd(C.byref(d), _ptr(x), _ptr(self.filter_weights), _ptr(self.biases), _ptr(y),
-                                      _ptr(ws), ws.numel(), _stream()), "aether_conv2d_fwd")
+            check(L.aether_conv2d_fwd_ex(C.byref(d), _ptr(x), _ptr(self.filter_weights), _ptr(self.biases), _ptr(y),
+                                         None, 0, _ptr(ws), ws.numel(), flags, _stream()), "aether_conv2d_fwd_ex")
         self.inputs = x
         self.output = y
         self._desc = d
@@ -203,9 +265,13 @@ class Conv_Layer:
             self.dbiases = _empty((d.Cout,))
         dx = _empty((d.S, d.H, d.W, d.Cin)) if need_dinputs else None
         shadow_ok = self._copies.flags(ws, x, self.filter_weights)
-        check(L.aether_conv2d_bwd(C.byref(d), _ptr(x), _ptr(dy), _ptr(self.filter_weights), _ptr(dx),
-                                  _ptr(self.dweights), _ptr(self.dbiases), _ptr(ws), ws.numel(), shadow_ok,
-                                  _stream()), "aether_conv2d_bwd")
+        rows = self._handed.dy_rows(ws, dy)
+        self._handed.dy = None
+        if rows:
+            shadow_ok |= _lib.CONV_DY_COPY_READY
+        check(L.aether_conv2d_bwd_ex(C.byref(d), _ptr(x), _ptr(dy), _ptr(self.filter_weights), _ptr(dx),
+                                     _ptr(self.dweights), _ptr(self.dbiases), _ptr(ws), ws.numel(), shadow_ok, rows,
+                                     _stream()), "aether_conv2d_bwd_ex")
         self.dinputs = dx
         return self.dinputs
 
@@ -463,6 +529,8 @@ class Batch_Norm:
         self.fused_dropout = None       # a Layer_Dropout_Spatial behind that activation whose mask is applied here too
         self.fused_pool = None          # a max Pooling behind those whose windows are reduced here too
         self.pooled_now = False         # the last forward produced the pooled tensor
+        self.copy_consumer = None       # the layer that reads the pooled tensor as x (its bf16 copy is written here)
+        self.copy_dy_consumer = None    # the Conv_Layer in front (the bf16 copy of its dvalues is written here)
         if n_features is not None:
             self._create(n_features)
 
@@ -520,13 +588,18 @@ class Batch_Norm:
                 mask = self.fused_dropout.draw_mask(Cc) if (training and self.fused_dropout is not None) else None
                 pooled = _empty((S, H // fH, W // fW, Cc))
                 self._pool_arg = _empty((S, H // fH, W // fW, Cc), torch.uint8)
-                check(L.aether_bn_act_pool_fwd(_ptr(x), _ptr(part[0]) if part else None, part[1] if part else 0,
-                                               _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
-                                               _ptr(self._bm) if training else None, _ptr(self._bv) if training else None,
-                                               _ptr(pooled), _ptr(self._pool_arg), S, H, W, Cc, fH, fW, float(self.epsilon),
-                                               float(self.momentum), float(self.fused_alpha), _ptr(mask),
-                                               1 if training else 0, _ptr(ws), ws.numel(), _stream()),
-                      "aether_bn_act_pool_fwd")
+                # the layer behind the pooling reads a bf16 copy of the pooled tensor: written by this same pass
+                target = self.copy_consumer.x_copy_target(tuple(pooled.shape)) if self.copy_consumer is not None else None
+                check(L.aether_bn_act_pool_fwd_copy(_ptr(x), _ptr(part[0]) if part else None, part[1] if part else 0,
+                                                    _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
+                                                    _ptr(self._bm) if training else None, _ptr(self._bv) if training else None,
+                                                    _ptr(pooled), _ptr(self._pool_arg), S, H, W, Cc, fH, fW,
+                                                    float(self.epsilon), float(self.momentum), float(self.fused_alpha),
+                                                    _ptr(mask), 1 if training else 0,
+                                                    C.c_void_p(target[0]) if target else None, target[1] if target else 0,
+                                                    _ptr(ws), ws.numel(), _stream()), "aether_bn_act_pool_fwd_copy")
+                if target:
+                    self.copy_consumer.x_copy_written(pooled)
                 self._fused_mask = mask
                 self.pooled_now = True
                 if training:
@@ -590,11 +663,21 @@ class Batch_Norm:
         if self.pooled_now:                  # dvalues is the gradient w.r.t. the POOLED output of the fused block tail
             S, H, W = x.shape[0], x.shape[1], x.shape[2]
             fH, fW = self.fused_pool.filter_size
-            check(L.aether_bn_act_pool_bwd(_ptr(x), _ptr(dy), _ptr(self._pool_arg), _ptr(self.gamma), _ptr(self.beta),
-                                           _ptr(self._bm), _ptr(self._bv), _ptr(dx), _ptr(self.dweights),
-                                           _ptr(self.dbiases), S, H, W, Cc, fH, fW, float(self.epsilon),
-                                           float(self.fused_alpha), _ptr(getattr(self, "_fused_mask", None)), _ptr(ws),
-                                           ws.numel(), _stream()), "aether_bn_act_pool_bwd")
+            # dx is the dvalues of the convolution in front: its bf16 copy and the column sums for that layer's bias
+            # gradient are written by this same pass
+            conv = self.copy_dy_consumer
+            target = conv.dy_copy_target() if (conv is not None and conv.output is x and 256 % max(Cc // 4, 1) == 0
+                                               and Cc // 4 <= 256) else None
+            rows = C.c_int(0)
+            check(L.aether_bn_act_pool_bwd_copy(_ptr(x), _ptr(dy), _ptr(self._pool_arg), _ptr(self.gamma), _ptr(self.beta),
+                                                _ptr(self._bm), _ptr(self._bv), _ptr(dx), _ptr(self.dweights),
+                                                _ptr(self.dbiases), S, H, W, Cc, fH, fW, float(self.epsilon),
+                                                float(self.fused_alpha), _ptr(getattr(self, "_fused_mask", None)),
+                                                C.c_void_p(target[0]) if target else None, target[1] if target else 0,
+                                                C.c_void_p(target[2]) if target else None, target[3] if target else 0,
+                                                C.byref(rows), _ptr(ws), ws.numel(), _stream()), "aether_bn_act_pool_bwd_copy")
+            if target:
+                conv.dy_copy_written(dx, rows.value)
         elif self.fused_alpha is not None:   # dvalues is the gradient w.r.t. the ACTIVATED output
             check(L.aether_bn_act_bwd(_ptr(x), _ptr(self.beta), _ptr(dy), _ptr(self.gamma), _ptr(self._bm),
                                       _ptr(self._bv), _ptr(dx), _ptr(self.dweights), _ptr(self.dbiases), rows, Cc,
@@ -653,6 +736,28 @@ class Layer_Dense:
         self.math_mode = math_mode or DEFAULT_MATH_MODE
         self._ws = _Workspace()
         self._copies = _OperandCopies()
+        self._handed = _HandedIn()
+
+    def x_copy_target(self, shape):
+        """(address, row length) where the bf16 copy of an input of `shape` (any shape that flattens to
+        (samples, n_inputs), e.g. the pooled NHWC tensor in front of a Flatten) goes, or None."""
+        n_in = self.weights.shape[0]
+        total = 1
+        for v in shape:
+            total *= int(v)
+        if len(shape) < 2 or total != int(shape[0]) * n_in:
+            return None
+        d = self._desc(int(shape[0]))
+        lay = _operand_layout(d)
+        # A row of the copy is one SAMPLE here, but the producer writes one PIXEL (shape[-1] channels) per row: the two
+        # are the same bytes only when the sample's row is not padded (n_inputs a multiple of 64).
+        if lay is None or lay.x_copy_ld != n_in:
+            return None
+        ws = self._ws.get(lib().aether_conv2d_workspace_bytes(C.byref(d)))
+        return ws.data_ptr() + lay.x_copy_offset, int(shape[-1])
+
+    def x_copy_written(self, x):
+        self._handed.x = (self._ws.buf.data_ptr(), _array_tag(x))
 
     def _desc(self, S):
         n_in, n_out = self.weights.shape
@@ -666,8 +771,10 @@ class Layer_Dense:
         L = lib()
         ws = self._ws.get(L.aether_conv2d_workspace_bytes(C.byref(d)))
         y = _empty((x.shape[0], self.weights.shape[1]))
-        check(L.aether_conv2d_fwd(C.byref(d), _ptr(x), _ptr(self.weights), _ptr(self.biases), _ptr(y), _ptr(ws),
-                                  ws.numel(), _stream()), "aether_conv2d_fwd")
+        flags = _lib.CONV_X_COPY_READY if self._handed.x_ready(ws, x) else 0
+        self._handed.x = None
+        check(L.aether_conv2d_fwd_ex(C.byref(d), _ptr(x), _ptr(self.weights), _ptr(self.biases), _ptr(y), None, 0, _ptr(ws),
+                                     ws.numel(), flags, _stream()), "aether_conv2d_fwd_ex")
         self.inputs = x
         self.output = y
         self._copies.record(ws, x, self.weights)

@@ -16,7 +16,7 @@ import pickle
 import numpy as np
 import torch
 
-from .layers import (Activation_Softmax_Loss_CategoricalCrossEntropy, Batch_Norm, Conv_Layer, Layer_Dropout_Spatial,
+from .layers import (Activation_Softmax_Loss_CategoricalCrossEntropy, Batch_Norm, Conv_Layer, Flatten, Layer_Dropout_Spatial,
                      Loss_CategoricalCrossEntropy, Pooling, ReLU, SoftMax, to_device, _labels_i32, _softmax_cce)
 
 
@@ -140,6 +140,16 @@ class Model:
                         and tuple(c.strides) == tuple(c.filter_size)):
                     a.fused_pool = c
                     c.fused_bn = a
+                    # The pooled tensor is the x of the layer behind (through a Flatten, if any) and the dx of this
+                    # block tail is the dvalues of the convolution in front: the tail's kernels write the bf16 copies
+                    # those layers' tensor-core kernels read, so neither runs a cast pass over the fp32 tensor.
+                    nxt = getattr(c, "next", None)
+                    if isinstance(nxt, Flatten):
+                        nxt = getattr(nxt, "next", None)
+                    if hasattr(nxt, "x_copy_target"):
+                        a.copy_consumer = nxt
+                    if isinstance(getattr(a, "prev", None), Conv_Layer):
+                        a.copy_dy_consumer = a.prev
         self.trainable_layers = [l for l in self.layers if hasattr(l, "weights")]
         if self.loss is not None:
             self.loss.remember_trainable_layers(self.trainable_layers)

@@ -110,6 +110,36 @@ int aether_conv2d_fwd_bnstats(const AetherConvDesc* desc, const float* x, const 
 int aether_conv2d_bwd(const AetherConvDesc* desc, const float* x, const float* dy, const float* w, float* dx, float* dw,
                       float* db, void* ws, size_t ws_bytes, int x_shadow_valid, void* stream);
 
+/* Operand-copy hand-off between neighbouring layers.  The reference passes fp32 activations from layer to layer
+ * (Pooling.output -> Conv_Layer.forward :70-120; Batch_Norm.backward :484-508 -> Conv_Layer.backward :123-154); the
+ * bf16 tensor-core kernels here read a bf16 copy of x and of dy that a cast pass makes from them.  The kernel that
+ * PRODUCES such an activation can write that copy itself, straight into the consuming layer's workspace, and the
+ * consumer is then told to skip its cast pass:
+ *   aether_conv2d_operand_layout: where in `ws` (byte offsets) the copies live and how wide their rows are (channels
+ *     padded to a multiple of 64).  Returns 1 and fills `out` when this shape runs on the bf16 tensor-core path,
+ *     0 otherwise (no copies are read: nothing to hand in).  The copy of x is [S*H*W][x_copy_ld] bf16, the copy of dy
+ *     [S*Ho*Wo][dy_copy_ld] bf16 (padding channels zero); with the copy of dy the producer also hands in per-block
+ *     column sums of dy for the bias gradient (:132), float [rows][Cout] at dy_colsum_offset, rows <= dy_colsum_rows_max.
+ *   aether_conv2d_fwd_ex: aether_conv2d_fwd (stats == NULL) / aether_conv2d_fwd_bnstats (stats given) with flags:
+ *     AETHER_CONV_X_COPY_READY = the copy of x is already in ws.
+ *   aether_conv2d_bwd_ex: aether_conv2d_bwd whose bit mask may also carry AETHER_CONV_DY_COPY_READY = the copy of dy
+ *     and dy_colsum_rows rows of column sums are already in ws.
+ * These entry points have no counterpart in the reference. */
+typedef struct AetherOperandLayout {
+    size_t x_copy_offset;
+    int32_t x_copy_ld;
+    size_t dy_copy_offset;
+    int32_t dy_copy_ld;
+    size_t dy_colsum_offset;
+    int32_t dy_colsum_rows_max;
+} AetherOperandLayout;
+enum { AETHER_CONV_X_COPY_READY = 1, AETHER_CONV_W_COPY_READY = 2, AETHER_CONV_DY_COPY_READY = 4 };
+int aether_conv2d_operand_layout(const AetherConvDesc* desc, AetherOperandLayout* out);
+int aether_conv2d_fwd_ex(const AetherConvDesc* desc, const float* x, const float* w, const float* b, float* y, float* stats,
+                         size_t stats_bytes, void* ws, size_t ws_bytes, int flags, void* stream);
+int aether_conv2d_bwd_ex(const AetherConvDesc* desc, const float* x, const float* dy, const float* w, float* dx, float* dw,
+                         float* db, void* ws, size_t ws_bytes, int x_shadow_valid, int dy_colsum_rows, void* stream);
+
 /* ---- Batch_Norm (CNN_classes_cupy.py:430-526); x is [rows][C], rows = product of leading axes --- */
 size_t aether_bn_workspace_bytes(int64_t rows, int C);
 /* Training forward :467-476.  Writes batch_mean/batch_var (biased), y, and updates running_* in place
@@ -193,6 +223,22 @@ int aether_bn_act_pool_bwd(const float* x, const float* dpooled, const uint8_t* 
                            const float* beta, const float* batch_mean, const float* batch_var, float* dx, float* dgamma,
                            float* dbeta, int S, int H, int W, int C, int fH, int fW, float eps, float alpha,
                            const float* channel_scale, void* ws, size_t ws_bytes, void* stream);
+/* The same two passes writing, from the values they already hold, the bf16 operand copy the neighbouring convolution
+ * reads (see aether_conv2d_operand_layout):
+ *   ..._fwd_copy: operand_copy (nullable) = the next layer's copy of x, [S*(H/fH)*(W/fW)][copy_ld] bf16, copy_ld >= C.
+ *   ..._bwd_copy: operand_copy (nullable) = the previous convolution's copy of dy, [S*H*W][copy_ld] bf16, together
+ *     with one row of column sums of dx per thread block in colsum_part [*colsum_rows <= colsum_rows_max][C]
+ *     (needs C/4 to divide 256).  With operand_copy == NULL they are the calls above. */
+int aether_bn_act_pool_fwd_copy(const float* x, const float* partials, int64_t nblocks, const float* gamma,
+                                const float* beta, float* running_mean, float* running_var, float* batch_mean,
+                                float* batch_var, float* pooled, uint8_t* argmax, int S, int H, int W, int C, int fH, int fW,
+                                float eps, float momentum, float alpha, const float* channel_scale, int training,
+                                void* operand_copy, int copy_ld, void* ws, size_t ws_bytes, void* stream);
+int aether_bn_act_pool_bwd_copy(const float* x, const float* dpooled, const uint8_t* argmax, const float* gamma,
+                                const float* beta, const float* batch_mean, const float* batch_var, float* dx, float* dgamma,
+                                float* dbeta, int S, int H, int W, int C, int fH, int fW, float eps, float alpha,
+                                const float* channel_scale, void* operand_copy, int copy_ld, float* colsum_part,
+                                int colsum_rows_max, int* colsum_rows, void* ws, size_t ws_bytes, void* stream);
 
 /* ---- Pooling, 'valid' padding (CNN_classes_cupy.py:204-312) ---------------------------------- */
 /* Forward :212-273.  argmax (uint8, same shape as y; max pooling only) receives i*fW+j of the first

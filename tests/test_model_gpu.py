@@ -403,3 +403,77 @@ def test_checkpoint_with_optimizer_state_resumes_training(env, tmp_path):
     c, _ = build(env, "fmnist", "bf16", False)              # per-layer state (no flat buffers) resumes as well
     c.load_parameters(path)
     assert c.optimizer.iterations == 2 and O.rel_l2(host(c.layers[0].weight_cache), cache2) <= 1e-7
+
+
+def test_block_tail_hands_operand_copies_to_neighbouring_layers(env):
+    """finalize(fuse=True): the fused block tail (Batch_Norm + ReLU + pooling) writes the bf16 operand copy of its
+    pooled output into the next layer's workspace (a Conv_Layer, or the Dense behind a Flatten) and, going back, the
+    copy of its dx plus the bias-gradient column sums into the convolution in front -- those layers then run no cast
+    pass.  Checked against the same model without the hand-off (identical tensor-core inputs, so the same numbers)
+    and against the oracle's layer-by-layer chain."""
+    torch, _lib, Ly, M = env
+
+    def make(hand_off):
+        np.random.seed(12)
+        m = M.Model()
+        m.add(Ly.Conv_Layer((16, 16, 16), 64, (3, 3), (1, 1), "same", math_mode="bf16"))
+        m.add(Ly.Batch_Norm(n_features=64))
+        m.add(Ly.ReLU())
+        m.add(Ly.Pooling((2, 2), (2, 2), "valid", "max"))
+        m.add(Ly.Conv_Layer((8, 8, 64), 96, (3, 3), (1, 1), "same", math_mode="bf16"))      # 96 channels: copy rows padded to 128
+        m.add(Ly.Batch_Norm(n_features=96))
+        m.add(Ly.Leaky_ReLU(0.1))
+        m.add(Ly.Pooling((2, 2), (2, 2), "valid", "max"))
+        m.add(Ly.Flatten())
+        m.add(Ly.Layer_Dense(4 * 4 * 96, 32, math_mode="bf16"))
+        m.add(Ly.Layer_Dense(32, 10, math_mode="bf16"))
+        m.add(Ly.SoftMax())
+        m.set(loss=Ly.Loss_CategoricalCrossEntropy(label_smoothing=0.01), optimizer=Ly.Optimizer_Adam(learning_rate=1e-3),
+              accuracy=M.Accuracy_Categorical())
+        m.finalize(flat=True, fuse=True)
+        bns = [l for l in m.layers if isinstance(l, Ly.Batch_Norm)]
+        assert isinstance(bns[0].copy_consumer, Ly.Conv_Layer) and isinstance(bns[1].copy_consumer, Ly.Layer_Dense)
+        assert all(isinstance(b.copy_dy_consumer, Ly.Conv_Layer) for b in bns)
+        if not hand_off:
+            for b in bns:
+                b.copy_consumer = b.copy_dy_consumer = None
+        return m
+
+    rng = np.random.default_rng(4)
+    X = rng.standard_normal((6, 16, 16, 16)).astype(np.float32)
+    y = rng.integers(0, 10, 6)
+    with_copy, without = make(True), make(False)
+    counts = []
+    for m in (with_copy, without):
+        m.forward(X, training=True)                      # sizes the workspaces
+        n0 = _lib.launch_count()
+        out = m.forward(X, training=True)
+        m.backward(out, y)
+        counts.append(_lib.launch_count() - n0)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    # two cast passes less going forward (conv 2, dense 1) and one less going back: the dy of conv 1; the tail behind
+    # conv 2 has 96 channels, and the column sums that go with a dy copy need C/4 to divide 256, so conv 2 casts itself
+    assert counts[1] - counts[0] == 3, counts
+    assert O.rel_l2(host(with_copy.layers[-1].output), host(without.layers[-1].output)) <= 1e-6
+    assert O.rel_l2(host(with_copy.flat_grads), host(without.flat_grads)) <= 1e-5
+    conv2 = with_copy.layers[4]
+    assert torch.equal(conv2.output, without.layers[4].output)      # the same bf16 operands went into the tensor cores
+    # ... and both agree with the oracle's chain
+    probs, grads = oracle_step(with_copy, Ly, X, y)
+    assert O.rel_l2(host(with_copy.layers[-1].output), probs) <= 2e-2
+    for k, (dw, db) in grads.items():                    # bf16 operands through six layers and two Batch_Norm backward passes: several per cent of the norm
+        l = with_copy.layers[k]
+        if not isinstance(l, Ly.Batch_Norm):
+            assert O.rel_l2(host(l.dweights), dw) <= 1e-1, k
+    # inference takes the same path (the copy is written by the evaluation pass too)
+    e1 = with_copy.forward(X, training=False)
+    e2 = without.forward(X, training=False)
+    assert O.rel_l2(host(e1), host(e2)) <= 1e-6
+    # an input the tail did not produce is cast by the layer itself
+    other = torch.randn((6, 8, 8, 64), device="cuda")
+    n0 = _lib.launch_count()
+    conv2.forward(other, True)
+    ref = Ly.Conv_Layer((8, 8, 64), 96, (3, 3), (1, 1), "same", math_mode="bf16")
+    ref.set_parameters(conv2.filter_weights, conv2.biases)
+    assert torch.equal(ref.forward(other, True), conv2.output)

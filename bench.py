@@ -34,12 +34,12 @@ sys.path.insert(0, ROOT)
 
 SHAPE = dict(S=256, H=56, W=56, Cin=64, Cout=128, f=3)
 WORKLOAD = "conv_fwd_bwd S=256 NHWC 56x56 Cin=64 Cout=128 3x3 stride1 same (largest shape of the isolated sweep)"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch on this workload (bf16): measured by ncu on one step at
-# batch 64 (one kernel kind per capture, see profiles/conv_step_56x56_64to128_S64_dram_traffic.txt) and scaled by 4 to
-# the batch of 256 -- every kernel's traffic is proportional to the batch.  Part of a kernel's output is still dirty
-# in L2 when it ends, so written bytes come out below the algorithmic figure.  operand_cast = mean of its two launches.
-DRAM_TRAFFIC_S256 = {"igemm_fwd": 102975744 + 353941760, "igemm_dx": 205719808 + 155275776, "dw": 308393216 + 356096,
-                     "operand_cast": (205520896 + 102760448 + 411041792 + 205520896) // 2}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch on this workload (bf16, batch 256), from the one-pass ncu
+# capture of one step summarised in profiles/conv_step_56x56_64to128_dram_traffic.txt.  Part of a kernel's output is
+# still dirty in L2 when it ends, so written bytes come out below the algorithmic figure.  operand_cast = mean of
+# its two launches (x: 254.6 MB, dy: 559.1 MB).
+DRAM_TRAFFIC_S256 = {"igemm_fwd": 102976000 + 353129216, "igemm_dx": 205717760 + 154724608, "dw": 308411136 + 3284224,
+                     "operand_cast": (205528320 + 49115136 + 411053824 + 147998976) // 2}
 # algorithmic bytes per launch (each operand read once, each result written once)
 def algorithmic_bytes(S, H, W, Cin, Cout):
     px = S * H * W
@@ -407,7 +407,7 @@ def run_gpu(args):
         dom = max(per_kind, key=lambda k: per_kind[k]["ms_per_step"])
         roof = dict(per_kind[dom])
         roof.update({"kernel": dom, "share_of_step": roof["ms_per_step"] / ms_step,
-                     "traffic_unit": "bytes per launch (dram read + write; ncu at batch 64, scaled by 4)",
+                     "traffic_unit": "bytes per launch (dram read + write, one-pass ncu capture of this workload)",
                      "peak_source": "%s (MEASURED_PEAKS.json: %s)" % (pk["source"], "hbm_gbs" if roof["bound"] == "hbm" else
                                                                       ("bf16_tflops_sustained" if ms_total > 1500 else "bf16_tflops")),
                      "timed_every": prof_stride})

@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(256) bn_act_pool_fwd_kernel(const float* __res
                     if (o.w > best.w) { best.w = o.w; code.w = k; }
                 }
             }
-        reinterpret_cast<float4*>(y)[idx] = best;
+        if (y != nullptr) reinterpret_cast<float4*>(y)[idx] = best;       // not written when only the bf16 copy is wanted
         reinterpret_cast<uchar4*>(arg)[idx] = code;
         if (copy != nullptr) store_operand_copy(copy, copy_ld, opix, (int)cv, C4, best);
     }
@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(256) bn_act_pool_bwd_apply_kernel(
                 if (cd.y == k) o.y = fmaf(k1.y, g.y * lrelu_grad(fmaf(ga.y, (v.y - mu.y) * inv.y, be.y), alpha), o.y);
                 if (cd.z == k) o.z = fmaf(k1.z, g.z * lrelu_grad(fmaf(ga.z, (v.z - mu.z) * inv.z, be.z), alpha), o.z);
                 if (cd.w == k) o.w = fmaf(k1.w, g.w * lrelu_grad(fmaf(ga.w, (v.w - mu.w) * inv.w, be.w), alpha), o.w);
-                reinterpret_cast<float4*>(dx)[cell] = o;
+                if (dx != nullptr) reinterpret_cast<float4*>(dx)[cell] = o;   // not written when only the bf16 copy is wanted
                 if (copy != nullptr) {
                     store_operand_copy(copy, copy_ld, (size_t)pix * fH * W + (size_t)wo * fW + (size_t)i * W + j, (int)cv, C4, o);
                     csum.x += o.x; csum.y += o.y; csum.z += o.z; csum.w += o.w;
@@ -256,7 +256,7 @@ extern "C" int aether_bn_act_pool_fwd_copy(const float* x, const float* partials
                                            int fH, int fW, float eps, float momentum, float alpha,
                                            const float* channel_scale, int training, void* operand_copy, int copy_ld,
                                            void* ws, size_t ws_bytes, void* stream) {
-    if (!x || !gamma || !beta || !running_mean || !running_var || !pooled || !argmax || !ws ||
+    if (!x || !gamma || !beta || !running_mean || !running_var || (!pooled && !operand_copy) || !argmax || !ws ||
         (training && (!batch_mean || !batch_var)))
         return set_error(AE_BAD_ARG, "aether_bn_act_pool_fwd: null pointer");
     if (operand_copy && (copy_ld < C || copy_ld % 4 || (reinterpret_cast<uintptr_t>(operand_copy) & 7)))
@@ -264,7 +264,7 @@ extern "C" int aether_bn_act_pool_fwd_copy(const float* x, const float* partials
     long long windows4 = 0;
     int rc = block_check("aether_bn_act_pool_fwd", S, H, W, C, fH, fW, alpha, &windows4);
     if (rc) return rc;
-    if (!aligned16(x) || !aligned16(pooled) || !aligned16(ws) || (reinterpret_cast<uintptr_t>(argmax) & 3))
+    if (!aligned16(x) || (pooled && !aligned16(pooled)) || !aligned16(ws) || (reinterpret_cast<uintptr_t>(argmax) & 3))
         return set_error(AE_BAD_ARG, "aether_bn_act_pool_fwd: arrays must be 16-byte aligned (argmax: 4)");
     const long long rows = 1LL * S * H * W;
     if (ws_bytes < aether_bn_workspace_bytes(rows, C)) return set_error(AE_BAD_ARG, "aether_bn_act_pool_fwd: workspace too small");
@@ -299,7 +299,8 @@ extern "C" int aether_bn_act_pool_bwd_copy(const float* x, const float* dpooled,
                                            float alpha, const float* channel_scale, void* operand_copy, int copy_ld,
                                            float* colsum_part, int colsum_rows_max, int* colsum_rows, void* ws,
                                            size_t ws_bytes, void* stream) {
-    if (!x || !dpooled || !argmax || !gamma || !beta || !batch_mean || !batch_var || !dx || !dgamma || !dbeta || !ws)
+    if (!x || !dpooled || !argmax || !gamma || !beta || !batch_mean || !batch_var || (!dx && !operand_copy) || !dgamma ||
+        !dbeta || !ws)
         return set_error(AE_BAD_ARG, "aether_bn_act_pool_bwd: null pointer");
     if (operand_copy) {
         if (copy_ld < C || copy_ld % 4 || (reinterpret_cast<uintptr_t>(operand_copy) & 7) || !colsum_part || !colsum_rows ||
@@ -312,7 +313,7 @@ extern "C" int aether_bn_act_pool_bwd_copy(const float* x, const float* dpooled,
     long long windows4 = 0;
     int rc = block_check("aether_bn_act_pool_bwd", S, H, W, C, fH, fW, alpha, &windows4);
     if (rc) return rc;
-    if (!aligned16(x) || !aligned16(dpooled) || !aligned16(dx) || !aligned16(ws) || !aligned16(gamma) || !aligned16(beta) ||
+    if (!aligned16(x) || !aligned16(dpooled) || (dx && !aligned16(dx)) || !aligned16(ws) || !aligned16(gamma) || !aligned16(beta) ||
         !aligned16(batch_mean) || !aligned16(batch_var) || (reinterpret_cast<uintptr_t>(argmax) & 3))
         return set_error(AE_BAD_ARG, "aether_bn_act_pool_bwd: arrays must be 16-byte aligned (argmax: 4)");
     const long long rows = 1LL * S * H * W;

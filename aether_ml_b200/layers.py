@@ -94,6 +94,19 @@ class _OperandCopies:
         return (1 if self._tag(x) == self.x else 0) | (2 if self._tag(w) == self.w else 0)
 
 
+def _mark_unwritten(t):
+    """Marks a device array whose fp32 contents were deliberately not written (lean mode: only its bf16 operand copy
+    exists, inside the consuming layer's workspace).  A layer that would have to READ such an array raises."""
+    t._aether_unwritten = True
+    return t
+
+
+def _require_written(t, who):
+    if getattr(t, "_aether_unwritten", False):
+        raise _lib.AetherError("%s: the input array was not materialised (Model.finalize(lean=True)) and its operand copy is "
+                               "no longer current; run the producing layer again" % who)
+
+
 def _array_tag(t):
     """Identity of a device array's contents as far as the host can tell: address, element count, version counter
     (a reshaped view of the same memory has the same tag)."""
@@ -227,6 +240,8 @@ class Conv_Layer:
         y = _empty((S, Ho, Wo, self.num_filters))
         flags = _lib.CONV_X_COPY_READY if self._handed.x_ready(ws, x) else 0
         self._handed.x = None
+        if not flags:
+            _require_written(x, "Conv_Layer.forward")
         # With emit_bn_stats the kernel's epilogue also writes the per-channel partial statistics that the
         # Batch_Norm behind this layer would otherwise compute in a pass of its own over y (:467-470).
         nblk = int(L.aether_conv2d_bnstats_blocks(C.byref(d))) if (training and self.emit_bn_stats) else 0
@@ -269,6 +284,10 @@ class Conv_Layer:
         self._handed.dy = None
         if rows:
             shadow_ok |= _lib.CONV_DY_COPY_READY
+        else:
+            _require_written(dy, "Conv_Layer.backward")
+        if not (shadow_ok & _lib.CONV_X_COPY_READY) and self.dweights is not None:
+            _require_written(x, "Conv_Layer.backward")
         check(L.aether_conv2d_bwd_ex(C.byref(d), _ptr(x), _ptr(dy), _ptr(self.filter_weights), _ptr(dx),
                                      _ptr(self.dweights), _ptr(self.dbiases), _ptr(ws), ws.numel(), shadow_ok, rows,
                                      _stream()), "aether_conv2d_bwd_ex")
@@ -529,6 +548,7 @@ class Batch_Norm:
         self.fused_dropout = None       # a Layer_Dropout_Spatial behind that activation whose mask is applied here too
         self.fused_pool = None          # a max Pooling behind those whose windows are reduced here too
         self.pooled_now = False         # the last forward produced the pooled tensor
+        self.lean = False               # do not write fp32 tensors whose only reader takes the bf16 copy (finalize(lean=True))
         self.copy_consumer = None       # the layer that reads the pooled tensor as x (its bf16 copy is written here)
         self.copy_dy_consumer = None    # the Conv_Layer in front (the bf16 copy of its dvalues is written here)
         if n_features is not None:
@@ -593,12 +613,15 @@ class Batch_Norm:
                 check(L.aether_bn_act_pool_fwd_copy(_ptr(x), _ptr(part[0]) if part else None, part[1] if part else 0,
                                                     _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
                                                     _ptr(self._bm) if training else None, _ptr(self._bv) if training else None,
-                                                    _ptr(pooled), _ptr(self._pool_arg), S, H, W, Cc, fH, fW,
+                                                    None if (self.lean and target) else _ptr(pooled), _ptr(self._pool_arg),
+                                                    S, H, W, Cc, fH, fW,
                                                     float(self.epsilon), float(self.momentum), float(self.fused_alpha),
                                                     _ptr(mask), 1 if training else 0,
                                                     C.c_void_p(target[0]) if target else None, target[1] if target else 0,
                                                     _ptr(ws), ws.numel(), _stream()), "aether_bn_act_pool_fwd_copy")
                 if target:
+                    if self.lean:
+                        _mark_unwritten(pooled)
                     self.copy_consumer.x_copy_written(pooled)
                 self._fused_mask = mask
                 self.pooled_now = True
@@ -670,13 +693,16 @@ class Batch_Norm:
                                                and Cc // 4 <= 256) else None
             rows = C.c_int(0)
             check(L.aether_bn_act_pool_bwd_copy(_ptr(x), _ptr(dy), _ptr(self._pool_arg), _ptr(self.gamma), _ptr(self.beta),
-                                                _ptr(self._bm), _ptr(self._bv), _ptr(dx), _ptr(self.dweights),
+                                                _ptr(self._bm), _ptr(self._bv), None if (self.lean and target) else _ptr(dx),
+                                                _ptr(self.dweights),
                                                 _ptr(self.dbiases), S, H, W, Cc, fH, fW, float(self.epsilon),
                                                 float(self.fused_alpha), _ptr(getattr(self, "_fused_mask", None)),
                                                 C.c_void_p(target[0]) if target else None, target[1] if target else 0,
                                                 C.c_void_p(target[2]) if target else None, target[3] if target else 0,
                                                 C.byref(rows), _ptr(ws), ws.numel(), _stream()), "aether_bn_act_pool_bwd_copy")
             if target:
+                if self.lean:
+                    _mark_unwritten(dx)
                 conv.dy_copy_written(dx, rows.value)
         elif self.fused_alpha is not None:   # dvalues is the gradient w.r.t. the ACTIVATED output
             check(L.aether_bn_act_bwd(_ptr(x), _ptr(self.beta), _ptr(dy), _ptr(self.gamma), _ptr(self._bm),
@@ -711,6 +737,8 @@ class Flatten:
         x = to_device(inputs)
         self.inputs_shape = x.shape
         self.output = x.reshape(x.shape[0], -1)
+        if getattr(x, "_aether_unwritten", False):
+            _mark_unwritten(self.output)
         return self.output
 
     def backward(self, dvalues):
@@ -773,6 +801,8 @@ class Layer_Dense:
         y = _empty((x.shape[0], self.weights.shape[1]))
         flags = _lib.CONV_X_COPY_READY if self._handed.x_ready(ws, x) else 0
         self._handed.x = None
+        if not flags:
+            _require_written(x, "Layer_Dense.forward")
         check(L.aether_conv2d_fwd_ex(C.byref(d), _ptr(x), _ptr(self.weights), _ptr(self.biases), _ptr(y), None, 0, _ptr(ws),
                                      ws.numel(), flags, _stream()), "aether_conv2d_fwd_ex")
         self.inputs = x
@@ -792,9 +822,11 @@ class Layer_Dense:
             self.dweights = torch.empty_like(self.weights)
             self.dbiases = torch.empty_like(self.biases)
         dx = torch.empty_like(x)
+        copy_flags = self._copies.flags(ws, x, self.weights)
+        if not (copy_flags & _lib.CONV_X_COPY_READY):
+            _require_written(x, "Layer_Dense.backward")
         check(L.aether_conv2d_bwd(C.byref(d), _ptr(x), _ptr(dy), _ptr(self.weights), _ptr(dx), _ptr(self.dweights),
-                                  _ptr(self.dbiases), _ptr(ws), ws.numel(), self._copies.flags(ws, x, self.weights),
-                                  _stream()), "aether_conv2d_bwd")
+                                  _ptr(self.dbiases), _ptr(ws), ws.numel(), copy_flags, _stream()), "aether_conv2d_bwd")
         if self.weight_regularizer_l1 > 0 or self.weight_regularizer_l2 > 0:
             check(L.aether_regularizer_grad(_ptr(self.weights), _ptr(self.dweights), self.weights.numel(),
                                             float(self.weight_regularizer_l1), float(self.weight_regularizer_l2),

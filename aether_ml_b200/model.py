@@ -107,7 +107,14 @@ class Model:
             self.accuracy = accuracy
 
     # ------------------------------------------------------------------ wiring
-    def finalize(self, flat=False, fuse=False):
+    def finalize(self, flat=False, fuse=False, lean=False):
+        """Wires the layers (CNN_model_cupy.py:27-64).  Beyond the reference: `flat` packs parameters and gradients
+        into flat buffers, `fuse` merges each block tail into one pass each way, and `lean` (with `fuse`) stops
+        writing fp32 tensors that only this library's own next kernel would read and that kernel reads as a bf16
+        operand copy anyway: the pooled output of a fused block tail in front of a Conv_Layer / Dense, and the dx of a
+        fused tail behind a tensor-core Conv_Layer.  Parameters, gradients and outputs of the model are the same
+        numbers as without it; the `.output` of such a Pooling and the `.dinputs` of such a Batch_Norm are then
+        placeholders (a layer asked to read one raises)."""
         self.input_layer = Layer_Input()
         chain = [self.input_layer] + self.layers + [self.loss]
         for pos, layer in enumerate(self.layers, start=1):
@@ -148,6 +155,7 @@ class Model:
                         nxt = getattr(nxt, "next", None)
                     if hasattr(nxt, "x_copy_target"):
                         a.copy_consumer = nxt
+                    a.lean = bool(lean)
                     if isinstance(getattr(a, "prev", None), Conv_Layer):
                         a.copy_dy_consumer = a.prev
         self.trainable_layers = [l for l in self.layers if hasattr(l, "weights")]

@@ -509,7 +509,7 @@ def run_sweep(args):
 
 
 # ----------------------------------------------------------------------------------- training workload
-def build_cnn(widen, math_mode, fuse=False):
+def build_cnn(widen, math_mode, fuse=False, lean=False):
     """The CIFAR-shaped 3-block CNN of the reference's README example (CNN/architectures/CNN_cifar1.py:16-55):
     Conv 3->32->64->128 (3x3 same) each with Batch_Norm / ReLU / [spatial dropout] / 2x2 max pool, Dense
     2048->256 LeakyReLU dropout, Dense 256->10, softmax + CCE (label smoothing 0.01), Adam lr 1e-3 decay 5e-5.
@@ -534,11 +534,11 @@ def build_cnn(widen, math_mode, fuse=False):
     m.add(Ly.SoftMax())
     m.set(loss=Ly.Loss_CategoricalCrossEntropy(label_smoothing=0.01),
           optimizer=Ly.Optimizer_Adam(learning_rate=1e-3, decay=5e-5), accuracy=Accuracy_Categorical())
-    m.finalize(flat=True, fuse=fuse)
+    m.finalize(flat=True, fuse=fuse, lean=lean and fuse)
     return m
 
 
-def train_block(args, world, rank, local, widen=4, global_batch=4096, fuse=True, graph=True, steps=None):
+def train_block(args, world, rank, local, widen=4, global_batch=4096, fuse=True, graph=True, steps=None, lean=True):
     """Training images/s of the 3-block CNN (widened 4x by default: channels 128/256/512, Dense 8192->1024->10) at a
     FIXED global batch sharded over the ranks (strong scaling).  One step = forward + loss gradient + backward +
     bucketed all-reduce of the flat gradient buffer (started during backward) + Adam; inputs resident on the device.
@@ -549,7 +549,7 @@ def train_block(args, world, rank, local, widen=4, global_batch=4096, fuse=True,
     dev = torch.device("cuda", local)
     lo, hi = dp.shard_bounds(global_batch, rank, world)
     np.random.seed(7)                                   # same initial parameters on every rank
-    model = build_cnn(widen, args.mode, fuse)
+    model = build_cnn(widen, args.mode, fuse, lean)
     dp.attach(model, buckets=args.buckets)
     g = torch.Generator(device="cpu").manual_seed(3)
     X_host = torch.rand((global_batch, 32, 32, 3), generator=g)[lo:hi].contiguous().pin_memory()
@@ -657,6 +657,7 @@ def train_block(args, world, rank, local, widen=4, global_batch=4096, fuse=True,
         "workload": "train step of the CIFAR-shaped 3-block CNN%s, NHWC (32,32,3) ~ U[0,1), labels uniform in [0,10), Adam lr 1e-3 "
                     "decay 5e-5" % (" widened 4x (128/256/512, Dense 8192->1024->10)" if widen == 4 else ""),
         "params": int(model.flat_params.numel()), "fused_block_tails": bool(fuse), "cuda_graph": note,
+        "lean": bool(lean and fuse),   # fp32 tensors read only as bf16 operand copies by our own next kernel are not written
         "allreduce_buckets": len(model.bucket_reducer.buckets) if world > 1 else 0,
         "allreduce_ms_alone": allreduce_ms, "launches_per_step": int(launches_per_step),
         "e2e_images_per_s": global_batch / (e2e_ms * 1e-3), "e2e_ms_per_step": e2e_ms,
@@ -680,7 +681,7 @@ def run_train(args):
     widen = 4 if args.workload == "train_wide" else 1
     global_batch = args.global_batch or (4096 if widen == 4 else 128)
     res = train_block(args, world, rank, local, widen=widen, global_batch=global_batch, fuse=args.fuse, graph=args.graph,
-                      steps=args.steps)
+                      steps=args.steps, lean=args.lean)
     if rank == 0:
         t = res["train"]
         line = {"metric": "train_images_per_s", "value": t["images_per_s"], "unit": "images/s", "n_gpus": world,
@@ -716,6 +717,8 @@ def main():
     ap.add_argument("--graph", action="store_true", help="--workload train*: replay the step from a captured CUDA graph")
     ap.add_argument("--fuse", action="store_true",
                     help="--workload train*: fused block tails (finalize(fuse=True))")
+    ap.add_argument("--lean", action="store_true",
+                    help="--workload train*: with --fuse, do not write fp32 tensors that only our own next kernel reads (as bf16 copies)")
     ap.add_argument("--buckets", type=int, default=2, help="all-reduce buckets of the flat gradient buffer (1 = one all-reduce after backward)")
     ap.add_argument("--skip-train", action="store_true", help="default workload: omit the `train` block")
     ap.add_argument("--skip-sweep", action="store_true", help="default workload: omit the `sweep` block")

@@ -228,7 +228,8 @@ int aether_bn_act_pool_bwd(const float* x, const float* dpooled, const uint8_t* 
  *   ..._fwd_copy: operand_copy (nullable) = the next layer's copy of x, [S*(H/fH)*(W/fW)][copy_ld] bf16, copy_ld >= C.
  *   ..._bwd_copy: operand_copy (nullable) = the previous convolution's copy of dy, [S*H*W][copy_ld] bf16, together
  *     with one row of column sums of dx per thread block in colsum_part [*colsum_rows <= colsum_rows_max][C]
- *     (needs C/4 to divide 256).  With operand_copy == NULL they are the calls above. */
+ *     (needs C/4 to divide 256).  With operand_copy == NULL they are the calls above.  With an operand copy the fp32
+ *     result itself (pooled / dx) may be NULL: a caller whose next kernel reads only the copy saves that write. */
 int aether_bn_act_pool_fwd_copy(const float* x, const float* partials, int64_t nblocks, const float* gamma,
                                 const float* beta, float* running_mean, float* running_var, float* batch_mean,
                                 float* batch_var, float* pooled, uint8_t* argmax, int S, int H, int W, int C, int fH, int fW,

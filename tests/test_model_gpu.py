@@ -477,3 +477,49 @@ def test_block_tail_hands_operand_copies_to_neighbouring_layers(env):
     ref = Ly.Conv_Layer((8, 8, 64), 96, (3, 3), (1, 1), "same", math_mode="bf16")
     ref.set_parameters(conv2.filter_weights, conv2.biases)
     assert torch.equal(ref.forward(other, True), conv2.output)
+
+
+def test_lean_mode_trains_to_the_same_parameters(env):
+    """finalize(fuse=True, lean=True): fp32 tensors that only this library's next kernel would read -- and reads as a
+    bf16 operand copy -- are not written.  The tensor cores get the same operands, so parameters, gradients and
+    predictions are the same numbers; the skipped arrays are placeholders that a layer refuses to read."""
+    torch, _lib, Ly, M = env
+    rng = np.random.default_rng(6)
+
+    def make(lean):
+        np.random.seed(33)
+        m = M.Model()
+        c_in, hw = 16, 16
+        for c_out in (64, 128):
+            m.add(Ly.Conv_Layer((hw, hw, c_in), c_out, (3, 3), (1, 1), "same", math_mode="bf16"))
+            m.add(Ly.Batch_Norm(n_features=c_out))
+            m.add(Ly.ReLU())
+            m.add(Ly.Pooling((2, 2), (2, 2), "valid", "max"))
+            c_in, hw = c_out, hw // 2
+        m.add(Ly.Flatten())
+        m.add(Ly.Layer_Dense(4 * 4 * 128, 64, math_mode="bf16"))
+        m.add(Ly.Layer_Dense(64, 10, math_mode="bf16"))
+        m.add(Ly.SoftMax())
+        m.set(loss=Ly.Loss_CategoricalCrossEntropy(label_smoothing=0.01), optimizer=Ly.Optimizer_Adam(learning_rate=1e-3),
+              accuracy=M.Accuracy_Categorical())
+        m.finalize(flat=True, fuse=True, lean=lean)
+        return m
+
+    lean, full = make(True), make(False)
+    for _ in range(3):
+        X = rng.standard_normal((8, 16, 16, 16)).astype(np.float32)
+        y = rng.integers(0, 10, 8)
+        lean.train_step(X, y)
+        full.train_step(X, y)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert torch.equal(lean.flat_params, full.flat_params)
+    assert torch.equal(lean.flat_grads, full.flat_grads)
+    Xe = rng.standard_normal((8, 16, 16, 16)).astype(np.float32)
+    assert torch.equal(lean.predict(Xe), full.predict(Xe))
+    # the placeholders: the first tail's pooled output (x of conv 2) and the second tail's dx (dvalues of conv 2)
+    bn1, bn2 = [l for l in lean.layers if isinstance(l, Ly.Batch_Norm)]
+    assert getattr(bn1.output, "_aether_unwritten", False) and getattr(bn2.dinputs, "_aether_unwritten", False)
+    foreign = Ly.Conv_Layer((8, 8, 64), 32, math_mode="bf16")
+    with pytest.raises(_lib.AetherError):
+        foreign.forward(bn1.output, True)                             # no copy of it in THAT layer's workspace

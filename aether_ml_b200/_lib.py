@@ -59,9 +59,9 @@ SIGNATURES = {
     "aether_conv2d_fwd_ex": (_I, [_D, _P, _P, _P, _P, _P, _SZ, _P, _SZ, _I, _P]),
     "aether_conv2d_bwd_ex": (_I, [_D, _P, _P, _P, _P, _P, _P, _P, _SZ, _I, _I, _P]),
     "aether_bn_act_pool_fwd_copy": (_I, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _F, _P,
-                                         _I, _P, _I, _P, _SZ, _P]),
+                                         _I, _P, _I, _P, _P, _SZ, _P]),
     "aether_bn_act_pool_bwd_copy": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P, _I,
-                                         _P, _I, C.POINTER(C.c_int), _P, _SZ, _P]),
+                                         _P, _I, C.POINTER(C.c_int), _P, _P, _SZ, _P]),
     "aether_bn_act_fwd_train": (_I, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _F, _P, _P, _SZ, _P]),
     "aether_bn_act_fwd_eval": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _SZ, _P]),
     "aether_bn_act_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I, _F, _F, _P, _P, _SZ, _P]),

@@ -39,7 +39,8 @@ __global__ void __launch_bounds__(256) bn_act_pool_fwd_kernel(const float* __res
                                                               const float* __restrict__ shift, float alpha,
                                                               float* __restrict__ y, uint8_t* __restrict__ arg,
                                                               unsigned total, int W, int C4, int fH_, int fW_, int Wo,
-                                                              __nv_bfloat16* __restrict__ copy, int copy_ld) {
+                                                              __nv_bfloat16* __restrict__ copy, int copy_ld,
+                                                              float* __restrict__ xsel) {
     const int fH = F ? F : fH_, fW = F ? F : fW_;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
         const unsigned cv = idx % (unsigned)C4;
@@ -50,7 +51,7 @@ __global__ void __launch_bounds__(256) bn_act_pool_fwd_kernel(const float* __res
         const float4 s = *reinterpret_cast<const float4*>(scale + cv * 4);
         const float4 t = *reinterpret_cast<const float4*>(shift + cv * 4);
         const float4* in = reinterpret_cast<const float4*>(x) + ((size_t)pix * fH * W + (size_t)wo * fW) * C4 + cv;
-        float4 best = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 best = make_float4(0.f, 0.f, 0.f, 0.f), sel = best;     // sel: the input value at the selected cell
         uchar4 code = make_uchar4(0, 0, 0, 0);
         float4 pre[F ? F * F : 1];
         if (F) {
@@ -68,16 +69,79 @@ __global__ void __launch_bounds__(256) bn_act_pool_fwd_kernel(const float* __res
                 const unsigned char k = (unsigned char)(i * fW + j);
                 if (k == 0) {
                     best = o;
+                    sel = v;
                 } else {                                      // first maximum in row-major window order, as Pooling
-                    if (o.x > best.x) { best.x = o.x; code.x = k; }
-                    if (o.y > best.y) { best.y = o.y; code.y = k; }
-                    if (o.z > best.z) { best.z = o.z; code.z = k; }
-                    if (o.w > best.w) { best.w = o.w; code.w = k; }
+                    if (o.x > best.x) { best.x = o.x; code.x = k; sel.x = v.x; }
+                    if (o.y > best.y) { best.y = o.y; code.y = k; sel.y = v.y; }
+                    if (o.z > best.z) { best.z = o.z; code.z = k; sel.z = v.z; }
+                    if (o.w > best.w) { best.w = o.w; code.w = k; sel.w = v.w; }
                 }
             }
         if (y != nullptr) reinterpret_cast<float4*>(y)[idx] = best;       // not written when only the bf16 copy is wanted
         reinterpret_cast<uchar4*>(arg)[idx] = code;
         if (copy != nullptr) store_operand_copy(copy, copy_ld, opix, (int)cv, C4, best);
+        if (xsel != nullptr) reinterpret_cast<float4*>(xsel)[idx] = sel;
+    }
+}
+
+// The backward statistics pass when the forward pass kept the input value at every window's selected cell (xsel,
+// shaped like the pooled tensor): only that cell has a gradient, so sum(g) and sum(g * xhat) need xsel and d_pooled
+// alone -- half of |x| in coalesced reads instead of all of x gathered cell by cell.  part[block][2][C].
+__global__ void __launch_bounds__(256) bn_act_pool_bwd_reduce_sel_kernel(
+    const float* __restrict__ xsel, const float* __restrict__ dpool, const float* __restrict__ gamma,
+    const float* __restrict__ beta, const float* __restrict__ mean, const float* __restrict__ var, float eps, float alpha,
+    long long windows, long long win_per_block, int C, float* __restrict__ part) {
+    const long long w0 = blockIdx.x * win_per_block;
+    long long w1 = w0 + win_per_block;
+    if (w1 > windows) w1 = windows;
+    const int CV = C >> 2;
+    const int cols = CV < 256 ? CV : 256;
+    const int lanes = 256 / cols;
+    __shared__ float4 sh_a4[256], sh_b4[256];
+    for (int cbase = 0; cbase < CV; cbase += cols) {
+        const int cv = cbase + threadIdx.x % cols;
+        const int rl = threadIdx.x / cols;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (rl < lanes && cv < CV) {
+            const int c = cv * 4;
+            const float4 mu = *reinterpret_cast<const float4*>(mean + c);
+            const float4 vr = *reinterpret_cast<const float4*>(var + c);
+            const float4 inv = make_float4(rsqrtf(vr.x + eps), rsqrtf(vr.y + eps), rsqrtf(vr.z + eps), rsqrtf(vr.w + eps));
+            const float4 ga = *reinterpret_cast<const float4*>(gamma + c);
+            const float4 be = *reinterpret_cast<const float4*>(beta + c);
+            const float4* gp = reinterpret_cast<const float4*>(dpool) + cv;
+            const float4* xp = reinterpret_cast<const float4*>(xsel) + cv;
+#pragma unroll 4
+            for (long long wdx = w0 + rl; wdx < w1; wdx += lanes) {
+                const float4 g = __ldcs(gp + (size_t)wdx * CV);
+                const float4 v = __ldcs(xp + (size_t)wdx * CV);
+                const float hx = (v.x - mu.x) * inv.x, hy = (v.y - mu.y) * inv.y;
+                const float hz = (v.z - mu.z) * inv.z, hw = (v.w - mu.w) * inv.w;
+                const float gx = g.x * lrelu_grad(fmaf(ga.x, hx, be.x), alpha), gy = g.y * lrelu_grad(fmaf(ga.y, hy, be.y), alpha);
+                const float gz = g.z * lrelu_grad(fmaf(ga.z, hz, be.z), alpha), gw = g.w * lrelu_grad(fmaf(ga.w, hw, be.w), alpha);
+                a.x += gx; a.y += gy; a.z += gz; a.w += gw;
+                b.x = fmaf(gx, hx, b.x); b.y = fmaf(gy, hy, b.y); b.z = fmaf(gz, hz, b.z); b.w = fmaf(gw, hw, b.w);
+            }
+        }
+        sh_a4[threadIdx.x] = a;
+        sh_b4[threadIdx.x] = b;
+        __syncthreads();
+        if (threadIdx.x < cols && cv < CV) {
+            float* out = part + (size_t)blockIdx.x * 2 * C + cv * 4;
+            const float* pa = reinterpret_cast<const float*>(sh_a4);
+            const float* pb = reinterpret_cast<const float*>(sh_b4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float sa = 0.f, sb = 0.f;
+                for (int l = 0; l < lanes; ++l) {
+                    sa += pa[(l * cols + threadIdx.x) * 4 + k];
+                    sb += pb[(l * cols + threadIdx.x) * 4 + k];
+                }
+                out[k] = sa;
+                out[C + k] = sb;
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -247,7 +311,7 @@ extern "C" int aether_bn_act_pool_fwd(const float* x, const float* partials, int
                                       int training, void* ws, size_t ws_bytes, void* stream) {
     return aether_bn_act_pool_fwd_copy(x, partials, nblocks, gamma, beta, running_mean, running_var, batch_mean, batch_var,
                                        pooled, argmax, S, H, W, C, fH, fW, eps, momentum, alpha, channel_scale, training,
-                                       nullptr, 0, ws, ws_bytes, stream);
+                                       nullptr, 0, nullptr, ws, ws_bytes, stream);
 }
 
 extern "C" int aether_bn_act_pool_fwd_copy(const float* x, const float* partials, int64_t nblocks, const float* gamma,
@@ -255,12 +319,13 @@ extern "C" int aether_bn_act_pool_fwd_copy(const float* x, const float* partials
                                            float* batch_var, float* pooled, uint8_t* argmax, int S, int H, int W, int C,
                                            int fH, int fW, float eps, float momentum, float alpha,
                                            const float* channel_scale, int training, void* operand_copy, int copy_ld,
-                                           void* ws, size_t ws_bytes, void* stream) {
+                                           float* selected_x, void* ws, size_t ws_bytes, void* stream) {
     if (!x || !gamma || !beta || !running_mean || !running_var || (!pooled && !operand_copy) || !argmax || !ws ||
         (training && (!batch_mean || !batch_var)))
         return set_error(AE_BAD_ARG, "aether_bn_act_pool_fwd: null pointer");
     if (operand_copy && (copy_ld < C || copy_ld % 4 || (reinterpret_cast<uintptr_t>(operand_copy) & 7)))
         return set_error(AE_BAD_ARG, "aether_bn_act_pool_fwd_copy: operand copy needs ld >= C, ld %% 4 == 0, 8-byte alignment");
+    if (selected_x && !aligned16(selected_x)) return set_error(AE_BAD_ARG, "aether_bn_act_pool_fwd_copy: selected_x must be 16-byte aligned");
     long long windows4 = 0;
     int rc = block_check("aether_bn_act_pool_fwd", S, H, W, C, fH, fW, alpha, &windows4);
     if (rc) return rc;
@@ -277,10 +342,10 @@ extern "C" int aether_bn_act_pool_fwd_copy(const float* x, const float* partials
     __nv_bfloat16* copy = static_cast<__nv_bfloat16*>(operand_copy);
     if (fH == 2 && fW == 2)
         bn_act_pool_fwd_kernel<2><<<fb, 256, 0, st>>>(x, coeff, coeff + C, alpha, pooled, argmax, (unsigned)windows4, W, C / 4,
-                                                     fH, fW, W / fW, copy, copy_ld);
+                                                     fH, fW, W / fW, copy, copy_ld, selected_x);
     else
         bn_act_pool_fwd_kernel<0><<<fb, 256, 0, st>>>(x, coeff, coeff + C, alpha, pooled, argmax, (unsigned)windows4, W, C / 4,
-                                                     fH, fW, W / fW, copy, copy_ld);
+                                                     fH, fW, W / fW, copy, copy_ld, selected_x);
     count_launch();
     return check_launch("aether_bn_act_pool_fwd");
 }
@@ -290,15 +355,15 @@ extern "C" int aether_bn_act_pool_bwd(const float* x, const float* dpooled, cons
                                       float* dgamma, float* dbeta, int S, int H, int W, int C, int fH, int fW, float eps,
                                       float alpha, const float* channel_scale, void* ws, size_t ws_bytes, void* stream) {
     return aether_bn_act_pool_bwd_copy(x, dpooled, argmax, gamma, beta, batch_mean, batch_var, dx, dgamma, dbeta, S, H, W, C, fH,
-                                       fW, eps, alpha, channel_scale, nullptr, 0, nullptr, 0, nullptr, ws, ws_bytes, stream);
+                                       fW, eps, alpha, channel_scale, nullptr, 0, nullptr, 0, nullptr, nullptr, ws, ws_bytes, stream);
 }
 
 extern "C" int aether_bn_act_pool_bwd_copy(const float* x, const float* dpooled, const uint8_t* argmax, const float* gamma,
                                            const float* beta, const float* batch_mean, const float* batch_var, float* dx,
                                            float* dgamma, float* dbeta, int S, int H, int W, int C, int fH, int fW, float eps,
                                            float alpha, const float* channel_scale, void* operand_copy, int copy_ld,
-                                           float* colsum_part, int colsum_rows_max, int* colsum_rows, void* ws,
-                                           size_t ws_bytes, void* stream) {
+                                           float* colsum_part, int colsum_rows_max, int* colsum_rows,
+                                           const float* selected_x, void* ws, size_t ws_bytes, void* stream) {
     if (!x || !dpooled || !argmax || !gamma || !beta || !batch_mean || !batch_var || (!dx && !operand_copy) || !dgamma ||
         !dbeta || !ws)
         return set_error(AE_BAD_ARG, "aether_bn_act_pool_bwd: null pointer");
@@ -324,8 +389,14 @@ extern "C" int aether_bn_act_pool_bwd_copy(const float* x, const float* dpooled,
     if (nb > windows) nb = (int)windows;
     float* part = static_cast<float*>(ws);
     float* coeff = part + (size_t)bn_partial_blocks(rows) * 3 * C;
-    bn_act_pool_bwd_reduce_kernel<<<nb, 256, 0, st>>>(x, dpooled, argmax, gamma, beta, batch_mean, batch_var, eps, alpha, windows,
-                                                      (windows + nb - 1) / nb, W, C, fH, fW, W / fW, part);
+    if (selected_x) {
+        if (!aligned16(selected_x)) return set_error(AE_BAD_ARG, "aether_bn_act_pool_bwd_copy: selected_x must be 16-byte aligned");
+        bn_act_pool_bwd_reduce_sel_kernel<<<nb, 256, 0, st>>>(selected_x, dpooled, gamma, beta, batch_mean, batch_var, eps, alpha,
+                                                              windows, (windows + nb - 1) / nb, C, part);
+    } else {
+        bn_act_pool_bwd_reduce_kernel<<<nb, 256, 0, st>>>(x, dpooled, argmax, gamma, beta, batch_mean, batch_var, eps, alpha, windows,
+                                                          (windows + nb - 1) / nb, W, C, fH, fW, W / fW, part);
+    }
     count_launch();
     bn_backward_coeffs(part, nb, C, rows, gamma, batch_mean, batch_var, eps, dgamma, dbeta, coeff, channel_scale, st);
     int fb = fused_blocks(windows4, 256, 16);

@@ -610,6 +610,8 @@ class Batch_Norm:
                 self._pool_arg = _empty((S, H // fH, W // fW, Cc), torch.uint8)
                 # the layer behind the pooling reads a bf16 copy of the pooled tensor: written by this same pass
                 target = self.copy_consumer.x_copy_target(tuple(pooled.shape)) if self.copy_consumer is not None else None
+                # x at every window's selected cell, for the backward statistics pass (training only)
+                self._xsel = _empty(tuple(pooled.shape)) if training else None
                 check(L.aether_bn_act_pool_fwd_copy(_ptr(x), _ptr(part[0]) if part else None, part[1] if part else 0,
                                                     _ptr(self.gamma), _ptr(self.beta), _ptr(self._rm), _ptr(self._rv),
                                                     _ptr(self._bm) if training else None, _ptr(self._bv) if training else None,
@@ -618,7 +620,8 @@ class Batch_Norm:
                                                     float(self.epsilon), float(self.momentum), float(self.fused_alpha),
                                                     _ptr(mask), 1 if training else 0,
                                                     C.c_void_p(target[0]) if target else None, target[1] if target else 0,
-                                                    _ptr(ws), ws.numel(), _stream()), "aether_bn_act_pool_fwd_copy")
+                                                    _ptr(self._xsel), _ptr(ws), ws.numel(), _stream()),
+                      "aether_bn_act_pool_fwd_copy")
                 if target:
                     if self.lean:
                         _mark_unwritten(pooled)
@@ -699,7 +702,8 @@ class Batch_Norm:
                                                 float(self.fused_alpha), _ptr(getattr(self, "_fused_mask", None)),
                                                 C.c_void_p(target[0]) if target else None, target[1] if target else 0,
                                                 C.c_void_p(target[2]) if target else None, target[3] if target else 0,
-                                                C.byref(rows), _ptr(ws), ws.numel(), _stream()), "aether_bn_act_pool_bwd_copy")
+                                                C.byref(rows), _ptr(getattr(self, "_xsel", None)), _ptr(ws), ws.numel(),
+                                                _stream()), "aether_bn_act_pool_bwd_copy")
             if target:
                 if self.lean:
                     _mark_unwritten(dx)

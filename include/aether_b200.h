@@ -229,17 +229,21 @@ int aether_bn_act_pool_bwd(const float* x, const float* dpooled, const uint8_t* 
  *   ..._bwd_copy: operand_copy (nullable) = the previous convolution's copy of dy, [S*H*W][copy_ld] bf16, together
  *     with one row of column sums of dx per thread block in colsum_part [*colsum_rows <= colsum_rows_max][C]
  *     (needs C/4 to divide 256).  With operand_copy == NULL they are the calls above.  With an operand copy the fp32
- *     result itself (pooled / dx) may be NULL: a caller whose next kernel reads only the copy saves that write. */
+ *     result itself (pooled / dx) may be NULL: a caller whose next kernel reads only the copy saves that write.
+ *   selected_x (nullable, float, shaped like the pooled tensor): the forward pass stores x at every window's selected
+ *     cell; given back to the backward pass, its statistics pass reads that and dpooled (half of |x|) instead of
+ *     gathering all of x.  Same sums: only the selected cell of a window has a gradient. */
 int aether_bn_act_pool_fwd_copy(const float* x, const float* partials, int64_t nblocks, const float* gamma,
                                 const float* beta, float* running_mean, float* running_var, float* batch_mean,
                                 float* batch_var, float* pooled, uint8_t* argmax, int S, int H, int W, int C, int fH, int fW,
                                 float eps, float momentum, float alpha, const float* channel_scale, int training,
-                                void* operand_copy, int copy_ld, void* ws, size_t ws_bytes, void* stream);
+                                void* operand_copy, int copy_ld, float* selected_x, void* ws, size_t ws_bytes, void* stream);
 int aether_bn_act_pool_bwd_copy(const float* x, const float* dpooled, const uint8_t* argmax, const float* gamma,
                                 const float* beta, const float* batch_mean, const float* batch_var, float* dx, float* dgamma,
                                 float* dbeta, int S, int H, int W, int C, int fH, int fW, float eps, float alpha,
                                 const float* channel_scale, void* operand_copy, int copy_ld, float* colsum_part,
-                                int colsum_rows_max, int* colsum_rows, void* ws, size_t ws_bytes, void* stream);
+                                int colsum_rows_max, int* colsum_rows, const float* selected_x, void* ws, size_t ws_bytes,
+                                void* stream);
 
 /* ---- Pooling, 'valid' padding (CNN_classes_cupy.py:204-312) ---------------------------------- */
 /* Forward :212-273.  argmax (uint8, same shape as y; max pooling only) receives i*fW+j of the first

@@ -165,3 +165,50 @@ def test_guard_bands_around_block_tail(env):
     for a in (x, gamma, beta, rm, rv, bm, bv, dgamma, dbeta, pooled, arg, dyp, dx, ws):
         assert a.intact()
     assert not bool((pooled.t.view(torch.int32) == POISON).any()) and not bool((dx.t.view(torch.int32) == POISON).any())
+
+
+def test_guard_bands_around_block_tail_with_operand_copies(env):
+    """The same passes in their hand-off form: bf16 operand copies (rows padded from 32 to 64 channels),
+    column sums, the selected-cell values, and the fp32 results left out (NULL) -- every buffer between poisoned bands."""
+    torch, _lib = env
+    L = _lib.lib()
+    S, H, W, Cc, ld = 3, 10, 6, 32, 64
+    rng = np.random.default_rng(6)
+    xh = rng.standard_normal((S, H, W, Cc)).astype(np.float32)
+    x = Banded(torch, xh.size, torch.float32, torch.from_numpy(xh).cuda())
+    vec = lambda v: Banded(torch, Cc, torch.float32, torch.from_numpy(np.asarray(v, np.float32)).cuda())
+    gamma, beta = vec(rng.random(Cc) + 0.5), vec(rng.standard_normal(Cc))
+    rm, rv, bm, bv = vec(np.zeros(Cc)), vec(np.ones(Cc)), vec(np.zeros(Cc)), vec(np.zeros(Cc))
+    dgamma, dbeta = vec(np.zeros(Cc)), vec(np.zeros(Cc))
+    n_win = S * (H // 2) * (W // 2)
+    arg = Banded(torch, n_win * Cc, torch.uint8)
+    xsel = Banded(torch, n_win * Cc, torch.float32)
+    copy_f = Banded(torch, n_win * ld * 2, torch.uint8)               # bf16 [windows][ld]
+    copy_b = Banded(torch, S * H * W * ld * 2, torch.uint8)           # bf16 [pixels][ld]
+    rows_max = 8
+    colsum = Banded(torch, rows_max * Cc, torch.float32)
+    dyp = Banded(torch, n_win * Cc, torch.float32, torch.from_numpy(rng.standard_normal(n_win * Cc).astype(np.float32)).cuda())
+    ws = Banded(torch, int(L.aether_bn_workspace_bytes(S * H * W, Cc)), torch.uint8)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = L.aether_bn_act_pool_fwd_copy(_ptr(x.t), None, 0, _ptr(gamma.t), _ptr(beta.t), _ptr(rm.t), _ptr(rv.t), _ptr(bm.t),
+                                       _ptr(bv.t), None, _ptr(arg.t), S, H, W, Cc, 2, 2, 1e-5, 0.9, 0.0, None, 1,
+                                       _ptr(copy_f.t), ld, _ptr(xsel.t), _ptr(ws.t), ws.t.numel(), stream)
+    assert rc == 0, L.aether_last_error()
+    rows = C.c_int(0)
+    rc = L.aether_bn_act_pool_bwd_copy(_ptr(x.t), _ptr(dyp.t), _ptr(arg.t), _ptr(gamma.t), _ptr(beta.t), _ptr(bm.t), _ptr(bv.t),
+                                       None, _ptr(dgamma.t), _ptr(dbeta.t), S, H, W, Cc, 2, 2, 1e-5, 0.0, None, _ptr(copy_b.t), ld,
+                                       _ptr(colsum.t), rows_max, C.byref(rows), _ptr(xsel.t), _ptr(ws.t), ws.t.numel(), stream)
+    assert rc == 0, L.aether_last_error()
+    torch.cuda.synchronize()
+    assert 1 <= rows.value <= rows_max
+    for a in (x, gamma, beta, rm, rv, bm, bv, dgamma, dbeta, arg, xsel, copy_f, copy_b, colsum, dyp, ws):
+        assert a.intact()
+    # the copies: values in the first Cc channels of every row, zeros in the padding
+    cf = copy_f.t.view(torch.bfloat16).view(n_win, ld).float()
+    cb = copy_b.t.view(torch.bfloat16).view(S * H * W, ld).float()
+    assert float(cf[:, Cc:].abs().max()) == 0.0 and float(cb[:, Cc:].abs().max()) == 0.0
+    assert float(cf[:, :Cc].abs().max()) > 0.0 and float(cb[:, :Cc].abs().max()) > 0.0
+    # column sums of the dx that was never written as fp32: compare with the copy's own column sums (bf16 rounding)
+    got = colsum.t.view(rows_max, Cc)[:rows.value].sum(dim=0)
+    want = cb[:, :Cc].sum(dim=0)
+    assert float((got - want).abs().max()) <= 2e-2 * float(cb.abs().sum(dim=0).max())

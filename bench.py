@@ -177,14 +177,11 @@ def run_reference(args):
     s = SHAPE
     threads = cpu_threads()
     images = CPU_IMAGES_PER_THREAD * threads
-    for _ in range(args.warmup):
-        cpu_conv_sample(images, threads)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_conv_sample(images, threads)
-    dt = time.perf_counter() - t0
-    fl = conv_flops(images, s["H"], s["W"], s["Cin"], s["Cout"], s["f"]) * args.steps
-    val = fl / dt / 1e12
+    if args.warmup:
+        cpu_conv_sample(images, threads, 1e9, args.warmup)
+    # exactly `steps` passes over one sample; only the passes are timed (not the generation of the sample), as in
+    # the cpu_baseline leg of the GPU arm
+    val, dt, _ = cpu_conv_sample(images, threads, 1e9, args.steps)
     sample = ("%d images of the workload shape per step (%d per worker thread), NumPy einsum over strided windows in float32 "
               "(the reference's algorithm) on %d worker threads" % (images, CPU_IMAGES_PER_THREAD, threads))
     line = {

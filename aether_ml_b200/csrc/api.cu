@@ -182,6 +182,10 @@ extern "C" size_t aether_conv2d_workspace_bytes(const AetherConvDesc* d) {
         size_t s = smallc_conv_workspace_bytes(*d);
         if (s > g) g = s;
     }
+    if (first_tc_bwd_eligible(*d)) {
+        size_t s = first_tc_bwd_workspace_bytes(*d);
+        if (s > g) g = s;
+    }
     if (tc_conv_eligible(*d)) {
         size_t t = tc_conv_workspace_bytes(*d);
         return t > g ? t : g;
@@ -193,7 +197,8 @@ extern "C" int aether_conv2d_operand_layout(const AetherConvDesc* d, AetherOpera
     if (!out) return 0;
     memset(out, 0, sizeof(*out));
     if (validate_desc(d, "aether_conv2d_operand_layout")) return 0;
-    return tc_conv_operand_layout(*d, out) ? 1 : 0;
+    if (tc_conv_eligible(*d)) return tc_conv_operand_layout(*d, out) ? 1 : 0;
+    return first_tc_operand_layout(*d, out) ? 1 : 0;       // first layers: a copy of dy only (x_copy_ld == 0)
 }
 
 extern "C" int aether_conv2d_fwd_ex(const AetherConvDesc* d, const float* x, const float* w, const float* b, float* y,
@@ -280,12 +285,14 @@ extern "C" int aether_conv2d_bwd_ex(const AetherConvDesc* d, const float* x, con
         return set_error(AE_BAD_ARG, "aether_conv2d_bwd: arrays must be 16-byte aligned");
     if ((rc = pending_timeout("aether_conv2d_bwd"))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if ((x_shadow_valid & AETHER_CONV_DY_COPY_READY) && !(tc_conv_eligible(*d) && d->math_mode == AETHER_MATH_BF16))
-        return set_error(AE_UNSUPPORTED, "aether_conv2d_bwd_ex: this shape / math mode reads no operand copy of dy "
-                                         "(aether_conv2d_operand_layout returned 0)");
+    const bool dy_ready = (x_shadow_valid & AETHER_CONV_DY_COPY_READY) != 0;
+    if (dy_ready && !((tc_conv_eligible(*d) && d->math_mode == AETHER_MATH_BF16) || (first_tc_bwd_eligible(*d) && !dx && dw)))
+        return set_error(AE_UNSUPPORTED, "aether_conv2d_bwd_ex: this shape / math mode / request reads no operand copy of dy "
+                                         "(aether_conv2d_operand_layout returned 0, or a first layer asked for dx)");
     if (tc_conv_eligible(*d)) return tc_conv_bwd(*d, x, dy, w, dx, dw, db, ws, ws_bytes, x_shadow_valid, dy_colsum_rows, st);
     if (dx && (rc = generic_conv_bwd_data(*d, dy, w, dx, st))) return rc;
-    if (dw && first_tc_bwd_eligible(*d)) return first_tc_bwd_filter(*d, x, dy, dw, db, ws, ws_bytes, st);
+    if (dw && first_tc_bwd_eligible(*d))
+        return first_tc_bwd_filter(*d, x, dy, dw, db, ws, ws_bytes, dy_ready ? dy_colsum_rows : 0, st);
     if ((dw || db) && smallc_conv_eligible(*d) && (!db || aligned16(db)))
         return smallc_conv_bwd_filter(*d, x, dy, dw, db, ws, ws_bytes, st);
     if (dw || db) return generic_conv_bwd_filter(*d, x, dy, dw, db, ws, ws_bytes, st);

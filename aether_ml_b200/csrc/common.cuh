@@ -85,7 +85,11 @@ int first_tc_fwd(const AetherConvDesc& d, const float* x, const float* w, const 
                  cudaStream_t st);
 bool first_tc_bwd_eligible(const AetherConvDesc& d);
 int first_tc_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy, float* dw, float* db, void* ws,
-                        size_t ws_bytes, cudaStream_t st);
+                        size_t ws_bytes, int dy_colsum_rows, cudaStream_t st);
+size_t first_tc_bwd_workspace_bytes(const AetherConvDesc& d);
+bool first_tc_operand_layout(const AetherConvDesc& d, AetherOperandLayout* out);
+// out[c] = sum over `rows` rows of part[row][C] in fixed order (conv_tc.cu)
+int colsum_finish(const float* part, int rows, int C, float* out, cudaStream_t st);
 int smallc_reduce_partials(const float* part, int nb, int K, int Cout, float* dw, float* db, cudaStream_t st);
 
 // ---- conv_tc.cu : tcgen05 implicit-GEMM convolution (stride 1)

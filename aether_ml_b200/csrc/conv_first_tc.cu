@@ -17,6 +17,7 @@
 #include "sm100_ptx.cuh"
 #include "stats_epilogue.cuh"
 #include "tc_host.cuh"
+#include "tc_host.cuh"
 
 namespace aether {
 
@@ -387,6 +388,11 @@ struct FirstDwParams {
     long long P;
     int stages, ntiles, stage_bytes;
     int groups;          // producer groups (divides FD_NP; <= stages)
+    // dy handed in as a bf16 copy [P][dy_ld] by the kernel that produced it (aether_conv2d_operand_layout): TMA brings
+    // the tile in already in operand form, the producers only gather the col tile, and dB comes from the column sums
+    // that arrived with the copy
+    CUtensorMap tm_dy;   // (dy_ld, P), box (64 channels, 128 pixels), 128-byte swizzle
+    int dy_bf16;
 };
 
 // Twelve producer warps: with one producer warp per scheduler every round of dy loads costs a full HBM round trip
@@ -422,11 +428,12 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            mbar_init(full_bar(s), FD_NP / p.groups);
+            mbar_init(full_bar(s), FD_NP / p.groups + (p.dy_bf16 ? 1 : 0));    // + the thread that posts the TMA bytes
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(done_bar, 1);
         mbar_fence_init();
+        if (p.dy_bf16) tma_prefetch_desc(&p.tm_dy);
     }
     for (int k = threadIdx.x; k < 64; k += blockDim.x) {
         const int kk = k < p.K ? k : 0;
@@ -482,7 +489,15 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
             // dy tile first (the long-latency loads): rows = pixels, 64-channel chunks of 128 bytes; chunk region c64
             // starts at 16 KB * (1 + c64).  All loads of a round are issued before the first use.
             uint8_t* reg = stage + FT_STAGE_BYTES * (1 + (my_chunk >> 3));
-            for (int pr0 = prow0; pr0 < 128; pr0 += FD_ROWS * prow_step) {
+            if (p.dy_bf16 && rg == 0) {
+                // the tile of the bf16 copy: one box per 64-channel chunk, rows past the last pixel are zero filled
+                const int real_chunks = (p.Cout + 63) >> 6;
+                mbar_arrive_expect_tx(full_bar(s), (uint32_t)real_chunks * FT_STAGE_BYTES);
+                for (int c64 = 0; c64 < real_chunks; ++c64)
+                    tma_load_2d(smem_base + (uint32_t)s * p.stage_bytes + FT_STAGE_BYTES * (1 + c64), &p.tm_dy, full_bar(s),
+                                c64 * 64, (int)pix0);
+            }
+            for (int pr0 = prow0; pr0 < 128 && !p.dy_bf16; pr0 += FD_ROWS * prow_step) {
                 float4 a[FD_ROWS], b[FD_ROWS];
 #pragma unroll
                 for (int u = 0; u < FD_ROWS; ++u) {
@@ -538,7 +553,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) first_dw_kernel(const __grid_co
 #pragma unroll
         for (int e = 0; e < 8; ++e) dbsum_s[r * 8 + e] = bs[e];
         named_bar_sync(1, FD_NP);
-        for (int c = r; c < p.Cout; c += FD_NP) {
+        for (int c = r; c < p.Cout; c += FD_NP) {          // (all zero when dy came as a copy: dB is taken elsewhere)
             const int ck = c >> 3, e = c & 7;
             float tsum = 0.f;
             for (int th = ck; th < FD_NP; th += C8) tsum += dbsum_s[th * 8 + e];
@@ -674,8 +689,44 @@ bool first_tc_bwd_eligible(const AetherConvDesc& d) {
     return first_tc_eligible(d) && smallc_conv_eligible(d) && d.Cout % 8 == 0;
 }
 
+// Workspace of the first-layer filter gradient: the per-CTA partials, then room for a bf16 copy of dy handed in by its
+// producer ([P][ld], ld = Cout padded to 64) and for the column sums that come with it.
+struct FirstDwLayout {
+    size_t part_bytes, dy_off, colsum_off, total;
+    int ld, rows_max;
+};
+static FirstDwLayout first_dw_layout(const AetherConvDesc& d, int K, long long P) {
+    FirstDwLayout l;
+    l.part_bytes = align_up((size_t)first_tc_grid((P + 127) / 128) * (K + 1) * d.Cout * sizeof(float), 1024);
+    l.ld = (d.Cout + 63) / 64 * 64;
+    l.dy_off = l.part_bytes;
+    l.colsum_off = l.dy_off + align_up((size_t)P * l.ld * 2, 1024);
+    l.rows_max = 8 * num_sms();
+    l.total = l.colsum_off + align_up((size_t)l.rows_max * d.Cout * sizeof(float), 1024);
+    return l;
+}
+
+size_t first_tc_bwd_workspace_bytes(const AetherConvDesc& d) {
+    int K, KP, NT, Ho, Wo;
+    if (!first_tc_bwd_eligible(d) || !first_tc_shape(d, K, KP, NT, Ho, Wo)) return 0;
+    return first_dw_layout(d, K, 1LL * d.S * Ho * Wo).total;
+}
+
+bool first_tc_operand_layout(const AetherConvDesc& d, AetherOperandLayout* out) {
+    int K, KP, NT, Ho, Wo;
+    if (!first_tc_bwd_eligible(d) || !first_tc_shape(d, K, KP, NT, Ho, Wo)) return false;
+    const FirstDwLayout l = first_dw_layout(d, K, 1LL * d.S * Ho * Wo);
+    out->x_copy_offset = 0;
+    out->x_copy_ld = 0;                     // the forward kernel gathers x itself: no copy of x to hand in
+    out->dy_copy_offset = l.dy_off;
+    out->dy_copy_ld = l.ld;
+    out->dy_colsum_offset = l.colsum_off;
+    out->dy_colsum_rows_max = l.rows_max;
+    return true;
+}
+
 int first_tc_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy, float* dw, float* db, void* ws,
-                        size_t ws_bytes, cudaStream_t st) {
+                        size_t ws_bytes, int dy_colsum_rows, cudaStream_t st) {
     int K, KP, NT, Ho, Wo;
     if (!first_tc_bwd_eligible(d) || !first_tc_shape(d, K, KP, NT, Ho, Wo))
         return set_error(AE_UNSUPPORTED, "first_tc_bwd_filter: shape not supported");
@@ -693,8 +744,17 @@ int first_tc_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy
     if (p.stages > 4) p.stages = 4;
     p.groups = p.stages < FD_MAX_GROUPS ? p.stages : FD_MAX_GROUPS;      // 1, 2 or 3: all divide FD_NP, FD_NP / groups is a multiple of 32
     const int grid = first_tc_grid(p.ntiles);
-    const size_t need = (size_t)grid * (K + 1) * d.Cout * sizeof(float);
+    const FirstDwLayout lay = first_dw_layout(d, K, p.P);
+    const size_t need = dy_colsum_rows > 0 ? lay.total : (size_t)grid * (K + 1) * d.Cout * sizeof(float);
     if (!ws || ws_bytes < need) return set_error(AE_BAD_ARG, "conv workspace too small: %zu < %zu", ws_bytes, need);
+    if (dy_colsum_rows > 0) {              // dy arrives as a bf16 copy with its column sums
+        if (dy_colsum_rows > lay.rows_max)
+            return set_error(AE_BAD_ARG, "aether_conv2d_bwd_ex: dy_colsum_rows %d outside [1, %d]", dy_colsum_rows, lay.rows_max);
+        int rc0 = make_map_2d(&p.tm_dy, static_cast<uint8_t*>(ws) + lay.dy_off, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, lay.ld, p.P,
+                              64, 128);
+        if (rc0) return rc0;
+        p.dy_bf16 = 1;
+    }
     const int smem = 1024 + p.stages * p.stage_bytes + tail;
     static PerDeviceSmem configured;
     if (int rc0 = ensure_dynamic_smem(first_dw_kernel, 232448, configured, "first_dw")) return rc0;
@@ -702,6 +762,12 @@ int first_tc_bwd_filter(const AetherConvDesc& d, const float* x, const float* dy
     count_launch();
     int rc = check_launch("first_dw_kernel");
     if (rc) return rc;
+    if (p.dy_bf16) {
+        if ((rc = smallc_reduce_partials(p.part, grid, K, d.Cout, dw, nullptr, st))) return rc;
+        return db ? colsum_finish(reinterpret_cast<const float*>(static_cast<uint8_t*>(ws) + lay.colsum_off), dy_colsum_rows,
+                                  d.Cout, db, st)
+                  : AE_OK;
+    }
     return smallc_reduce_partials(p.part, grid, K, d.Cout, dw, db, st);
 }
 

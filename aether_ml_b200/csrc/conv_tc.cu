@@ -799,6 +799,12 @@ __global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restr
     }
 }
 
+int colsum_finish(const float* part, int rows, int C, float* out, cudaStream_t st) {
+    colsum_finish_kernel<<<ceil_div(C, 8), 256, 0, st>>>(part, rows, C, out);
+    count_launch();
+    return check_launch("colsum_finish_kernel");
+}
+
 // Filter shadows.  w is (taps, Cin, Cout) fp32; the operand copies are zero padded to Cin_p / Cout_p channels.
 // They are made through 32 x 32 tiles in shared memory, so that both the reads (consecutive n of w's innermost Cout axis)
 // and the writes (consecutive k of the operand's innermost axis) are coalesced; a Dense layer's 8192 x 1024 weight

@@ -176,6 +176,7 @@ class Conv_Layer:
         self._desc = None
         self._copies = _OperandCopies()
         self._handed = _HandedIn()
+        self.first_in_model = False     # Model.finalize: this layer's dinputs are never needed
 
     # `weights` is the same array object as `filter_weights` (:68); in-place optimizer updates on
     # either name are visible through both.
@@ -204,7 +205,7 @@ class Conv_Layer:
             return None
         d, Ho, Wo = self._make_desc(*shape)
         lay = _operand_layout(d) if (Ho >= 1 and Wo >= 1) else None
-        if lay is None:
+        if lay is None or lay.x_copy_ld == 0:          # (first layers gather x themselves: no copy of x is read)
             return None
         ws = self._ws.get(lib().aether_conv2d_workspace_bytes(C.byref(d)))
         return ws.data_ptr() + lay.x_copy_offset, lay.x_copy_ld
@@ -218,6 +219,10 @@ class Conv_Layer:
             return None
         lay = _operand_layout(self._desc)
         if lay is None:
+            return None
+        # A first layer's filter-gradient kernel takes the copy, but its dX runs on the CUDA cores from the fp32 array:
+        # the hand-off is only for a layer whose dinputs nobody asks for (the first layer of a Model).
+        if lay.x_copy_ld == 0 and not self.first_in_model:
             return None
         ws = self._ws.get(lib().aether_conv2d_workspace_bytes(C.byref(self._desc)))
         return ws.data_ptr() + lay.dy_copy_offset, lay.dy_copy_ld, ws.data_ptr() + lay.dy_colsum_offset, lay.dy_colsum_rows_max
@@ -282,6 +287,8 @@ class Conv_Layer:
         shadow_ok = self._copies.flags(ws, x, self.filter_weights)
         rows = self._handed.dy_rows(ws, dy)
         self._handed.dy = None
+        if rows and self.first_in_model and need_dinputs:
+            rows = 0                        # a first layer asked for dinputs after all: that path reads the fp32 array
         if rows:
             shadow_ok |= _lib.CONV_DY_COPY_READY
         else:

@@ -121,6 +121,8 @@ class Model:
             layer.prev = chain[pos - 1]
             layer.next = chain[pos + 1]
         self.output_layer_activation = self.layers[-1]
+        if isinstance(self.layers[0], Conv_Layer):
+            self.layers[0].first_in_model = True        # backward never asks it for dinputs
         # A Batch_Norm directly behind a Conv_Layer takes its batch statistics from the convolution's epilogue
         # (when the kernel that serves the shape provides them) instead of reducing the activation again.
         for a, b in zip(self.layers[:-1], self.layers[1:]):

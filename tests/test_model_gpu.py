@@ -523,3 +523,49 @@ def test_lean_mode_trains_to_the_same_parameters(env):
     foreign = Ly.Conv_Layer((8, 8, 64), 32, math_mode="bf16")
     with pytest.raises(_lib.AetherError):
         foreign.forward(bn1.output, True)                             # no copy of it in THAT layer's workspace
+
+
+@pytest.mark.parametrize("lean", [False, True])
+def test_first_layer_takes_the_dy_copy_from_its_block_tail(env, lean):
+    """A first layer (3 input channels: thread-built operands) reads dvalues as the bf16 copy its block tail wrote,
+    brought in by TMA already in operand form, and its bias gradient from the tail's column sums: same gradients as
+    with the fp32 array converted inside the kernel."""
+    torch, _lib, Ly, M = env
+
+    def make(hand_off):
+        np.random.seed(21)
+        m = M.Model()
+        m.add(Ly.Conv_Layer((16, 16, 3), 64, (3, 3), (1, 1), "same", math_mode="bf16"))
+        m.add(Ly.Batch_Norm(n_features=64))
+        m.add(Ly.ReLU())
+        m.add(Ly.Pooling((2, 2), (2, 2), "valid", "max"))
+        m.add(Ly.Flatten())
+        m.add(Ly.Layer_Dense(8 * 8 * 64, 10, math_mode="bf16"))
+        m.add(Ly.SoftMax())
+        m.set(loss=Ly.Loss_CategoricalCrossEntropy(), optimizer=Ly.Optimizer_Adam(learning_rate=1e-3),
+              accuracy=M.Accuracy_Categorical())
+        m.finalize(flat=True, fuse=True, lean=lean and hand_off)
+        bn = m.layers[1]
+        assert bn.copy_dy_consumer is m.layers[0] and m.layers[0].first_in_model
+        if not hand_off:
+            bn.copy_dy_consumer = None
+        return m
+
+    rng = np.random.default_rng(2)
+    X = rng.random((300, 16, 16, 3)).astype(np.float32)      # 600 tiles of 128 pixels: several per CTA, ragged last one
+    y = rng.integers(0, 10, 300)
+    a, b = make(True), make(False)
+    for m in (a, b):
+        out = m.forward(X, training=True)
+        m.backward(out, y)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    ca, cb = a.layers[0], b.layers[0]
+    assert O.rel_l2(host(ca.dweights), host(cb.dweights)) <= 1e-6
+    assert np.abs(host(ca.dbiases) - host(cb.dbiases)).max() <= 1e-5 * np.abs(host(b.flat_grads)).max()   # ~0 in front of a Batch_Norm
+    if lean:
+        assert getattr(a.layers[1].dinputs, "_aether_unwritten", False)
+    # asked for dinputs after all, the layer falls back to the fp32 array (which must exist then)
+    if not lean:
+        dx = ca.backward(a.layers[1].dinputs, need_dinputs=True)
+        assert dx is not None and O.rel_l2(host(ca.dweights), host(cb.dweights)) <= 1e-6

@@ -94,6 +94,8 @@ class Model:
         self._m_last = self._m_sum = None
         self.bucket_reducer = None # dp.BucketReducer: all-reduces the flat gradients bucket by bucket during backward
         self._bucket_of_layer = {}
+        self._update_stream = None # side stream on which finished buckets are updated while backward goes on
+        self._updated_early = set()
 
     def add(self, layer):
         self.layers.append(layer)
@@ -240,6 +242,27 @@ class Model:
             b = self._bucket_of_layer.get(id(layer))
             if b is not None:                   # this layer's gradients complete a bucket: start reducing it
                 self.bucket_reducer.start(b)
+                self._update_bucket_early(b)
+
+    def _update_bucket_early(self, b):
+        """Every bucket but the last is updated as soon as its all-reduce is through, on a side stream, while the
+        main stream goes on back-propagating the layers in front: nobody reads those parameters again in this step
+        (their layers' backward is over), and the update -- Adam moves 28 bytes per parameter, the dense head is most
+        of them -- runs beside tensor-bound convolution kernels instead of after them."""
+        r = self.bucket_reducer
+        if b == len(r.buckets) - 1 or self.flat_params is None or not hasattr(self.optimizer, "update_flat"):
+            return
+        if self._update_stream is None:
+            self._update_stream = torch.cuda.Stream()
+        main = torch.cuda.current_stream()
+        side = self._update_stream
+        side.wait_stream(main)
+        self.optimizer.pre_update_parameters()          # this step's learning rate (idempotent within a step)
+        lo, hi, _ = r.buckets[b]
+        with torch.cuda.stream(side):
+            r.wait(b)
+            self.optimizer.update_flat(self.flat_params[lo:hi], self.flat_grads[lo:hi], self.flat_m[lo:hi], self.flat_v[lo:hi])
+        self._updated_early.add(b)
 
     def _apply_optimizer(self, run_hook=True):
         opt = self.optimizer
@@ -249,10 +272,15 @@ class Model:
         if self.bucket_reducer is not None and self.flat_params is not None and hasattr(opt, "update_flat"):
             # one update per bucket, each behind its own all-reduce only (the first bucket's update overlaps the
             # second bucket's all-reduce)
+            if self._updated_early:
+                torch.cuda.current_stream().wait_stream(self._update_stream)
             for i, (lo, hi, _) in enumerate(self.bucket_reducer.buckets):
+                if i in self._updated_early:
+                    continue
                 if run_hook:
                     self.bucket_reducer.wait(i)
                 opt.update_flat(self.flat_params[lo:hi], self.flat_grads[lo:hi], self.flat_m[lo:hi], self.flat_v[lo:hi])
+            self._updated_early = set()
         elif self.flat_params is not None and hasattr(opt, "update_flat"):
             opt.update_flat(self.flat_params, self.flat_grads, self.flat_m, self.flat_v)
         else:

@@ -88,6 +88,8 @@ SIGNATURES = {
     "aether_regularizer_grad": (_I, [_P, _P, _I64, _F, _F, _P]),
     "aether_regularizer_loss": (_I, [_P, _I64, _F, _F, _P, _P]),
     "aether_softmax_cce": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P]),
+    "aether_softmax_bwd": (_I, [_P, _P, _P, _I, _I, _P]),
+    "aether_softmax_cce_targets": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P]),
 }
 
 _lib = None

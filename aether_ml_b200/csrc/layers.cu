@@ -1063,7 +1063,7 @@ __global__ void __launch_bounds__(256) softmax_cce_kernel(const float* __restric
                                                           float* __restrict__ prob, float* __restrict__ loss,
                                                           float* __restrict__ dz, int* __restrict__ correct, int rows,
                                                           int classes, float smooth_fwd, float smooth_bwd,
-                                                          int input_is_prob) {
+                                                          int input_is_prob, const float* __restrict__ targets) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (warp >= rows) return;
@@ -1084,14 +1084,31 @@ __global__ void __launch_bounds__(256) softmax_cce_kernel(const float* __restric
         for (int k = lane; k < classes; k += 32) sum += expf(zr[k] - mx);
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     }
-    const int label = labels ? labels[warp] : -1;
+    // targets: class indices (labels) or rows of target probabilities (one-hot or soft, :625-637); for the accuracy a
+    // row of targets stands for its arg-max (CNN_model_cupy.py:383-385)
+    int label = labels ? labels[warp] : -1;
+    if (targets) {
+        const float* tr = targets + (size_t)warp * classes;
+        float tm = -INFINITY;
+        int ta = 0;
+        for (int k = lane; k < classes; k += 32) {
+            const float v = tr[k];
+            if (v > tm) { tm = v; ta = k; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float om = __shfl_xor_sync(0xffffffffu, tm, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, ta, o);
+            if (om > tm || (om == tm && oa < ta)) { tm = om; ta = oa; }
+        }
+        label = ta;
+    }
     const float inv_rows = 1.f / (float)rows;
     float l = 0.f;
     for (int k = lane; k < classes; k += 32) {
         const float pk = input_is_prob ? zr[k] : expf(zr[k] - mx) / sum;
         if (prob) prob[(size_t)warp * classes + k] = pk;
-        if (labels) {
-            const float onehot = (k == label) ? 1.f : 0.f;
+        if (labels || targets) {
+            const float onehot = targets ? targets[(size_t)warp * classes + k] : ((k == label) ? 1.f : 0.f);
             const float tf = onehot * (1.f - smooth_fwd) + smooth_fwd / classes;
             const float tb = onehot * (1.f - smooth_bwd) + smooth_bwd / classes;
             const float pc = fminf(fmaxf(pk, 1e-7f), 1.f - 1e-7f);
@@ -1106,9 +1123,31 @@ __global__ void __launch_bounds__(256) softmax_cce_kernel(const float* __restric
     }
 }
 
+// SoftMax.backward (CNN_classes_cupy.py:549-560): per sample dinputs = (diag(p) - p p^T) dvalues = p * (dv - <p, dv>).
+// One warp per sample, the dot product reduced with shuffles in a fixed order.
+__global__ void __launch_bounds__(256) softmax_bwd_kernel(const float* __restrict__ p, const float* __restrict__ dv,
+                                                          float* __restrict__ dx, int rows, int classes) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= rows) return;
+    const float* pr = p + (size_t)warp * classes;
+    const float* dr = dv + (size_t)warp * classes;
+    float dot = 0.f;
+    for (int k = lane; k < classes; k += 32) dot = fmaf(pr[k], dr[k], dot);
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    for (int k = lane; k < classes; k += 32) dx[(size_t)warp * classes + k] = pr[k] * (dr[k] - dot);
+}
+
 }  // namespace aether
 
 // ====================================================================================== C ABI
+extern "C" int aether_softmax_bwd(const float* p, const float* dvalues, float* dinputs, int rows, int classes, void* stream) {
+    if (!p || !dvalues || !dinputs || rows <= 0 || classes <= 0) return set_error(AE_BAD_ARG, "aether_softmax_bwd: bad argument");
+    softmax_bwd_kernel<<<ceil_div(rows * 32, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(p, dvalues, dinputs, rows, classes);
+    count_launch();
+    return check_launch("aether_softmax_bwd");
+}
+
 extern "C" int aether_pool_fwd(const float* x, float* y, uint8_t* argmax, int S, int H, int W, int C, int fH, int fW,
                                int sH, int sW, int kind, void* stream) {
     if (!x || !y || (kind == AETHER_POOL_MAX && !argmax)) return set_error(AE_BAD_ARG, "aether_pool_fwd: null pointer");
@@ -1286,7 +1325,18 @@ extern "C" int aether_softmax_cce(const float* z, const int32_t* labels, float* 
     if (!labels && (loss || dz || correct)) return set_error(AE_BAD_ARG, "aether_softmax_cce: labels required for loss/gradient");
     const int threads = 256;
     const int blocks = ceil_div(rows * 32, threads);
-    softmax_cce_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(z, labels, prob, loss, dz, correct, rows, classes, smooth_fwd, smooth_bwd, input_is_prob);
+    softmax_cce_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(z, labels, prob, loss, dz, correct, rows, classes, smooth_fwd, smooth_bwd, input_is_prob, nullptr);
     count_launch();
     return check_launch("aether_softmax_cce");
+}
+
+extern "C" int aether_softmax_cce_targets(const float* z, const float* targets, float* prob, float* loss, float* dz,
+                                          int32_t* correct, int rows, int classes, float smooth_fwd, float smooth_bwd,
+                                          int input_is_prob, void* stream) {
+    if (!z || !targets || rows <= 0 || classes <= 0) return set_error(AE_BAD_ARG, "aether_softmax_cce_targets: bad argument");
+    const int threads = 256;
+    const int blocks = ceil_div(rows * 32, threads);
+    softmax_cce_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(z, nullptr, prob, loss, dz, correct, rows, classes, smooth_fwd, smooth_bwd, input_is_prob, targets);
+    count_launch();
+    return check_launch("aether_softmax_cce_targets");
 }

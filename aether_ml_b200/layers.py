@@ -859,9 +859,11 @@ class Layer_Dense:
 
 # ------------------------------------------------------------------------------------- softmax / loss
 def _labels_i32(y_true):
+    """Targets as the kernels take them: class indices (int32, shape (rows,)) or, for 2-D input, the rows of target
+    probabilities themselves (float32): one-hot or soft, the loss uses them as they are (CNN_classes_cupy.py:625-637)."""
     y = y_true if isinstance(y_true, torch.Tensor) else torch.as_tensor(np.asarray(y_true))
-    if y.ndim == 2:                   # one-hot rows -> class indices
-        y = y.argmax(dim=1)
+    if y.ndim == 2:
+        return to_device(y, torch.float32)
     return to_device(y, torch.int32)
 
 
@@ -871,22 +873,39 @@ def _softmax_cce(z, labels, want_prob, want_loss, want_dz, want_correct, smooth_
     loss = _empty((rows,)) if want_loss else None
     dz = _empty((rows, classes)) if want_dz else None
     correct = _empty((rows,), torch.int32) if want_correct else None
-    check(lib().aether_softmax_cce(_ptr(z), _ptr(labels), _ptr(prob), _ptr(loss), _ptr(dz), _ptr(correct), rows,
-                                   classes, float(smooth_fwd), float(smooth_bwd), 1 if input_is_prob else 0,
-                                   _stream()), "aether_softmax_cce")
+    if labels is not None and labels.ndim == 2:
+        if tuple(labels.shape) != (rows, classes):
+            raise ValueError(f"targets have shape {tuple(labels.shape)}, expected {(rows, classes)}")
+        check(lib().aether_softmax_cce_targets(_ptr(z), _ptr(labels), _ptr(prob), _ptr(loss), _ptr(dz), _ptr(correct), rows,
+                                               classes, float(smooth_fwd), float(smooth_bwd), 1 if input_is_prob else 0,
+                                               _stream()), "aether_softmax_cce_targets")
+    else:
+        check(lib().aether_softmax_cce(_ptr(z), _ptr(labels), _ptr(prob), _ptr(loss), _ptr(dz), _ptr(correct), rows,
+                                       classes, float(smooth_fwd), float(smooth_bwd), 1 if input_is_prob else 0,
+                                       _stream()), "aether_softmax_cce")
     return prob, loss, dz, correct
 
 
 class SoftMax:
-    """Drop-in for ``SoftMax`` (CNN_classes_cupy.py:541-563).  The standalone Jacobian ``backward`` of
-    the reference (:549-560) is not provided: every network in the reference ends in SoftMax +
-    categorical cross-entropy and takes the combined backward (:666-680)."""
+    """Drop-in for ``SoftMax`` (CNN_classes_cupy.py:541-563).  ``backward`` is the reference's stand-alone Jacobian
+    product (:549-560), as one kernel instead of a Python loop over the samples; networks that end in SoftMax +
+    categorical cross-entropy take the combined backward (:666-680) and never call it."""
 
     def forward(self, inputs, training=True):
         z = to_device(inputs)
         self.inputs = z
         self.output, _, _, _ = _softmax_cce(z, None, True, False, False, False, 0.0, 0.0)
         return self.output
+
+    def backward(self, dvalues):
+        dv = to_device(dvalues)
+        if tuple(dv.shape) != tuple(self.output.shape):
+            raise ValueError(f"dvalues has shape {tuple(dv.shape)}, expected {tuple(self.output.shape)}")
+        dx = torch.empty_like(dv)
+        check(lib().aether_softmax_bwd(_ptr(self.output), _ptr(dv), _ptr(dx), dv.shape[0], dv.shape[1], _stream()),
+              "aether_softmax_bwd")
+        self.dinputs = dx
+        return self.dinputs
 
     def predictions(self, outputs):
         return to_device(outputs).argmax(dim=1)

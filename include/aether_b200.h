@@ -299,6 +299,14 @@ int aether_regularizer_loss(const float* w, int64_t n, float l1, float l2, float
  *      (the reference's loss classes take the softmax OUTPUT), so the softmax itself is skipped. */
 int aether_softmax_cce(const float* z, const int32_t* labels, float* prob, float* loss, float* dz, int32_t* correct,
                        int rows, int classes, float smooth_fwd, float smooth_bwd, int input_is_prob, void* stream);
+/* The same with rows of target probabilities, float [rows][classes], instead of class indices: one-hot rows or soft
+ * targets, used as they are (after label smoothing) by the loss and its gradient (:625-637, :644-650, :672-680);
+ * `correct` compares arg-maxes. */
+int aether_softmax_cce_targets(const float* z, const float* targets, float* prob, float* loss, float* dz, int32_t* correct,
+                               int rows, int classes, float smooth_fwd, float smooth_bwd, int input_is_prob, void* stream);
+/* SoftMax.backward on its own (:549-560, the per-sample Jacobian loop): dinputs = p * (dvalues - sum_k p_k dvalues_k)
+ * per row; p is the softmax output. */
+int aether_softmax_bwd(const float* p, const float* dvalues, float* dinputs, int rows, int classes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -345,6 +345,17 @@ def softmax(z):
     return e / e.sum(axis=1, keepdims=True)
 
 
+def softmax_backward(p, dvalues):
+    """SoftMax.backward, CNN_classes_cupy.py:549-560: per sample (diagflat(p) - p p^T) @ dvalues."""
+    p = np.asarray(p, dtype=np.float64)
+    dv = np.asarray(dvalues, dtype=np.float64)
+    out = np.empty_like(dv)
+    for i, (pi, di) in enumerate(zip(p, dv)):
+        col = pi.reshape(-1, 1)
+        out[i] = (np.diagflat(col) - col @ col.T) @ di
+    return out
+
+
 def _smooth_targets(y_true, n_classes, label_smoothing):
     y_true = np.asarray(y_true)
     if y_true.ndim == 1:

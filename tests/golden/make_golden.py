@@ -144,6 +144,15 @@ def main(ref_root):
                         dx=np.array(dense.dinputs), w_hist=np.stack(hist_w), b_hist=np.stack(hist_b),
                         lrs=np.array(lrs), m_w=np.array(dense.weight_momentums), v_w=np.array(dense.weight_cache))
 
+    # ------------------------------------------------------------------ SoftMax.backward on its own (the Jacobian loop)
+    sm = R.SoftMax()
+    zs = rng.standard_normal((7, 10)) * 2.0
+    ps = sm.forward(zs, True)
+    dvs = rng.standard_normal((7, 10))
+    sm.backward(dvs)
+    np.savez_compressed(os.path.join(out_dir, "softmax_backward.npz"), z=zs, p=np.array(ps), dvalues=dvs,
+                        dinputs=np.array(sm.dinputs))
+
     # ------------------------------------------------------------------ notebook known answers
     np.savez_compressed(
         os.path.join(out_dir, "notebook_kat.npz"),

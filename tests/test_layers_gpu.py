@@ -390,3 +390,45 @@ def test_regularization_loss(env):
     w = host(d1.weights).astype(np.float64); b = host(d1.biases).astype(np.float64)
     expect = 2e-5 * (w * w).sum() + 1e-3 * np.abs(b).sum()
     assert np.isclose(float(loss.regularization_loss()), expect, rtol=1e-5)
+
+
+def test_softmax_standalone_backward(env, golden):
+    """SoftMax.backward on its own (the reference's per-sample Jacobian loop, CNN_classes_cupy.py:549-560)."""
+    torch, _lib, layers = env
+    g = golden("softmax_backward")
+    sm = layers.SoftMax()
+    p = sm.forward(g["z"].astype(np.float32), True)
+    assert O.rel_l2(host(p), g["p"]) <= 1e-6
+    dx = sm.backward(g["dvalues"].astype(np.float32))
+    assert O.rel_l2(host(dx), g["dinputs"]) <= 1e-5
+    rng = np.random.default_rng(3)
+    z = rng.standard_normal((300, 1000)).astype(np.float32) * 3
+    dv = rng.standard_normal((300, 1000)).astype(np.float32)
+    p = sm.forward(z, True)
+    assert O.rel_l2(host(sm.backward(dv)), O.softmax_backward(host(p), dv)) <= 1e-5
+    with pytest.raises(ValueError):
+        sm.backward(dv[:, :10])
+
+
+def test_cross_entropy_with_rows_of_target_probabilities(env):
+    """2-D targets -- one-hot rows and soft rows -- are used as they are by the loss and its gradients
+    (CNN_classes_cupy.py:625-637, 644-650, 672-680), label smoothing applied on top."""
+    torch, _lib, layers = env
+    rng = np.random.default_rng(12)
+    z = rng.standard_normal((33, 10)).astype(np.float32) * 2
+    p = O.softmax(z)
+    idx = rng.integers(0, 10, 33)
+    onehot = np.eye(10)[idx]
+    soft = rng.random((33, 10)); soft /= soft.sum(axis=1, keepdims=True)
+    for smooth in (0.0, 0.05):
+        loss = layers.Loss_CategoricalCrossEntropy(label_smoothing=smooth)
+        comb = layers.Activation_Softmax_Loss_CategoricalCrossEntropy(label_smoothing=smooth)
+        for tgt in (onehot, soft):
+            got = loss.forward(p.astype(np.float32), tgt.astype(np.float32), training=True)
+            assert O.rel_l2(host(got), O.cce_loss(p, tgt, smooth)) <= 1e-5
+            dz = comb.backward(p.astype(np.float32), tgt.astype(np.float32))
+            assert O.rel_l2(host(dz), O.softmax_cce_backward(p, tgt, smooth)) <= 1e-5
+        # one-hot rows and class indices are the same targets
+        a = comb.backward(p.astype(np.float32), onehot.astype(np.float32)).clone()
+        b = comb.backward(p.astype(np.float32), idx)
+        assert torch.equal(a, b)

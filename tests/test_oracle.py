@@ -167,3 +167,14 @@ def test_reference_checkpoint_format_loads_without_cupy(golden):
     evil = pickle.dumps(os.system)                         # a global that is not an array constructor
     with pytest.raises(pickle.UnpicklingError):
         _CheckpointUnpickler(io.BytesIO(evil)).load()
+
+
+def test_softmax_backward_matches_reference(golden):
+    """The oracle's stand-alone SoftMax.backward against the array the reference's own Jacobian loop produced."""
+    g = golden("softmax_backward")
+    assert O.rel_l2(O.softmax(g["z"]), g["p"]) <= 1e-12
+    assert O.rel_l2(O.softmax_backward(g["p"], g["dvalues"]), g["dinputs"]) <= 1e-12
+    # the closed form the kernel uses: p * (dv - <p, dv>)
+    p, dv = g["p"], g["dvalues"]
+    closed = p * (dv - (p * dv).sum(axis=1, keepdims=True))
+    assert O.rel_l2(closed, g["dinputs"]) <= 1e-12

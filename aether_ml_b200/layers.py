@@ -54,6 +54,36 @@ def _empty(shape, dtype=torch.float32):
     return torch.empty(shape, dtype=dtype, device=_device())
 
 
+class _Saved:
+    """Pickling of a layer / loss / optimizer for ``Model.save`` (the reference pickles the whole model after
+    stripping the per-step arrays, CNN_model_cupy.py:291-309): device arrays travel as NumPy arrays, everything that
+    belongs to one forward/backward pass (activations, gradients, workspaces, operand-copy bookkeeping, links to the
+    neighbouring layers) is left out and rebuilt empty on loading."""
+
+    _TRANSIENT = ("inputs", "output", "dinputs", "dweights", "dbiases", "prev", "next", "bn_partials", "binary_mask",
+                  "channel_mask", "batch_mean", "batch_var", "running_mean", "running_var", "inputs_shape",
+                  "trainable_layers", "accumulated_sum", "accumulated_count", "step_dev", "stats_from", "fused_dropout",
+                  "fused_pool", "fused_bn", "copy_consumer", "copy_dy_consumer", "fixed_mask", "fused_into_prev")
+
+    def __getstate__(self):
+        state = {}
+        for k, v in self.__dict__.items():
+            if k in self._TRANSIENT or (k.startswith("_") and k not in ("_rm", "_rv", "_calls")):
+                continue
+            state[k] = ("__device_array__", v.detach().cpu().numpy()) if isinstance(v, torch.Tensor) else v
+        return state
+
+    def __setstate__(self, state):
+        for k, v in state.items():
+            if isinstance(v, tuple) and len(v) == 2 and isinstance(v[0], str) and v[0] == "__device_array__":
+                v = to_device(v[1], torch.from_numpy(v[1]).dtype)
+            self.__dict__[k] = v
+        self._restore_transient()
+
+    def _restore_transient(self):
+        pass
+
+
 class _Workspace:
     """Grow-only byte buffer owned by a layer and handed to the library as scratch."""
 
@@ -138,7 +168,7 @@ def _operand_layout(d):
 
 
 # ------------------------------------------------------------------------------------- Conv_Layer
-class Conv_Layer:
+class Conv_Layer(_Saved):
     """Drop-in for ``Conv_Layer`` (CNN_classes_cupy.py:37-161).
 
     Same constructor arguments and attributes (``filter_weights``/``weights`` alias, ``biases``, the
@@ -177,6 +207,16 @@ class Conv_Layer:
         self._copies = _OperandCopies()
         self._handed = _HandedIn()
         self.first_in_model = False     # Model.finalize: this layer's dinputs are never needed
+
+    def _restore_transient(self):
+        self._ws = _Workspace()
+        self._stats_ws = _Workspace()
+        self.bn_partials = None
+        self._desc = None
+        self._copies = _OperandCopies()
+        self._handed = _HandedIn()
+        self.emit_bn_stats = False
+        self.first_in_model = False
 
     # `weights` is the same array object as `filter_weights` (:68); in-place optimizer updates on
     # either name are visible through both.
@@ -315,7 +355,7 @@ class Conv_Layer:
 
 
 # ------------------------------------------------------------------------------------- Pooling
-class Pooling:
+class Pooling(_Saved):
     """Drop-in for ``Pooling`` (CNN_classes_cupy.py:204-312), 'valid' padding, max or average.
     The argmax is kept as one byte per output (window-local index of the first maximum);
     ``max_indicies`` reconstructs the reference's (rows, cols) pair on demand."""
@@ -326,6 +366,9 @@ class Pooling:
         self.padding = padding
         self.pooling_type = pooling_type
         self.fused_bn = None            # a Batch_Norm that pools inside its own kernels (Model.finalize(fuse=True))
+
+    def _restore_transient(self):
+        self.fused_bn = None
 
     def _kind(self):
         if self.pooling_type == "max":
@@ -382,7 +425,7 @@ class Pooling:
 
 
 # ------------------------------------------------------------------------------------- activations
-class ReLU:
+class ReLU(_Saved):
     """Drop-in for ``ReLU`` (CNN_classes_cupy.py:406-415).  With ``fused_into_prev`` (set by
     ``Model.finalize(fuse=True)`` when the layer follows a Batch_Norm) the activation is applied by that
     Batch_Norm's kernels and this layer only hands tensors through."""
@@ -425,7 +468,7 @@ class Leaky_ReLU(ReLU):
 
 
 # ------------------------------------------------------------------------------------- dropout
-class Layer_Dropout_Spatial:
+class Layer_Dropout_Spatial(_Saved):
     """Drop-in for ``Layer_Dropout_Spatial`` (CNN_classes_cupy.py:384-404): one Bernoulli(keep) draw per
     channel, shared by the whole batch, scaled by 1/keep.  The draw uses NumPy's global generator like
     the reference's NumPy twin; ``channel_mask`` (1,1,1,C) may be overwritten before ``forward`` by
@@ -441,6 +484,11 @@ class Layer_Dropout_Spatial:
         Layer_Dropout_Spatial._next_seed += 1
         self.step_dev = None            # int64 device counter: draw the mask on the device (CUDA-graph train step)
         self.fused_into_prev = False    # the Batch_Norm in front applies the mask (Model.finalize(fuse=True))
+
+    def _restore_transient(self):
+        self.fixed_mask = None
+        self.step_dev = None
+        self.fused_into_prev = False
 
     def draw_mask(self, Cc):
         """Draws this step's channel mask (Bernoulli(keep)/keep per channel) into ``channel_mask``."""
@@ -485,7 +533,7 @@ class Layer_Dropout_Spatial:
         return self.dinputs
 
 
-class Layer_Dropout:
+class Layer_Dropout(_Saved):
     """Drop-in for ``Layer_Dropout`` (CNN_classes_cupy.py:364-382).  ``rate`` is the drop rate; the
     element mask Bernoulli(1-rate)/(1-rate) is drawn on the device from a Philox stream keyed by
     ``seed`` and a per-call offset (``rank_offset`` separates data-parallel ranks)."""
@@ -499,6 +547,9 @@ class Layer_Dropout:
         self.seed = int(seed)
         self.rank_offset = int(rank_offset)
         self._calls = 0
+        self.step_dev = None
+
+    def _restore_transient(self):
         self.step_dev = None
 
     def forward(self, inputs, training):
@@ -530,7 +581,7 @@ class Layer_Dropout:
 
 
 # ------------------------------------------------------------------------------------- Batch_Norm
-class Batch_Norm:
+class Batch_Norm(_Saved):
     """Drop-in for ``Batch_Norm`` (CNN_classes_cupy.py:430-526) for 4-D (NHWC) and 2-D inputs.
     ``gamma``/``beta`` (aliased as ``weights``/``biases``) have shape (C,); ``running_mean`` /
     ``running_var`` / ``batch_mean`` / ``batch_var`` are exposed with the reference's keep-dims shape
@@ -560,6 +611,23 @@ class Batch_Norm:
         self.copy_dy_consumer = None    # the Conv_Layer in front (the bf16 copy of its dvalues is written here)
         if n_features is not None:
             self._create(n_features)
+
+    def _restore_transient(self):
+        self._ws = _Workspace()
+        self._keep = None
+        self.stats_from = None
+        self.fused_alpha = None
+        self.fused_dropout = None
+        self.fused_pool = None
+        self.pooled_now = False
+        self.lean = False
+        self.copy_consumer = None
+        self.copy_dy_consumer = None
+        if getattr(self, "gamma", None) is not None:
+            self.running_mean = self._rm
+            self.running_var = self._rv
+        else:
+            self.running_mean = self.running_var = None
 
     def _create(self, Cc):
         dev = _device()
@@ -741,7 +809,7 @@ class Batch_Norm:
 
 
 # ------------------------------------------------------------------------------------- Flatten / Dense
-class Flatten:
+class Flatten(_Saved):
     """Drop-in for ``Flatten`` (CNN_classes_cupy.py:528-539); a view, no kernel."""
 
     def forward(self, inputs, training):
@@ -757,7 +825,7 @@ class Flatten:
         return self.dinputs
 
 
-class Layer_Dense:
+class Layer_Dense(_Saved):
     """Drop-in for ``Layer_Dense`` (CNN_classes_cupy.py:315-362).  The three products run through the
     convolution kernels as a 1x1 convolution on a 1x1 image (x (S,n_in) is NHWC with H=W=1; weights
     (n_in,n_out) are a (1,1,Cin,Cout) filter), so they use the same tensor-core path.  Parameters are
@@ -773,6 +841,11 @@ class Layer_Dense:
         self.bias_regularizer_l1 = bias_regularizer_l1
         self.bias_regularizer_l2 = bias_regularizer_l2
         self.math_mode = math_mode or DEFAULT_MATH_MODE
+        self._ws = _Workspace()
+        self._copies = _OperandCopies()
+        self._handed = _HandedIn()
+
+    def _restore_transient(self):
         self._ws = _Workspace()
         self._copies = _OperandCopies()
         self._handed = _HandedIn()
@@ -886,7 +959,7 @@ def _softmax_cce(z, labels, want_prob, want_loss, want_dz, want_correct, smooth_
     return prob, loss, dz, correct
 
 
-class SoftMax:
+class SoftMax(_Saved):
     """Drop-in for ``SoftMax`` (CNN_classes_cupy.py:541-563).  ``backward`` is the reference's stand-alone Jacobian
     product (:549-560), as one kernel instead of a Python loop over the samples; networks that end in SoftMax +
     categorical cross-entropy take the combined backward (:666-680) and never call it."""
@@ -911,7 +984,7 @@ class SoftMax:
         return to_device(outputs).argmax(dim=1)
 
 
-class Loss:
+class Loss(_Saved):
     """Accumulating loss base class, ``Loss`` (CNN_classes_cupy.py:565-609)."""
 
     def remember_trainable_layers(self, trainable_layers):
@@ -994,7 +1067,7 @@ class Activation_Softmax_Loss_CategoricalCrossEntropy:
 
 
 # ------------------------------------------------------------------------------------- Adam
-class Optimizer_Adam:
+class Optimizer_Adam(_Saved):
     """Drop-in for ``Optimizer_Adam`` (CNN_classes_cupy.py:685-736).  State lives on the layer under the
     reference's attribute names (``weight_momentums``, ``weight_cache``, ``bias_momentums``,
     ``bias_cache``) and parameters are updated in place.  ``grad_scale`` multiplies every gradient
@@ -1010,6 +1083,9 @@ class Optimizer_Adam:
         self.beta_2 = beta_2
         self.grad_scale = 1.0
         self.step_dev = None            # int64 device copy of `iterations` (CUDA-graph train step)
+
+    def _restore_transient(self):
+        self.step_dev = None
 
     def pre_update_parameters(self):
         if self.decay:

@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from .layers import (Activation_Softmax_Loss_CategoricalCrossEntropy, Batch_Norm, Conv_Layer, Flatten, Layer_Dropout_Spatial,
-                     Loss_CategoricalCrossEntropy, Pooling, ReLU, SoftMax, to_device, _labels_i32, _softmax_cce)
+                     Loss_CategoricalCrossEntropy, Pooling, ReLU, SoftMax, to_device, _labels_i32, _softmax_cce, _Saved)
 
 
 class Layer_Input:
@@ -27,7 +27,7 @@ class Layer_Input:
         self.output = inputs
 
 
-class Accuracy:
+class Accuracy(_Saved):
     """Running accuracy (CNN_model_cupy.py:344-363)."""
 
     def calculate(self, predictions, y):
@@ -109,6 +109,49 @@ class Model:
             self.accuracy = accuracy
 
     # ------------------------------------------------------------------ wiring
+    # ------------------------------------------------------------------ whole-model files
+    def __getstate__(self):
+        """What ``save`` writes: the layer list, loss, optimizer and accuracy objects (each without its per-step
+        arrays) and the options of the last ``finalize``; flat buffers, graphs and wiring are rebuilt on loading."""
+        return {"layers": self.layers, "loss": self.loss, "optimizer": self.optimizer, "accuracy": self.accuracy,
+                "finalize_options": getattr(self, "_finalize_options", None)}
+
+    def __setstate__(self, state):
+        self.__init__()
+        self.layers = state["layers"]
+        self.loss, self.optimizer, self.accuracy = state["loss"], state["optimizer"], state["accuracy"]
+        if state.get("finalize_options") is not None:
+            had_state = [(l, {n: getattr(l, n) for n in ("weight_momentums", "weight_cache", "bias_momentums", "bias_cache")
+                              if hasattr(l, n)}) for l in self.layers]
+            self.finalize(**state["finalize_options"])
+            for l, st in had_state:                      # Adam's moments go back into the (possibly flat) state arrays
+                for n, arr in st.items():
+                    if getattr(l, n) is not arr:
+                        getattr(l, n).copy_(arr.reshape(getattr(l, n).shape))
+
+    def save(self, path):
+        """Writes the whole model to one file (``Model.save``, CNN_model_cupy.py:291-309).  As in the reference the
+        per-step arrays (inputs, outputs, gradients) and the accumulated loss / accuracy are left out; parameters,
+        Adam's state, running statistics and the layer configuration are kept.  Device arrays are stored as NumPy
+        arrays; the file is a pickle of this package's classes (it is not interchangeable with the reference's own
+        whole-model pickles, which name the reference's modules)."""
+        if self.loss is not None:
+            self.loss.new_pass()
+        if self.accuracy is not None:
+            self.accuracy.new_pass()
+        with open(path, 'wb') as f:
+            pickle.dump(self, f)
+
+    @staticmethod
+    def load(path):
+        """Reads a file written by ``save`` (``Model.load``, CNN_model_cupy.py:311-317) and returns the model, wired
+        with the same ``finalize`` options it had and ready to predict or to go on training."""
+        with open(path, 'rb') as f:
+            model = pickle.load(f)
+        if not isinstance(model, Model):
+            raise TypeError("%s does not hold a Model" % path)
+        return model
+
     def finalize(self, flat=False, fuse=False, lean=False):
         """Wires the layers (CNN_model_cupy.py:27-64).  Beyond the reference: `flat` packs parameters and gradients
         into flat buffers, `fuse` merges each block tail into one pass each way, and `lean` (with `fuse`) stops
@@ -117,6 +160,7 @@ class Model:
         fused tail behind a tensor-core Conv_Layer.  Parameters, gradients and outputs of the model are the same
         numbers as without it; the `.output` of such a Pooling and the `.dinputs` of such a Batch_Norm are then
         placeholders (a layer asked to read one raises)."""
+        self._finalize_options = {"flat": bool(flat), "fuse": bool(fuse), "lean": bool(lean)}
         self.input_layer = Layer_Input()
         chain = [self.input_layer] + self.layers + [self.loss]
         for pos, layer in enumerate(self.layers, start=1):

@@ -569,3 +569,32 @@ def test_first_layer_takes_the_dy_copy_from_its_block_tail(env, lean):
     if not lean:
         dx = ca.backward(a.layers[1].dinputs, need_dinputs=True)
         assert dx is not None and O.rel_l2(host(ca.dweights), host(cb.dweights)) <= 1e-6
+
+
+@pytest.mark.parametrize("flat,fuse", [(False, False), (True, True)])
+def test_whole_model_save_and_load(env, tmp_path, flat, fuse):
+    """Model.save / Model.load (CNN_model_cupy.py:291-317): the loaded model predicts the same and goes on training
+    to the same parameters as the one that was saved (Adam's moments and step count travel with it)."""
+    torch, _lib, Ly, M = env
+    rng = np.random.default_rng(40)
+    m, shape = build(env, "cifar", "bf16", flat, fuse=fuse)
+    m.enable_device_step() if flat else None
+    batches = [(rng.random((8,) + shape).astype(np.float32), rng.integers(0, 10, 8)) for _ in range(3)]
+    for X, y in batches[:2]:
+        m.train_step(X, y)
+    path = os.path.join(tmp_path, "whole_model")
+    m.save(path)
+    loaded = M.Model.load(path)
+    assert [type(l).__name__ for l in loaded.layers] == [type(l).__name__ for l in m.layers]
+    assert loaded.optimizer.iterations == 2 and (loaded.flat_params is not None) == flat
+    assert not hasattr(loaded.layers[0], "output") or loaded.layers[0].__dict__.get("output") is None
+    Xe = rng.random((8,) + shape).astype(np.float32)
+    assert O.rel_l2(host(loaded.predict(Xe)), host(m.predict(Xe))) <= 1e-6
+    if flat:
+        loaded.enable_device_step()
+        for a, b in zip(m.layers, loaded.layers):          # the same dropout streams from here on
+            if hasattr(a, "seed"):
+                assert a.seed == b.seed
+        m.train_step(*batches[2]); loaded.train_step(*batches[2])
+        assert O.rel_l2(host(loaded.flat_params), host(m.flat_params)) <= 1e-6
+        assert O.rel_l2(host(loaded.flat_m), host(m.flat_m)) <= 1e-6

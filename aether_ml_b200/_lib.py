@@ -105,7 +105,11 @@ def lib():
                 "(there is no fallback path)" % LIB_PATH)
         h = C.CDLL(LIB_PATH)
         for name, (res, args) in SIGNATURES.items():
-            fn = getattr(h, name)
+            try:
+                fn = getattr(h, name)
+            except AttributeError:
+                raise AetherError("%s does not export %s: it was built from older sources -- rebuild it with "
+                                  "`python -m aether_ml_b200.build`" % (LIB_PATH, name)) from None
             fn.restype = res
             fn.argtypes = args
         _lib = h

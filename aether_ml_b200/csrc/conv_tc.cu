@@ -127,26 +127,39 @@ static constexpr int IGEMM_THREADS = 64 + 32 * IGEMM_EPI_WARPS;   // warp 0 TMA 
 static constexpr int IGEMM_TAIL = 1024;         // barriers, TMEM pointer
 static constexpr int IGEMM_STATS_BYTES = IGEMM_EPI_WARPS * STATS_WARP_FLOATS * 4;   // per-warp running column sums and pivots
 
-template <int NT>
+// PAIR: two CTAs of a cluster share one 256-row MMA (cta_group::2).  Each holds its own 128 pixel rows and HALF of the
+// filter tile (NT/2 rows), so a stage is smaller and every SM pulls a third less from L2 per FLOP.
+template <int NT, bool PAIR = false>
 struct IgemmCfg {
-    static constexpr int STAGES = (NT == 256) ? 4 : (NT == 128 ? 6 : 8);
-    static constexpr int TILE_B_BYTES = NT * 128;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * (TILE_A_BYTES + TILE_B_BYTES) + IGEMM_TAIL + IGEMM_STATS_BYTES;
+    static constexpr int B_ROWS = PAIR ? NT / 2 : NT;           // filter rows this CTA stages
+    static constexpr int TILE_B_BYTES = B_ROWS * 128;
+    // 128-byte K chunks per stage: one thread issues for both SMs of a pair, and with one chunk per stage its
+    // per-stage work (barrier wait, four MMAs, two commits) is not hidden behind the MMAs; a pair's stage takes two
+    static constexpr int KS = PAIR ? 2 : 1;
+    static constexpr int STAGE_A_BYTES = KS * TILE_A_BYTES, STAGE_B_BYTES = KS * TILE_B_BYTES;
+    static constexpr int STAGES = PAIR ? (NT == 256 ? 3 : 4) : ((NT == 256) ? 4 : (NT == 128 ? 6 : 8));
+    static constexpr int SMEM_BYTES = 1024 + STAGES * (STAGE_A_BYTES + STAGE_B_BYTES) + IGEMM_TAIL + IGEMM_STATS_BYTES;
 };
 
 // STATS: the epilogue also accumulates per-channel (count, mean, M2) of the output about the bias, one block per
 // CTA group and 32-row quarter; the launch must use a grid that is a multiple of n_tiles_n so that every CTA keeps
 // one column tile for all its tiles.
-template <bool TF32, int NT, bool STATS>
+//
+// PAIR (launched as clusters of two CTAs): the work unit is a pair of consecutive pixel tiles times one column tile;
+// CTA rank r of the pair loads pixel tile 2u + r and filter rows [r * NT/2, (r+1) * NT/2) of the column tile into its
+// own shared memory, with the byte counts of both CTAs landing on the even CTA's full barrier.  The even CTA issues
+// M = 256 MMAs that read both CTAs' stages and write both CTAs' TMEM (rows of its own pixels, all NT columns), and
+// signals both CTAs' barriers; the epilogue warps of both CTAs release the accumulator on the even CTA's barrier.
+template <bool TF32, int NT, bool STATS, bool PAIR>
 __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __grid_constant__ IgemmParams p) {
-    using Cfg = IgemmCfg<NT>;
+    using Cfg = IgemmCfg<NT, PAIR>;
     constexpr int STAGES = Cfg::STAGES;
     constexpr int KC = TF32 ? 32 : 64;            // K elements per 128-byte row
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sA = smem_base;
-    const uint32_t sB = sA + STAGES * TILE_A_BYTES;
-    const uint32_t sBar = sB + STAGES * Cfg::TILE_B_BYTES;
+    const uint32_t sB = sA + STAGES * Cfg::STAGE_A_BYTES;
+    const uint32_t sBar = sB + STAGES * Cfg::STAGE_B_BYTES;
     // barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then the TMEM base address
     auto full_bar = [&](int s) { return sBar + 8u * s; };
     auto empty_bar = [&](int s) { return sBar + 8u * (STAGES + s); };
@@ -159,6 +172,8 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int cta_rank = PAIR ? (int)cluster_cta_rank() : 0;
+    const bool issuer = cta_rank == 0;            // the CTA whose warp 1 issues the MMAs
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -167,83 +182,134 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), IGEMM_EPI_WARPS);
+            mbar_init(tempty_bar(b), (PAIR ? 2 : 1) * IGEMM_EPI_WARPS);
         }
         mbar_fence_init();
         tma_prefetch_desc(&p.tm_in);
         tma_prefetch_desc(&p.tm_w);
     }
     if (warp == 1) {
-        tmem_alloc(sTmemPtr, 2 * NT);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(sTmemPtr, 2 * NT);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(sTmemPtr, 2 * NT);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();     // the other CTA's barriers exist before anything is sent to them
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_generic;
 
+    // Work units: pixel tiles (PAIR: pairs of consecutive pixel tiles) x column tiles, unit u -> column tile u % n_tiles_n.
     const long long m_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
-    const long long total_tiles = m_tiles * p.n_tiles_n;
+    const long long total_tiles = (PAIR ? (m_tiles + 1) / 2 : m_tiles) * p.n_tiles_n;
+    const long long t_first = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+    const long long t_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
+    // pixel tile of this CTA in unit t; one past the last tile (odd tile count) decodes to an image index outside the
+    // tensor: its loads are zero-filled and none of its rows is stored
+    auto decode = [&](long long t, int& nt, int& w0, int& h0, int& n0) {
+        nt = (int)(t % p.n_tiles_n);
+        long long mt = t / p.n_tiles_n;
+        if (PAIR) mt = 2 * mt + cta_rank;
+        const int tw = (int)(mt % p.tiles_w);
+        mt /= p.tiles_w;
+        const int th = (int)(mt % p.tiles_h);
+        const int tn = (int)(mt / p.tiles_h);
+        w0 = tw * p.BW; h0 = th * p.BH; n0 = tn * p.BN;
+    };
     const int taps = p.fH * p.fW;
     const int kiters = taps * p.kchunks;
-    const uint32_t stage_tx = (uint32_t)p.rows * 128u + (uint32_t)NT * 128u;
+    // bytes per stage on the full barrier: this CTA's two boxes, in a pair those of both CTAs
+    const uint32_t chunk_tx = ((uint32_t)p.rows * 128u + (uint32_t)Cfg::B_ROWS * 128u) * (PAIR ? 2u : 1u);
+    constexpr int KS = Cfg::KS;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int nt = (int)(t % p.n_tiles_n);
-                long long mt = t / p.n_tiles_n;
-                const int tw = (int)(mt % p.tiles_w);
-                mt /= p.tiles_w;
-                const int th = (int)(mt % p.tiles_h);
-                const int tn = (int)(mt / p.tiles_h);
-                const int w0 = tw * p.BW, h0 = th * p.BH, n0 = tn * p.BN;
-                for (int tap = 0; tap < taps && ok; ++tap) {
-                    const int i = tap / p.fW, j = tap % p.fW;
-                    for (int kc = 0; kc < p.kchunks; ++kc, ++it) {
-                        const int s = it % STAGES;
-                        const uint32_t ph = (it / STAGES) & 1u;
-                        if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) { ok = false; break; }
-                        mbar_arrive_expect_tx(full_bar(s), stage_tx);
-                        tma_load_4d(sA + s * TILE_A_BYTES, &p.tm_in, full_bar(s), kc * KC, w0 + p.sgn * j + p.off_w,
-                                    h0 + p.sgn * i + p.off_h, n0);
-                        tma_load_2d(sB + s * Cfg::TILE_B_BYTES, &p.tm_w, full_bar(s), kc * KC,
-                                    tap * p.rows_per_tap + nt * NT);
+            for (long long t = t_first; t < total_tiles && ok; t += t_step) {
+                int nt, w0, h0, n0;
+                decode(t, nt, w0, h0, n0);
+                int tap = 0, kc = 0;                       // the (tap, K chunk) of the next chunk to load
+                for (int k0 = 0; k0 < kiters && ok; k0 += KS, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    const int nsub = kiters - k0 < KS ? kiters - k0 : KS;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) { ok = false; break; }
+                    if (issuer) mbar_arrive_expect_tx(full_bar(s), chunk_tx * (uint32_t)nsub);
+                    const uint32_t bar = PAIR ? cluster_map_shared(full_bar(s), 0) : full_bar(s);   // PAIR: the even CTA's
+                    for (int c = 0; c < nsub; ++c) {
+                        const int i = tap / p.fW, j = tap % p.fW;
+                        const uint32_t dA = sA + s * Cfg::STAGE_A_BYTES + c * TILE_A_BYTES;
+                        const uint32_t dB = sB + s * Cfg::STAGE_B_BYTES + c * Cfg::TILE_B_BYTES;
+                        if (PAIR) {
+                            tma_load_4d_pair(dA, &p.tm_in, bar, kc * KC, w0 + p.sgn * j + p.off_w, h0 + p.sgn * i + p.off_h, n0);
+                            tma_load_2d_pair(dB, &p.tm_w, bar, kc * KC, tap * p.rows_per_tap + nt * NT + cta_rank * Cfg::B_ROWS);
+                        } else {
+                            tma_load_4d(dA, &p.tm_in, bar, kc * KC, w0 + p.sgn * j + p.off_w, h0 + p.sgn * i + p.off_h, n0);
+                            tma_load_2d(dB, &p.tm_w, bar, kc * KC, tap * p.rows_per_tap + nt * NT);
+                        }
+                        if (++kc == p.kchunks) { kc = 0; ++tap; }
                     }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (one thread)
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(TF32 ? 2u : 1u, 0u, 0u, 128u, (uint32_t)NT);
+        if (lane == 0 && issuer) {
+            constexpr uint32_t idesc = make_idesc(TF32 ? 2u : 1u, 0u, 0u, PAIR ? 256u : 128u, (uint32_t)NT);
             uint32_t it = 0;
             uint32_t lt = 0;
             bool ok = true;
-            for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
+            for (long long t = t_first; t < total_tiles && ok; t += t_step, ++lt) {
                 const uint32_t buf = lt & 1u;
                 const uint32_t aph = (lt >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * NT;
-                for (int ki = 0; ki < kiters; ++ki, ++it) {
+                for (int k0 = 0; k0 < kiters; k0 += KS, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
+                    const int nsub = kiters - k0 < KS ? kiters - k0 : KS;
                     if (!mbar_wait(full_bar(s), ph, p.status, DS_TIMEOUT_FULL)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a0 = sA + s * TILE_A_BYTES;
-                    const uint32_t b0 = sB + s * Cfg::TILE_B_BYTES;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        umma<TF32>(d_tmem, make_smem_desc(a0 + k * 32, 16, 1024), make_smem_desc(b0 + k * 32, 16, 1024),
-                                   idesc, (ki > 0 || k > 0) ? 1u : 0u);
+                    for (int c = 0; c < KS; ++c) {
+                        if (c < nsub) {
+                            const uint32_t a0 = sA + s * Cfg::STAGE_A_BYTES + c * TILE_A_BYTES;
+                            const uint32_t b0 = sB + s * Cfg::STAGE_B_BYTES + c * Cfg::TILE_B_BYTES;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const uint32_t acc = (k0 + c > 0 || k > 0) ? 1u : 0u;
+                                if (PAIR)
+                                    umma_pair<TF32>(d_tmem, make_smem_desc(a0 + k * 32, 16, 1024),
+                                                    make_smem_desc(b0 + k * 32, 16, 1024), idesc, acc);
+                                else
+                                    umma<TF32>(d_tmem, make_smem_desc(a0 + k * 32, 16, 1024), make_smem_desc(b0 + k * 32, 16, 1024),
+                                               idesc, acc);
+                            }
+                        }
                     }
-                    umma_commit(empty_bar(s));   // stage is free once these MMAs have read it
+                    // the stage is free (in both CTAs) once these MMAs have read it
+                    if (PAIR) {
+                        umma_commit_pair(empty_bar(s));
+                        umma_commit_pair(cluster_map_shared(empty_bar(s), 1));
+                    } else {
+                        umma_commit(empty_bar(s));
+                    }
                 }
-                if (ok) umma_commit(tfull_bar(buf));
+                if (ok) {
+                    if (PAIR) {
+                        umma_commit_pair(tfull_bar(buf));
+                        umma_commit_pair(cluster_map_shared(tfull_bar(buf), 1));
+                    } else {
+                        umma_commit(tfull_bar(buf));
+                    }
+                }
             }
         }
     } else {
@@ -276,14 +342,9 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
         }
         uint32_t lt = 0;
         bool ok = true;
-        for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
-            const int nt = (int)(t % p.n_tiles_n);
-            long long mt = t / p.n_tiles_n;
-            const int tw = (int)(mt % p.tiles_w);
-            mt /= p.tiles_w;
-            const int th = (int)(mt % p.tiles_h);
-            const int tn = (int)(mt / p.tiles_h);
-            const int w0 = tw * p.BW, h0 = th * p.BH, n0 = tn * p.BN;
+        for (long long t = t_first; t < total_tiles && ok; t += t_step, ++lt) {
+            int nt, w0, h0, n0;
+            decode(t, nt, w0, h0, n0);
             const int col0 = nt * NT + col_begin + tcol4;             // first of this thread's columns
             float* rowp[4];
 #pragma unroll
@@ -324,7 +385,10 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
                 if (cb + 16 * IGEMM_EPI_UB >= ncols) {           // accumulator fully read by this warp
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                    if (lane == 0) {
+                        if (PAIR) mbar_arrive_cluster(cluster_map_shared(tempty_bar(buf), 0));
+                        else mbar_arrive(tempty_bar(buf));
+                    }
                 }
 #pragma unroll
                 for (int u = 0; u < IGEMM_EPI_UB; ++u) {
@@ -399,8 +463,10 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
             // (count, mean, M2) of this warp's rows over all tiles of the CTA.  The grid is a multiple of
             // n_tiles_n, so the CTA kept column tile blockIdx.x % n_tiles_n; the n_tiles_n CTAs of a group fill the
             // disjoint column ranges of block (group * 4 + q) of [3][n_out].
-            const int ntc = blockIdx.x % p.n_tiles_n;
-            float* sp = p.stats + ((size_t)(blockIdx.x / p.n_tiles_n) * 4 + q) * 3 * (size_t)p.n_out;
+            // (PAIR: the same with pairs in the place of CTAs and one block group per CTA of the pair.)
+            const int ntc = (int)(t_first % p.n_tiles_n);
+            const size_t group = PAIR ? (size_t)(t_first / p.n_tiles_n) * 2 + cta_rank : (size_t)(t_first / p.n_tiles_n);
+            float* sp = p.stats + (group * 4 + q) * 3 * (size_t)p.n_out;
             for (int cc = 0; cc < ncols; cc += 16) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -418,10 +484,12 @@ __global__ void __launch_bounds__(IGEMM_THREADS, 1) igemm_conv_kernel(const __gr
     }
 
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();     // neither CTA leaves while the other may still address its barriers or TMEM
+    else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 2 * NT);
+        if (PAIR) tmem_dealloc_pair(tmem_base, 2 * NT);
+        else tmem_dealloc(tmem_base, 2 * NT);
     }
 }
 
@@ -966,24 +1034,63 @@ static int igemm_grid(long long m_tiles, int n_tiles_n, bool stats) {
     return grid;
 }
 
-template <bool TF32, int NT, bool STATS>
+// CTA pairs are used for 256- and 128-wide column tiles where there is enough work to give every pair of SMs at
+// least two units.  Measured on B200 (batch 4096, bf16, single CTAs -> pairs): 16x16 128->256 forward 0.544 -> 0.461 ms
+// and its dX (128 columns) 0.663 -> 0.597 ms, 8x8 256->512 forward 0.451 -> 0.406 ms and its dX 0.415 -> 0.383 ms.
+// With one K chunk per stage the 128-column pair was SLOWER than single CTAs (0.709 ms): the one issuing thread then
+// has 256 tensor clocks per stage for a barrier wait, four MMAs and two commits; two chunks per stage fixed that
+// and also gave the 256-column pair 3-4 %.
+static bool igemm_use_pairs(long long m_tiles, int nt, int n_tiles_n) {
+    return (nt == 256 || nt == 128) && (m_tiles + 1) / 2 * n_tiles_n >= 2LL * (num_sms() / 2);
+}
+static int igemm_pair_grid(long long m_tiles, int n_tiles_n, bool stats) {
+    const long long units = (m_tiles + 1) / 2 * n_tiles_n;
+    int pairs = (int)(units < num_sms() / 2 ? units : num_sms() / 2);
+    if (stats && pairs > n_tiles_n) pairs -= pairs % n_tiles_n;
+    return 2 * pairs;
+}
+
+template <bool TF32, int NT, bool STATS, bool PAIR>
 static int launch_igemm_k(const IgemmParams& p, cudaStream_t st) {
-    using Cfg = IgemmCfg<NT>;
+    using Cfg = IgemmCfg<NT, PAIR>;
     static PerDeviceSmem configured;
-    if (int rc = ensure_dynamic_smem(igemm_conv_kernel<TF32, NT, STATS>, Cfg::SMEM_BYTES, configured, "igemm_conv")) return rc;
-    const int grid = igemm_grid(1LL * p.tiles_w * p.tiles_h * p.tiles_n, p.n_tiles_n, STATS);
-    if (STATS && grid % p.n_tiles_n) return set_error(AE_UNSUPPORTED, "conv forward statistics: %d column tiles on %d CTAs", p.n_tiles_n, grid);
+    if (int rc = ensure_dynamic_smem(igemm_conv_kernel<TF32, NT, STATS, PAIR>, Cfg::SMEM_BYTES, configured, "igemm_conv")) return rc;
+    const long long m_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
+    const int grid = PAIR ? igemm_pair_grid(m_tiles, p.n_tiles_n, STATS) : igemm_grid(m_tiles, p.n_tiles_n, STATS);
+    if (STATS && (grid / (PAIR ? 2 : 1)) % p.n_tiles_n)
+        return set_error(AE_UNSUPPORTED, "conv forward statistics: %d column tiles on %d CTAs", p.n_tiles_n, grid);
     const int pk = p.sgn > 0 ? PK_IGEMM_FWD : PK_IGEMM_DX;
     prof_begin(pk, st);
-    igemm_conv_kernel<TF32, NT, STATS><<<grid, IGEMM_THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    if (PAIR) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(grid, 1, 1);
+        cfg.blockDim = dim3(IGEMM_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+        cfg.stream = st;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, igemm_conv_kernel<TF32, NT, STATS, PAIR>, p);
+        if (e != cudaSuccess) return set_error(AE_CUDA, "igemm_conv_kernel (CTA pairs): %s", cudaGetErrorString(e));
+    } else {
+        igemm_conv_kernel<TF32, NT, STATS, PAIR><<<grid, IGEMM_THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    }
     prof_end(pk, st);
     count_launch();
     return check_launch("igemm_conv_kernel");
 }
 
 template <bool TF32, int NT>
-static int launch_igemm(const IgemmParams& p, cudaStream_t st) {
-    return p.stats ? launch_igemm_k<TF32, NT, true>(p, st) : launch_igemm_k<TF32, NT, false>(p, st);
+static int launch_igemm(const IgemmParams& p, bool pair, cudaStream_t st) {
+    if constexpr (NT == 256 || NT == 128) {
+        if (pair) return p.stats ? launch_igemm_k<TF32, NT, true, true>(p, st) : launch_igemm_k<TF32, NT, false, true>(p, st);
+    }
+    return p.stats ? launch_igemm_k<TF32, NT, true, false>(p, st) : launch_igemm_k<TF32, NT, false, false>(p, st);
 }
 
 static int pick_nt(int n_padded) {
@@ -994,12 +1101,12 @@ static int pick_nt(int n_padded) {
 }
 
 template <bool TF32>
-static int dispatch_igemm(IgemmParams& p, int nt, cudaStream_t st) {
+static int dispatch_igemm(IgemmParams& p, int nt, bool pair, cudaStream_t st) {
     switch (nt) {
-        case 256: return launch_igemm<TF32, 256>(p, st);
-        case 128: return launch_igemm<TF32, 128>(p, st);
-        case 64: return launch_igemm<TF32, 64>(p, st);
-        default: return launch_igemm<TF32, 32>(p, st);
+        case 256: return launch_igemm<TF32, 256>(p, pair, st);
+        case 128: return launch_igemm<TF32, 128>(p, pair, st);
+        case 64: return launch_igemm<TF32, 64>(p, false, st);
+        default: return launch_igemm<TF32, 32>(p, false, st);
     }
 }
 
@@ -1023,9 +1130,10 @@ static int run_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, in
     const int KC = 128 / elt;
     const CUtensorMapDataType dt = tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     const int nt = pick_nt(n_padded);
+    const bool pair = igemm_use_pairs(til.total(), nt, ceil_div(n_padded, nt));   // each CTA of a pair stages half the filter rows
     int rc;
     if ((rc = make_map_nhwc(&p.tm_in, in, dt, elt, in_C, in_W, in_H, S, KC, til.BW, til.BH, til.BN))) return rc;
-    if ((rc = make_map_2d(&p.tm_w, wmat, dt, elt, w_inner, 1LL * taps * rows_per_tap, KC, nt))) return rc;
+    if ((rc = make_map_2d(&p.tm_w, wmat, dt, elt, w_inner, 1LL * taps * rows_per_tap, KC, pair ? nt / 2 : nt))) return rc;
     if ((reinterpret_cast<uintptr_t>(out) & 15u) || (out_C & 3))
         return set_error(AE_BAD_ARG, "conv output must be 16-byte aligned with a channel count that is a multiple of 4");
     p.out = out;
@@ -1040,7 +1148,7 @@ static int run_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, in
     p.rows_per_tap = rows_per_tap;
     p.fH = fH; p.fW = fW; p.sgn = sgn; p.off_h = off_h; p.off_w = off_w;
     p.kchunks = ceil_div(in_C, KC);
-    return tf32 ? dispatch_igemm<true>(p, nt, st) : dispatch_igemm<false>(p, nt, st);
+    return tf32 ? dispatch_igemm<true>(p, nt, pair, st) : dispatch_igemm<false>(p, nt, pair, st);
 }
 
 static int launch_cast(const float* src, __nv_bfloat16* dst, long long rows, int C, int Cp, float* colsum_part,
@@ -1070,7 +1178,13 @@ long long tc_conv_stats_blocks(const AetherConvDesc& d) {
                                                  pl.Cout_p, d.fH, d.fW);
     if (hb > 0) return hb;
     // per-tap kernel: one block per CTA group (the CTAs of one set of pixel tiles) and 32-row quarter
-    const int n_tiles_n = ceil_div(pl.Cout_p, pick_nt(pl.Cout_p));
+    const int nt = pick_nt(pl.Cout_p);
+    const int n_tiles_n = ceil_div(pl.Cout_p, nt);
+    if (igemm_use_pairs(pl.til_out.total(), nt, n_tiles_n)) {       // one block group per CTA of a pair
+        const int pairs = igemm_pair_grid(pl.til_out.total(), n_tiles_n, true) / 2;
+        if (pairs % n_tiles_n) return 0;
+        return 4LL * 2 * (pairs / n_tiles_n);
+    }
     const int grid = igemm_grid(pl.til_out.total(), n_tiles_n, true);
     if (grid % n_tiles_n) return 0;
     return 4LL * (grid / n_tiles_n);

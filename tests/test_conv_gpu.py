@@ -85,6 +85,8 @@ SHAPES = [
     (16, 8, 8, 256, 256, 3, "same"), (4, 14, 14, 32, 64, 3, "same"), (5, 9, 7, 64, 64, 3, "valid"),
     (3, 10, 10, 48, 80, 5, "same"), (200, 1, 1, 512, 128, 1, "valid"), (2, 33, 17, 16, 20, 3, "same"),
     (1, 3, 3, 64, 192, 3, "same"), (130, 4, 4, 64, 64, 3, "same"), (2, 20, 150, 32, 32, 3, "same"),
+    # enough 256-wide work for CTA pairs: an odd number of pixel tiles (forward), dX at 256 input channels, two column tiles
+    (61, 24, 24, 128, 256, 3, "same"), (150, 16, 16, 256, 128, 3, "same"), (300, 8, 8, 128, 512, 3, "same"),
 ]
 
 

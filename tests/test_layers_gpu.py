@@ -76,6 +76,9 @@ def test_batch_norm_shapes(env, shape):
                                   (16, 8, 8, 256, 256, "bf16", True), (40, 8, 8, 128, 512, "bf16", True),
                                   (50, 16, 16, 128, 256, "bf16", True), (7, 10, 10, 32, 96, "tf32", True),
                                   (3, 5, 7, 32, 40, "bf16", True), (700, 6, 6, 16, 96, "bf16", True),
+                                  # per-tap kernel on CTA pairs: odd number of pixel tiles, two column tiles, TF32
+                                  (61, 24, 24, 128, 256, "bf16", True), (300, 8, 8, 128, 512, "bf16", True),
+                                  (149, 16, 16, 64, 256, "tf32", True),
                                   (4, 12, 12, 8, 16, "fp32", False)])
 def test_batch_norm_statistics_from_conv_epilogue(env, case):
     """Conv_Layer -> Batch_Norm with the batch statistics taken in the convolution's epilogue: same result as

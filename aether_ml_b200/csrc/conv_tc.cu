@@ -525,10 +525,16 @@ struct DwCfg {
     static_assert(STAGES >= 2, "need at least two stages");
 };
 
-template <bool TF32, int NB>
+// PAIR (clusters of two CTAs, cta_group::2): an M group is 256 rows -- each CTA stages the MB units of its own half --
+// and a column tile 2 * NT channels of dy, of which each CTA stages its own NT.  Per stage a CTA loads the same bytes as
+// a single CTA but the pair does four times one CTA's products with them: the kernel is bound by what an SM can pull
+// from L2, and that halves per FLOP.  p.MG, p.gpc and p.n_tiles_n then count pair groups and pair column tiles.
+template <bool TF32, int NB, bool PAIR>
 __global__ void __launch_bounds__(DW_THREADS, 1) dw_conv_kernel(const __grid_constant__ DwParams p) {
     using Cfg = DwCfg<TF32, NB>;
     constexpr int STAGES = Cfg::STAGES, MB = Cfg::MB, NT = Cfg::NT, UC = Cfg::UC;
+    constexpr int PF = PAIR ? 2 : 1;              // CTAs per M group and column tile
+    constexpr int NTP = PF * NT;                  // accumulator columns of one M group
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -541,6 +547,8 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_conv_kernel(const __grid_con
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int cta_rank = PAIR ? (int)cluster_cta_rank() : 0;
+    const bool issuer = cta_rank == 0;
 
     // Rows past p.rows are never written by TMA but are read by the MMAs: keep them zero.
     {
@@ -560,22 +568,28 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_conv_kernel(const __grid_con
         tma_prefetch_desc(&p.tm_dy);
     }
     if (warp == 1) {
-        tmem_alloc(sTmemPtr, 512);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(sTmemPtr, 512);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(sTmemPtr, 512);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_generic;
 
-    const int split = blockIdx.x, splits = gridDim.x;
+    const int split = PAIR ? (blockIdx.x >> 1) : blockIdx.x, splits = PAIR ? (gridDim.x >> 1) : gridDim.x;
     const int gc = blockIdx.y / p.n_tiles_n;
     const int nt = blockIdx.y % p.n_tiles_n;
     const int g_begin = gc * p.gpc;
     const int g_end = min(p.MG, g_begin + p.gpc);
     const int ngroups = g_end - g_begin;
     const long long total_ptiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
-    const uint32_t stage_tx = (uint32_t)(MB + NB) * (uint32_t)p.rows * 128u;
+    const uint32_t stage_tx = (uint32_t)(MB + NB) * (uint32_t)p.rows * 128u * (uint32_t)PF;   // both CTAs' boxes
     const int ksteps = (p.rows + Cfg::KROWS - 1) / Cfg::KROWS;
 
     if (warp == 0) {
@@ -593,25 +607,28 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_conv_kernel(const __grid_con
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) { ok = false; break; }
-                    mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                    if (issuer) mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                    const uint32_t bar = PAIR ? cluster_map_shared(full_bar(s), 0) : full_bar(s);   // PAIR: the even CTA's
                     const uint32_t st = smem_base + s * Cfg::STAGE_BYTES;
                     for (int m = 0; m < MB; ++m) {
-                        int u = g * MB + m;
+                        int u = (g * PF + cta_rank) * MB + m;
                         if (u >= p.U) u = p.U - 1;       // padding unit of the last group: results are dropped
                         const int tap = u / p.cblocks, cb = u % p.cblocks;
                         const int i = tap / p.fW, j = tap % p.fW;
-                        tma_load_4d(st + m * TILE_A_BYTES, &p.tm_x, full_bar(s), cb * UC, w0 + j - p.padW,
-                                    h0 + i - p.padH, n0);
+                        if (PAIR) tma_load_4d_pair(st + m * TILE_A_BYTES, &p.tm_x, bar, cb * UC, w0 + j - p.padW, h0 + i - p.padH, n0);
+                        else tma_load_4d(st + m * TILE_A_BYTES, &p.tm_x, bar, cb * UC, w0 + j - p.padW, h0 + i - p.padH, n0);
                     }
-                    for (int nb = 0; nb < NB; ++nb)
-                        tma_load_4d(st + (MB + nb) * TILE_A_BYTES, &p.tm_dy, full_bar(s), (nt * NB + nb) * UC, w0, h0,
-                                    n0);
+                    for (int nb = 0; nb < NB; ++nb) {
+                        const int dyc = ((nt * PF + cta_rank) * NB + nb) * UC;
+                        if (PAIR) tma_load_4d_pair(st + (MB + nb) * TILE_A_BYTES, &p.tm_dy, bar, dyc, w0, h0, n0);
+                        else tma_load_4d(st + (MB + nb) * TILE_A_BYTES, &p.tm_dy, bar, dyc, w0, h0, n0);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(TF32 ? 2u : 1u, 1u, 1u, 128u, (uint32_t)NT);
+        if (lane == 0 && issuer) {
+            constexpr uint32_t idesc = make_idesc(TF32 ? 2u : 1u, 1u, 1u, 128u * PF, (uint32_t)NTP);
             uint32_t it = 0;
             bool ok = true;
             bool first = true;
@@ -623,20 +640,34 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_conv_kernel(const __grid_con
                     tc_fence_after();
                     const uint32_t a0 = smem_base + s * Cfg::STAGE_BYTES;
                     const uint32_t b0 = a0 + MB * TILE_A_BYTES;
-                    const uint32_t d_tmem = tmem_base + g * NT;
+                    const uint32_t d_tmem = tmem_base + g * NTP;
                     for (int kk = 0; kk < ksteps; ++kk) {
                         const uint32_t koff = kk * Cfg::KROWS * 128;
                         // MN-major operands: 16-bit types use the plain 128-byte swizzle (8-row K groups);
                         // 32-bit types need the 32-byte-unit variant (4-row K groups).
                         constexpr uint32_t LT = TF32 ? 1u : 2u;
                         constexpr uint32_t SBO = TF32 ? 512u : 1024u;
-                        umma<TF32>(d_tmem, make_smem_desc(a0 + koff, TILE_A_BYTES, SBO, LT),
-                                   make_smem_desc(b0 + koff, TILE_A_BYTES, SBO, LT), idesc, (!first || kk > 0) ? 1u : 0u);
+                        if (PAIR)
+                            umma_pair<TF32>(d_tmem, make_smem_desc(a0 + koff, TILE_A_BYTES, SBO, LT),
+                                            make_smem_desc(b0 + koff, TILE_A_BYTES, SBO, LT), idesc, (!first || kk > 0) ? 1u : 0u);
+                        else
+                            umma<TF32>(d_tmem, make_smem_desc(a0 + koff, TILE_A_BYTES, SBO, LT),
+                                       make_smem_desc(b0 + koff, TILE_A_BYTES, SBO, LT), idesc, (!first || kk > 0) ? 1u : 0u);
                     }
-                    umma_commit(empty_bar(s));
+                    if (PAIR) {
+                        umma_commit_pair(empty_bar(s));
+                        umma_commit_pair(cluster_map_shared(empty_bar(s), 1));
+                    } else {
+                        umma_commit(empty_bar(s));
+                    }
                 }
             }
-            umma_commit(done_bar);
+            if (PAIR) {
+                umma_commit_pair(done_bar);
+                umma_commit_pair(cluster_map_shared(done_bar, 1));
+            } else {
+                umma_commit(done_bar);
+            }
         }
     } else {
         const int q = warp & 3;
@@ -648,12 +679,12 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_conv_kernel(const __grid_con
         if (ok) {
             const int m = row / UC, c_in = row % UC;
             for (int g = 0; g < ngroups; ++g) {
-                const int u = (g_begin + g) * MB + m;
+                const int u = ((g_begin + g) * PF + cta_rank) * MB + m;
 #pragma unroll 1
-                for (int ch = 0; ch < NT / 32; ++ch) {
+                for (int ch = 0; ch < NTP / 32; ++ch) {
                     uint32_t r[32];
                     if (any_tiles) {
-                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + g * NT + ch * 32, r);
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + g * NTP + ch * 32, r);
                         tmem_ld_wait();
                     } else {
 #pragma unroll
@@ -661,7 +692,7 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_conv_kernel(const __grid_con
                     }
                     if (u < p.U) {
                         float4* dst = reinterpret_cast<float4*>(
-                            p.part + (((size_t)split * p.U + u) * UC + c_in) * (size_t)p.ldn + nt * NT + ch * 32);
+                            p.part + (((size_t)split * p.U + u) * UC + c_in) * (size_t)p.ldn + nt * NTP + ch * 32);
 #pragma unroll
                         for (int k = 0; k < 8; ++k)
                             dst[k] = make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]),
@@ -673,10 +704,12 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_conv_kernel(const __grid_con
     }
 
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();
+    else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        if (PAIR) tmem_dealloc_pair(tmem_base, 512);
+        else tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -924,6 +957,8 @@ struct TcPlan {
     size_t off_xsh, off_dysh, off_wf, off_wd, off_part, off_dbpart, total;
     // dW decomposition
     int dw_nb, dw_nt, dw_cblocks, dw_U, dw_MG, dw_gpc, dw_ngc, dw_ntn, dw_splits;
+    bool dw_pair;     // per-tap dW kernel on CTA pairs: dw_MG / dw_gpc / dw_ntn count pair groups and pair column tiles
+    int dw_halo_splits;   // most splits the halo dW kernel may write (sizes the partial buffer with dw_splits)
     int db_blocks, db_rows_max;
     PixelTiling til_out;   // tiles over output pixels (forward, dW)
     PixelTiling til_in;    // tiles over input pixels (dX)
@@ -962,17 +997,32 @@ static TcPlan make_plan(const AetherConvDesc& d) {
     pl.dw_nt = pl.dw_nb * UC;
     pl.dw_cblocks = pl.Cin_p / UC;
     pl.dw_U = pl.taps * pl.dw_cblocks;
-    pl.dw_MG = ceil_div(pl.dw_U, MB);
-    const int max_gpc = 512 / pl.dw_nt;
-    pl.dw_ngc = ceil_div(pl.dw_MG, max_gpc);
-    pl.dw_gpc = ceil_div(pl.dw_MG, pl.dw_ngc);
-    pl.dw_ngc = ceil_div(pl.dw_MG, pl.dw_gpc);
-    pl.dw_ntn = pl.Cout_p / pl.dw_nt;
-    long long ptiles = pl.til_out.total();
-    long long want = num_sms() / (pl.dw_ngc * pl.dw_ntn);
-    if (want < 1) want = 1;
-    if (want > ptiles) want = ptiles;
-    pl.dw_splits = (int)want;
+    const long long ptiles = pl.til_out.total();
+    auto decompose = [&](int pf) {       // pf CTAs per M group and column tile; returns the split count
+        pl.dw_MG = ceil_div(pl.dw_U, MB * pf);
+        const int max_gpc = 512 / (pl.dw_nt * pf);
+        pl.dw_ngc = ceil_div(pl.dw_MG, max_gpc);
+        pl.dw_gpc = ceil_div(pl.dw_MG, pl.dw_ngc);
+        pl.dw_ngc = ceil_div(pl.dw_MG, pl.dw_gpc);
+        pl.dw_ntn = pl.Cout_p / (pl.dw_nt * pf);
+        long long want = (num_sms() / pf) / (pl.dw_ngc * pl.dw_ntn);
+        if (want > ptiles) want = ptiles;
+        return (int)want;
+    };
+    // pairs: the channel counts must fill 256 rows and two column halves, and every pair needs a few pixel tiles
+    pl.dw_halo_splits = decompose(1);
+    if (pl.dw_halo_splits < 1) pl.dw_halo_splits = 1;
+    pl.dw_splits = pl.dw_halo_splits;
+    pl.dw_pair = pl.dw_nb == 2 && pl.Cout_p % (2 * pl.dw_nt) == 0 && pl.dw_U >= 2 * MB;
+    if (pl.dw_pair) {
+        const int ps = decompose(2);
+        if (ps < 1 || ptiles < 4LL * ps) {
+            pl.dw_pair = false;
+            decompose(1);
+        } else {
+            pl.dw_splits = ps;
+        }
+    }
     const long long out_rows = 1LL * d.S * pl.Ho * pl.Wo;
     pl.db_blocks = (int)(out_rows < 4LL * num_sms() * 64 ? (out_rows + 63) / 64 : 4LL * num_sms());
     if (pl.db_blocks < 1) pl.db_blocks = 1;
@@ -985,7 +1035,7 @@ static TcPlan make_plan(const AetherConvDesc& d) {
     pl.off_dysh = take(pl.tf32 ? 0 : (size_t)out_rows * pl.Cout_p * 2);
     pl.off_wf = take((size_t)pl.taps * pl.Cout_p * pl.Cin_p * pl.elt);
     pl.off_wd = take(pl.tf32 ? 0 : (size_t)pl.taps * pl.Cin_p * pl.Cout_p * pl.elt);
-    int part_splits = pl.dw_splits;
+    int part_splits = pl.dw_splits > pl.dw_halo_splits ? pl.dw_splits : pl.dw_halo_splits;
     if (!pl.tf32) {
         const int rs = rows_dw_max_splits(pl.Cin_p, pl.Cout_p, pl.Ho, pl.Wo, d.S, d.fH, d.fW);
         if (rs > part_splits) part_splits = rs;
@@ -1216,13 +1266,31 @@ int tc_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, const f
                      pl.til_out, pl.Cout_p, d.fH, d.fW, +1, -d.padH, -d.padW, b, stats, st);
 }
 
-template <bool TF32, int NB>
+template <bool TF32, int NB, bool PAIR>
 static int launch_dw(const DwParams& p, int splits, int grid_y, cudaStream_t st) {
     using Cfg = DwCfg<TF32, NB>;
     static PerDeviceSmem configured;
-    if (int rc = ensure_dynamic_smem(dw_conv_kernel<TF32, NB>, Cfg::SMEM_BYTES, configured, "dw_conv")) return rc;
+    if (int rc = ensure_dynamic_smem(dw_conv_kernel<TF32, NB, PAIR>, Cfg::SMEM_BYTES, configured, "dw_conv")) return rc;
     prof_begin(PK_DW, st);
-    dw_conv_kernel<TF32, NB><<<dim3(splits, grid_y), DW_THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    if (PAIR) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(2 * splits, grid_y, 1);
+        cfg.blockDim = dim3(DW_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+        cfg.stream = st;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, dw_conv_kernel<TF32, NB, PAIR>, p);
+        if (e != cudaSuccess) return set_error(AE_CUDA, "dw_conv_kernel (CTA pairs): %s", cudaGetErrorString(e));
+    } else {
+        dw_conv_kernel<TF32, NB, PAIR><<<dim3(splits, grid_y), DW_THREADS, Cfg::SMEM_BYTES, st>>>(p);
+    }
     prof_end(PK_DW, st);
     count_launch();
     return check_launch("dw_conv_kernel");
@@ -1292,7 +1360,13 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
 
     // ---- dW: split over pixel tiles, fixed-order reduction of the partials
     bool dw_done = false;
-    if (dw && !pl.tf32) {   // wide images: halo-reuse kernel (every tap re-reads one shared-memory window)
+    // Which dW kernel (bf16).  The kernels that reuse a shared-memory window across the taps win on wide images; on
+    // 16..20-pixel rows the per-tap kernel on CTA pairs is faster (a fifth of such a window is halo).  Measured on B200,
+    // 128 -> 256 channels, window kernel / pair kernel in ms: 32x32 (batch 1024) 0.518 / 0.545, 24x24 (2048) 0.556 /
+    // 0.654, 20x20 (2048) 0.474 / 0.452, 16x16 (4096) 0.597 / 0.531, 16x16 256 -> 256 (2048) 0.656 / 0.486,
+    // 12x12 (4096) 0.296 / 0.326.
+    const bool per_tap_pairs = pl.dw_pair && pl.Wo >= 16 && pl.Wo <= 20;
+    if (dw && !pl.tf32 && !per_tap_pairs) {   // wide images: halo-reuse kernel (every tap re-reads one shared-memory window)
         int splits = 0;
         float* part = reinterpret_cast<float*>(wsb + pl.off_part);
         int sa = 0, sb = 0, tap_split = 0;
@@ -1307,7 +1381,7 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
         }
         if (!dw_done) {
             if ((rc = run_halo_dw(x_op, pl.Cin_p, d.H, d.W, d.S, dy_op, pl.Cout_p, pl.Ho, pl.Wo, d.fH, d.fW, d.padH, d.padW,
-                                  part, pl.dw_splits, &splits, st, &dw_done)))
+                                  part, pl.dw_halo_splits, &splits, st, &dw_done)))
                 return rc;
             if (dw_done) {
                 dw_reduce_kernel<<<dw_reduce_grid(pl.taps, d.Cin, d.Cout), 256, 0, st>>>(part, dw, splits, pl.dw_U, pl.KC, pl.Cout_p, pl.dw_cblocks,
@@ -1340,8 +1414,9 @@ int tc_conv_bwd(const AetherConvDesc& d, const float* x, const float* dy, const 
         p.cblocks = pl.dw_cblocks; p.U = pl.dw_U; p.MG = pl.dw_MG; p.gpc = pl.dw_gpc;
         p.n_tiles_n = pl.dw_ntn; p.ldn = pl.Cout_p;
         const int gy = pl.dw_ngc * pl.dw_ntn;
-        if (pl.tf32) rc = (pl.dw_nb == 2) ? launch_dw<true, 2>(p, pl.dw_splits, gy, st) : launch_dw<true, 1>(p, pl.dw_splits, gy, st);
-        else rc = (pl.dw_nb == 2) ? launch_dw<false, 2>(p, pl.dw_splits, gy, st) : launch_dw<false, 1>(p, pl.dw_splits, gy, st);
+        if (pl.dw_pair) rc = pl.tf32 ? launch_dw<true, 2, true>(p, pl.dw_splits, gy, st) : launch_dw<false, 2, true>(p, pl.dw_splits, gy, st);
+        else if (pl.tf32) rc = (pl.dw_nb == 2) ? launch_dw<true, 2, false>(p, pl.dw_splits, gy, st) : launch_dw<true, 1, false>(p, pl.dw_splits, gy, st);
+        else rc = (pl.dw_nb == 2) ? launch_dw<false, 2, false>(p, pl.dw_splits, gy, st) : launch_dw<false, 1, false>(p, pl.dw_splits, gy, st);
         if (rc) return rc;
         if (!direct) {
             dw_reduce_kernel<<<dw_reduce_grid(pl.taps, d.Cin, d.Cout), 256, 0, st>>>(p.part, dw, pl.dw_splits, pl.dw_U, pl.KC, pl.Cout_p,

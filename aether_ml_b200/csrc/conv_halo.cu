@@ -60,10 +60,23 @@ static constexpr int HALO_TAIL = 2048;          // barriers, TMEM pointer, bias
 static constexpr int HALO_STATS_BYTES = HALO_EPI_WARPS * STATS_WARP_FLOATS * 4;   // per-warp running column sums and pivots
 
 // MMA with descriptors given as (low word, shared high word); K-major 128-byte-swizzle operands.
-template <bool TF32>
+// PAIR: the 256-row form issued by the even CTA of a CTA pair (cta_group::2).
+template <bool TF32, bool PAIR>
 __device__ __forceinline__ void umma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
                                           uint32_t accumulate) {
-    if constexpr (TF32) {
+    if constexpr (PAIR && TF32) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], da, db, %3, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(hi), "r"(accumulate)
+            : "memory");
+    } else if constexpr (PAIR) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(hi), "r"(accumulate)
+            : "memory");
+    } else if constexpr (TF32) {
         asm volatile(
             "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
             "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %3, p;\n\t}"
@@ -79,7 +92,11 @@ __device__ __forceinline__ void umma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32
 }
 
 // STATS: the epilogue also accumulates per-channel statistics of the output (p.stats must be set).
-template <bool TF32, bool STATS>
+// PAIR (clusters of two CTAs, cta_group::2): CTA rank r of a pair takes tile 2u + r of unit u and keeps filter rows
+// [r * NT/2, (r+1) * NT/2) of every tap resident; the even CTA issues 256-row MMAs that read both CTAs' windows and
+// filter halves and write both CTAs' accumulators.  Half a filter per SM leaves room for more window stages (and lets a
+// TF32 filter of 9 x 128 x 64 fit at all), and each MMA reads half as many filter bytes from each SM's shared memory.
+template <bool TF32, bool STATS, bool PAIR>
 __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid_constant__ HaloParams p) {
     constexpr int KC = TF32 ? 32 : 64;
     extern __shared__ uint8_t smem_raw[];
@@ -101,6 +118,9 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int NT = p.NT;
+    const int cta_rank = PAIR ? (int)cluster_cta_rank() : 0;
+    const bool issuer = cta_rank == 0;
+    constexpr int PF = PAIR ? 2 : 1;
     // up to four accumulators (the 512 TMEM columns allow it) so the MMA issuer can run ahead of the epilogue
     const uint32_t NB = (4 * NT <= 512) ? 4u : (3 * NT <= 512) ? 3u : 2u;
     const uint32_t need_cols = NB * (uint32_t)NT;
@@ -113,7 +133,7 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
         }
         for (int b = 0; b < 4; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), HALO_EPI_WARPS);
+            mbar_init(tempty_bar(b), PF * HALO_EPI_WARPS);
         }
         mbar_init(wfull_bar, 1);
         mbar_fence_init();
@@ -122,32 +142,45 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
     }
     for (int i = threadIdx.x; i < NT; i += blockDim.x) bias_s[i] = (p.bias != nullptr && i < p.n_out) ? p.bias[i] : 0.f;
     if (warp == 1) {
-        tmem_alloc(sTmemPtr, tmem_cols);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(sTmemPtr, tmem_cols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(sTmemPtr, tmem_cols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_generic;
 
     const int taps = p.fH * p.fW;
     const int total_tiles = p.tiles_h * p.n_images;          // host guarantees it fits in 31 bits
-    const int grid = (int)gridDim.x;
-    const uint32_t region_tx = (uint32_t)p.region_rows * 128u;
-    const uint32_t wtile_bytes = (uint32_t)NT * 128u;
+    const int grid = (int)gridDim.x;                         // tiles per round: CTA b takes tiles b, b + grid, ...
+    // PAIR: with an odd tile count the odd CTA's last tile is one past the end: its window is zero-filled (image index
+    // out of range) and none of its rows is stored; the loops of a pair run while the EVEN CTA's tile exists
+    const int t_first = blockIdx.x, t_lead = blockIdx.x - cta_rank;
+    const uint32_t region_tx = (uint32_t)p.region_rows * 128u * (uint32_t)PF;     // both CTAs' windows
+    const uint32_t wtile_bytes = (uint32_t)(NT / PF) * 128u;                       // this CTA's rows of one filter tile
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            mbar_arrive_expect_tx(wfull_bar, (uint32_t)p.w_bytes);
+            // resident filter: p.w_bytes per CTA; a pair's two halves are counted on the even CTA's barrier
+            if (issuer) mbar_arrive_expect_tx(wfull_bar, (uint32_t)p.w_bytes * (uint32_t)PF);
+            const uint32_t wbar = PAIR ? cluster_map_shared(wfull_bar, 0) : wfull_bar;
             for (int t = 0; t < taps; ++t)
-                for (int kc = 0; kc < p.kchunks; ++kc)
-                    tma_load_2d(sW + (uint32_t)(t * p.kchunks + kc) * wtile_bytes, &p.tm_w, wfull_bar, kc * KC,
-                                t * p.rows_per_tap);
+                for (int kc = 0; kc < p.kchunks; ++kc) {
+                    const uint32_t dst = sW + (uint32_t)(t * p.kchunks + kc) * wtile_bytes;
+                    if (PAIR) tma_load_2d_pair(dst, &p.tm_w, wbar, kc * KC, t * p.rows_per_tap + cta_rank * (NT / 2));
+                    else tma_load_2d(dst, &p.tm_w, wbar, kc * KC, t * p.rows_per_tap);
+                }
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += grid) {
+            for (int t = t_first; t - cta_rank < total_tiles && ok; t += grid) {
                 const int n = t / p.tiles_h;
                 const int h0 = (t - n * p.tiles_h) * p.BH;
                 const int tp = t + 2 * grid;                       // tile after next: warm L2 with its window
@@ -155,17 +188,21 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                 const int hp = (tp - np * p.tiles_h) * p.BH;
                 for (int kc = 0; kc < p.kchunks; ++kc) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) { ok = false; break; }
-                    mbar_arrive_expect_tx(full_bar(s), region_tx);
-                    tma_load_4d(sR + s * p.region_stride, &p.tm_in, full_bar(s), kc * KC, -p.padL, h0 - p.padT, n);
+                    if (issuer) mbar_arrive_expect_tx(full_bar(s), region_tx);
+                    if (PAIR)
+                        tma_load_4d_pair(sR + s * p.region_stride, &p.tm_in, cluster_map_shared(full_bar(s), 0), kc * KC,
+                                         -p.padL, h0 - p.padT, n);
+                    else
+                        tma_load_4d(sR + s * p.region_stride, &p.tm_in, full_bar(s), kc * KC, -p.padL, h0 - p.padT, n);
                     if (tp < total_tiles) tma_prefetch_l2_4d(&p.tm_in, kc * KC, -p.padL, hp - p.padT, np);
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 && issuer) {
         // ------------------------------------------------------------------ MMA issuer
         const bool leader = elect_one();
-        const uint32_t idesc = make_idesc(TF32 ? 2u : 1u, 0u, 0u, 128u, (uint32_t)NT);
+        const uint32_t idesc = make_idesc(TF32 ? 2u : 1u, 0u, 0u, 128u * PF, (uint32_t)NT);
         const uint64_t proto = make_smem_desc(0, 16, 1024);
         const uint32_t hi = (uint32_t)(proto >> 32);
         const uint32_t lo_proto = (uint32_t)proto;                         // LBO field; start address added below
@@ -179,7 +216,7 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
         bool ok = __all_sync(0xffffffffu, mbar_wait_spin(wfull_bar, 0, p.status, DS_TIMEOUT_FULL));
         int s = 0;
         uint32_t ph = 0, buf = 0, aph = 0;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += grid) {
+        for (int t = t_lead; t < total_tiles && ok; t += grid) {
             bool w_ok = mbar_wait_spin(tempty_bar(buf), aph ^ 1u, p.status, DS_TIMEOUT_TMEM_EMPTY);
             w_ok = __all_sync(0xffffffffu, w_ok);
             if (!w_ok) { ok = false; break; }
@@ -198,10 +235,10 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                     uint32_t a_tap = a_row;
                     for (int tj = 0; tj < p.fW; ++tj) {
                         if (leader) {
-                            umma_lohi<TF32>(d_tmem, a_tap, b_cur, hi, idesc, acc);
-                            umma_lohi<TF32>(d_tmem, a_tap + 2, b_cur + 2, hi, idesc, 1u);
-                            umma_lohi<TF32>(d_tmem, a_tap + 4, b_cur + 4, hi, idesc, 1u);
-                            umma_lohi<TF32>(d_tmem, a_tap + 6, b_cur + 6, hi, idesc, 1u);
+                            umma_lohi<TF32, PAIR>(d_tmem, a_tap, b_cur, hi, idesc, acc);
+                            umma_lohi<TF32, PAIR>(d_tmem, a_tap + 2, b_cur + 2, hi, idesc, 1u);
+                            umma_lohi<TF32, PAIR>(d_tmem, a_tap + 4, b_cur + 4, hi, idesc, 1u);
+                            umma_lohi<TF32, PAIR>(d_tmem, a_tap + 6, b_cur + 6, hi, idesc, 1u);
                         }
                         acc = 1u;
                         a_tap += 8u;
@@ -209,14 +246,28 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                     }
                     a_row += row_step;
                 }
-                if (leader) umma_commit(empty_bar(s));
+                if (leader) {
+                    if (PAIR) {
+                        umma_commit_pair(empty_bar(s));
+                        umma_commit_pair(cluster_map_shared(empty_bar(s), 1));
+                    } else {
+                        umma_commit(empty_bar(s));
+                    }
+                }
                 if (++s == S) { s = 0; ph ^= 1u; }
             }
-            if (ok && leader) umma_commit(tfull_bar(buf));
+            if (ok && leader) {
+                if (PAIR) {
+                    umma_commit_pair(tfull_bar(buf));
+                    umma_commit_pair(cluster_map_shared(tfull_bar(buf), 1));
+                } else {
+                    umma_commit(tfull_bar(buf));
+                }
+            }
             if (++buf == NB) { buf = 0; aph ^= 1u; }
             __syncwarp();
         }
-    } else {
+    } else if (warp >= 2) {
         // ------------------------------------------------------------------ epilogue
         // Warp (q, half): TMEM lanes [32q, 32q+32), columns [half*NT/2, (half+1)*NT/2).  Accumulators are read
         // with the 16-lane x 256-bit shape: thread t receives, per 8-column group, columns 2*(t%4)+{0,1} of rows
@@ -253,10 +304,10 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
         const size_t image_floats = (size_t)p.Hout * p.Wout * p.n_out;
         uint32_t buf = 0, aph = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += grid) {
+        for (int t = t_first; t - cta_rank < total_tiles && ok; t += grid) {
             const int n = t / p.tiles_h;
             const int th = t - n * p.tiles_h;
-            const int rows_left = p.Hout - th * p.BH;
+            const int rows_left = t < total_tiles ? p.Hout - th * p.BH : 0;      // a pair's tile past the end stores nothing
             float* tile_base = p.out + (size_t)n * image_floats + (size_t)th * strip_floats;
             float* rowp[4];
 #pragma unroll
@@ -290,7 +341,10 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
                 if (cb + 16 * HALO_EPI_UB >= ncols) {            // accumulator fully read by this warp
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(buf));
+                    if (lane == 0) {
+                        if (PAIR) mbar_arrive_cluster(cluster_map_shared(tempty_bar(buf), 0));
+                        else mbar_arrive(tempty_bar(buf));
+                    }
                 }
 #pragma unroll
                 for (int u = 0; u < HALO_EPI_UB; ++u) {
@@ -382,16 +436,20 @@ __global__ void __launch_bounds__(HALO_THREADS, 1) halo_conv_kernel(const __grid
     }
 
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();
+    else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, tmem_cols);
+        if (PAIR) tmem_dealloc_pair(tmem_base, tmem_cols);
+        else tmem_dealloc(tmem_base, tmem_cols);
     }
 }
 
 // Decides whether the halo kernel takes this problem; if so launches it and sets *used.
 struct HaloGeom {
     int Wp, BH, tiles_h, kchunks, w_bytes, region_rows, region_stride, stages, fixed;
+    bool pair;      // CTA pairs: w_bytes is then the half filter each CTA keeps
+    int grid;       // CTAs (2 x pairs)
 };
 static constexpr int HALO_SMEM_MAX = 232448;
 
@@ -411,13 +469,30 @@ static bool halo_geometry(bool tf32, int in_C, int S, int taps, int out_C, int o
     const double eff = (double)out_H * out_W / ((double)g.tiles_h * 128.0);
     if (eff < 0.70) return false;
     g.kchunks = ceil_div(in_C, KC);
-    g.w_bytes = taps * g.kchunks * n_padded * 128;
     g.region_rows = (g.BH + fH - 1) * g.Wp;
     g.region_stride = (int)align_up((size_t)g.region_rows * 128, 1024);
-    g.fixed = 1024 + (int)align_up(g.w_bytes, 1024) + HALO_TAIL + HALO_STATS_BYTES;
-    g.stages = (HALO_SMEM_MAX - g.fixed) / g.region_stride;
-    if (g.stages > 4) g.stages = 4;
-    if (g.stages < 2) return false;
+    const long long total = 1LL * g.tiles_h * S;
+    // Single CTAs where the whole filter fits beside two window stages.  Where it does not (TF32, 64 -> 128 channels:
+    // 295 KB), CTA pairs keep half of it each -- if every pair of SMs gets at least two units of two tiles.  Pairs are
+    // NOT used where single CTAs fit: measured on B200 (bf16, batch 256) the pair form took 0.144 ms against 0.117 ms
+    // for the 56x56 64 -> 128 forward and 0.044 against 0.037 ms at 32x32 64 -> 64 (two SMs that wait for each
+    // other's store-bound epilogues), and gained only 5 % on the 56x56 dX (0.127 against 0.134 ms).
+    g.pair = false;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        g.w_bytes = taps * g.kchunks * (g.pair ? n_padded / 2 : n_padded) * 128;
+        g.fixed = 1024 + (int)align_up(g.w_bytes, 1024) + HALO_TAIL + HALO_STATS_BYTES;
+        g.stages = (HALO_SMEM_MAX - g.fixed) / g.region_stride;
+        if (g.stages > 4) g.stages = 4;
+        if (g.stages >= 2) break;
+        if (attempt == 1 || n_padded % 32 != 0 || total < 4LL * (num_sms() / 2)) return false;
+        g.pair = true;
+    }
+    if (g.pair) {
+        const long long units = (total + 1) / 2;
+        g.grid = 2 * (int)(units < num_sms() / 2 ? units : num_sms() / 2);
+    } else {
+        g.grid = (int)(total < num_sms() ? total : num_sms());
+    }
     // every tap reads 128 rows from its shifted start; the furthest read must stay inside the allocation
     const int overhang_rows = (fH - 1) * g.Wp + (fW - 1) + 128 - g.region_rows;
     // (what the last stage reads past its region -- barriers, bias, statistics -- only feeds by-product rows)
@@ -432,8 +507,7 @@ long long halo_igemm_stats_blocks(bool tf32, int in_C, int S, int taps, int out_
                                   int fH, int fW) {
     HaloGeom g;
     if (!halo_geometry(tf32, in_C, S, taps, out_C, out_H, out_W, n_padded, fH, fW, g)) return 0;
-    const long long total = 1LL * g.tiles_h * S;
-    return 4LL * (total < num_sms() ? total : num_sms());       // one block per CTA and 32-row quarter
+    return 4LL * g.grid;       // one block per CTA and 32-row quarter
 }
 
 int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int S, const void* wmat, int w_inner,
@@ -454,7 +528,8 @@ int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int 
     const CUtensorMapDataType dt = tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     int rc;
     if ((rc = make_map_nhwc(&p.tm_in, in, dt, elt, in_C, in_W, in_H, S, KC, Wp, BH + fH - 1, 1))) return rc;
-    if ((rc = make_map_2d(&p.tm_w, wmat, dt, elt, w_inner, 1LL * taps * rows_per_tap, KC, n_padded))) return rc;
+    if ((rc = make_map_2d(&p.tm_w, wmat, dt, elt, w_inner, 1LL * taps * rows_per_tap, KC, g.pair ? n_padded / 2 : n_padded)))
+        return rc;
     p.out = out;
     p.bias = bias;
     p.stats = stats;
@@ -468,17 +543,35 @@ int run_halo_igemm(bool tf32, const void* in, int in_C, int in_H, int in_W, int 
     p.region_rows = region_rows; p.region_stride = region_stride; p.stages = stages; p.w_bytes = w_bytes;
     const int smem = fixed + stages * region_stride;
 
-    // four instantiations: operand type x (with / without the statistics epilogue)
+    // eight instantiations: operand type x (with / without the statistics epilogue) x (single CTAs / CTA pairs)
     using KernelFn = void (*)(const HaloParams);
-    static const KernelFn kernels[4] = {halo_conv_kernel<false, false>, halo_conv_kernel<true, false>,
-                                        halo_conv_kernel<false, true>, halo_conv_kernel<true, true>};
-    static PerDeviceSmem configured[4];
-    const int ki = (tf32 ? 1 : 0) + (stats ? 2 : 0);
+    static const KernelFn kernels[8] = {halo_conv_kernel<false, false, false>, halo_conv_kernel<true, false, false>,
+                                        halo_conv_kernel<false, true, false>,  halo_conv_kernel<true, true, false>,
+                                        halo_conv_kernel<false, false, true>,  halo_conv_kernel<true, false, true>,
+                                        halo_conv_kernel<false, true, true>,   halo_conv_kernel<true, true, true>};
+    static PerDeviceSmem configured[8];
+    const int ki = (tf32 ? 1 : 0) + (stats ? 2 : 0) + (g.pair ? 4 : 0);
     if ((rc = ensure_dynamic_smem(kernels[ki], smem_max, configured[ki], "halo_conv"))) return rc;
-    const long long total = 1LL * tiles_h * S;
-    const int grid = (int)(total < num_sms() ? total : num_sms());
     prof_begin(prof_kind, st);
-    kernels[ki]<<<grid, HALO_THREADS, smem, st>>>(p);
+    if (g.pair) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(g.grid, 1, 1);
+        cfg.blockDim = dim3(HALO_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernels[ki], p);
+        if (e != cudaSuccess) return set_error(AE_CUDA, "halo_conv_kernel (CTA pairs): %s", cudaGetErrorString(e));
+    } else {
+        kernels[ki]<<<g.grid, HALO_THREADS, smem, st>>>(p);
+    }
     prof_end(prof_kind, st);
     count_launch();
     *used = true;

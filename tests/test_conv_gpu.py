@@ -87,6 +87,8 @@ SHAPES = [
     (1, 3, 3, 64, 192, 3, "same"), (130, 4, 4, 64, 64, 3, "same"), (2, 20, 150, 32, 32, 3, "same"),
     # enough 256-wide work for CTA pairs: an odd number of pixel tiles (forward), dX at 256 input channels, two column tiles
     (61, 24, 24, 128, 256, 3, "same"), (150, 16, 16, 256, 128, 3, "same"), (300, 8, 8, 128, 512, 3, "same"),
+    # 27 strips per image x 11: in TF32 the 295 KB filter only fits the window kernel as two halves on a CTA pair
+    (11, 54, 56, 64, 128, 3, "same"),
 ]
 
 

@@ -79,6 +79,8 @@ def test_batch_norm_shapes(env, shape):
                                   # per-tap kernel on CTA pairs: odd number of pixel tiles, two column tiles, TF32
                                   (61, 24, 24, 128, 256, "bf16", True), (300, 8, 8, 128, 512, "bf16", True),
                                   (149, 16, 16, 64, 256, "tf32", True),
+                                  # window kernel on CTA pairs (TF32 filter too large for one CTA; odd number of strips)
+                                  (11, 54, 56, 64, 128, "tf32", True),
                                   (4, 12, 12, 8, 16, "fp32", False)])
 def test_batch_norm_statistics_from_conv_epilogue(env, case):
     """Conv_Layer -> Batch_Norm with the batch statistics taken in the convolution's epilogue: same result as

@@ -698,6 +698,50 @@ def run_train(args):
         dist.destroy_process_group()
 
 
+def run_cell(args):
+    """One cell of the sweep on its own: `--cell S,H,W,Cin,Cout` = fwd+bwd of one 3x3 stride-1 'same' Conv_Layer of that
+    shape, `--warmup` + `--steps` passes, per-kernel-kind times from the library's event recorder.  The profiler
+    captures of single kernels are taken on this command."""
+    import ctypes as C
+    import torch
+    from aether_ml_b200 import _lib
+    from aether_ml_b200.layers import Conv_Layer
+    S, H, W, Cin, Cout = (int(v) for v in args.cell.split(","))
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    np.random.seed(99)
+    layer = Conv_Layer((H, W, Cin), Cout, (3, 3), (1, 1), "same", math_mode=args.mode)
+    g = torch.Generator(device="cuda").manual_seed(S + H + Cin)
+    x = torch.randn((S, H, W, Cin), generator=g, device=dev)
+    dy = torch.randn((S, H, W, Cout), generator=g, device=dev)
+    for _ in range(args.warmup):
+        layer.forward(x, True)
+        layer.backward(dy)
+    torch.cuda.synchronize()
+    L = _lib.lib()
+    L.aether_profile_reset()
+    L.aether_profile_enable(1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        layer.forward(x, True)
+        layer.backward(dy)
+    e1.record()
+    torch.cuda.synchronize()
+    kinds = {}
+    for kind, name in enumerate(["igemm_fwd", "igemm_dx", "dw", "operand_cast"]):
+        tot, n = C.c_double(0), C.c_int(0)
+        L.aether_profile_read(kind, C.byref(tot), C.byref(n))
+        kinds[name] = {"launches": n.value, "avg_ms": tot.value / max(n.value, 1)}
+    L.aether_profile_enable(0)
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel abandoned a bounded wait: status %d" % _lib.device_status())
+    ms = e0.elapsed_time(e1) / max(args.steps, 1)
+    print(json.dumps({"cell": [S, H, W, Cin, Cout], "mode": args.mode, "steps": args.steps, "ms_per_step": ms,
+                      "tflops": conv_flops(S, H, W, Cin, Cout, 3) / (ms * 1e-3) / 1e12 if ms > 0 else None,
+                      "note": "an event pair around every kernel: the step time is a few per cent above the sweep's", "kernels": kinds}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="conv", choices=["conv", "train", "train_wide"],
@@ -719,6 +763,8 @@ def main():
     ap.add_argument("--buckets", type=int, default=2, help="all-reduce buckets of the flat gradient buffer (1 = one all-reduce after backward)")
     ap.add_argument("--skip-train", action="store_true", help="default workload: omit the `train` block")
     ap.add_argument("--skip-sweep", action="store_true", help="default workload: omit the `sweep` block")
+    ap.add_argument("--cell", default=None, metavar="S,H,W,Cin,Cout",
+                    help="time fwd+bwd of one 3x3 'same' Conv_Layer of this shape (one GPU) and print its per-kernel times")
     args = ap.parse_args()
     # NCCL's in-switch reduction (NVLS) binds the ranks' buffers to an NVLink multicast object; a rank that dies while
     # bound can fault its peers' GPUs.  The collectives here (<= 40 MB) run without it unless the caller asks for it.
@@ -726,6 +772,8 @@ def main():
     SHAPE["S"] = args.batch
     if args.impl == "reference":
         run_reference(args)
+    elif args.cell:
+        run_cell(args)
     elif args.workload == "conv":
         run_gpu(args)
     else:

@@ -33,9 +33,14 @@ struct FirstParams {
     int stages, ntiles;
 };
 
-static constexpr int FT_PROD_WARPS = 8;       // two threads per pixel: a lone producer warp per scheduler cannot hide the gather latency
+// Producer warps: about two threads per pixel -- a lone producer warp per scheduler cannot hide the gather latency.
+// The kernel with the statistics epilogue runs 7 of them: 16 warps are four per scheduler and 128 registers per thread,
+// 17 warps put five on one scheduler and cap every thread at 96, which the statistics' running sums do not fit in.
 static constexpr int FT_EPI_WARPS = 8;
-static constexpr int FT_THREADS = 32 * (FT_PROD_WARPS + 1 + FT_EPI_WARPS);   // producers, MMA issuer, epilogue
+template <bool STATS> struct FirstCfg {
+    static constexpr int PROD_WARPS = STATS ? 7 : 8;
+    static constexpr int THREADS = 32 * (PROD_WARPS + 1 + FT_EPI_WARPS);   // producers, MMA issuer, epilogue
+};
 static constexpr int FT_STAGE_BYTES = 128 * 128;                             // 128 pixel rows of 128 bytes
 static constexpr int FT_TAIL = 2048;                                         // barriers, TMEM pointer, bias, k tables
 static constexpr int FT_STATS_BYTES = FT_EPI_WARPS * STATS_WARP_FLOATS * 4;
@@ -55,7 +60,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 
 template <bool STATS>
-__global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_constant__ FirstParams p) {
+__global__ void __launch_bounds__(FirstCfg<STATS>::THREADS, 1) first_conv_kernel(const __grid_constant__ FirstParams p) {
+    constexpr int FT_PROD_WARPS = FirstCfg<STATS>::PROD_WARPS;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -124,29 +130,34 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
     const int grid = (int)gridDim.x;
 
     if (warp < FT_PROD_WARPS) {
-        // ------------------------------------------------------------------ producers: one output pixel per thread pair
-        const int r = threadIdx.x & 127;                            // row of the operand tile
-        const int ch0 = threadIdx.x >> 7, ch_step = (32 * FT_PROD_WARPS) >> 7;   // this thread's 16-byte chunks of the row
-        uint8_t* row_gen = gen_base + (sA - smem_base) + r * 128;
-        const int chunks = p.KP >> 3;
+        // ------------------------------------------------------------------ producers
+        // A tile is 128 rows x (KP / 8) 16-byte chunks; the producer threads take the (row, chunk) pairs round robin.
+        constexpr int NPT = 32 * FT_PROD_WARPS;
+        uint8_t* tile_gen = gen_base + (sA - smem_base);
+        const int ntasks = (p.KP >> 3) << 7;
         const long long HoWo = (long long)p.Ho * p.Wo;
         int s = 0;
         uint32_t ph = 0;
         for (int t = blockIdx.x; t < p.ntiles; t += grid) {
-            const long long pix = (long long)t * 128 + r;
-            int h0 = -(1 << 20), w0 = 0;
-            long long base = 0;
-            if (pix < p.P) {
-                const long long n = pix / HoWo;
-                const int rem = (int)(pix - n * HoWo);
-                const int ho = rem / p.Wo, wo = rem - ho * p.Wo;
-                h0 = ho * p.sH - p.pH;
-                w0 = wo * p.sW - p.pW;
-                base = ((n * p.H + h0) * p.W + w0) * p.Cin;          // may point before the image: only used with valid taps
-            }
             if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, DS_TIMEOUT_EMPTY)) break;
-            uint8_t* dst = row_gen + s * FT_STAGE_BYTES;
-            for (int ch = ch0; ch < chunks; ch += ch_step) {
+            uint8_t* stage_gen = tile_gen + s * FT_STAGE_BYTES;
+            int r_prev = -1, h0 = 0, w0 = 0;
+            long long base = 0;
+            for (int task = threadIdx.x; task < ntasks; task += NPT) {
+                const int r = task & 127, ch = task >> 7;
+                if (r != r_prev) {                                  // with 256 producer threads: once per thread and tile
+                    r_prev = r;
+                    const long long pix = (long long)t * 128 + r;
+                    h0 = -(1 << 20); w0 = 0; base = 0;
+                    if (pix < p.P) {
+                        const long long n = pix / HoWo;
+                        const int rem = (int)(pix - n * HoWo);
+                        const int ho = rem / p.Wo, wo = rem - ho * p.Wo;
+                        h0 = ho * p.sH - p.pH;
+                        w0 = wo * p.sW - p.pW;
+                        base = ((n * p.H + h0) * p.W + w0) * p.Cin;  // may point before the image: only used with valid taps
+                    }
+                }
                 float v[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
@@ -155,7 +166,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
                     v[e] = (hi >= 0 && hi < p.H && wi >= 0 && wi < p.W) ? __ldg(p.x + base + koff_s[k]) : 0.f;
                 }
                 const uint4 q = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-                *reinterpret_cast<uint4*>(dst + ((ch ^ (r & 7)) << 4)) = q;
+                *reinterpret_cast<uint4*>(stage_gen + r * 128 + ((ch ^ (r & 7)) << 4)) = q;
             }
             fence_proxy_async_smem();                               // generic-proxy writes -> visible to the tensor core
             mbar_arrive(full_bar(s));
@@ -213,17 +224,21 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
 #pragma unroll
         for (int j = 0; j < 4; ++j) row_in_tile[j] = q * 32 + (j >> 1) * 16 + trow + (j & 1) * 8;
         const float* bias4 = bias_s + col_begin + tcol4;
+        const f32x2 one2 = pack2(1.f, 1.f);
         // Statistics: per-thread sums of its (4 rows x 4 columns) cells per 16-column group.  With one column batch
         // per tile (ncols <= 64) they run over all tiles of the CTA and the lanes are combined once at the end --
         // the epilogue is this kernel's critical path, and a per-tile lane reduction doubles its length.
         const bool persist = ncols <= 64;
-        float4 st_s[4], st_q[4];
+        Stats4 st[4];                              // packed running sums of this thread's four 16-column groups
 #pragma unroll
-        for (int u = 0; u < 4; ++u) st_s[u] = st_q[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int u = 0; u < 4; ++u) st[u].clear();
         // adds the lanes with equal lane%4 (same 4 columns, 8 row groups) and accumulates into the warp's sums
         // (about the columns' pivots, see stats_epilogue.cuh; `first`: the sums are the warp's first tile, taken
         // without pivots, which are set from them)
         auto flush_stats = [&](int cb, bool first, float rows) {
+            float4 st_s[4], st_q[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { st_s[u] = st[u].sum(); st_q[u] = st[u].sumsq(); }
 #pragma unroll
             for (int m = 4; m <= 16; m <<= 1) {
 #pragma unroll
@@ -268,7 +283,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
             for (int cb0 = 0; cb0 < ncols; cb0 += 64) {
                 if (STATS && !persist) {
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) st_s[u] = st_q[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int u = 0; u < 4; ++u) st[u].clear();
                 }
                 // two half batches of 2 x 16 columns: 32 accumulator registers in flight beside the running sums
 #pragma unroll
@@ -296,8 +311,12 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
                             const int g = hb * 2 + u;             // 16-column group within the 64-column batch
                             const float4 b4 = *reinterpret_cast<const float4*>(bias4 + cc);
                             const bool cols_ok = all_cols || col_begin + tcol4 + cc < p.Cout;
-                            float4 pv = make_float4(0.f, 0.f, 0.f, 0.f);  // pivot of this lane's four columns
-                            if (STATS) pv = *reinterpret_cast<const float4*>(stat_w + 256 + cc + tcol4);
+                            f32x2 npv01 = 0ull, npv23 = 0ull;             // minus the pivots of this lane's four columns
+                            if (STATS) {
+                                const float4 pv = *reinterpret_cast<const float4*>(stat_w + 256 + cc + tcol4);
+                                npv01 = pack2(-pv.x, -pv.y);
+                                npv23 = pack2(-pv.z, -pv.w);
+                            }
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 // quad exchange: 2+2 columns per lane -> 4 consecutive columns per lane (64-byte row segments)
@@ -319,11 +338,10 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
                                     __stcs(reinterpret_cast<float4*>(rowp[j] + cc),
                                            make_float4(a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w));
                                 if (STATS) {
-                                    a.x = wr ? a.x - pv.x : 0.f; a.y = wr ? a.y - pv.y : 0.f;
-                                    a.z = wr ? a.z - pv.z : 0.f; a.w = wr ? a.w - pv.w : 0.f;
-                                    st_s[g].x += a.x; st_s[g].y += a.y; st_s[g].z += a.z; st_s[g].w += a.w;
-                                    st_q[g].x = fmaf(a.x, a.x, st_q[g].x); st_q[g].y = fmaf(a.y, a.y, st_q[g].y);
-                                    st_q[g].z = fmaf(a.z, a.z, st_q[g].z); st_q[g].w = fmaf(a.w, a.w, st_q[g].w);
+                                    // rows past the last pixel hold zeros (their operand rows are zero): a product with
+                                    // the row's 0/1 factor removes them from the sums
+                                    const f32x2 m2 = (cols_ok && rowp[j] != nullptr) ? one2 : 0ull;
+                                    st[g].add(mul2(add2(pack2(a.x, a.y), npv01), m2), mul2(add2(pack2(a.z, a.w), npv23), m2));
                                 }
                             }
                         }
@@ -336,7 +354,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) first_conv_kernel(const __grid_
                         flush_stats(cb0, first_stats, tile_rows);
                         if (persist) {
 #pragma unroll
-                            for (int u = 0; u < 4; ++u) st_s[u] = st_q[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            for (int u = 0; u < 4; ++u) st[u].clear();
                         }
                     }
                 }
@@ -677,8 +695,8 @@ int first_tc_fwd(const AetherConvDesc& d, const float* x, const float* w, const 
                        : ensure_dynamic_smem(first_conv_kernel<false>, 232448, configured[0], "first_conv"))
         return rc;
     const int grid = first_tc_grid(p.ntiles);
-    if (stats) first_conv_kernel<true><<<grid, FT_THREADS, smem, st>>>(p);
-    else first_conv_kernel<false><<<grid, FT_THREADS, smem, st>>>(p);
+    if (stats) first_conv_kernel<true><<<grid, FirstCfg<true>::THREADS, smem, st>>>(p);
+    else first_conv_kernel<false><<<grid, FirstCfg<false>::THREADS, smem, st>>>(p);
     count_launch();
     return check_launch("first_conv_kernel");
 }

@@ -3,6 +3,7 @@
 // take: the first layers with 1 or 3 input channels (HBM-bound, a few FLOP per byte), strided
 // convolutions, channel counts that are not a multiple of 4, and AETHER_MATH_FP32.
 #include "common.cuh"
+#include "tc_host.cuh"
 
 namespace aether {
 
@@ -69,10 +70,22 @@ __global__ void __launch_bounds__(256) gen_fwd_kernel(const float* __restrict__ 
 // Cout = 10): with one thread per output element a batch of 512 rows is 5120 threads walking 1024 channels each.
 // Here a warp takes a row: the lanes split the channels (float4 loads of x, the row is read once), keep Cout partial
 // sums each and combine them with shuffles in a fixed order.
+// The filter is kept transposed in shared memory, wT[d][Cin], so a lane's four channels of output d are one 16-byte
+// shared-memory read (4 * Cout scalar global loads per four channels before).
+__device__ __forceinline__ void head_load_filter_T(const float* __restrict__ w, float* wT, int Cin, int Cout) {
+    for (int i = threadIdx.x; i < Cin * Cout; i += blockDim.x) {
+        const int c = i / Cout, d = i - c * Cout;
+        wT[d * Cin + c] = w[i];
+    }
+    __syncthreads();
+}
+
 template <int MAXD>
 __global__ void __launch_bounds__(256) gen_fwd_pointwise_few_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                                     const float* __restrict__ b, float* __restrict__ y,
                                                                     long long rows, int Cin, int Cout) {
+    extern __shared__ __align__(16) float head_wT[];
+    head_load_filter_T(w, head_wT, Cin, Cout);
     const int lane = threadIdx.x & 31;
     const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -84,11 +97,12 @@ __global__ void __launch_bounds__(256) gen_fwd_pointwise_few_kernel(const float*
         const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * Cin);
         for (int c4 = lane; c4 < C4; c4 += 32) {
             const float4 v = xr[c4];
-            const float* wr = w + (size_t)(4 * c4) * Cout;
 #pragma unroll
             for (int d = 0; d < MAXD; ++d) {
-                if (d < Cout)
-                    acc[d] = fmaf(v.x, wr[d], fmaf(v.y, wr[Cout + d], fmaf(v.z, wr[2 * Cout + d], fmaf(v.w, wr[3 * Cout + d], acc[d]))));
+                if (d < Cout) {
+                    const float4 k = *reinterpret_cast<const float4*>(head_wT + d * Cin + 4 * c4);
+                    acc[d] = fmaf(v.x, k.x, fmaf(v.y, k.y, fmaf(v.z, k.z, fmaf(v.w, k.w, acc[d]))));
+                }
             }
         }
 #pragma unroll
@@ -251,6 +265,94 @@ __global__ void gen_dw_reduce_kernel(const float* __restrict__ part, int nblocks
     }
 }
 
+// ---------------------------------------------------------------------------------- classifier heads, backward
+// dx[p][c] = sum_d dy[p][d] * w[c][d] for a pointwise layer with few outputs: a block takes a row at a time, a thread
+// four channels; the filter is read transposed from shared memory, the row of dy is the same address for every thread.
+template <int MAXD>
+__global__ void __launch_bounds__(256) head_dx_kernel(const float* __restrict__ dy, const float* __restrict__ w,
+                                                      float* __restrict__ dx, long long rows, int Cin, int Cout) {
+    extern __shared__ __align__(16) float head_wT[];
+    head_load_filter_T(w, head_wT, Cin, Cout);
+    const int C4 = Cin >> 2;
+    float gn[MAXD];                                     // the next row's dy values, requested one row ahead
+#pragma unroll
+    for (int d = 0; d < MAXD; ++d) gn[d] = (d < Cout && blockIdx.x < rows) ? __ldg(dy + (size_t)blockIdx.x * Cout + d) : 0.f;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        float g[MAXD];
+        const long long nrow = row + gridDim.x;
+#pragma unroll
+        for (int d = 0; d < MAXD; ++d) {
+            g[d] = gn[d];
+            gn[d] = (d < Cout && nrow < rows) ? __ldg(dy + (size_t)nrow * Cout + d) : 0.f;
+        }
+        float4* out = reinterpret_cast<float4*>(dx + (size_t)row * Cin);
+        for (int c4 = threadIdx.x; c4 < C4; c4 += blockDim.x) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int d = 0; d < MAXD; ++d) {
+                if (d < Cout) {
+                    const float4 k = *reinterpret_cast<const float4*>(head_wT + d * Cin + 4 * c4);
+                    a.x = fmaf(g[d], k.x, a.x); a.y = fmaf(g[d], k.y, a.y); a.z = fmaf(g[d], k.z, a.z); a.w = fmaf(g[d], k.w, a.w);
+                }
+            }
+            out[c4] = a;
+        }
+    }
+}
+
+// dw[c][d] = sum_p x[p][c] * dy[p][d], db[d] = sum_p dy[p][d] over this block's rows, written as the partials
+// gen_dw_reduce_kernel adds up ([block][Cin * Cout + Cout]).  A thread keeps four channels x Cout sums; x is read once,
+// coalesced; the row of dy is the same address for every thread.  blockIdx.y walks the channels in groups of 1024.
+template <int MAXD>
+__global__ void __launch_bounds__(256) head_dw_partial_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                              float* __restrict__ part, long long rows, int Cin, int Cout,
+                                                              long long rows_per_block) {
+    const long long r0 = blockIdx.x * rows_per_block;
+    long long r1 = r0 + rows_per_block;
+    if (r1 > rows) r1 = rows;
+    const int C4 = Cin >> 2;
+    const int c4 = blockIdx.y * blockDim.x + threadIdx.x;
+    const int entries = Cin * Cout;
+    float* out = part + (size_t)blockIdx.x * (entries + Cout);
+    if (c4 < C4) {
+        float4 acc[MAXD];
+#pragma unroll
+        for (int d = 0; d < MAXD; ++d) acc[d] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4* xp = reinterpret_cast<const float4*>(x) + c4;
+#pragma unroll 2
+        for (long long r = r0; r < r1; ++r) {
+            const float4 v = xp[(size_t)r * C4];
+            const float* gr = dy + (size_t)r * Cout;
+#pragma unroll
+            for (int d = 0; d < MAXD; ++d) {
+                if (d < Cout) {
+                    const float g = __ldg(gr + d);
+                    acc[d].x = fmaf(v.x, g, acc[d].x); acc[d].y = fmaf(v.y, g, acc[d].y);
+                    acc[d].z = fmaf(v.z, g, acc[d].z); acc[d].w = fmaf(v.w, g, acc[d].w);
+                }
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < MAXD; ++d) {
+            if (d < Cout) {
+                out[(size_t)(4 * c4 + 0) * Cout + d] = acc[d].x; out[(size_t)(4 * c4 + 1) * Cout + d] = acc[d].y;
+                out[(size_t)(4 * c4 + 2) * Cout + d] = acc[d].z; out[(size_t)(4 * c4 + 3) * Cout + d] = acc[d].w;
+            }
+        }
+    }
+    if (blockIdx.y == 0 && (int)threadIdx.x < Cout) {
+        float sdy = 0.f;
+        for (long long r = r0; r < r1; ++r) sdy += dy[(size_t)r * Cout + threadIdx.x];
+        out[entries + threadIdx.x] = sdy;
+    }
+}
+
+// Pointwise layer with at most 16 outputs whose transposed filter fits in shared memory (a classifier head).
+static bool head_shape(const AetherConvDesc& d) {
+    return d.fH == 1 && d.fW == 1 && d.sH == 1 && d.sW == 1 && d.padH == 0 && d.padW == 0 && d.Cout <= 16 && d.Cin >= 128 &&
+           (d.Cin & 3) == 0 && (size_t)d.Cin * d.Cout * sizeof(float) <= 96 * 1024;
+}
+
 // ---------------------------------------------------------------------------------- host
 static int gen_blocks(long long total, int threads) {
     long long b = (total + threads - 1) / threads;
@@ -265,10 +367,14 @@ int generic_conv_fwd(const AetherConvDesc& d, const float* x, const float* w, co
     conv_out_hw(d, Ho, Wo);
     const long long total = 1LL * d.S * Ho * Wo * d.Cout;
     const int wcount = d.fH * d.fW * d.Cin * d.Cout;
-    if (d.fH == 1 && d.fW == 1 && d.sH == 1 && d.sW == 1 && d.padH == 0 && d.padW == 0 && d.Cout <= 16 && d.Cin >= 128 &&
-        (d.Cin & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+    if (head_shape(d) && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
         const long long rows = 1LL * d.S * d.H * d.W;
-        gen_fwd_pointwise_few_kernel<16><<<gen_blocks(rows * 32, 256), 256, 0, st>>>(x, w, b, y, rows, d.Cin, d.Cout);
+        const int smem = d.Cin * d.Cout * (int)sizeof(float);
+        static PerDeviceSmem configured;
+        if (int rc = ensure_dynamic_smem(gen_fwd_pointwise_few_kernel<16>, 96 * 1024, configured, "head forward")) return rc;
+        long long nb = (rows + 7) / 8;                        // a warp per row, 8 rows per block and pass
+        if (nb > 2LL * num_sms()) nb = 2LL * num_sms();       // every block loads the filter once
+        gen_fwd_pointwise_few_kernel<16><<<(int)nb, 256, smem, st>>>(x, w, b, y, rows, d.Cin, d.Cout);
         count_launch();
         return check_launch("gen_fwd_pointwise_few_kernel");
     }
@@ -302,6 +408,16 @@ int generic_conv_bwd_data(const AetherConvDesc& d, const float* dy, const float*
         count_launch();
         return check_launch("gen_dx_fewc_kernel");
     }
+    if (head_shape(d) && (reinterpret_cast<uintptr_t>(dx) & 15u) == 0) {
+        const long long rows = 1LL * d.S * d.H * d.W;
+        const int smem = d.Cin * d.Cout * (int)sizeof(float);
+        static PerDeviceSmem configured;
+        if (int rc = ensure_dynamic_smem(head_dx_kernel<16>, 96 * 1024, configured, "head dX")) return rc;
+        long long nb = rows < 2LL * num_sms() ? rows : 2LL * num_sms();
+        head_dx_kernel<16><<<(int)nb, 256, smem, st>>>(dy, w, dx, rows, d.Cin, d.Cout);
+        count_launch();
+        return check_launch("head_dx_kernel");
+    }
     gen_dx_kernel<<<gen_blocks(total, 256), 256, 0, st>>>(dy, w, dx, d.S, d.H, d.W, d.Cin, d.Cout, d.fH, d.fW, d.sH,
                                                           d.sW, d.padH, d.padW, Ho, Wo);
     count_launch();
@@ -334,6 +450,15 @@ int generic_conv_bwd_filter(const AetherConvDesc& d, const float* x, const float
     const long long ppb = (npix + nb - 1) / nb;
     const int entries = d.fH * d.fW * d.Cin * d.Cout;
     float* part = static_cast<float*>(ws);
+    if (head_shape(d) && x != nullptr && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+        head_dw_partial_kernel<16><<<dim3(nb, ceil_div(d.Cin / 4, 256)), 256, 0, st>>>(x, dy, part, npix, d.Cin, d.Cout, ppb);
+        count_launch();
+        int rc = check_launch("head_dw_partial_kernel");
+        if (rc) return rc;
+        gen_dw_reduce_kernel<<<ceil_div(entries + d.Cout, 256), 256, 0, st>>>(part, nb, entries, d.Cout, dw, db);
+        count_launch();
+        return check_launch("gen_dw_reduce_kernel");
+    }
     int egroups = ceil_div(entries + d.Cout, 256);
     if (egroups > 4096) egroups = 4096;
     gen_dw_partial_kernel<<<dim3(nb, egroups), 256, 0, st>>>(x, dy, part, d.S, d.H, d.W, d.Cin, d.Cout, d.fH, d.fW, d.sH, d.sW, d.padH,

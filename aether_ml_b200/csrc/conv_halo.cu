@@ -484,7 +484,7 @@ static bool halo_geometry(bool tf32, int in_C, int S, int taps, int out_C, int o
         g.stages = (HALO_SMEM_MAX - g.fixed) / g.region_stride;
         if (g.stages > 4) g.stages = 4;
         if (g.stages >= 2) break;
-        if (attempt == 1 || n_padded % 32 != 0 || total < 4LL * (num_sms() / 2)) return false;
+        if (attempt == 1 || n_padded % 32 != 0 || total < 4LL * (num_sms() / 2) || !cta_pairs_available()) return false;
         g.pair = true;
     }
     if (g.pair) {

@@ -978,6 +978,38 @@ int num_sms() {
     return n;
 }
 
+// A stand-in with the pair kernels' launch shape for the occupancy query below.
+__global__ void __launch_bounds__(IGEMM_THREADS, 1) pair_probe_kernel() {}
+
+bool cta_pairs_available() {
+    static std::atomic<int> cache[AE_MAX_DEVICES];       // 0 = not asked yet, 1 = yes, 2 = no
+    const int dev = current_device();
+    int v = cache[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
+        v = 2;
+        const int smem = IgemmCfg<256, true>::SMEM_BYTES;
+        if (cudaFuncSetAttribute(pair_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) {
+            cudaLaunchConfig_t cfg;
+            memset(&cfg, 0, sizeof(cfg));
+            cfg.gridDim = dim3(2 * (num_sms() / 2), 1, 1);
+            cfg.blockDim = dim3(IGEMM_THREADS, 1, 1);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr;
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 2;
+            attr.val.clusterDim.y = 1;
+            attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, pair_probe_kernel, &cfg) == cudaSuccess && clusters >= num_sms() / 2) v = 1;
+        }
+        (void)cudaGetLastError();
+        cache[dev].store(v, std::memory_order_relaxed);
+    }
+    return v == 1;
+}
+
 static TcPlan make_plan(const AetherConvDesc& d) {
     TcPlan pl{};
     pl.tf32 = (d.math_mode == AETHER_MATH_TF32);
@@ -1013,7 +1045,7 @@ static TcPlan make_plan(const AetherConvDesc& d) {
     pl.dw_halo_splits = decompose(1);
     if (pl.dw_halo_splits < 1) pl.dw_halo_splits = 1;
     pl.dw_splits = pl.dw_halo_splits;
-    pl.dw_pair = pl.dw_nb == 2 && pl.Cout_p % (2 * pl.dw_nt) == 0 && pl.dw_U >= 2 * MB;
+    pl.dw_pair = pl.dw_nb == 2 && pl.Cout_p % (2 * pl.dw_nt) == 0 && pl.dw_U >= 2 * MB && cta_pairs_available();
     if (pl.dw_pair) {
         const int ps = decompose(2);
         if (ps < 1 || ptiles < 4LL * ps) {
@@ -1091,7 +1123,7 @@ static int igemm_grid(long long m_tiles, int n_tiles_n, bool stats) {
 // has 256 tensor clocks per stage for a barrier wait, four MMAs and two commits; two chunks per stage fixed that
 // and also gave the 256-column pair 3-4 %.
 static bool igemm_use_pairs(long long m_tiles, int nt, int n_tiles_n) {
-    return (nt == 256 || nt == 128) && (m_tiles + 1) / 2 * n_tiles_n >= 2LL * (num_sms() / 2);
+    return (nt == 256 || nt == 128) && (m_tiles + 1) / 2 * n_tiles_n >= 2LL * (num_sms() / 2) && cta_pairs_available();
 }
 static int igemm_pair_grid(long long m_tiles, int n_tiles_n, bool stats) {
     const long long units = (m_tiles + 1) / 2 * n_tiles_n;

@@ -6,6 +6,9 @@
 namespace aether {
 
 int num_sms();
+// Whether this device can co-schedule the CTA pairs (clusters of two CTAs with ~210 KB of shared memory each) the
+// cta_group::2 kernels are launched as, on every pair of SMs; looked up once per device.  False keeps the single-CTA forms.
+bool cta_pairs_available();
 // NHWC tensor seen as 4-D (C, W, H, N), box (box_c, BW, BH, BN); 128-byte swizzle unless told otherwise.
 int make_map_nhwc(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elt, int C, int W, int H, int N,
                   int box_c, int BW, int BH, int BN, CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B);

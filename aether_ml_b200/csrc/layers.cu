@@ -240,42 +240,33 @@ __global__ void __launch_bounds__(FIN_THREADS) bn_finalize_fwd_kernel(const floa
                                        float momentum, float* __restrict__ running_mean,
                                        float* __restrict__ running_var, float* __restrict__ batch_mean,
                                        float* __restrict__ batch_var, float* __restrict__ scale_shift) {
-    // Two division-free passes over the per-block triples: total count and sum first, then M2 about the global
-    // mean; lanes are combined in fixed order.
-    __shared__ double red_a[FIN_LANES][FIN_CH], red_b[FIN_LANES][FIN_CH];
+    // One pass over the per-block triples, all in double: N = sum n, S = sum n * mean, Q = sum (M2 + n * mean^2); then
+    // M2 = Q - N * M^2.  The subtraction loses log2(mean^2 / var) of double's 53 bits, harmless for any ratio a float
+    // tensor can show (the per-block M2 themselves carry 24 bits).  Lanes are combined in fixed order.
+    __shared__ double red_a[FIN_LANES][FIN_CH], red_b[FIN_LANES][FIN_CH], red_c[FIN_LANES][FIN_CH];
     const int cl = threadIdx.x % FIN_CH, ln = threadIdx.x / FIN_CH;
     const int c = blockIdx.x * FIN_CH + cl;
-    double n_sum = 0.0, s_sum = 0.0;
+    double n_sum = 0.0, s_sum = 0.0, q_sum = 0.0;
     if (c < C)
 #pragma unroll 4
         for (int b = ln; b < nblocks; b += FIN_LANES) {
             const float* p = part + (size_t)b * 3 * C;
-            const double nl = p[c];
+            const double nl = p[c], ml = p[C + c];
             n_sum += nl;
-            s_sum += nl * (double)p[C + c];
+            s_sum += nl * ml;
+            q_sum += (double)p[2 * C + c] + nl * ml * ml;
         }
     red_a[ln][cl] = n_sum;
     red_b[ln][cl] = s_sum;
-    __syncthreads();
-    double N = 0.0, S1 = 0.0;
-#pragma unroll 8
-    for (int l = 0; l < FIN_LANES; ++l) { N += red_a[l][cl]; S1 += red_b[l][cl]; }
-    const double M = N > 0 ? S1 / N : 0.0;
-    __syncthreads();
-    double m2 = 0.0;
-    if (c < C)
-#pragma unroll 4
-        for (int b = ln; b < nblocks; b += FIN_LANES) {
-            const float* p = part + (size_t)b * 3 * C;
-            const double d = (double)p[C + c] - M;
-            m2 += (double)p[2 * C + c] + (double)p[c] * d * d;
-        }
-    red_a[ln][cl] = m2;
+    red_c[ln][cl] = q_sum;
     __syncthreads();
     if (ln != 0 || c >= C) return;
-    double M2 = 0.0;
+    double N = 0.0, S1 = 0.0, Q = 0.0;
 #pragma unroll 8
-    for (int l = 0; l < FIN_LANES; ++l) M2 += red_a[l][cl];
+    for (int l = 0; l < FIN_LANES; ++l) { N += red_a[l][cl]; S1 += red_b[l][cl]; Q += red_c[l][cl]; }
+    const double M = N > 0 ? S1 / N : 0.0;
+    double M2 = Q - N * M * M;
+    if (M2 < 0.0) M2 = 0.0;
     const double var = N > 0 ? M2 / N : 0.0;
     batch_mean[c] = (float)M;
     batch_var[c] = (float)var;
